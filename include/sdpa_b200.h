@@ -1,0 +1,154 @@
+/*
+ * sdpa_b200.h - C ABI of libsdpa_b200.so: scaled-dot-product attention forward, backward
+ * and split-KV decode for NVIDIA B200 (sm_100a), written to stand where torch_mlu binds
+ * Cambricon's closed attention library.
+ *
+ * What each entry point replaces in the reference (paths inside Cambricon/torch_mlu):
+ *   sdpa_b200_fwd            <- mha_varlen_fwd, i.e. cnnlFlashAttentionForward_v2
+ *                               torch_mlu/csrc/aten/operators/cnnl/internal/FlashAttention_internal.cpp:57-267
+ *                               (declared cnnl_internal.h:1461-1476)
+ *   sdpa_b200_bwd            <- mha_varlen_bwd, i.e. cnnlFlashAttentionBackward
+ *                               .../internal/FlashAttention_internal.cpp:269-483 (cnnl_internal.h:1478-1495)
+ *   sdpa_b200_*_workspace_bytes
+ *                            <- cnnlGetFlashAttention{Forward,Backward}WorkspaceSize_v2
+ *                               .../internal/FlashAttention_internal.cpp:215-230, 437-447
+ *   sdpa_b200_status_string  <- TORCH_CNNL_CHECK's status-to-text, torch_mlu/csrc/aten/utils/exceptions.h:77-83
+ *
+ * Conventions
+ *   - Plain C: pointers, sizes, one POD struct. No C++ or torch types cross this boundary.
+ *   - Every pointer in sdpa_b200_params is a DEVICE pointer on the caller's current device.
+ *   - The caller owns every buffer including the workspace; the library allocates no device
+ *     memory and keeps no per-call state.
+ *   - Calls enqueue work on `stream` and return without synchronising.
+ *   - Errors are integer status codes; nothing throws, aborts or traps the device. A kernel
+ *     whose internal wait runs out writes SDPA_B200_DEVICE_TIMEOUT into the first word of
+ *     the workspace; sdpa_b200_read_device_status() fetches it (it synchronises the stream).
+ *   - Layout: element strides for (batch, head, row); the head_dim stride must be 1.
+ *       dense   : cu_seqlens_* == NULL, batch b / head h / row r of q lives at
+ *                 q + b*q_batch_stride + h*q_head_stride + r*q_row_stride (any BHLD/BLHD view)
+ *       varlen  : cu_seqlens_q/k are int32[batch+1] exclusive prefix sums; tensors are packed
+ *                 [total_tokens, heads, head_dim]; *_batch_stride is ignored and row r of
+ *                 sequence b is token cu_seqlens[b] + r.
+ *   - lse (natural-log logsumexp of scale*QK^T over the visible keys, fp32):
+ *       dense   : [batch, heads_q, seqlen_q] contiguous
+ *       varlen  : [heads_q, total_q] contiguous (the buffer mha_varlen_fwd allocates,
+ *                 FlashAttention_internal.cpp:129)
+ *     A row with no visible key gets out = 0 and lse = +inf.
+ *   - Causal masking is bottom-right aligned: key j is visible to query i when
+ *     j <= i + seqlen_k - seqlen_q (the reference test oracle's rule,
+ *     test/torch_ops/test_scaled_dot_product_attention.py:69). With seqlen_q == seqlen_k it is
+ *     the usual lower triangle.
+ *   - GQA/MQA: heads_q % heads_kv == 0; query head h reads KV head h / (heads_q/heads_kv)
+ *     (FlashAttention_internal.cpp:117-124).
+ */
+#ifndef SDPA_B200_H_
+#define SDPA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SDPA_B200_VERSION 100
+
+#if defined(__GNUC__)
+#define SDPA_B200_API __attribute__((visibility("default")))
+#else
+#define SDPA_B200_API
+#endif
+
+/* status codes */
+enum {
+  SDPA_B200_OK = 0,
+  SDPA_B200_INVALID_ARG = 1,    /* null pointer, bad shape, bad stride/alignment, workspace too small */
+  SDPA_B200_UNSUPPORTED = 2,    /* valid request this build has no kernel for (dtype, head_dim, dropout) */
+  SDPA_B200_LAUNCH_FAILED = 3,  /* CUDA reported an error while configuring or launching */
+  SDPA_B200_DEVICE_TIMEOUT = 4, /* a bounded wait inside a kernel ran out (read back from workspace) */
+  SDPA_B200_NO_DEVICE = 5       /* not an sm_100 device / no CUDA driver */
+};
+
+enum { SDPA_B200_BF16 = 0 }; /* element type of q, k, v, out and gradients */
+
+/* kernel selection for the forward entry point */
+enum {
+  SDPA_B200_KERNEL_AUTO = 0,    /* decode when max_seqlen_q is small, prefill otherwise */
+  SDPA_B200_KERNEL_PREFILL = 1, /* TMA + tcgen05 tile kernel */
+  SDPA_B200_KERNEL_DECODE = 2   /* split-KV streaming kernel */
+};
+
+typedef struct sdpa_b200_params {
+  /* inputs */
+  const void* q; /* bf16 */
+  const void* k;
+  const void* v;
+  /* forward outputs (inputs of backward) */
+  void* out;  /* bf16, same shape as q */
+  float* lse; /* fp32, layout above */
+  /* backward only */
+  const void* dout; /* bf16, same shape/strides family as out */
+  void* dq;         /* bf16, shape of q */
+  void* dk;         /* bf16, shape of k */
+  void* dv;         /* bf16, shape of v */
+
+  /* varlen: device int32[batch+1]; NULL for dense */
+  const int32_t* cu_seqlens_q;
+  const int32_t* cu_seqlens_k;
+
+  int32_t batch;
+  int32_t heads_q;
+  int32_t heads_kv;
+  int32_t head_dim;
+  int32_t max_seqlen_q; /* dense: seqlen_q */
+  int32_t max_seqlen_k; /* dense: seqlen_k */
+  int32_t total_q;      /* varlen: rows of q/out; dense: ignored */
+  int32_t total_k;      /* varlen: rows of k/v;   dense: ignored */
+
+  /* element strides; head_dim stride is 1 */
+  int64_t q_batch_stride, q_head_stride, q_row_stride;
+  int64_t k_batch_stride, k_head_stride, k_row_stride;
+  int64_t v_batch_stride, v_head_stride, v_row_stride;
+  int64_t o_batch_stride, o_head_stride, o_row_stride;
+  /* backward */
+  int64_t do_batch_stride, do_head_stride, do_row_stride;
+  int64_t dq_batch_stride, dq_head_stride, dq_row_stride;
+  int64_t dk_batch_stride, dk_head_stride, dk_row_stride;
+  int64_t dv_batch_stride, dv_head_stride, dv_row_stride;
+
+  float softmax_scale; /* > 0; the reference default is 1/sqrt(head_dim), sdp_utils.h:40-47 */
+  float dropout_p;     /* must be 0 */
+  int32_t is_causal;
+  int32_t dtype;      /* SDPA_B200_BF16 */
+  int32_t kernel;     /* SDPA_B200_KERNEL_* (forward only) */
+  int32_t num_splits; /* decode: 0 = choose; otherwise the number of KV splits */
+  int32_t reserved[4]; /* zero */
+} sdpa_b200_params;
+
+SDPA_B200_API int sdpa_b200_version(void);
+SDPA_B200_API const char* sdpa_b200_status_string(int status);
+/* Text of the last error raised on the calling thread (what was wrong and where). */
+SDPA_B200_API const char* sdpa_b200_last_error(void);
+
+/* Workspace size the matching call needs for these params (>= 256 bytes; 256-byte aligned
+ * base required). */
+SDPA_B200_API int sdpa_b200_fwd_workspace_bytes(const sdpa_b200_params* p, size_t* bytes);
+SDPA_B200_API int sdpa_b200_bwd_workspace_bytes(const sdpa_b200_params* p, size_t* bytes);
+
+/* out, lse <- attention(q, k, v). `stream` is a cudaStream_t passed as void*. */
+SDPA_B200_API int sdpa_b200_fwd(const sdpa_b200_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* dq, dk, dv <- backward(dout, q, k, v, out, lse). */
+SDPA_B200_API int sdpa_b200_bwd(const sdpa_b200_params* p, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Synchronises `stream`, reads the status word a kernel may have left in `workspace` and
+ * returns it in *device_status (SDPA_B200_OK or SDPA_B200_DEVICE_TIMEOUT). */
+SDPA_B200_API int sdpa_b200_read_device_status(const void* workspace, void* stream, int* device_status);
+
+/* How many of this library's kernels the calling process has launched so far. */
+SDPA_B200_API uint64_t sdpa_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SDPA_B200_H_ */

@@ -1,0 +1,41 @@
+// Internal launch interface between the C-ABI front end (sdpa_api.cu) and the kernel files.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/sdpa_b200.h"
+
+namespace sdpa_b200 {
+
+// First 256 bytes of every workspace: word 0 is the device status, the rest is reserved.
+constexpr size_t kWorkspaceHeaderBytes = 256;
+
+// Thread-local error text (set by whoever returns a non-OK status).
+void set_error(const char* fmt, ...);
+void count_launch(int n = 1);
+
+// Builds a 4-D bf16 tensor map {head_dim, rows, heads, batch} with a {64, box_rows, 1, 1}
+// box and 128-byte swizzle. Strides are in ELEMENTS. Returns an SDPA_B200_* status.
+int make_tensor_map_bf16(CUtensorMap* map, const void* base, int head_dim, int64_t rows,
+                         int64_t heads, int64_t batch, int64_t row_stride, int64_t head_stride,
+                         int64_t batch_stride, int box_rows);
+
+// Prefill forward (TMA + tcgen05). `debug` (nullable, device) receives per-row dumps of the
+// first CTA when the library is asked for them by the test hook.
+int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t stream,
+                       float* debug);
+
+// Split-KV decode forward. Workspace layout is private to decode_splitkv.cu.
+size_t decode_workspace_bytes(const sdpa_b200_params& p, int* num_splits_out);
+int launch_fwd_decode(const sdpa_b200_params& p, void* workspace, size_t workspace_bytes,
+                      cudaStream_t stream);
+
+// Backward: delta pre-pass + dK/dV kernel + dQ kernel.
+size_t bwd_workspace_bytes(const sdpa_b200_params& p);
+int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_bytes,
+               cudaStream_t stream);
+
+}  // namespace sdpa_b200

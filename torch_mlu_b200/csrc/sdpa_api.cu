@@ -1,0 +1,344 @@
+// C-ABI front end of libsdpa_b200.so: argument validation (the checks mha_varlen_fwd/bwd make
+// at torch_mlu/csrc/aten/operators/cnnl/internal/FlashAttention_internal.cpp:73-127, 291-366,
+// plus the dispatcher constraints of .../transformers/sdp_utils.h:231-255, 371-431 that apply
+// to this path), workspace sizing, kernel selection and TMA descriptor construction.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "kernels.h"
+
+namespace sdpa_b200 {
+
+namespace {
+thread_local char g_error[512] = "";
+std::atomic<uint64_t> g_launches{0};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+    if (err == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    (void)cudaGetLastError();
+  });
+  return fn;
+}
+}  // namespace
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
+
+int make_tensor_map_bf16(CUtensorMap* map, const void* base, int head_dim, int64_t rows,
+                         int64_t heads, int64_t batch, int64_t row_stride, int64_t head_stride,
+                         int64_t batch_stride, int box_rows) {
+  EncodeTiledFn encode = get_encode_fn();
+  if (encode == nullptr) {
+    set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+    return SDPA_B200_NO_DEVICE;
+  }
+  if (rows < 1) rows = 1;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(rows),
+                        static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
+  // a size-1 dimension never advances, but its stride must still be a legal value
+  if (heads == 1 && (head_stride <= 0)) head_stride = row_stride;
+  if (batch == 1) batch_stride = row_stride;
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(row_stride) * 2, static_cast<cuuint64_t>(head_stride) * 2,
+                           static_cast<cuuint64_t>(batch_stride) * 2};
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box,
+                      estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed (CUresult %d): dims {%d,%lld,%lld,%lld} strides(elements) "
+              "{row %lld, head %lld, batch %lld}",
+              static_cast<int>(r), head_dim, (long long)rows, (long long)heads, (long long)batch,
+              (long long)row_stride, (long long)head_stride, (long long)batch_stride);
+    return SDPA_B200_INVALID_ARG;
+  }
+  return SDPA_B200_OK;
+}
+
+namespace {
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// strides must keep every row 16-byte aligned (TMA and 128-bit loads/stores)
+bool stride_ok(int64_t s) { return s > 0 && (s % 8) == 0; }
+
+int check_tensor(const char* name, const void* ptr, int64_t bs, int64_t hs, int64_t rs, bool varlen,
+                 int64_t batch, int64_t heads) {
+  if (ptr == nullptr) {
+    set_error("%s is NULL", name);
+    return SDPA_B200_INVALID_ARG;
+  }
+  if (!aligned16(ptr)) {
+    set_error("%s must be 16-byte aligned", name);
+    return SDPA_B200_INVALID_ARG;
+  }
+  if (!stride_ok(rs) || (heads > 1 && !stride_ok(hs)) || (!varlen && batch > 1 && !stride_ok(bs))) {
+    set_error("%s: row/head/batch strides must be positive multiples of 8 elements with unit head_dim "
+              "stride (got batch %lld, head %lld, row %lld)",
+              name, (long long)bs, (long long)hs, (long long)rs);
+    return SDPA_B200_INVALID_ARG;
+  }
+  return SDPA_B200_OK;
+}
+
+// Checks shared by forward and backward.
+int validate_common(const sdpa_b200_params* p) {
+  if (p == nullptr) {
+    set_error("params is NULL");
+    return SDPA_B200_INVALID_ARG;
+  }
+  if (p->dtype != SDPA_B200_BF16) {
+    set_error("only bf16 q/k/v are supported (dtype code %d)", p->dtype);
+    return SDPA_B200_UNSUPPORTED;
+  }
+  if (p->dropout_p != 0.f) {
+    set_error("dropout_p must be 0 (got %g)", static_cast<double>(p->dropout_p));
+    return SDPA_B200_UNSUPPORTED;
+  }
+  if (p->batch <= 0 || p->heads_q <= 0 || p->heads_kv <= 0) {
+    set_error("batch, heads_q and heads_kv must be positive (got %d, %d, %d)", p->batch, p->heads_q, p->heads_kv);
+    return SDPA_B200_INVALID_ARG;
+  }
+  if (p->heads_q % p->heads_kv != 0) {
+    set_error("Number of heads in key/value must divide number of heads in query (%d vs %d)", p->heads_kv,
+              p->heads_q);
+    return SDPA_B200_INVALID_ARG;
+  }
+  if (p->head_dim <= 0 || p->head_dim % 8 != 0 || p->head_dim > 256) {
+    set_error("head_dim must be a multiple of 8 and at most 256 (got %d)", p->head_dim);
+    return SDPA_B200_INVALID_ARG;
+  }
+  if (p->head_dim != 128) {
+    set_error("this build has kernels for head_dim 128 only (got %d)", p->head_dim);
+    return SDPA_B200_UNSUPPORTED;
+  }
+  if (!(p->softmax_scale > 0.f) || !(p->softmax_scale < 3.0e38f)) {
+    set_error("softmax_scale must be positive and finite (got %g)", static_cast<double>(p->softmax_scale));
+    return SDPA_B200_INVALID_ARG;
+  }
+  const bool varlen = p->cu_seqlens_q != nullptr || p->cu_seqlens_k != nullptr;
+  if (varlen && (p->cu_seqlens_q == nullptr || p->cu_seqlens_k == nullptr)) {
+    set_error("cu_seqlens_q and cu_seqlens_k must both be given or both be NULL");
+    return SDPA_B200_INVALID_ARG;
+  }
+  if (p->max_seqlen_q <= 0 || p->max_seqlen_k <= 0) {
+    set_error("sequence lengths must be positive (max_seqlen_q %d, max_seqlen_k %d)", p->max_seqlen_q,
+              p->max_seqlen_k);
+    return SDPA_B200_INVALID_ARG;
+  }
+  if (varlen && (p->total_q <= 0 || p->total_k <= 0)) {
+    set_error("varlen needs total_q and total_k > 0 (got %d, %d)", p->total_q, p->total_k);
+    return SDPA_B200_INVALID_ARG;
+  }
+  for (int i = 0; i < 4; ++i) {
+    if (p->reserved[i] != 0) {
+      set_error("reserved fields must be zero");
+      return SDPA_B200_INVALID_ARG;
+    }
+  }
+  int st;
+  if ((st = check_tensor("q", p->q, p->q_batch_stride, p->q_head_stride, p->q_row_stride, varlen, p->batch,
+                         p->heads_q)) != SDPA_B200_OK)
+    return st;
+  if ((st = check_tensor("k", p->k, p->k_batch_stride, p->k_head_stride, p->k_row_stride, varlen, p->batch,
+                         p->heads_kv)) != SDPA_B200_OK)
+    return st;
+  if ((st = check_tensor("v", p->v, p->v_batch_stride, p->v_head_stride, p->v_row_stride, varlen, p->batch,
+                         p->heads_kv)) != SDPA_B200_OK)
+    return st;
+  if ((st = check_tensor("out", p->out, p->o_batch_stride, p->o_head_stride, p->o_row_stride, varlen, p->batch,
+                         p->heads_q)) != SDPA_B200_OK)
+    return st;
+  if (p->lse == nullptr) {
+    set_error("lse is NULL");
+    return SDPA_B200_INVALID_ARG;
+  }
+  return SDPA_B200_OK;
+}
+
+int validate_workspace(void* workspace, size_t have, size_t need) {
+  if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
+    set_error("workspace must be a non-NULL device pointer aligned to 256 bytes");
+    return SDPA_B200_INVALID_ARG;
+  }
+  if (have < need) {
+    set_error("workspace too small: %zu bytes given, %zu needed", have, need);
+    return SDPA_B200_INVALID_ARG;
+  }
+  return SDPA_B200_OK;
+}
+
+int check_device() {
+  static int cached_dev = -1;
+  static int cached_status = SDPA_B200_NO_DEVICE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    set_error("no CUDA device is available; this library has no CPU path");
+    return SDPA_B200_NO_DEVICE;
+  }
+  if (dev == cached_dev) return cached_status;
+  int major = 0;
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  cached_dev = dev;
+  cached_status = (major == 10) ? SDPA_B200_OK : SDPA_B200_NO_DEVICE;
+  if (cached_status != SDPA_B200_OK) set_error("device %d has compute capability %d.x; sm_100 is required", dev, major);
+  return cached_status;
+}
+
+// Decode is chosen when there are too few query rows to fill a 128-row MMA tile.
+bool use_decode(const sdpa_b200_params* p) {
+  if (p->kernel == SDPA_B200_KERNEL_DECODE) return true;
+  if (p->kernel == SDPA_B200_KERNEL_PREFILL) return false;
+  return p->cu_seqlens_q == nullptr && p->max_seqlen_q == 1;
+}
+
+float* g_debug_buffer = nullptr;  // test hook, see sdpa_b200_set_debug_buffer
+
+}  // namespace
+}  // namespace sdpa_b200
+
+using namespace sdpa_b200;
+
+extern "C" {
+
+int sdpa_b200_version(void) { return SDPA_B200_VERSION; }
+
+const char* sdpa_b200_status_string(int status) {
+  switch (status) {
+    case SDPA_B200_OK: return "ok";
+    case SDPA_B200_INVALID_ARG: return "invalid argument";
+    case SDPA_B200_UNSUPPORTED: return "unsupported configuration";
+    case SDPA_B200_LAUNCH_FAILED: return "CUDA launch failed";
+    case SDPA_B200_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out";
+    case SDPA_B200_NO_DEVICE: return "no sm_100 CUDA device";
+    default: return "unknown status";
+  }
+}
+
+const char* sdpa_b200_last_error(void) { return g_error; }
+
+uint64_t sdpa_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int sdpa_b200_fwd_workspace_bytes(const sdpa_b200_params* p, size_t* bytes) {
+  if (bytes == nullptr) {
+    set_error("bytes is NULL");
+    return SDPA_B200_INVALID_ARG;
+  }
+  int st = validate_common(p);
+  if (st != SDPA_B200_OK) return st;
+  size_t need = kWorkspaceHeaderBytes;
+  if (use_decode(p)) need += decode_workspace_bytes(*p, nullptr);
+  *bytes = need;
+  return SDPA_B200_OK;
+}
+
+int sdpa_b200_bwd_workspace_bytes(const sdpa_b200_params* p, size_t* bytes) {
+  if (bytes == nullptr) {
+    set_error("bytes is NULL");
+    return SDPA_B200_INVALID_ARG;
+  }
+  int st = validate_common(p);
+  if (st != SDPA_B200_OK) return st;
+  *bytes = kWorkspaceHeaderBytes + bwd_workspace_bytes(*p);
+  return SDPA_B200_OK;
+}
+
+int sdpa_b200_fwd(const sdpa_b200_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+  int st = validate_common(p);
+  if (st != SDPA_B200_OK) return st;
+  size_t need = 0;
+  st = sdpa_b200_fwd_workspace_bytes(p, &need);
+  if (st != SDPA_B200_OK) return st;
+  st = validate_workspace(workspace, workspace_bytes, need);
+  if (st != SDPA_B200_OK) return st;
+  st = check_device();
+  if (st != SDPA_B200_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(workspace, 0, kWorkspaceHeaderBytes, s) != cudaSuccess) {
+    set_error("clearing the workspace header failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return SDPA_B200_LAUNCH_FAILED;
+  }
+  if (use_decode(p)) {
+    if (p->cu_seqlens_q != nullptr) {
+      set_error("the decode kernel takes dense tensors only");
+      return SDPA_B200_UNSUPPORTED;
+    }
+    return launch_fwd_decode(*p, workspace, workspace_bytes, s);
+  }
+  return launch_fwd_prefill(*p, workspace, s, g_debug_buffer);
+}
+
+int sdpa_b200_bwd(const sdpa_b200_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+  int st = validate_common(p);
+  if (st != SDPA_B200_OK) return st;
+  const bool varlen = p->cu_seqlens_q != nullptr;
+  if ((st = check_tensor("dout", p->dout, p->do_batch_stride, p->do_head_stride, p->do_row_stride, varlen,
+                         p->batch, p->heads_q)) != SDPA_B200_OK)
+    return st;
+  if ((st = check_tensor("dq", p->dq, p->dq_batch_stride, p->dq_head_stride, p->dq_row_stride, varlen, p->batch,
+                         p->heads_q)) != SDPA_B200_OK)
+    return st;
+  if ((st = check_tensor("dk", p->dk, p->dk_batch_stride, p->dk_head_stride, p->dk_row_stride, varlen, p->batch,
+                         p->heads_kv)) != SDPA_B200_OK)
+    return st;
+  if ((st = check_tensor("dv", p->dv, p->dv_batch_stride, p->dv_head_stride, p->dv_row_stride, varlen, p->batch,
+                         p->heads_kv)) != SDPA_B200_OK)
+    return st;
+  const size_t need = kWorkspaceHeaderBytes + bwd_workspace_bytes(*p);
+  st = validate_workspace(workspace, workspace_bytes, need);
+  if (st != SDPA_B200_OK) return st;
+  st = check_device();
+  if (st != SDPA_B200_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(workspace, 0, kWorkspaceHeaderBytes, s) != cudaSuccess) {
+    set_error("clearing the workspace header failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return SDPA_B200_LAUNCH_FAILED;
+  }
+  return launch_bwd(*p, workspace, workspace_bytes, s);
+}
+
+int sdpa_b200_read_device_status(const void* workspace, void* stream, int* device_status) {
+  if (workspace == nullptr || device_status == nullptr) {
+    set_error("workspace and device_status must be non-NULL");
+    return SDPA_B200_INVALID_ARG;
+  }
+  uint32_t word = 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t err = cudaMemcpyAsync(&word, workspace, sizeof(word), cudaMemcpyDeviceToHost, s);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+  if (err != cudaSuccess) {
+    set_error("reading the device status failed: %s", cudaGetErrorString(err));
+    return SDPA_B200_LAUNCH_FAILED;
+  }
+  *device_status = static_cast<int>(word);
+  return SDPA_B200_OK;
+}
+
+// Test hook (not declared in the public header): a device buffer of 2*128*260 floats that
+// receives, for the first CTA of the next prefill launches, each row's raw first S tile,
+// its un-normalised O accumulator and its running (max, sum). Pass NULL to switch it off.
+SDPA_B200_API void sdpa_b200_set_debug_buffer(float* device_buffer) { g_debug_buffer = device_buffer; }
+
+}  // extern "C"

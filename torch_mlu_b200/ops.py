@@ -1,0 +1,335 @@
+"""Host-side mirror of torch_mlu's attention operator interface, over the C ABI.
+
+Each function keeps the name, argument order, return tuple and error behaviour of the
+reference operator it stands for (torch-2.1 schemas, codegen/mlu_functions.yaml:1312-1316):
+
+* ``_scaled_dot_product_flash_attention``           <- cnnl__scaled_dot_product_flash_attention
+  (torch_mlu/csrc/aten/operators/cnnl/transformers/attention.cpp:58-159)
+* ``_flash_attention_forward``                      <- cnnl__flash_attention_forward (attention.cpp:161-203)
+* ``_scaled_dot_product_flash_attention_backward``  <- attention.cpp:205-297
+* ``_flash_attention_backward``                     <- cnnl__flash_attention_backward (attention.cpp:299-348)
+
+Unlike the reference wrappers, nothing is re-packed: tensors go to the kernels with their
+strides (any [B,H,L,D] / [B,L,H,D] view with unit head_dim stride), so the five
+``cnnl_contiguous`` copies of attention.cpp:124-129, 260-269 do not exist here.
+
+torch is used for device memory and the current stream only. There is no CPU path: a call
+on a machine without the built library or without an sm_100 GPU raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _cabi
+
+__all__ = [
+    "_scaled_dot_product_flash_attention",
+    "_scaled_dot_product_flash_attention_backward",
+    "_flash_attention_forward",
+    "_flash_attention_backward",
+    "decode_attention",
+    "calculate_scale",
+    "workspace_for",
+]
+
+_DECODE_MAX_Q = 1
+
+
+def calculate_scale(query: torch.Tensor, scale: Optional[float]) -> float:
+    """Default softmax scale 1/sqrt(head_dim) (sdp_utils.h:40-47)."""
+    return float(scale) if scale is not None else 1.0 / math.sqrt(query.size(-1))
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _check_inputs(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        _check(t.is_cuda, "Input tensor must be on a CUDA device (this path has no CPU fallback)")
+        # FlashAttention_internal.cpp:74-80
+        _check(t.dtype == torch.bfloat16,
+               "FlashAttention only support fp16 and bf16 data type; this build implements bf16 "
+               f"(got {t.dtype})")
+        # FlashAttention_internal.cpp:100-108
+        _check(t.stride(-1) == 1, "Input tensor must have contiguous last dimension")
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _set_strides_bhld(p: _cabi.SdpaParams, prefix: str, t: torch.Tensor) -> None:
+    """t is [B, H, L, D] (any strides, unit last)."""
+    setattr(p, f"{prefix}_batch_stride", t.stride(0))
+    setattr(p, f"{prefix}_head_stride", t.stride(1))
+    setattr(p, f"{prefix}_row_stride", t.stride(2))
+
+
+def _set_strides_thd(p: _cabi.SdpaParams, prefix: str, t: torch.Tensor) -> None:
+    """t is packed [total, H, D]."""
+    setattr(p, f"{prefix}_batch_stride", 0)
+    setattr(p, f"{prefix}_head_stride", t.stride(1))
+    setattr(p, f"{prefix}_row_stride", t.stride(0))
+
+
+class _Workspace:
+    """Per-device cache of one growing workspace buffer (torch owns the memory)."""
+
+    _bufs: dict = {}
+
+    @classmethod
+    def get(cls, device: torch.device, nbytes: int) -> torch.Tensor:
+        key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+        buf = cls._bufs.get(key)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+            cls._bufs[key] = buf
+        return buf
+
+
+def workspace_for(params: _cabi.SdpaParams, backward: bool, device: torch.device) -> torch.Tensor:
+    lib = _cabi.load()
+    need = ctypes.c_size_t(0)
+    fn = lib.sdpa_b200_bwd_workspace_bytes if backward else lib.sdpa_b200_fwd_workspace_bytes
+    _cabi.check(fn(ctypes.byref(params), ctypes.byref(need)), "workspace query")
+    return _Workspace.get(device, need.value)
+
+
+def _run_fwd(p: _cabi.SdpaParams, device: torch.device) -> None:
+    lib = _cabi.load()
+    ws = workspace_for(p, False, device)
+    _cabi.check(lib.sdpa_b200_fwd(ctypes.byref(p), ws.data_ptr(), ws.numel(), _stream_ptr()),
+                "sdpa_b200_fwd")
+
+
+def _run_bwd(p: _cabi.SdpaParams, device: torch.device) -> None:
+    lib = _cabi.load()
+    ws = workspace_for(p, True, device)
+    _cabi.check(lib.sdpa_b200_bwd(ctypes.byref(p), ws.data_ptr(), ws.numel(), _stream_ptr()),
+                "sdpa_b200_bwd")
+
+
+def device_status(device: Optional[torch.device] = None) -> int:
+    """Synchronise the current stream and return the status word the last call's kernels
+    left in the workspace (0, or DEVICE_TIMEOUT when a bounded in-kernel wait ran out)."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    ws = _Workspace.get(device, 256)
+    out = ctypes.c_int(0)
+    _cabi.check(_cabi.load().sdpa_b200_read_device_status(ws.data_ptr(), _stream_ptr(), ctypes.byref(out)),
+                "read_device_status")
+    return out.value
+
+
+def _empty_like_debug(q: torch.Tensor) -> torch.Tensor:
+    return torch.empty((0,), dtype=q.dtype, device=q.device)
+
+
+def _philox_placeholders(q: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    # dropout is 0: seed/offset are empty int64 tensors, as FlashAttention_internal.cpp:212-213
+    e = torch.empty((0,), dtype=torch.int64, device=q.device)
+    return e, e.clone()
+
+
+# --------------------------------------------------------------------------------------
+# dense [B, H, L, D]
+# --------------------------------------------------------------------------------------
+def _dense_params(query, key, value, out, lse, is_causal, scale, kernel=_cabi.KERNEL_AUTO,
+                  num_splits=0) -> _cabi.SdpaParams:
+    p = _cabi.SdpaParams()
+    p.q, p.k, p.v = query.data_ptr(), key.data_ptr(), value.data_ptr()
+    p.out, p.lse = out.data_ptr(), lse.data_ptr()
+    p.batch, p.heads_q, p.heads_kv, p.head_dim = query.size(0), query.size(1), key.size(1), query.size(3)
+    p.max_seqlen_q, p.max_seqlen_k = query.size(2), key.size(2)
+    _set_strides_bhld(p, "q", query)
+    _set_strides_bhld(p, "k", key)
+    _set_strides_bhld(p, "v", value)
+    _set_strides_bhld(p, "o", out)
+    p.softmax_scale = scale
+    p.dropout_p = 0.0
+    p.is_causal = int(bool(is_causal))
+    p.dtype = _cabi.DTYPE_BF16
+    p.kernel = kernel
+    p.num_splits = num_splits
+    return p
+
+
+def _dense_forward(query, key, value, is_causal, scale, allow_gqa, kernel=_cabi.KERNEL_AUTO, num_splits=0):
+    # attention.cpp:70-100
+    _check(query.dim() == 4 and key.dim() == 4 and value.dim() == 4,
+           "query, key and value must be 4-dimensional [batch, heads, seq_len, head_dim]")
+    _check(query.size(0) == key.size(0) == value.size(0), "query, key and value must have the same batch size")
+    _check(key.size(2) == value.size(2), "Key and Value must have the same sequence length")
+    if allow_gqa:
+        _check(key.size(1) == value.size(1) and query.size(1) % key.size(1) == 0,
+               "Number of heads in key/value must divide number of heads in query")
+    else:
+        _check(query.size(1) == key.size(1) == value.size(1),
+               "query, key and value must have the same number of heads")
+    _check(query.size(3) == key.size(3) == value.size(3), "query, key and value must have the same head_dim")
+    _check_inputs(query, key, value)
+    B, H, Lq, D = query.shape
+    # the reference returns a [B,H,L,D] view of a [B,L,H,D] buffer (attention.cpp:146-148)
+    out = torch.empty((B, Lq, H, D), dtype=query.dtype, device=query.device).transpose(1, 2)
+    lse = torch.empty((B, H, Lq), dtype=torch.float32, device=query.device)
+    p = _dense_params(query, key, value, out, lse, is_causal, scale, kernel, num_splits)
+    _run_fwd(p, query.device)
+    return out, lse
+
+
+def _scaled_dot_product_flash_attention(query, key, value, dropout_p: float = 0.0, is_causal: bool = False,
+                                        return_debug_mask: bool = False, *, scale: Optional[float] = None):
+    """(output, logsumexp, cum_seq_q, cum_seq_k, max_q, max_k, philox_seed, philox_offset, debug_attn_mask).
+
+    output is [B,H,Lq,D] bf16, logsumexp [B,H,Lq] fp32 (natural log, scale included).
+    """
+    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
+    out, lse = _dense_forward(query, key, value, is_causal, calculate_scale(query, scale), allow_gqa=False)
+    B, _, Lq, _ = query.shape
+    Lk = key.size(2)
+    # attention.cpp:109-119; kept for callers that pass them on to the backward op
+    cum_q = torch.arange(0, (B + 1) * Lq, Lq, dtype=torch.int32, device=query.device)
+    cum_k = torch.arange(0, (B + 1) * Lk, Lk, dtype=torch.int32, device=query.device)
+    seed, offset = _philox_placeholders(query)
+    return out, lse, cum_q, cum_k, Lq, Lk, seed, offset, _empty_like_debug(query)
+
+
+def _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, scale):
+    _check_inputs(grad_out, query, key, value, out)
+    _check(logsumexp.dtype == torch.float32 and logsumexp.is_contiguous(), "logsumexp must be contiguous fp32")
+    B, H, Lq, D = query.shape
+    _check(tuple(logsumexp.shape) == (B, H, Lq), "logsumexp must be [batch, heads, seqlen_q]")
+    dq = torch.empty((B, Lq, H, D), dtype=query.dtype, device=query.device).transpose(1, 2)
+    dk = torch.empty((B, key.size(2), key.size(1), D), dtype=key.dtype, device=key.device).transpose(1, 2)
+    dv = torch.empty((B, key.size(2), key.size(1), D), dtype=key.dtype, device=key.device).transpose(1, 2)
+    p = _dense_params(query, key, value, out, logsumexp, is_causal, scale)
+    p.dout, p.dq, p.dk, p.dv = grad_out.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    _set_strides_bhld(p, "do", grad_out)
+    _set_strides_bhld(p, "dq", dq)
+    _set_strides_bhld(p, "dk", dk)
+    _set_strides_bhld(p, "dv", dv)
+    _run_bwd(p, query.device)
+    return dq, dk, dv
+
+
+def _scaled_dot_product_flash_attention_backward(grad_out, query, key, value, out, logsumexp, cum_seq_q, cum_seq_k,
+                                                 max_q, max_k, dropout_p, is_causal, philox_seed, philox_offset,
+                                                 *, scale: Optional[float] = None):
+    """(grad_q, grad_k, grad_v), each shaped like its input (attention.cpp:205-297)."""
+    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
+    if grad_out.stride(-1) != 1:
+        grad_out = grad_out.contiguous()
+    return _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, calculate_scale(query, scale))
+
+
+# --------------------------------------------------------------------------------------
+# packed varlen [total, H, D] + int32 cu_seqlens
+# --------------------------------------------------------------------------------------
+def _varlen_params(query, key, value, out, lse, cu_q, cu_k, max_q, max_k, is_causal, scale) -> _cabi.SdpaParams:
+    p = _cabi.SdpaParams()
+    p.q, p.k, p.v = query.data_ptr(), key.data_ptr(), value.data_ptr()
+    p.out, p.lse = out.data_ptr(), lse.data_ptr()
+    p.cu_seqlens_q, p.cu_seqlens_k = cu_q.data_ptr(), cu_k.data_ptr()
+    p.batch = cu_q.numel() - 1
+    p.heads_q, p.heads_kv, p.head_dim = query.size(1), key.size(1), query.size(2)
+    p.max_seqlen_q, p.max_seqlen_k = int(max_q), int(max_k)
+    p.total_q, p.total_k = query.size(0), key.size(0)
+    _set_strides_thd(p, "q", query)
+    _set_strides_thd(p, "k", key)
+    _set_strides_thd(p, "v", value)
+    _set_strides_thd(p, "o", out)
+    p.softmax_scale = scale
+    p.dropout_p = 0.0
+    p.is_causal = int(bool(is_causal))
+    p.dtype = _cabi.DTYPE_BF16
+    p.kernel = _cabi.KERNEL_PREFILL
+    return p
+
+
+def _check_varlen(query, key, value, cu_q, cu_k):
+    # FlashAttention_internal.cpp:81-84, 112-127
+    _check(query.dim() == 3 and key.dim() == 3 and value.dim() == 3,
+           "varlen query, key and value must be packed [total_tokens, heads, head_dim]")
+    _check(cu_q.dtype == torch.int32, "cu_seqlens_q must have dtype int32")
+    _check(cu_k.dtype == torch.int32, "cu_seqlens_k must have dtype int32")
+    _check(cu_q.is_cuda and cu_k.is_cuda, "cu_seqlens must be on the device")
+    _check(cu_q.is_contiguous() and cu_k.is_contiguous(), "cu_seqlens must be contiguous")
+    _check(cu_q.numel() == cu_k.numel() and cu_q.numel() >= 2, "cu_seqlens_q and cu_seqlens_k must have batch+1 entries")
+    _check(key.size(1) == value.size(1) and query.size(1) % key.size(1) == 0,
+           "Number of heads in key/value must divide number of heads in query")
+    _check(query.size(2) == key.size(2) == value.size(2), "query, key and value must have the same head_dim")
+    _check(key.size(0) == value.size(0), "Key and Value must have the same number of tokens")
+    _check_inputs(query, key, value)
+
+
+def _flash_attention_forward(query, key, value, cum_seq_q, cum_seq_k, max_q: int, max_k: int, dropout_p: float,
+                             is_causal: bool, return_debug_mask: bool, *, scale: Optional[float] = None):
+    """(output, softmax_logsumexp, philox_seed, philox_offset, debug_attn_mask).
+
+    output is [total_q, Hq, D]; softmax_logsumexp is [Hq, total_q] fp32, the buffer
+    mha_varlen_fwd allocates (FlashAttention_internal.cpp:129). The reference then views it
+    as [Hq, B, max_q] (:261-265), which only exists for equal-length batches; ragged batches
+    keep the packed layout here.
+    """
+    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
+    _check_varlen(query, key, value, cum_seq_q, cum_seq_k)
+    out = torch.empty_like(query, memory_format=torch.contiguous_format)
+    lse = torch.empty((query.size(1), query.size(0)), dtype=torch.float32, device=query.device)
+    p = _varlen_params(query, key, value, out, lse, cum_seq_q, cum_seq_k, max_q, max_k, is_causal,
+                       calculate_scale(query, scale))
+    _run_fwd(p, query.device)
+    seed, offset = _philox_placeholders(query)
+    return out, lse, seed, offset, _empty_like_debug(query)
+
+
+def _flash_attention_backward(grad_out, query, key, value, out, logsumexp, cum_seq_q, cum_seq_k, max_q: int,
+                              max_k: int, dropout_p: float, is_causal: bool, philox_seed, philox_offset,
+                              *, scale: Optional[float] = None):
+    """(dq, dk, dv) for packed varlen tensors. dk/dv have Hkv heads: the GQA group is reduced
+    inside the kernel (the reference's shape check at FlashAttention_internal.cpp:363-364
+    cannot pass for Hq != Hkv; here it can)."""
+    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
+    _check_varlen(query, key, value, cum_seq_q, cum_seq_k)
+    if grad_out.stride(-1) != 1:
+        grad_out = grad_out.contiguous()
+    _check_inputs(grad_out, out)
+    _check(logsumexp.dtype == torch.float32 and logsumexp.is_contiguous()
+           and tuple(logsumexp.shape) == (query.size(1), query.size(0)),
+           "logsumexp must be contiguous fp32 [heads_q, total_q]")
+    dq = torch.empty_like(query, memory_format=torch.contiguous_format)
+    dk = torch.empty_like(key, memory_format=torch.contiguous_format)
+    dv = torch.empty_like(value, memory_format=torch.contiguous_format)
+    p = _varlen_params(query, key, value, out, logsumexp, cum_seq_q, cum_seq_k, max_q, max_k, is_causal,
+                       calculate_scale(query, scale))
+    p.dout, p.dq, p.dk, p.dv = grad_out.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    _set_strides_thd(p, "do", grad_out)
+    _set_strides_thd(p, "dq", dq)
+    _set_strides_thd(p, "dk", dk)
+    _set_strides_thd(p, "dv", dv)
+    _run_bwd(p, query.device)
+    return dq, dk, dv
+
+
+# --------------------------------------------------------------------------------------
+# decode (seqlen_q == 1, GQA allowed) - no reference counterpart
+# --------------------------------------------------------------------------------------
+def decode_attention(query, key_cache, value_cache, *, scale: Optional[float] = None, num_splits: int = 0):
+    """query [B,Hq,1,D], key/value cache [B,Hkv,Lkv,D] -> (output [B,Hq,1,D], logsumexp [B,Hq,1]).
+
+    Split-KV streaming kernel; the key range is cut into ``num_splits`` pieces (0 = choose)."""
+    _check(query.dim() == 4 and query.size(2) == 1, "decode_attention needs query of shape [B, Hq, 1, D]")
+    out, lse = _dense_forward(query, key_cache, value_cache, False, calculate_scale(query, scale),
+                              allow_gqa=True, kernel=_cabi.KERNEL_DECODE, num_splits=num_splits)
+    return out, lse
+
+
+def gqa_prefill(query, key, value, *, is_causal: bool = False, scale: Optional[float] = None):
+    """Dense [B,Hq,L,D] x [B,Hkv,L,D] prefill with head broadcast (the dense reference op
+    refuses Hq != Hkv, attention.cpp:82-83; the kernel underneath does not)."""
+    return _dense_forward(query, key, value, is_causal, calculate_scale(query, scale), allow_gqa=True,
+                          kernel=_cabi.KERNEL_PREFILL)
