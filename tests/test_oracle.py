@@ -1,0 +1,109 @@
+"""CPU checks of the oracle itself: against the golden vectors produced by the reference's
+attention_ref, between its independent statements, and on the reference's CPU-runnable config."""
+import glob
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle
+from oracle import sdpa_oracle as orc
+from torch_mlu_b200 import workloads
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "attention_ref_*.npz")))
+
+
+def load_golden(path):
+    z = np.load(path)
+    bits = lambda a: torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)
+    scale = float(z["scale"])
+    return dict(q=bits(z["q"]), k=bits(z["k"]), v=bits(z["v"]), dout=bits(z["dout"]),
+                out=torch.from_numpy(z["out"]), dq=torch.from_numpy(z["dq"]), dk=torch.from_numpy(z["dk"]),
+                dv=torch.from_numpy(z["dv"]), lse=torch.from_numpy(z["lse_derived"]),
+                causal=bool(z["causal"]), scale=None if scale < 0 else scale)
+
+
+def test_golden_files_present():
+    assert len(GOLDEN) >= 6
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[14:-4] for p in GOLDEN])
+def test_oracle_statements_match_reference_golden(path):
+    g = load_golden(path)
+    kw = dict(causal=g["causal"], scale=g["scale"])
+    # explicit math (fp32): same formulation as the reference oracle -> tight
+    out, lse = orc.attention_math(g["q"], g["k"], g["v"], **kw)
+    assert orc.error_stats(out, g["out"])[0] < 2e-5
+    orc.assert_close_lse(lse, g["lse"], max_abs=5e-6)
+    dq, dk, dv = orc.attention_math_backward(g["q"], g["k"], g["v"], g["dout"], **kw)
+    for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
+        assert orc.error_stats(got, g[name])[0] < 1e-4, name
+    # torch CPU fused SDPA (fp32)
+    out2, lse2 = orc.cpu_sdpa_forward(g["q"], g["k"], g["v"], **kw)
+    assert orc.error_stats(out2, g["out"])[0] < 2e-5
+    orc.assert_close_lse(lse2, g["lse"], max_abs=5e-6)
+    dq2, dk2, dv2 = orc.cpu_sdpa_backward(g["dout"], g["q"], g["k"], g["v"], out2, lse2, **kw)
+    for name, got in (("dq", dq2), ("dk", dk2), ("dv", dv2)):
+        assert orc.error_stats(got, g[name])[0] < 1e-4, name
+    # plain C, fp64 accumulation
+    out3, lse3 = c_oracle.forward(g["q"], g["k"], g["v"], **kw)
+    assert orc.error_stats(out3, g["out"])[0] < 2e-5
+    orc.assert_close_lse(lse3, g["lse"], max_abs=5e-6)
+    dq3, dk3, dv3 = c_oracle.backward(g["q"], g["k"], g["v"], g["dout"], **kw)
+    for name, got in (("dq", dq3), ("dk", dk3), ("dv", dv3)):
+        assert orc.error_stats(got, g[name])[0] < 1e-4, name
+
+
+def test_config1_cpu_reference_case():
+    """BASELINE config 1: fp32 B2 H8 L256 D64 non-causal, seed 0 - the case the reference path
+    (torch CPU SDPA) runs as is. LSE is the natural-log logsumexp of the scaled scores."""
+    c = workloads.config1_cpu_reference()
+    out, lse = orc.cpu_sdpa_forward(c.q, c.k, c.v, causal=False, scale=c.softmax_scale)
+    out_m, lse_m = orc.attention_math(c.q, c.k, c.v, causal=False, scale=c.softmax_scale, dtype=torch.float64)
+    assert orc.error_stats(out, out_m)[0] < 5e-6
+    assert orc.error_stats(lse, lse_m)[0] < 5e-6
+    scores = torch.einsum("bhtd,bhsd->bhts", c.q.double(), c.k.double()) / math.sqrt(64)
+    assert orc.error_stats(lse, torch.logsumexp(scores, -1))[0] < 5e-6
+    assert c.forward_flops() == pytest.approx(2.684e8, rel=1e-3)
+
+
+def test_config4_lengths_are_the_documented_draw():
+    g = torch.Generator().manual_seed(3)
+    lens = torch.randint(512, 4097, (16,), generator=g).tolist()
+    assert lens == workloads.CONFIG4_SEQLENS
+    assert sum(lens) == 34004 and max(lens) == 4038
+
+
+def test_varlen_oracle_equals_per_sequence_dense():
+    g = torch.Generator().manual_seed(7)
+    lens = [5, 33, 1, 64]
+    cu = [0]
+    for l in lens:
+        cu.append(cu[-1] + l)
+    q = torch.randn(cu[-1], 4, 32, generator=g)
+    k = torch.randn(cu[-1], 2, 32, generator=g)
+    v = torch.randn(cu[-1], 2, 32, generator=g)
+    out, lse = orc.varlen_forward(q, k, v, cu, cu, causal=True)
+    assert out.shape == q.shape and lse.shape == (4, cu[-1])
+    i = 1
+    o1, l1 = orc.attention_math(q[cu[i]:cu[i + 1]].transpose(0, 1)[None], k[cu[i]:cu[i + 1]].transpose(0, 1)[None],
+                                v[cu[i]:cu[i + 1]].transpose(0, 1)[None], causal=True)
+    assert orc.error_stats(out[cu[i]:cu[i + 1]], o1[0].transpose(0, 1))[0] < 1e-5
+    assert orc.error_stats(lse[:, cu[i]:cu[i + 1]], l1[0])[0] < 1e-5
+    dout = torch.randn(q.shape, generator=g)
+    dq, dk, dv = orc.varlen_backward(dout, q, k, v, cu, cu, causal=True)
+    assert dq.shape == q.shape and dk.shape == k.shape and dv.shape == v.shape
+
+
+def test_fully_masked_rows_follow_library_convention():
+    """Lq > Lk with bottom-right causal: the first Lq-Lk rows see no key -> out 0, lse +inf."""
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(1, 1, 6, 16, generator=g)
+    k = torch.randn(1, 1, 4, 16, generator=g)
+    v = torch.randn(1, 1, 4, 16, generator=g)
+    for fn in (orc.attention_math, orc.cpu_sdpa_forward, c_oracle.forward):
+        out, lse = fn(q, k, v, causal=True)
+        assert torch.all(out[0, 0, :2] == 0) and torch.all(torch.isinf(lse[0, 0, :2]) & (lse[0, 0, :2] > 0))
+        assert torch.isfinite(lse[0, 0, 2:]).all()
