@@ -1,0 +1,55 @@
+"""Runs a few launches of one kernel on a sized-down case, for use under a profiler.
+
+    python -m torch_mlu_b200.profile_case prefill --batch 2 --heads 32 --seqlen 4096 --launches 3
+    python -m torch_mlu_b200.profile_case decode  --batch 8 --seqlen-k 32768 --launches 3
+    python -m torch_mlu_b200.profile_case backward --batch 2 --heads 16 --seqlen 2048 --launches 3
+
+Inputs are device-generated N(0,1) bf16; sizes default to a few hundred MB so that a
+multi-pass profiler capture stays short while the working set still exceeds L2.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import ops
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["prefill", "decode", "backward"])
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--heads-kv", type=int, default=0)
+    ap.add_argument("--seqlen", type=int, default=4096)
+    ap.add_argument("--seqlen-k", type=int, default=32768)
+    ap.add_argument("--launches", type=int, default=3)
+    ap.add_argument("--non-causal", action="store_true")
+    a = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    rn = lambda *s: torch.randn(*s, generator=g, device=dev).to(torch.bfloat16)
+    hkv = a.heads_kv or a.heads
+    if a.kernel == "decode":
+        hkv = a.heads_kv or 8
+        q, k, v = rn(a.batch, a.heads, 1, 128), rn(a.batch, hkv, a.seqlen_k, 128), rn(a.batch, hkv, a.seqlen_k, 128)
+        for _ in range(a.launches):
+            ops.decode_attention(q, k, v)
+    else:
+        q, k, v = rn(a.batch, a.heads, a.seqlen, 128), rn(a.batch, hkv, a.seqlen, 128), rn(a.batch, hkv, a.seqlen, 128)
+        causal = not a.non_causal
+        if a.kernel == "prefill":
+            for _ in range(a.launches):
+                ops.gqa_prefill(q, k, v, is_causal=causal)
+        else:
+            do = rn(a.batch, a.heads, a.seqlen, 128)
+            out, lse = ops.gqa_prefill(q, k, v, is_causal=causal)
+            for _ in range(a.launches):
+                ops._dense_backward(do, q, k, v, out, lse, causal, 128 ** -0.5)
+    torch.cuda.synchronize()
+    print("device status", ops.device_status())
+
+
+if __name__ == "__main__":
+    main()
