@@ -60,6 +60,7 @@ struct FwdKernelParams {
   uint32_t* status;
   int64_t o_batch_stride, o_head_stride, o_row_stride;
   int seqlen_q, seqlen_k, total_q, heads_q, kv_group;
+  int num_m_blocks, num_bh, heads_per_wave;  // tile scheduler, see tile_coords()
   float scale_log2;
   int is_causal;
 };
@@ -97,9 +98,23 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int b = blockIdx.z;
-  const int h = blockIdx.y;
-  const int m_block = gridDim.x - 1 - blockIdx.x;  // heaviest causal tiles first
+  // Tile order. (batch, head) pairs are taken in groups of `heads_per_wave` whose K/V fit
+  // L2 together; inside a group the 256-row tiles go heaviest first (largest m_block, i.e.
+  // most causal key blocks) across all its heads, so each group - and the whole grid - ends
+  // on its lightest tiles instead of on one long straggler.
+  int b, h, m_block;
+  {
+    const int per_group = p.heads_per_wave * p.num_m_blocks;
+    const int grp = blockIdx.x / per_group;
+    const int w = blockIdx.x - grp * per_group;
+    const int size = min(p.heads_per_wave, p.num_bh - grp * p.heads_per_wave);
+    const int rank = w / size;
+    const int bh = grp * p.heads_per_wave + (w - rank * size);
+    if (rank >= p.num_m_blocks) return;  // padding slots of a short last group
+    m_block = p.num_m_blocks - 1 - rank;
+    b = bh / p.heads_q;
+    h = bh - b * p.heads_q;
+  }
 
   int q_off = 0, k_off = 0, len_q = p.seqlen_q, len_k = p.seqlen_k, bcoord = b;
   if (p.cu_q != nullptr) {
@@ -277,7 +292,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
       }
       if (kDebug) {
-        if (p.debug != nullptr && j == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        if (p.debug != nullptr && j == 0 && m_block == 0 && h == 0 && b == 0) {
           float* d = p.debug + (t * kBlockM + row_in_tile) * 260;
           for (int i = 0; i < kBlockN; ++i) d[i] = s[i];
         }
@@ -375,7 +390,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
           for (int i = 0; i < 32; ++i) r[i] = 0u;
         }
         if (kDebug) {
-          if (p.debug != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+          if (p.debug != nullptr && m_block == 0 && h == 0 && b == 0) {
             float* d = p.debug + (t * kBlockM + row_in_tile) * 260 + 128 + cc * 32;
             for (int i = 0; i < 32; ++i) d[i] = __uint_as_float(r[i]);
           }
@@ -391,7 +406,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
       }
       if (kDebug) {
-        if (p.debug != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        if (p.debug != nullptr && m_block == 0 && h == 0 && b == 0) {
           float* d = p.debug + (t * kBlockM + row_in_tile) * 260 + 256;
           d[0] = m_run;
           d[1] = l_run;
@@ -459,7 +474,18 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
     set_error("prefill: cudaFuncSetAttribute(%u bytes smem): %s", kSmemBytes, cudaGetErrorString(err));
     return SDPA_B200_LAUNCH_FAILED;
   }
-  dim3 grid((p.max_seqlen_q + 2 * kBlockM - 1) / (2 * kBlockM), p.heads_q, p.batch);
+  kp.num_m_blocks = (p.max_seqlen_q + 2 * kBlockM - 1) / (2 * kBlockM);
+  kp.num_bh = p.batch * p.heads_q;
+  {
+    // K+V bytes one query head streams, shared by the heads of its GQA group
+    const double kv_bytes = 2.0 * p.max_seqlen_k * p.head_dim * 2 / kp.kv_group;
+    int hpw = static_cast<int>((48.0 * 1024 * 1024) / kv_bytes);
+    hpw = hpw < 1 ? 1 : (hpw > 32 ? 32 : hpw);
+    if (hpw > kp.num_bh) hpw = kp.num_bh;
+    kp.heads_per_wave = hpw;
+  }
+  const int groups = (kp.num_bh + kp.heads_per_wave - 1) / kp.heads_per_wave;
+  dim3 grid(groups * kp.heads_per_wave * kp.num_m_blocks, 1, 1);
   kernel<<<grid, kNumThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, kp);
   err = cudaGetLastError();
   if (err != cudaSuccess) {
