@@ -1,8 +1,551 @@
+// Backward attention kernels for sm_100a.
+//
+// Replaces the device work behind mha_varlen_bwd -> cnnlFlashAttentionBackward
+// (torch_mlu/csrc/aten/operators/cnnl/internal/FlashAttention_internal.cpp:449-480):
+// given dO, Q, K, V, O and the saved logsumexp, recompute P = exp(scale*QK^T - lse) and
+//   dV = P^T dO,  dP = dO V^T,  dS = P o (dP - delta),  dQ = scale dS K,  dK = scale dS^T Q
+// with delta = rowsum(dO o O). GQA: dK/dV of one KV head sum over its query heads inside one
+// CTA, so nothing is accumulated with atomics and results are bit-reproducible.
+//
+// Three launches:
+//   1. bwd_preprocess_kernel: delta and the log2-domain logsumexp into a padded
+//      [batch, heads_q, ceil128(max_seqlen_q)] workspace (rows past a sequence get lse = +inf,
+//      which later turns their P into exact zeros).
+//   2. bwd_tile_kernel<kModeDKDV>: one CTA per (batch, kv head, 128-key block). K and V tiles
+//      stay in shared memory; (Q, dO) tiles stream through a 2-stage TMA ring. Per Q tile:
+//      S^T = K Q^T and dP^T = V dO^T on tcgen05 into TMEM, the compute warpgroup (thread = key
+//      row = TMEM lane) forms P^T and dS^T, writes them back to TMEM as bf16, and two more
+//      MMAs with the TMEM operand accumulate dV += P^T dO and dK += dS^T Q (the streamed tiles
+//      are re-read in place as MN-major operands).
+//   3. bwd_tile_kernel<kModeDQ>: one CTA per (batch, query head, 128-query block); Q and dO
+//      stay, (K, V) stream; S = Q K^T, dP = dO V^T, dS -> TMEM, dQ += dS K.
+// TMEM: T1 [0,128) T2 [128,256) ACC1 [256,384) ACC2 [384,512).
+#include <cuda_bf16.h>
+
 #include "kernels.h"
+#include "ptx_sm100.cuh"
+
 namespace sdpa_b200 {
-size_t bwd_workspace_bytes(const sdpa_b200_params& p) { return 0; }
+namespace {
+
+constexpr int kTile = 128;  // rows per tile (queries or keys) and head_dim
+constexpr uint32_t kTileBytes = kTile * kTile * 2;
+constexpr uint32_t kHalfBytes = kTileBytes / 2;
+constexpr int kStages = 2;
+constexpr int kThreads = 192;  // warps 0-3 compute, warp 4 TMA, warp 5 MMA
+constexpr int kModeDKDV = 0;
+constexpr int kModeDQ = 1;
+
+constexpr uint32_t kSmemX = 0;                                   // stationary pair, 64 KB
+constexpr uint32_t kSmemY = 2 * kTileBytes;                      // kStages x 64 KB
+constexpr uint32_t kSmemVec = kSmemY + kStages * 2 * kTileBytes; // kStages x (lse2[128], delta[128])
+constexpr uint32_t kSmemBar = kSmemVec + kStages * 1024;
+constexpr uint32_t kBarXFull = 0;
+constexpr uint32_t kBarYFull = 8;
+constexpr uint32_t kBarYEmpty = kBarYFull + 8 * kStages;
+constexpr uint32_t kBarTFull = kBarYEmpty + 8 * kStages;
+constexpr uint32_t kBarPFull = kBarTFull + 8;
+constexpr uint32_t kBarAccFull = kBarPFull + 8;
+constexpr uint32_t kSmemTmemPtr = kBarAccFull + 8;
+constexpr uint32_t kSmemAbort = kSmemTmemPtr + 4;
+constexpr uint32_t kSmemBytes = kSmemBar + 256 + 1024;
+
+struct BwdKernelParams {
+  const float* lse2;   // padded [batch, heads_q, lq_pad]
+  const float* delta;  // padded [batch, heads_q, lq_pad]
+  __nv_bfloat16* dq;
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  const int32_t* cu_q;
+  const int32_t* cu_k;
+  uint32_t* status;
+  int64_t dq_batch_stride, dq_head_stride, dq_row_stride;
+  int64_t dk_batch_stride, dk_head_stride, dk_row_stride;
+  int64_t dv_batch_stride, dv_head_stride, dv_row_stride;
+  int seqlen_q, seqlen_k, heads_q, heads_kv, kv_group, lq_pad;
+  int num_row_blocks;  // blocks of 128 stationary rows (keys for dK/dV, queries for dQ)
+  float scale, scale_log2;
+  int is_causal;
+};
+
+constexpr uint32_t kIdescSS = umma_idesc_bf16(kTile, kTile, false, false);
+constexpr uint32_t kIdescTS = umma_idesc_bf16(kTile, kTile, false, true);
+
+// T = X Y^T, contraction over head_dim, both operands K-major in shared memory
+__device__ __forceinline__ void issue_xyT(uint32_t t, uint32_t x_smem, uint32_t y_smem) {
+#pragma unroll
+  for (int ks = 0; ks < kTile / 16; ++ks) {
+    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+    umma_ss(t, umma_desc_kmajor(x_smem + off), umma_desc_kmajor(y_smem + off), kIdescSS, ks > 0 ? 1u : 0u);
+  }
+}
+
+// ACC (+)= W Y, W bf16 in TMEM (lane = row), contraction over the 128 rows of the Y tile
+__device__ __forceinline__ void issue_wy(uint32_t acc, uint32_t w_tmem, uint32_t y_smem, bool accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < kTile / 16; ++ks) {
+    umma_ts(acc, w_tmem + ks * 8, umma_desc_mnmajor(y_smem + ks * 2048, kHalfBytes), kIdescTS,
+            (accumulate || ks > 0) ? 1u : 0u);
+  }
+}
+
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                const BwdKernelParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // grid: x = stationary row block (heaviest first), y = head (kv head for dK/dV), z = batch
+  const int b = blockIdx.z;
+  const int hx = blockIdx.y;
+  int q_off = 0, k_off = 0, len_q = p.seqlen_q, len_k = p.seqlen_k, bcoord = b;
+  if (p.cu_q != nullptr) {
+    q_off = p.cu_q[b];
+    len_q = p.cu_q[b + 1] - q_off;
+    k_off = p.cu_k[b];
+    len_k = p.cu_k[b + 1] - k_off;
+    bcoord = 0;
+  }
+  const int causal_off = len_k - len_q;
+  const int len_x = (kMode == kModeDKDV) ? len_k : len_q;
+  // dK/dV: block 0 sees every query (heaviest) -> ascending; dQ: last block heaviest -> descending
+  const int xb = (kMode == kModeDKDV) ? static_cast<int>(blockIdx.x) : p.num_row_blocks - 1 - static_cast<int>(blockIdx.x);
+  const int x0 = xb * kTile;
+  if (x0 >= len_x) return;
+
+  // streamed tile range [y_lo, y_hi) (in tiles of 128) per head, and heads per CTA
+  int y_lo = 0, y_hi = 0;
+  if (kMode == kModeDKDV) {
+    y_hi = (len_q + kTile - 1) / kTile;
+    if (p.is_causal) y_lo = max(0, (x0 - causal_off) / kTile);  // first query tile with a row >= x0 - off
+    if (p.is_causal && x0 - causal_off > len_q - 1) y_lo = y_hi;
+  } else {
+    int vis_end = len_k;
+    if (p.is_causal) vis_end = min(len_k, x0 + kTile + causal_off);
+    y_hi = vis_end > 0 ? (vis_end + kTile - 1) / kTile : 0;
+  }
+  const int tiles_per_head = max(0, y_hi - y_lo);
+  const int heads_here = (kMode == kModeDKDV) ? p.kv_group : 1;
+  const int n_items = tiles_per_head * heads_here;
+
+  const uint32_t bar = base + kSmemBar;
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kSmemBar + kSmemAbort);
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + kSmemBar + kSmemTmemPtr);
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar + kBarXFull, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar + kBarYFull + 8 * s, 1);
+      mbar_init(bar + kBarYEmpty + 8 * s, 1);
+    }
+    mbar_init(bar + kBarTFull, 1);
+    mbar_init(bar + kBarPFull, kTile);
+    mbar_init(bar + kBarAccFull, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(base + kSmemBar + kSmemTmemPtr, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  const uint32_t t1 = tmem_base, t2 = tmem_base + 128, acc1 = tmem_base + 256, acc2 = tmem_base + 384;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_items > 0) {
+      const CUtensorMap* tmx1 = (kMode == kModeDKDV) ? &tm_k : &tm_q;
+      const CUtensorMap* tmx2 = (kMode == kModeDKDV) ? &tm_v : &tm_do;
+      const CUtensorMap* tmy1 = (kMode == kModeDKDV) ? &tm_q : &tm_k;
+      const CUtensorMap* tmy2 = (kMode == kModeDKDV) ? &tm_do : &tm_v;
+      const int x_row = ((kMode == kModeDKDV) ? k_off : q_off) + x0;
+      const int y_off = (kMode == kModeDKDV) ? q_off : k_off;
+      mbar_arrive_expect_tx(bar + kBarXFull, 2 * kTileBytes);
+      tma_load_4d(base + kSmemX, tmx1, bar + kBarXFull, 0, x_row, hx, bcoord);
+      tma_load_4d(base + kSmemX + kHalfBytes, tmx1, bar + kBarXFull, 64, x_row, hx, bcoord);
+      tma_load_4d(base + kSmemX + kTileBytes, tmx2, bar + kBarXFull, 0, x_row, hx, bcoord);
+      tma_load_4d(base + kSmemX + kTileBytes + kHalfBytes, tmx2, bar + kBarXFull, 64, x_row, hx, bcoord);
+      for (int i = 0; i < n_items; ++i) {
+        const int s = i % kStages;
+        const uint32_t use = static_cast<uint32_t>(i / kStages);
+        if (!mbar_wait(bar + kBarYEmpty + 8 * s, (use & 1u) ^ 1u, abort_flag)) break;
+        const int hi = i / tiles_per_head;
+        const int yt = y_lo + (i - hi * tiles_per_head);
+        // dK/dV streams the query heads of this KV head; dQ streams the KV head of this query head
+        const int hy = (kMode == kModeDKDV) ? hx * p.kv_group + hi : hx / p.kv_group;
+        const uint32_t full = bar + kBarYFull + 8 * s;
+        const uint32_t dst = base + kSmemY + s * 2 * kTileBytes;
+        const int row = y_off + yt * kTile;
+        if (kMode == kModeDKDV) {
+          mbar_arrive_expect_tx(full, 2 * kTileBytes + 1024);
+          const size_t vec = (static_cast<size_t>(b) * p.heads_q + hy) * p.lq_pad + static_cast<size_t>(yt) * kTile;
+          bulk_load_1d(base + kSmemVec + s * 1024, p.lse2 + vec, 512, full);
+          bulk_load_1d(base + kSmemVec + s * 1024 + 512, p.delta + vec, 512, full);
+        } else {
+          mbar_arrive_expect_tx(full, 2 * kTileBytes);
+        }
+        tma_load_4d(dst, tmy1, full, 0, row, hy, bcoord);
+        tma_load_4d(dst + kHalfBytes, tmy1, full, 64, row, hy, bcoord);
+        tma_load_4d(dst + kTileBytes, tmy2, full, 0, row, hy, bcoord);
+        tma_load_4d(dst + kTileBytes + kHalfBytes, tmy2, full, 64, row, hy, bcoord);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_items > 0) {
+      bool ok = mbar_wait(bar + kBarXFull, 0, abort_flag);
+      for (int i = 0; ok && i < n_items; ++i) {
+        const int s = i % kStages;
+        const uint32_t y1 = base + kSmemY + s * 2 * kTileBytes;
+        const uint32_t y2 = y1 + kTileBytes;
+        ok = mbar_wait(bar + kBarYFull + 8 * s, (i / kStages) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        // T1 = X1 Y1^T, T2 = X2 Y2^T (issued after the previous item's TMEM-operand MMAs, so
+        // the bf16 tiles those read from T1/T2 are consumed before being overwritten)
+        issue_xyT(t1, base + kSmemX, y1);
+        issue_xyT(t2, base + kSmemX + kTileBytes, y2);
+        umma_commit(bar + kBarTFull);
+        ok = mbar_wait(bar + kBarPFull, i & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (kMode == kModeDKDV) {
+          issue_wy(acc1, t1, y2, i > 0);  // dV += P^T dO
+          issue_wy(acc2, t2, y1, i > 0);  // dK += dS^T Q
+        } else {
+          issue_wy(acc1, t2, y1, i > 0);  // dQ += dS K
+        }
+        umma_commit(bar + kBarYEmpty + 8 * s);
+        if (i == n_items - 1) umma_commit(bar + kBarAccFull);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ compute warpgroup
+    const int r = warp * 32 + lane;  // stationary row in the tile = TMEM lane
+    const int xr = x0 + r;           // key index (dK/dV) or query index (dQ) within the sequence
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const float c = p.scale_log2;
+    bool ok = true;
+    float my_lse2 = 0.f, my_delta = 0.f;
+    if (kMode == kModeDQ) {
+      const size_t vec = (static_cast<size_t>(b) * p.heads_q + hx) * p.lq_pad + xr;
+      my_lse2 = p.lse2[vec];
+      my_delta = p.delta[vec];
+    }
+    for (int i = 0; i < n_items; ++i) {
+      const int s = i % kStages;
+      const int hi = i / tiles_per_head;
+      const int y0 = (y_lo + (i - hi * tiles_per_head)) * kTile;
+      ok = mbar_wait(bar + kBarTFull, i & 1, abort_flag);
+      if (!ok) break;
+      if (kMode == kModeDKDV) {
+        // the per-query vectors arrive with the stage's bulk copies; observe that barrier directly
+        ok = mbar_wait(bar + kBarYFull + 8 * s, (i / kStages) & 1, abort_flag);
+        if (!ok) break;
+      }
+      tc_fence_after_sync();
+      const float* vec_lse = reinterpret_cast<const float*>(smem + kSmemVec + s * 1024);
+      const float* vec_delta = vec_lse + 128;
+      // visibility of element (row xr, column y0 + j)
+      //   dK/dV: key xr, query y0+j : visible iff xr <= y0 + j + off  <=>  j >= xr - off - y0
+      //   dQ   : query xr, key y0+j : visible iff y0 + j <= xr + off and y0 + j < len_k
+      int j_lo = 0, j_hi = kTile;
+      if (kMode == kModeDKDV) {
+        if (p.is_causal) j_lo = xr - causal_off - y0;
+      } else {
+        j_hi = len_k - y0;
+        if (p.is_causal) j_hi = min(j_hi, xr + causal_off + 1 - y0);
+      }
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t a[32], d[32];
+        tmem_ld_x32(t1 + lane_base + cc * 32, a);
+        tmem_ld_x32(t2 + lane_base + cc * 32, d);
+        tmem_wait_ld();
+        uint32_t pw[16], dw[16];
+#pragma unroll
+        for (int j2 = 0; j2 < 16; ++j2) {
+          float pv[2], dsv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int j = cc * 32 + 2 * j2 + e;
+            const float l2 = (kMode == kModeDKDV) ? vec_lse[j] : my_lse2;
+            const float dl = (kMode == kModeDKDV) ? vec_delta[j] : my_delta;
+            float pr = ex2_approx(fmaf(__uint_as_float(a[2 * j2 + e]), c, -l2));
+            pr = (j >= j_lo && j < j_hi) ? pr : 0.f;
+            pv[e] = pr;
+            dsv[e] = pr * (__uint_as_float(d[2 * j2 + e]) - dl);
+          }
+          pw[j2] = pack_bf16x2(pv[0], pv[1]);
+          dw[j2] = pack_bf16x2(dsv[0], dsv[1]);
+        }
+        if (kMode == kModeDKDV) tmem_st_x16(t1 + lane_base + cc * 16, pw);
+        tmem_st_x16(t2 + lane_base + cc * 16, dw);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(bar + kBarPFull);
+    }
+
+    // ---- epilogue: accumulators -> scale -> bf16 -> global
+    if (ok && n_items > 0) ok = mbar_wait(bar + kBarAccFull, 0, abort_flag);
+    if (ok) {
+      tc_fence_after_sync();
+      const bool valid = xr < len_x;
+      const int n_out = (kMode == kModeDKDV) ? 2 : 1;
+#pragma unroll
+      for (int which = 0; which < n_out; ++which) {
+        __nv_bfloat16* dst;
+        float mul;
+        uint32_t acc;
+        if (kMode == kModeDQ) {
+          dst = p.dq + ((p.cu_q != nullptr) ? static_cast<int64_t>(q_off + xr) * p.dq_row_stride
+                                            : b * p.dq_batch_stride + static_cast<int64_t>(xr) * p.dq_row_stride) +
+                hx * p.dq_head_stride;
+          mul = p.scale;
+          acc = acc1;
+        } else if (which == 0) {
+          dst = p.dv + ((p.cu_q != nullptr) ? static_cast<int64_t>(k_off + xr) * p.dv_row_stride
+                                            : b * p.dv_batch_stride + static_cast<int64_t>(xr) * p.dv_row_stride) +
+                hx * p.dv_head_stride;
+          mul = 1.f;
+          acc = acc1;
+        } else {
+          dst = p.dk + ((p.cu_q != nullptr) ? static_cast<int64_t>(k_off + xr) * p.dk_row_stride
+                                            : b * p.dk_batch_stride + static_cast<int64_t>(xr) * p.dk_row_stride) +
+                hx * p.dk_head_stride;
+          mul = p.scale;
+          acc = acc2;
+        }
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t v[32];
+          if (n_items > 0) {
+            tmem_ld_x32(acc + lane_base + cc * 32, v);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0u;
+          }
+          if (valid) {
+            uint4* o4 = reinterpret_cast<uint4*>(dst + cc * 32);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]) * mul, __uint_as_float(v[8 * j + 1]) * mul);
+              w.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]) * mul, __uint_as_float(v[8 * j + 3]) * mul);
+              w.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]) * mul, __uint_as_float(v[8 * j + 5]) * mul);
+              w.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]) * mul, __uint_as_float(v[8 * j + 7]) * mul);
+              o4[j] = w;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, SDPA_B200_DEVICE_TIMEOUT);
+}
+
+// delta[row] = sum_d dO[row,d] * O[row,d]; lse2[row] = lse[row] * log2(e). One warp per row,
+// rows padded to lq_pad per (batch, head): padding rows get lse2 = +inf, delta = 0.
+struct PreParams {
+  const __nv_bfloat16* out;
+  const __nv_bfloat16* dout;
+  const float* lse;
+  float* lse2;
+  float* delta;
+  const int32_t* cu_q;
+  int64_t o_batch_stride, o_head_stride, o_row_stride;
+  int64_t do_batch_stride, do_head_stride, do_row_stride;
+  int seqlen_q, total_q, heads_q, lq_pad;
+};
+
+__global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 8 + warp;  // row within the padded sequence
+  const int h = blockIdx.y, b = blockIdx.z;
+  if (row >= p.lq_pad) return;
+  int q_off = 0, len_q = p.seqlen_q;
+  if (p.cu_q != nullptr) {
+    q_off = p.cu_q[b];
+    len_q = p.cu_q[b + 1] - q_off;
+  }
+  const size_t dst = (static_cast<size_t>(b) * p.heads_q + h) * p.lq_pad + row;
+  if (row >= len_q) {
+    if (lane == 0) {
+      p.lse2[dst] = INFINITY;
+      p.delta[dst] = 0.f;
+    }
+    return;
+  }
+  const __nv_bfloat16* o;
+  const __nv_bfloat16* dout;
+  float lse;
+  if (p.cu_q != nullptr) {
+    o = p.out + static_cast<int64_t>(q_off + row) * p.o_row_stride + h * p.o_head_stride;
+    dout = p.dout + static_cast<int64_t>(q_off + row) * p.do_row_stride + h * p.do_head_stride;
+    lse = p.lse[static_cast<size_t>(h) * p.total_q + q_off + row];
+  } else {
+    o = p.out + b * p.o_batch_stride + h * p.o_head_stride + static_cast<int64_t>(row) * p.o_row_stride;
+    dout = p.dout + b * p.do_batch_stride + h * p.do_head_stride + static_cast<int64_t>(row) * p.do_row_stride;
+    lse = p.lse[(static_cast<size_t>(b) * p.heads_q + h) * p.seqlen_q + row];
+  }
+  const uint2 ov = *reinterpret_cast<const uint2*>(o + lane * 4);
+  const uint2 dv = *reinterpret_cast<const uint2*>(dout + lane * 4);
+  const __nv_bfloat162 o0 = *reinterpret_cast<const __nv_bfloat162*>(&ov.x);
+  const __nv_bfloat162 o1 = *reinterpret_cast<const __nv_bfloat162*>(&ov.y);
+  const __nv_bfloat162 d0 = *reinterpret_cast<const __nv_bfloat162*>(&dv.x);
+  const __nv_bfloat162 d1 = *reinterpret_cast<const __nv_bfloat162*>(&dv.y);
+  float acc = __bfloat162float(o0.x) * __bfloat162float(d0.x) + __bfloat162float(o0.y) * __bfloat162float(d0.y) +
+              __bfloat162float(o1.x) * __bfloat162float(d1.x) + __bfloat162float(o1.y) * __bfloat162float(d1.y);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) {
+    p.lse2[dst] = lse * 1.4426950408889634f;  // +inf stays +inf
+    p.delta[dst] = acc;
+  }
+}
+
+int lq_padded(const sdpa_b200_params& p) { return ((p.max_seqlen_q + kTile - 1) / kTile) * kTile; }
+
+}  // namespace
+
+size_t bwd_workspace_bytes(const sdpa_b200_params& p) {
+  return 2 * static_cast<size_t>(p.batch) * p.heads_q * lq_padded(p) * sizeof(float);
+}
+
 int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
-  set_error("backward not built yet");
-  return SDPA_B200_UNSUPPORTED;
+  (void)workspace_bytes;
+  const bool varlen = p.cu_seqlens_q != nullptr;
+  const int lq_pad = lq_padded(p);
+  const size_t vec_elems = static_cast<size_t>(p.batch) * p.heads_q * lq_pad;
+  float* lse2 = reinterpret_cast<float*>(static_cast<char*>(workspace) + kWorkspaceHeaderBytes);
+  float* delta = lse2 + vec_elems;
+
+  PreParams pre;
+  pre.out = static_cast<const __nv_bfloat16*>(p.out);
+  pre.dout = static_cast<const __nv_bfloat16*>(p.dout);
+  pre.lse = p.lse;
+  pre.lse2 = lse2;
+  pre.delta = delta;
+  pre.cu_q = p.cu_seqlens_q;
+  pre.o_batch_stride = p.o_batch_stride;
+  pre.o_head_stride = p.o_head_stride;
+  pre.o_row_stride = p.o_row_stride;
+  pre.do_batch_stride = p.do_batch_stride;
+  pre.do_head_stride = p.do_head_stride;
+  pre.do_row_stride = p.do_row_stride;
+  pre.seqlen_q = p.max_seqlen_q;
+  pre.total_q = p.total_q;
+  pre.heads_q = p.heads_q;
+  pre.lq_pad = lq_pad;
+  bwd_preprocess_kernel<<<dim3(lq_pad / 8, p.heads_q, p.batch), 256, 0, stream>>>(pre);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("backward preprocess: launch failed: %s", cudaGetErrorString(err));
+    return SDPA_B200_LAUNCH_FAILED;
+  }
+  count_launch();
+
+  CUtensorMap tm_q, tm_k, tm_v, tm_do;
+  const int64_t rows_q = varlen ? p.total_q : p.max_seqlen_q;
+  const int64_t rows_k = varlen ? p.total_k : p.max_seqlen_k;
+  const int64_t nb = varlen ? 1 : p.batch;
+  int st;
+  if ((st = make_tensor_map_bf16(&tm_q, p.q, p.head_dim, rows_q, p.heads_q, nb, p.q_row_stride, p.q_head_stride,
+                                 p.q_batch_stride, kTile)) != SDPA_B200_OK)
+    return st;
+  if ((st = make_tensor_map_bf16(&tm_k, p.k, p.head_dim, rows_k, p.heads_kv, nb, p.k_row_stride, p.k_head_stride,
+                                 p.k_batch_stride, kTile)) != SDPA_B200_OK)
+    return st;
+  if ((st = make_tensor_map_bf16(&tm_v, p.v, p.head_dim, rows_k, p.heads_kv, nb, p.v_row_stride, p.v_head_stride,
+                                 p.v_batch_stride, kTile)) != SDPA_B200_OK)
+    return st;
+  if ((st = make_tensor_map_bf16(&tm_do, p.dout, p.head_dim, rows_q, p.heads_q, nb, p.do_row_stride,
+                                 p.do_head_stride, p.do_batch_stride, kTile)) != SDPA_B200_OK)
+    return st;
+
+  BwdKernelParams kp;
+  kp.lse2 = lse2;
+  kp.delta = delta;
+  kp.dq = static_cast<__nv_bfloat16*>(p.dq);
+  kp.dk = static_cast<__nv_bfloat16*>(p.dk);
+  kp.dv = static_cast<__nv_bfloat16*>(p.dv);
+  kp.cu_q = p.cu_seqlens_q;
+  kp.cu_k = p.cu_seqlens_k;
+  kp.status = static_cast<uint32_t*>(workspace);
+  kp.dq_batch_stride = p.dq_batch_stride;
+  kp.dq_head_stride = p.dq_head_stride;
+  kp.dq_row_stride = p.dq_row_stride;
+  kp.dk_batch_stride = p.dk_batch_stride;
+  kp.dk_head_stride = p.dk_head_stride;
+  kp.dk_row_stride = p.dk_row_stride;
+  kp.dv_batch_stride = p.dv_batch_stride;
+  kp.dv_head_stride = p.dv_head_stride;
+  kp.dv_row_stride = p.dv_row_stride;
+  kp.seqlen_q = p.max_seqlen_q;
+  kp.seqlen_k = p.max_seqlen_k;
+  kp.heads_q = p.heads_q;
+  kp.heads_kv = p.heads_kv;
+  kp.kv_group = p.heads_q / p.heads_kv;
+  kp.lq_pad = lq_pad;
+  kp.scale = p.softmax_scale;
+  kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
+  kp.is_causal = p.is_causal;
+
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e1 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDKDV>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e2 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e1 != cudaSuccess || e2 != cudaSuccess) {
+      set_error("backward: cudaFuncSetAttribute(%u bytes smem) failed", kSmemBytes);
+      return SDPA_B200_LAUNCH_FAILED;
+    }
+    attr_done = true;
+  }
+
+  kp.num_row_blocks = (p.max_seqlen_k + kTile - 1) / kTile;
+  bwd_tile_kernel<kModeDKDV><<<dim3(kp.num_row_blocks, p.heads_kv, p.batch), kThreads, kSmemBytes, stream>>>(
+      tm_q, tm_k, tm_v, tm_do, kp);
+  err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("backward dK/dV: launch failed: %s", cudaGetErrorString(err));
+    return SDPA_B200_LAUNCH_FAILED;
+  }
+  count_launch();
+  kp.num_row_blocks = (p.max_seqlen_q + kTile - 1) / kTile;
+  bwd_tile_kernel<kModeDQ><<<dim3(kp.num_row_blocks, p.heads_q, p.batch), kThreads, kSmemBytes, stream>>>(
+      tm_q, tm_k, tm_v, tm_do, kp);
+  err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("backward dQ: launch failed: %s", cudaGetErrorString(err));
+    return SDPA_B200_LAUNCH_FAILED;
+  }
+  count_launch();
+  return SDPA_B200_OK;
 }
-}
+
+}  // namespace sdpa_b200
