@@ -65,24 +65,37 @@ struct FwdKernelParams {
   int is_causal;
 };
 
+// Debug builds of the kernel time-stamp pipeline events of one CTA (the heaviest tile of
+// batch 0, head 0) into the debug buffer: [role 0..2][iteration 0..23][event 0..7] floats of
+// SM cycles since the CTA's set-up barrier, after the 2*128*260 per-row dump.
+constexpr int kStampBase = 2 * 128 * 260;
+#define SDPA_STAMP(role, iter, ev)                                                              \
+  do {                                                                                          \
+    if (kDebug && stamp_on && (iter) < 24)                                                      \
+      p.debug[kStampBase + ((role) * 24 + (iter)) * 8 + (ev)] = static_cast<float>(clock64() - t_start); \
+  } while (0)
+
 constexpr uint32_t kIdescQK = umma_idesc_bf16(kBlockM, kBlockN, false, false);
 constexpr uint32_t kIdescPV = umma_idesc_bf16(kBlockM, kHeadDim, false, true);
 
 __device__ __forceinline__ void issue_qk(uint32_t t_s, uint32_t q_smem, uint32_t k_smem) {
+  const uint32_t a_lo = umma_desc_lo_kmajor(q_smem);
+  const uint32_t b_lo = umma_desc_lo_kmajor(k_smem);
+  umma_ss_lo<kIdescQK, false>(t_s, a_lo, b_lo);
 #pragma unroll
-  for (int ks = 0; ks < kHeadDim / 16; ++ks) {
-    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-    umma_ss(t_s, umma_desc_kmajor(q_smem + off), umma_desc_kmajor(k_smem + off), kIdescQK,
-            ks > 0 ? 1u : 0u);
+  for (int ks = 1; ks < kHeadDim / 16; ++ks) {
+    const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+    umma_ss_lo<kIdescQK, true>(t_s, a_lo + off, b_lo + off);
   }
 }
 
 __device__ __forceinline__ void issue_pv(uint32_t t_o, uint32_t t_p, uint32_t v_smem,
                                          bool accumulate) {
+  const uint32_t b_lo = umma_desc_lo_mnmajor(v_smem, kHalfBytes);
+  umma_ts_lo<kIdescPV>(t_o, t_p, b_lo, accumulate ? 1u : 0u);
 #pragma unroll
-  for (int ks = 0; ks < kBlockN / 16; ++ks) {
-    umma_ts(t_o, t_p + ks * 8, umma_desc_mnmajor(v_smem + ks * 2048, kHalfBytes), kIdescPV,
-            (accumulate || ks > 0) ? 1u : 0u);
+  for (int ks = 1; ks < kBlockN / 16; ++ks) {
+    umma_ts_lo<kIdescPV>(t_o, t_p + ks * 8, b_lo + ks * (2048 >> 4), 1u);
   }
 }
 
@@ -165,6 +178,8 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
+  const long long t_start = kDebug ? clock64() : 0;
+  const bool stamp_cta = kDebug && p.debug != nullptr && m_block == p.num_m_blocks - 1 && h == 0 && b == 0;
 
   if (warp >= 8) {
     reg_decrease<40>();
@@ -225,12 +240,15 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
         const bool more = (j + 1 < n_iter);
         ok = mbar_wait(bar + kBarKVFull + 8 * sv, (iv / kStages) & 1, abort_flag);
         if (!ok) break;
+        const bool stamp_on = stamp_cta;
+        SDPA_STAMP(2, j, 0);
         bool k_ready = false;
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j < nblk[t]) {
             ok = mbar_wait(bar + kBarPFull + 8 * t, j & 1, abort_flag);
             if (!ok) break;
+            SDPA_STAMP(2, j, 1 + 3 * t);
             tc_fence_after_sync();
             issue_pv(t_o[t], t_s[t], v_smem, j > 0);
             umma_commit(bar + kBarOFull + 8 * t);
@@ -242,10 +260,12 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
             tc_fence_after_sync();
             k_ready = true;
           }
+          SDPA_STAMP(2, j, 2 + 3 * t);
           if (j + 1 < nblk[t]) {
             issue_qk(t_s[t], q_smem[t], k_smem);
             umma_commit(bar + kBarSFull + 8 * t);
           }
+          SDPA_STAMP(2, j, 3 + 3 * t);
           if (t == 1 && more) umma_commit(bar + kBarKVEmpty + 8 * sk);
         }
       }
@@ -278,19 +298,22 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       const int n0 = j * kBlockN;
       ok = mbar_wait(bar_s, j & 1, abort_flag);
       if (!ok) break;
+      const bool stamp_on = stamp_cta && row_in_tile == 0;
+      SDPA_STAMP(t, j, 0);
       tc_fence_after_sync();
 
       float s[kBlockN];
       {
-        uint32_t r[32];
+        uint32_t r[kBlockN];
+        tmem_ld_x32_at<0>(t_s, r);
+        tmem_ld_x32_at<32>(t_s + 32, r);
+        tmem_ld_x32_at<64>(t_s + 64, r);
+        tmem_ld_x32_at<96>(t_s + 96, r);
+        tmem_wait_ld();
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          tmem_ld_x32(t_s + cc * 32, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) s[cc * 32 + i] = __uint_as_float(r[i]);
-        }
+        for (int i = 0; i < kBlockN; ++i) s[i] = __uint_as_float(r[i]);
       }
+      SDPA_STAMP(t, j, 1);
       if (kDebug) {
         if (p.debug != nullptr && j == 0 && m_block == 0 && h == 0 && b == 0) {
           float* d = p.debug + (t * kBlockM + row_in_tile) * 260;
@@ -306,14 +329,15 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       float mx0 = neg_inf, mx1 = neg_inf, mx2 = neg_inf, mx3 = neg_inf;
 #pragma unroll
-      for (int i = 0; i < kBlockN; i += 4) {
-        mx0 = fmaxf(mx0, s[i]);
-        mx1 = fmaxf(mx1, s[i + 1]);
-        mx2 = fmaxf(mx2, s[i + 2]);
-        mx3 = fmaxf(mx3, s[i + 3]);
+      for (int i = 0; i < kBlockN; i += 8) {
+        mx0 = max3(mx0, s[i], s[i + 1]);
+        mx1 = max3(mx1, s[i + 2], s[i + 3]);
+        mx2 = max3(mx2, s[i + 4], s[i + 5]);
+        mx3 = max3(mx3, s[i + 6], s[i + 7]);
       }
       const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;
       const float m_new = fmaxf(m_run, m_blk);
+      SDPA_STAMP(t, j, 2);
       if (j == 0) {
         m_run = m_new;
       } else {
@@ -339,16 +363,18 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       const float m_use = (m_run == neg_inf) ? 0.f : m_run;
       const float neg_m = -m_use;
-      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      const float2 c2 = make_float2(c, c);
+      const float2 nm2 = make_float2(neg_m, neg_m);
+      float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
 #pragma unroll
       for (int cc = 0; cc < 8; ++cc) {
         uint32_t pk[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float p0 = ex2_approx(fmaf(s[cc * 16 + 2 * i], c, neg_m));
-          const float p1 = ex2_approx(fmaf(s[cc * 16 + 2 * i + 1], c, neg_m));
-          if (i & 1) { l2 += p0; l3 += p1; } else { l0 += p0; l1 += p1; }
-          pk[i] = pack_bf16x2(p0, p1);
+          const float2 x = fma2(make_float2(s[cc * 16 + 2 * i], s[cc * 16 + 2 * i + 1]), c2, nm2);
+          const float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+          if (i & 1) lb = add2(lb, pr); else la = add2(la, pr);
+          pk[i] = pack_bf16x2(pr.x, pr.y);
         }
         // P_t overwrites the front of S_t: 8 columns = 16 keys per store
         asm volatile(
@@ -357,10 +383,12 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
             "r"(pk[5]), "r"(pk[6]), "r"(pk[7])
             : "memory");
       }
-      l_run += (l0 + l1) + (l2 + l3);
+      l_run += (la.x + la.y) + (lb.x + lb.y);
+      SDPA_STAMP(t, j, 3);
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(bar_p);
+      SDPA_STAMP(t, j, 4);
     }
 
     // ---- epilogue: O / l -> bf16, LSE

@@ -50,6 +50,43 @@ __device__ __forceinline__ float lg2_approx(float x) {
   return y;
 }
 
+// three-input max (one FMNMX3 instead of two FMNMX)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// packed fp32x2 arithmetic: one issue slot for two lanes of work
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t"
+      ".reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "mov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t"
+      "}\n"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t"
+      ".reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t"
+      "}\n"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
 // Warpgroup-wide register re-allocation (all four warps of the warpgroup execute it).
 template <int kRegs>
 __device__ __forceinline__ void reg_increase() {
@@ -215,6 +252,25 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 
+// 32 columns into r[kOff .. kOff+31] of a larger register array (lets a caller issue several
+// loads back to back and wait once)
+template <int kOff, int kN>
+__device__ __forceinline__ void tmem_ld_x32_at(uint32_t taddr, uint32_t (&r)[kN]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[kOff + 0]), "=r"(r[kOff + 1]), "=r"(r[kOff + 2]), "=r"(r[kOff + 3]), "=r"(r[kOff + 4]),
+        "=r"(r[kOff + 5]), "=r"(r[kOff + 6]), "=r"(r[kOff + 7]), "=r"(r[kOff + 8]), "=r"(r[kOff + 9]),
+        "=r"(r[kOff + 10]), "=r"(r[kOff + 11]), "=r"(r[kOff + 12]), "=r"(r[kOff + 13]), "=r"(r[kOff + 14]),
+        "=r"(r[kOff + 15]), "=r"(r[kOff + 16]), "=r"(r[kOff + 17]), "=r"(r[kOff + 18]), "=r"(r[kOff + 19]),
+        "=r"(r[kOff + 20]), "=r"(r[kOff + 21]), "=r"(r[kOff + 22]), "=r"(r[kOff + 23]), "=r"(r[kOff + 24]),
+        "=r"(r[kOff + 25]), "=r"(r[kOff + 26]), "=r"(r[kOff + 27]), "=r"(r[kOff + 28]), "=r"(r[kOff + 29]),
+        "=r"(r[kOff + 30]), "=r"(r[kOff + 31])
+      : "r"(taddr)
+      : "memory");
+}
+
 __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -283,6 +339,47 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, bool a_mn_m
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
          (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
          (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+// Cheap descriptor arithmetic for issue loops. A descriptor splits into a low word
+// (start address >> 4 | LBO >> 4 << 16) and a constant high word (SBO, version, swizzle); moving
+// along a tile only adds (byte offset >> 4) to the low word. Shared memory is < 256 KB, so the
+// 14-bit address field never carries into the LBO field.
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, SWIZZLE_128B
+__device__ __forceinline__ uint32_t umma_desc_lo_kmajor(uint32_t smem_addr) { return (smem_addr >> 4) | (1u << 16); }
+__device__ __forceinline__ uint32_t umma_desc_lo_mnmajor(uint32_t smem_addr, uint32_t mn_chunk_stride) {
+  return (smem_addr >> 4) | ((mn_chunk_stride >> 4) << 16);
+}
+
+// D[tmem] (+)= A[smem] * B[smem], descriptors given as low words (high word = kDescHiSw128)
+template <uint32_t kIdesc, bool kAccumulate>
+__device__ __forceinline__ void umma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kDescHiSw128), "r"(kIdesc), "r"(kAccumulate ? 1u : 0u)
+      : "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]
+template <uint32_t kIdesc>
+__device__ __forceinline__ void umma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(kDescHiSw128), "r"(kIdesc), "r"(accumulate)
+      : "memory");
 }
 
 // D[tmem] (+)= A[smem] * B[smem]
