@@ -44,8 +44,8 @@ constexpr uint32_t kBarQFull = 0;
 constexpr uint32_t kBarKVFull = 8;                    // kStages
 constexpr uint32_t kBarKVEmpty = kBarKVFull + 8 * kStages;
 constexpr uint32_t kBarSFull = kBarKVEmpty + 8 * kStages;  // 2
-constexpr uint32_t kBarPFull = kBarSFull + 16;             // 2
-constexpr uint32_t kBarOFull = kBarPFull + 16;             // 2
+constexpr uint32_t kBarPFull = kBarSFull + 16;             // 2 tiles x 2 halves (keys 0-63, 64-127)
+constexpr uint32_t kBarOFull = kBarPFull + 32;             // 2
 constexpr uint32_t kSmemTmemPtr = kBarOFull + 16;
 constexpr uint32_t kSmemAbort = kSmemTmemPtr + 4;
 constexpr uint32_t kSmemUsed = kSmemBar + 256;
@@ -89,13 +89,14 @@ __device__ __forceinline__ void issue_qk(uint32_t t_s, uint32_t q_smem, uint32_t
   }
 }
 
-__device__ __forceinline__ void issue_pv(uint32_t t_o, uint32_t t_p, uint32_t v_smem,
-                                         bool accumulate) {
+// O_t (+)= P_t V for keys [64*half, 64*half + 64) of the block: four K = 16 steps
+__device__ __forceinline__ void issue_pv_half(uint32_t t_o, uint32_t t_p, uint32_t v_smem, int half,
+                                              bool accumulate) {
   const uint32_t b_lo = umma_desc_lo_mnmajor(v_smem, kHalfBytes);
-  umma_ts_lo<kIdescPV>(t_o, t_p, b_lo, accumulate ? 1u : 0u);
 #pragma unroll
-  for (int ks = 1; ks < kBlockN / 16; ++ks) {
-    umma_ts_lo<kIdescPV>(t_o, t_p + ks * 8, b_lo + ks * (2048 >> 4), 1u);
+  for (int i = 0; i < 4; ++i) {
+    const int ks = half * 4 + i;
+    umma_ts_lo<kIdescPV>(t_o, t_p + ks * 8, b_lo + ks * (2048 >> 4), (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 
@@ -163,7 +164,8 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar + kBarSFull + 8 * t, 1);
-      mbar_init(bar + kBarPFull + 8 * t, kBlockM);
+      mbar_init(bar + kBarPFull + 16 * t, kBlockM);
+      mbar_init(bar + kBarPFull + 16 * t + 8, kBlockM);
       mbar_init(bar + kBarOFull + 8 * t, 1);
     }
     *abort_flag = 0;
@@ -246,11 +248,17 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j < nblk[t]) {
-            ok = mbar_wait(bar + kBarPFull + 8 * t, j & 1, abort_flag);
+            // P arrives in two halves so the first four MMAs overlap the second half's exponentials
+            ok = mbar_wait(bar + kBarPFull + 16 * t, j & 1, abort_flag);
             if (!ok) break;
             SDPA_STAMP(2, j, 1 + 3 * t);
             tc_fence_after_sync();
-            issue_pv(t_o[t], t_s[t], v_smem, j > 0);
+            issue_pv_half(t_o[t], t_s[t], v_smem, 0, j > 0);
+            ok = mbar_wait(bar + kBarPFull + 16 * t + 8, j & 1, abort_flag);
+            if (!ok) break;
+            if (t == 0) SDPA_STAMP(2, j, 7);
+            tc_fence_after_sync();
+            issue_pv_half(t_o[t], t_s[t], v_smem, 1, true);
             umma_commit(bar + kBarOFull + 8 * t);
           }
           if (t == 1) umma_commit(bar + kBarKVEmpty + 8 * sv);
@@ -282,7 +290,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t t_s = lane_base + t * 128;
     const uint32_t t_o = lane_base + 256 + t * 128;
     const uint32_t bar_s = bar + kBarSFull + 8 * t;
-    const uint32_t bar_p = bar + kBarPFull + 8 * t;
+    const uint32_t bar_p = bar + kBarPFull + 16 * t;
     const uint32_t bar_o = bar + kBarOFull + 8 * t;
     const float c = p.scale_log2;
     const float neg_inf = -INFINITY;
@@ -376,6 +384,13 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
           if (i & 1) lb = add2(lb, pr); else la = add2(la, pr);
           pk[i] = pack_bf16x2(pr.x, pr.y);
         }
+        if (cc == 4) {
+          // keys 0-63 of P were stored one chunk of arithmetic ago, so this wait is short:
+          // let the MMA warp start on them while the rest of the row is exponentiated
+          tmem_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(bar_p);
+        }
         // P_t overwrites the front of S_t: 8 columns = 16 keys per store
         asm volatile(
             "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
@@ -387,7 +402,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       SDPA_STAMP(t, j, 3);
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(bar_p);
+      mbar_arrive(bar_p + 8);
       SDPA_STAMP(t, j, 4);
     }
 
