@@ -1,0 +1,97 @@
+"""The dispatcher glue on a GPU: the b200_sdpa operators (reference schemas) with autograd, and
+the opt-in aten overrides that put F.scaled_dot_product_attention on these kernels."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import sdpa_oracle as orc
+from torch_mlu_b200 import _cabi, backends, torch_glue
+
+pytestmark = pytest.mark.gpu
+
+
+def rand(shape, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(shape, generator=g).bfloat16()
+
+
+def test_registered_ops_forward_backward_autograd(cuda_device, native_lib):
+    torch_glue.load()
+    dev = cuda_device
+    q, k, v, do = (rand((2, 4, 384, 128), s) for s in (1, 2, 3, 4))
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    res = torch.ops.b200_sdpa._scaled_dot_product_flash_attention(qd, kd, vd, 0.0, True, False)
+    out, lse = res[0], res[1]
+    assert len(res) == 9 and res[4] == 384 and res[5] == 384
+    out.backward(do.to(dev))
+    o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=True)
+    dq, dk, dv = orc.cpu_sdpa_backward(do, q, k, v, o_ref, l_ref, causal=True)
+    orc.assert_close_bf16(out, o_ref, "out")
+    orc.assert_close_lse(lse, l_ref)
+    orc.assert_close_grad_bf16(qd.grad, dq, "dq")
+    orc.assert_close_grad_bf16(kd.grad, dk, "dk")
+    orc.assert_close_grad_bf16(vd.grad, dv, "dv")
+
+
+def test_registered_varlen_op_autograd(cuda_device, native_lib):
+    torch_glue.load()
+    dev = cuda_device
+    lens = [100, 260, 33]
+    cu = [0, 100, 360, 393]
+    q, k, v, do = rand((393, 4, 128), 1), rand((393, 2, 128), 2), rand((393, 2, 128), 3), rand((393, 4, 128), 4)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    out, lse, *_ = torch.ops.b200_sdpa._flash_attention_forward(qd, kd, vd, cu_t, cu_t, max(lens), max(lens), 0.0, True, False)
+    out.backward(do.to(dev))
+    o_ref, l_ref = orc.varlen_forward(q, k, v, cu, cu, causal=True)
+    dq, dk, dv = orc.varlen_backward(do, q, k, v, cu, cu, causal=True)
+    orc.assert_close_bf16(out, o_ref, "out")
+    orc.assert_close_lse(lse, l_ref)
+    orc.assert_close_grad_bf16(qd.grad, dq, "dq")
+    orc.assert_close_grad_bf16(kd.grad, dk, "dk")
+    orc.assert_close_grad_bf16(vd.grad, dv, "dv")
+
+
+def test_functional_sdpa_reaches_these_kernels_when_overridden(cuda_device, native_lib):
+    """Same call pattern as the reference tests: F.scaled_dot_product_attention inside
+    sdp_kernel(enable_flash=True, enable_math=False, enable_mem_efficient=False)
+    (test/torch_ops/test_scaled_dot_product_attention.py:630-640)."""
+    dev = cuda_device
+    q, k, v, do = (rand((1, 16, 512, 128), s) for s in (1, 2, 3, 4))
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    torch_glue.install_aten_overrides()
+    try:
+        before = _cabi.launch_count()
+        with backends.sdp_kernel(enable_flash=True, enable_math=False, enable_mem_efficient=False):
+            out = F.scaled_dot_product_attention(qd, kd, vd, is_causal=True)
+        out.backward(do.to(dev))
+        torch.cuda.synchronize()
+        assert _cabi.launch_count() - before == 4  # forward + (preprocess, dK/dV, dQ)
+    finally:
+        torch_glue.remove_aten_overrides()
+    o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=True)
+    dq, dk, dv = orc.cpu_sdpa_backward(do, q, k, v, o_ref, l_ref, causal=True)
+    orc.assert_close_bf16(out, o_ref, "out")
+    orc.assert_close_grad_bf16(qd.grad, dq, "dq")
+    orc.assert_close_grad_bf16(kd.grad, dk, "dk")
+    orc.assert_close_grad_bf16(vd.grad, dv, "dv")
+    # with the overrides removed the stock kernel is back (no launches of this library)
+    before = _cabi.launch_count()
+    with backends.sdp_kernel(enable_flash=True, enable_math=False, enable_mem_efficient=False):
+        F.scaled_dot_product_attention(qd.detach(), kd.detach(), vd.detach(), is_causal=True)
+    torch.cuda.synchronize()
+    assert _cabi.launch_count() == before
+
+
+def test_glue_rejects_what_the_reference_rejects(cuda_device, native_lib):
+    torch_glue.load()
+    dev = cuda_device
+    q = rand((1, 2, 64, 128), 1).to(dev)
+    with pytest.raises(RuntimeError, match="same number of heads"):
+        torch.ops.b200_sdpa._scaled_dot_product_flash_attention(q, q[:, :1], q[:, :1])
+    with pytest.raises(RuntimeError, match="fp16 and bf16"):
+        torch.ops.b200_sdpa._scaled_dot_product_flash_attention(q.float(), q.float(), q.float())
+    with pytest.raises(RuntimeError, match="dropout"):
+        torch.ops.b200_sdpa._scaled_dot_product_flash_attention(q, q, q, 0.5)
+    with pytest.raises(RuntimeError, match="head_dim 128 only"):
+        torch.ops.b200_sdpa._scaled_dot_product_flash_attention(q[..., :64], q[..., :64], q[..., :64])

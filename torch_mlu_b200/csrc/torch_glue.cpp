@@ -1,0 +1,402 @@
+// Thin PyTorch dispatcher glue over the C ABI of libsdpa_b200.so.
+//
+// Stands where torch_mlu's generated registration (codegen/templates/RegisterMLU.cpp:185-188,
+// schemas from codegen/mlu_functions.yaml:1313-1316) binds the attention operators of
+// torch_mlu/csrc/aten/operators/cnnl/transformers/attention.cpp:
+//   * TORCH_LIBRARY(b200_sdpa): the four operators with the reference's exact (torch 2.1)
+//     schemas, implemented for the CUDA key.
+//   * b200_sdpa::_install_aten_overrides(): registers CUDA-key kernels for the same four aten
+//     operators with the INSTALLED torch's schemas, so F.scaled_dot_product_attention under the
+//     flash backend, and upstream autograd, land in these kernels.
+// Nothing here copies or re-packs tensors (the reference wrappers make five contiguous copies,
+// attention.cpp:124-129, 260-269): strides go straight into sdpa_b200_params. torch supplies
+// device memory (outputs, workspace) and the current stream only.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include <cmath>
+#include <memory>
+#include <tuple>
+
+#include "../../include/sdpa_b200.h"
+
+namespace {
+
+using at::Tensor;
+
+void check_status(int st, const char* what) {
+  TORCH_CHECK(st == SDPA_B200_OK, what, ": ", sdpa_b200_status_string(st), ": ", sdpa_b200_last_error());
+}
+
+// FlashAttention_internal.cpp:73-108: device, dtype and last-dim stride checks
+void check_input(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be on a CUDA device (this path has no CPU fallback)");
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16,
+              "FlashAttention only support fp16 and bf16 data type; this build implements bf16 (", name, " is ",
+              t.scalar_type(), ")");
+  TORCH_CHECK(t.stride(-1) == 1, "Input tensor must have contiguous last dimension (", name, ")");
+}
+
+double scale_or_default(const Tensor& q, c10::optional<double> scale) {  // sdp_utils.h:40-47
+  return scale.has_value() ? *scale : 1.0 / std::sqrt(static_cast<double>(q.size(-1)));
+}
+
+void set_bhld(int64_t& bs, int64_t& hs, int64_t& rs, const Tensor& t) {
+  bs = t.stride(0);
+  hs = t.stride(1);
+  rs = t.stride(2);
+}
+
+void set_thd(int64_t& bs, int64_t& hs, int64_t& rs, const Tensor& t) {
+  bs = 0;
+  hs = t.stride(1);
+  rs = t.stride(0);
+}
+
+void base_params(sdpa_b200_params& p, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out,
+                 const Tensor& lse, bool causal, double scale) {
+  std::memset(&p, 0, sizeof(p));
+  p.q = q.data_ptr();
+  p.k = k.data_ptr();
+  p.v = v.data_ptr();
+  p.out = out.data_ptr();
+  p.lse = lse.data_ptr<float>();
+  p.softmax_scale = static_cast<float>(scale);
+  p.is_causal = causal ? 1 : 0;
+  p.dtype = SDPA_B200_BF16;
+  p.kernel = SDPA_B200_KERNEL_AUTO;
+}
+
+void dense_params(sdpa_b200_params& p, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out,
+                  const Tensor& lse, bool causal, double scale) {
+  base_params(p, q, k, v, out, lse, causal, scale);
+  p.batch = static_cast<int32_t>(q.size(0));
+  p.heads_q = static_cast<int32_t>(q.size(1));
+  p.heads_kv = static_cast<int32_t>(k.size(1));
+  p.head_dim = static_cast<int32_t>(q.size(3));
+  p.max_seqlen_q = static_cast<int32_t>(q.size(2));
+  p.max_seqlen_k = static_cast<int32_t>(k.size(2));
+  set_bhld(p.q_batch_stride, p.q_head_stride, p.q_row_stride, q);
+  set_bhld(p.k_batch_stride, p.k_head_stride, p.k_row_stride, k);
+  set_bhld(p.v_batch_stride, p.v_head_stride, p.v_row_stride, v);
+  set_bhld(p.o_batch_stride, p.o_head_stride, p.o_row_stride, out);
+}
+
+void varlen_params(sdpa_b200_params& p, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out,
+                   const Tensor& lse, const Tensor& cu_q, const Tensor& cu_k, int64_t max_q, int64_t max_k, bool causal,
+                   double scale) {
+  base_params(p, q, k, v, out, lse, causal, scale);
+  p.cu_seqlens_q = cu_q.data_ptr<int32_t>();
+  p.cu_seqlens_k = cu_k.data_ptr<int32_t>();
+  p.batch = static_cast<int32_t>(cu_q.numel() - 1);
+  p.heads_q = static_cast<int32_t>(q.size(1));
+  p.heads_kv = static_cast<int32_t>(k.size(1));
+  p.head_dim = static_cast<int32_t>(q.size(2));
+  p.max_seqlen_q = static_cast<int32_t>(max_q);
+  p.max_seqlen_k = static_cast<int32_t>(max_k);
+  p.total_q = static_cast<int32_t>(q.size(0));
+  p.total_k = static_cast<int32_t>(k.size(0));
+  p.kernel = SDPA_B200_KERNEL_PREFILL;
+  set_thd(p.q_batch_stride, p.q_head_stride, p.q_row_stride, q);
+  set_thd(p.k_batch_stride, p.k_head_stride, p.k_row_stride, k);
+  set_thd(p.v_batch_stride, p.v_head_stride, p.v_row_stride, v);
+  set_thd(p.o_batch_stride, p.o_head_stride, p.o_row_stride, out);
+}
+
+void run(const sdpa_b200_params& p, bool backward, const Tensor& like) {
+  size_t bytes = 0;
+  check_status(backward ? sdpa_b200_bwd_workspace_bytes(&p, &bytes) : sdpa_b200_fwd_workspace_bytes(&p, &bytes),
+               "sdpa_b200 workspace query");
+  Tensor ws = at::empty({static_cast<int64_t>(bytes)}, like.options().dtype(at::kByte));
+  void* stream = at::cuda::getCurrentCUDAStream(like.get_device()).stream();
+  check_status(backward ? sdpa_b200_bwd(&p, ws.data_ptr(), bytes, stream) : sdpa_b200_fwd(&p, ws.data_ptr(), bytes, stream),
+               backward ? "sdpa_b200_bwd" : "sdpa_b200_fwd");
+}
+
+void check_varlen(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& cu_q, const Tensor& cu_k) {
+  // FlashAttention_internal.cpp:81-84, 112-127
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3,
+              "varlen query, key and value must be packed [total_tokens, heads, head_dim]");
+  TORCH_CHECK(cu_q.scalar_type() == at::kInt, "cu_seqlens_q must have dtype int32");
+  TORCH_CHECK(cu_k.scalar_type() == at::kInt, "cu_seqlens_k must have dtype int32");
+  TORCH_CHECK(cu_q.is_cuda() && cu_k.is_cuda() && cu_q.is_contiguous() && cu_k.is_contiguous(),
+              "cu_seqlens must be contiguous device tensors");
+  TORCH_CHECK(cu_q.numel() == cu_k.numel() && cu_q.numel() >= 2, "cu_seqlens_q and cu_seqlens_k must have batch+1 entries");
+  TORCH_CHECK(k.size(1) == v.size(1) && q.size(1) % k.size(1) == 0,
+              "Number of heads in key/value must divide number of heads in query");
+  check_input(q, "query");
+  check_input(k, "key");
+  check_input(v, "value");
+}
+
+// ------------------------------------------------------------------------- dense [B,H,L,D]
+std::tuple<Tensor, Tensor> dense_forward(const Tensor& q, const Tensor& k, const Tensor& v, bool causal, double scale,
+                                         bool allow_gqa) {
+  // attention.cpp:70-100
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4,
+              "query, key and value must be 4-dimensional [batch, heads, seq_len, head_dim]");
+  TORCH_CHECK(q.size(0) == k.size(0) && q.size(0) == v.size(0), "query, key and value must have the same batch size");
+  TORCH_CHECK(k.size(2) == v.size(2), "Key and Value must have the same sequence length");
+  if (allow_gqa) {
+    TORCH_CHECK(k.size(1) == v.size(1) && q.size(1) % k.size(1) == 0,
+                "Number of heads in key/value must divide number of heads in query");
+  } else {
+    TORCH_CHECK(q.size(1) == k.size(1) && q.size(1) == v.size(1), "query, key and value must have the same number of heads");
+  }
+  TORCH_CHECK(q.size(3) == k.size(3) && q.size(3) == v.size(3), "query, key and value must have the same head_dim");
+  check_input(q, "query");
+  check_input(k, "key");
+  check_input(v, "value");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t B = q.size(0), H = q.size(1), L = q.size(2), D = q.size(3);
+  // [B,H,L,D] view of a [B,L,H,D] buffer, as the reference returns (attention.cpp:146-148)
+  Tensor out = at::empty({B, L, H, D}, q.options()).transpose(1, 2);
+  Tensor lse = at::empty({B, H, L}, q.options().dtype(at::kFloat));
+  sdpa_b200_params p;
+  dense_params(p, q, k, v, out, lse, causal, scale);
+  run(p, false, q);
+  return {out, lse};
+}
+
+std::tuple<Tensor, Tensor, Tensor> dense_backward(const Tensor& dout_in, const Tensor& q, const Tensor& k, const Tensor& v,
+                                                  const Tensor& out, const Tensor& lse, bool causal, double scale) {
+  Tensor dout = dout_in.stride(-1) == 1 ? dout_in : dout_in.contiguous();
+  check_input(dout, "grad_out");
+  check_input(q, "query");
+  check_input(k, "key");
+  check_input(v, "value");
+  check_input(out, "out");
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.dim() == 3 && lse.size(0) == q.size(0) &&
+                  lse.size(1) == q.size(1) && lse.size(2) == q.size(2),
+              "logsumexp must be contiguous fp32 [batch, heads, seqlen_q]");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t B = q.size(0), D = q.size(3);
+  Tensor dq = at::empty({B, q.size(2), q.size(1), D}, q.options()).transpose(1, 2);
+  Tensor dk = at::empty({B, k.size(2), k.size(1), D}, k.options()).transpose(1, 2);
+  Tensor dv = at::empty({B, v.size(2), v.size(1), D}, v.options()).transpose(1, 2);
+  sdpa_b200_params p;
+  dense_params(p, q, k, v, out, lse, causal, scale);
+  p.dout = dout.data_ptr();
+  p.dq = dq.data_ptr();
+  p.dk = dk.data_ptr();
+  p.dv = dv.data_ptr();
+  set_bhld(p.do_batch_stride, p.do_head_stride, p.do_row_stride, dout);
+  set_bhld(p.dq_batch_stride, p.dq_head_stride, p.dq_row_stride, dq);
+  set_bhld(p.dk_batch_stride, p.dk_head_stride, p.dk_row_stride, dk);
+  set_bhld(p.dv_batch_stride, p.dv_head_stride, p.dv_row_stride, dv);
+  run(p, true, q);
+  return {dq, dk, dv};
+}
+
+// ------------------------------------------------------------------ packed [total,H,D]
+std::tuple<Tensor, Tensor> varlen_forward(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& cu_q,
+                                          const Tensor& cu_k, int64_t max_q, int64_t max_k, bool causal, double scale) {
+  check_varlen(q, k, v, cu_q, cu_k);
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = at::empty(q.sizes(), q.options());
+  Tensor lse = at::empty({q.size(1), q.size(0)}, q.options().dtype(at::kFloat));  // FlashAttention_internal.cpp:129
+  sdpa_b200_params p;
+  varlen_params(p, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, causal, scale);
+  run(p, false, q);
+  return {out, lse};
+}
+
+std::tuple<Tensor, Tensor, Tensor> varlen_backward(const Tensor& dout_in, const Tensor& q, const Tensor& k, const Tensor& v,
+                                                   const Tensor& out, const Tensor& lse, const Tensor& cu_q,
+                                                   const Tensor& cu_k, int64_t max_q, int64_t max_k, bool causal,
+                                                   double scale) {
+  check_varlen(q, k, v, cu_q, cu_k);
+  Tensor dout = dout_in.stride(-1) == 1 ? dout_in : dout_in.contiguous();
+  check_input(dout, "grad_out");
+  check_input(out, "out");
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.dim() == 2 && lse.size(0) == q.size(1) &&
+                  lse.size(1) == q.size(0),
+              "logsumexp must be contiguous fp32 [heads_q, total_q]");
+  c10::cuda::CUDAGuard guard(q.device());
+  Tensor dq = at::empty(q.sizes(), q.options());
+  Tensor dk = at::empty(k.sizes(), k.options());
+  Tensor dv = at::empty(v.sizes(), v.options());
+  sdpa_b200_params p;
+  varlen_params(p, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, causal, scale);
+  p.dout = dout.data_ptr();
+  p.dq = dq.data_ptr();
+  p.dk = dk.data_ptr();
+  p.dv = dv.data_ptr();
+  set_thd(p.do_batch_stride, p.do_head_stride, p.do_row_stride, dout);
+  set_thd(p.dq_batch_stride, p.dq_head_stride, p.dq_row_stride, dq);
+  set_thd(p.dk_batch_stride, p.dk_head_stride, p.dk_row_stride, dk);
+  set_thd(p.dv_batch_stride, p.dv_head_stride, p.dv_row_stride, dv);
+  run(p, true, q);
+  return {dq, dk, dv};
+}
+
+void check_no_dropout(double dropout_p) {
+  TORCH_CHECK(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library");
+}
+
+Tensor empty_i64(const Tensor& like) { return at::empty({0}, like.options().dtype(at::kLong)); }
+
+// ------------------------------------------------ operators with the reference's schemas
+std::tuple<Tensor, Tensor, Tensor, Tensor, int64_t, int64_t, Tensor, Tensor, Tensor> ref_sdpa_flash(
+    const Tensor& q, const Tensor& k, const Tensor& v, double dropout_p, bool is_causal, bool return_debug_mask,
+    c10::optional<double> scale) {
+  C10_LOG_API_USAGE_ONCE("torch.sdpa.flash_attention");  // attention.cpp:67
+  (void)return_debug_mask;
+  check_no_dropout(dropout_p);
+  auto [out, lse] = dense_forward(q, k, v, is_causal, scale_or_default(q, scale), /*allow_gqa=*/false);
+  const int64_t B = q.size(0), Lq = q.size(2), Lk = k.size(2);
+  auto iopt = q.options().dtype(at::kInt);
+  Tensor cum_q = at::arange(0, (B + 1) * Lq, Lq, iopt);  // attention.cpp:109-119
+  Tensor cum_k = at::arange(0, (B + 1) * Lk, Lk, iopt);
+  return {out, lse, cum_q, cum_k, Lq, Lk, empty_i64(q), empty_i64(q), at::empty({0}, q.options())};
+}
+
+std::tuple<Tensor, Tensor, Tensor> ref_sdpa_flash_backward(const Tensor& grad_out, const Tensor& q, const Tensor& k,
+                                                           const Tensor& v, const Tensor& out, const Tensor& lse,
+                                                           const Tensor& cum_q, const Tensor& cum_k, int64_t max_q,
+                                                           int64_t max_k, double dropout_p, bool is_causal,
+                                                           const Tensor& philox_seed, const Tensor& philox_offset,
+                                                           c10::optional<double> scale) {
+  (void)cum_q; (void)cum_k; (void)max_q; (void)max_k; (void)philox_seed; (void)philox_offset;
+  check_no_dropout(dropout_p);
+  return dense_backward(grad_out, q, k, v, out, lse, is_causal, scale_or_default(q, scale));
+}
+
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> ref_flash_forward(const Tensor& q, const Tensor& k, const Tensor& v,
+                                                                     const Tensor& cum_q, const Tensor& cum_k,
+                                                                     int64_t max_q, int64_t max_k, double dropout_p,
+                                                                     bool is_causal, bool return_debug_mask,
+                                                                     c10::optional<double> scale) {
+  (void)return_debug_mask;
+  check_no_dropout(dropout_p);
+  auto [out, lse] = varlen_forward(q, k, v, cum_q, cum_k, max_q, max_k, is_causal, scale_or_default(q, scale));
+  return {out, lse, empty_i64(q), empty_i64(q), at::empty({0}, q.options())};
+}
+
+std::tuple<Tensor, Tensor, Tensor> ref_flash_backward(const Tensor& grad_out, const Tensor& q, const Tensor& k,
+                                                      const Tensor& v, const Tensor& out, const Tensor& lse,
+                                                      const Tensor& cum_q, const Tensor& cum_k, int64_t max_q,
+                                                      int64_t max_k, double dropout_p, bool is_causal,
+                                                      const Tensor& philox_seed, const Tensor& philox_offset,
+                                                      c10::optional<double> scale) {
+  (void)philox_seed; (void)philox_offset;
+  check_no_dropout(dropout_p);
+  return varlen_backward(grad_out, q, k, v, out, lse, cum_q, cum_k, max_q, max_k, is_causal, scale_or_default(q, scale));
+}
+
+// ------------------------------------ CUDA-key kernels for the installed torch's aten schemas
+std::tuple<Tensor, Tensor, Tensor, Tensor, c10::SymInt, c10::SymInt, Tensor, Tensor, Tensor> aten_sdpa_flash(
+    const Tensor& q, const Tensor& k, const Tensor& v, double dropout_p, bool is_causal, bool return_debug_mask,
+    c10::optional<double> scale) {
+  (void)return_debug_mask;
+  check_no_dropout(dropout_p);
+  auto [out, lse] = dense_forward(q, k, v, is_causal, scale_or_default(q, scale), /*allow_gqa=*/true);
+  Tensor none = at::empty({0}, q.options().dtype(at::kInt));
+  return {out, lse, none, none, c10::SymInt(q.size(2)), c10::SymInt(k.size(2)), empty_i64(q), empty_i64(q),
+          at::empty({0}, q.options())};
+}
+
+std::tuple<Tensor, Tensor, Tensor> aten_sdpa_flash_backward(const Tensor& grad_out, const Tensor& q, const Tensor& k,
+                                                            const Tensor& v, const Tensor& out, const Tensor& lse,
+                                                            const Tensor& cum_q, const Tensor& cum_k, c10::SymInt max_q,
+                                                            c10::SymInt max_k, double dropout_p, bool is_causal,
+                                                            const Tensor& philox_seed, const Tensor& philox_offset,
+                                                            c10::optional<double> scale) {
+  (void)cum_q; (void)cum_k; (void)max_q; (void)max_k; (void)philox_seed; (void)philox_offset;
+  check_no_dropout(dropout_p);
+  return dense_backward(grad_out, q, k, v, out, lse, is_causal, scale_or_default(q, scale));
+}
+
+void check_unsupported_kwargs(const c10::optional<c10::SymInt>& wl, const c10::optional<c10::SymInt>& wr, bool causal) {
+  // a causal call arrives as window (-1, 0); anything else is a sliding window
+  const bool left_ok = !wl.has_value() || wl->expect_int() < 0;
+  const bool right_ok = !wr.has_value() || wr->expect_int() < 0 || (causal && wr->expect_int() == 0);
+  TORCH_CHECK(left_ok && right_ok, "sliding-window attention (window_size_left/right) is not built in this library");
+}
+
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> aten_flash_forward(
+    const Tensor& q, const Tensor& k, const Tensor& v, const c10::optional<Tensor>& cum_q, const c10::optional<Tensor>& cum_k,
+    c10::SymInt max_q, c10::SymInt max_k, double dropout_p, bool is_causal, bool return_debug_mask,
+    c10::optional<double> scale, c10::optional<c10::SymInt> window_size_left, c10::optional<c10::SymInt> window_size_right,
+    const c10::optional<Tensor>& seqused_k, const c10::optional<Tensor>& alibi_slopes) {
+  (void)return_debug_mask;
+  check_no_dropout(dropout_p);
+  check_unsupported_kwargs(window_size_left, window_size_right, is_causal);
+  TORCH_CHECK(!seqused_k.has_value() || !seqused_k->defined(), "seqused_k is not built in this library");
+  TORCH_CHECK(!alibi_slopes.has_value() || !alibi_slopes->defined(), "alibi_slopes is not built in this library");
+  const double sc = scale_or_default(q, scale);
+  Tensor out, lse;
+  if (cum_q.has_value() && cum_q->defined()) {
+    TORCH_CHECK(cum_k.has_value() && cum_k->defined(), "cum_seq_q and cum_seq_k must be given together");
+    std::tie(out, lse) = varlen_forward(q, k, v, *cum_q, *cum_k, max_q.expect_int(), max_k.expect_int(), is_causal, sc);
+  } else {
+    // dense form of the installed torch: [batch, seq, heads, head_dim]
+    TORCH_CHECK(q.dim() == 4, "dense _flash_attention_forward expects [batch, seq_len, heads, head_dim]");
+    auto [o, l] = dense_forward(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal, sc, /*allow_gqa=*/true);
+    out = o.transpose(1, 2);
+    lse = l;
+  }
+  return {out, lse, empty_i64(q), empty_i64(q), at::empty({0}, q.options())};
+}
+
+std::tuple<Tensor, Tensor, Tensor> aten_flash_backward(
+    const Tensor& grad_out, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out, const Tensor& lse,
+    const Tensor& cum_q, const Tensor& cum_k, c10::SymInt max_q, c10::SymInt max_k, double dropout_p, bool is_causal,
+    const Tensor& rng_state, const Tensor& unused, c10::optional<double> scale, c10::optional<c10::SymInt> window_size_left,
+    c10::optional<c10::SymInt> window_size_right) {
+  (void)rng_state; (void)unused;
+  check_no_dropout(dropout_p);
+  check_unsupported_kwargs(window_size_left, window_size_right, is_causal);
+  const double sc = scale_or_default(q, scale);
+  if (cum_q.defined() && cum_q.numel() > 0) {
+    return varlen_backward(grad_out, q, k, v, out, lse, cum_q, cum_k, max_q.expect_int(), max_k.expect_int(), is_causal, sc);
+  }
+  auto [dq, dk, dv] = dense_backward(grad_out.transpose(1, 2), q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                     out.transpose(1, 2), lse, is_causal, sc);
+  return {dq.transpose(1, 2), dk.transpose(1, 2), dv.transpose(1, 2)};
+}
+
+std::unique_ptr<torch::Library> g_aten_overrides;
+
+void install_aten_overrides() {
+  if (g_aten_overrides) return;
+  g_aten_overrides = std::make_unique<torch::Library>(torch::Library::IMPL, "aten", c10::DispatchKey::CUDA, __FILE__, __LINE__);
+  g_aten_overrides->impl("_scaled_dot_product_flash_attention", aten_sdpa_flash);
+  g_aten_overrides->impl("_scaled_dot_product_flash_attention_backward", aten_sdpa_flash_backward);
+  g_aten_overrides->impl("_flash_attention_forward", aten_flash_forward);
+  g_aten_overrides->impl("_flash_attention_backward", aten_flash_backward);
+}
+
+void remove_aten_overrides() { g_aten_overrides.reset(); }
+
+int64_t launch_count() { return static_cast<int64_t>(sdpa_b200_launch_count()); }
+
+}  // namespace
+
+TORCH_LIBRARY(b200_sdpa, m) {
+  // codegen/mlu_functions.yaml:1313-1316, verbatim argument lists
+  m.def("_scaled_dot_product_flash_attention(Tensor query, Tensor key, Tensor value, float dropout_p=0.0, bool is_causal=False, "
+        "bool return_debug_mask=False, *, float? scale=None) -> (Tensor ouput, Tensor logsumexp, Tensor cum_seq_q, "
+        "Tensor cum_seq_k, int max_q, int max_k, Tensor philox_seed, Tensor philox_offset, Tensor debug_attn_mask)");
+  m.def("_scaled_dot_product_flash_attention_backward(Tensor grad_out, Tensor query, Tensor key, Tensor value, Tensor out, "
+        "Tensor logsumexp, Tensor cum_seq_q, Tensor cum_seq_k, int max_q, int max_k, float dropout_p, bool is_causal, "
+        "Tensor philox_seed, Tensor philox_offset, *, float? scale=None) -> (Tensor grad_query, Tensor grad_key, Tensor grad_value)");
+  m.def("_flash_attention_forward(Tensor query, Tensor key, Tensor value, Tensor cum_seq_q, Tensor cum_seq_k, int max_q, "
+        "int max_k, float dropout_p, bool is_causal, bool return_debug_mask, *, float? scale=None) -> (Tensor output, "
+        "Tensor softmax_logsumexp, Tensor philox_seed, Tensor philox_offset, Tensor debug_attn_mask)");
+  m.def("_flash_attention_backward(Tensor grad_out, Tensor query, Tensor key, Tensor value, Tensor out, Tensor logsumexp, "
+        "Tensor cum_seq_q, Tensor cum_seq_k, int max_q, int max_k, float dropout_p, bool is_causal, Tensor philox_seed, "
+        "Tensor philox_offset, *, float? scale=None) -> (Tensor, Tensor, Tensor)");
+  m.def("_install_aten_overrides() -> ()", install_aten_overrides);
+  m.def("_remove_aten_overrides() -> ()", remove_aten_overrides);
+  m.def("_launch_count() -> int", launch_count);
+}
+
+TORCH_LIBRARY_IMPL(b200_sdpa, CUDA, m) {
+  m.impl("_scaled_dot_product_flash_attention", ref_sdpa_flash);
+  m.impl("_scaled_dot_product_flash_attention_backward", ref_sdpa_flash_backward);
+  m.impl("_flash_attention_forward", ref_flash_forward);
+  m.impl("_flash_attention_backward", ref_flash_backward);
+}
