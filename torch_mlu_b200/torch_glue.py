@@ -53,12 +53,12 @@ def _register_autograd() -> None:
     wires for the aten operators the reference registers)."""
     ns = torch.ops.b200_sdpa
 
-    def dense_setup(ctx, inputs, output):
+    def dense_setup(ctx, inputs, keyword_only_inputs, output):
         query, key, value, dropout_p, is_causal, _dbg = inputs[:6]
         out, lse, cum_q, cum_k, max_q, max_k, seed, offset, _ = output
         ctx.save_for_backward(query, key, value, out, lse, cum_q, cum_k, seed, offset)
         ctx.args = (max_q, max_k, dropout_p, is_causal)
-        ctx.scale = inputs[6] if len(inputs) > 6 else None
+        ctx.scale = keyword_only_inputs.get("scale")
 
     def dense_backward(ctx, grad_out, *ignored):
         query, key, value, out, lse, cum_q, cum_k, seed, offset = ctx.saved_tensors
@@ -66,21 +66,21 @@ def _register_autograd() -> None:
         dq, dk, dv = ns._scaled_dot_product_flash_attention_backward(grad_out, query, key, value, out, lse, cum_q, cum_k,
                                                                       max_q, max_k, dropout_p, is_causal, seed, offset,
                                                                       scale=ctx.scale)
-        return dq, dk, dv, None, None, None, None
+        return dq, dk, dv, None, None, None
 
-    def varlen_setup(ctx, inputs, output):
+    def varlen_setup(ctx, inputs, keyword_only_inputs, output):
         query, key, value, cum_q, cum_k, max_q, max_k, dropout_p, is_causal, _dbg = inputs[:10]
         out, lse, seed, offset, _ = output
         ctx.save_for_backward(query, key, value, out, lse, cum_q, cum_k, seed, offset)
         ctx.args = (max_q, max_k, dropout_p, is_causal)
-        ctx.scale = inputs[10] if len(inputs) > 10 else None
+        ctx.scale = keyword_only_inputs.get("scale")
 
     def varlen_backward(ctx, grad_out, *ignored):
         query, key, value, out, lse, cum_q, cum_k, seed, offset = ctx.saved_tensors
         max_q, max_k, dropout_p, is_causal = ctx.args
         dq, dk, dv = ns._flash_attention_backward(grad_out, query, key, value, out, lse, cum_q, cum_k, max_q, max_k,
                                                   dropout_p, is_causal, seed, offset, scale=ctx.scale)
-        return dq, dk, dv, None, None, None, None, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None, None, None
 
     torch.library.register_autograd("b200_sdpa::_scaled_dot_product_flash_attention", dense_backward,
                                     setup_context=dense_setup)
