@@ -145,6 +145,18 @@ SDPA_B200_API int sdpa_b200_bwd(const sdpa_b200_params* p, void* workspace, size
  * returns it in *device_status (SDPA_B200_OK or SDPA_B200_DEVICE_TIMEOUT). */
 SDPA_B200_API int sdpa_b200_read_device_status(const void* workspace, void* stream, int* device_status);
 
+/* Split-KV decode (dense tensors, seqlen_q == 1) for callers that cannot allocate device memory
+ * where they call it - inside an allocator or memory-pool callback, or after the process has
+ * frozen its memory plan. No counterpart in the reference: its attention calls always take a
+ * workspace from the caching allocator (FlashAttention_internal.cpp:215-230). The caller passes
+ * inputs and outputs only; the split partials live in a fixed SDPA_B200_STATIC_SCRATCH_BYTES
+ * array inside the library (held by every GPU that loads it). Requests whose partials
+ * (batch * heads_q * splits * 516 bytes) exceed it are refused with SDPA_B200_INVALID_ARG. The
+ * first call on each device looks the array's address up; make it outside stream capture. Calls
+ * that overlap on one GPU race on the shared array - order them on one stream. */
+#define SDPA_B200_STATIC_SCRATCH_BYTES (16u << 20)
+SDPA_B200_API int sdpa_b200_decode_static(const sdpa_b200_params* p, void* stream);
+
 /* How many of this library's kernels the calling process has launched so far. */
 SDPA_B200_API uint64_t sdpa_b200_launch_count(void);
 

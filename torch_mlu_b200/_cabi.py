@@ -26,8 +26,10 @@ EXPORTED_SYMBOLS = (
     "sdpa_b200_fwd",
     "sdpa_b200_bwd",
     "sdpa_b200_read_device_status",
+    "sdpa_b200_decode_static",
     "sdpa_b200_launch_count",
 )
+STATIC_SCRATCH_BYTES = 16 << 20
 
 
 class SdpaParams(ctypes.Structure):
@@ -90,6 +92,8 @@ def load() -> ctypes.CDLL:
         fn.argtypes = [POINTER(SdpaParams), c_void_p, c_size_t, c_void_p]
     lib.sdpa_b200_read_device_status.restype = c_int
     lib.sdpa_b200_read_device_status.argtypes = [c_void_p, c_void_p, POINTER(c_int)]
+    lib.sdpa_b200_decode_static.restype = c_int
+    lib.sdpa_b200_decode_static.argtypes = [POINTER(SdpaParams), c_void_p]
     lib.sdpa_b200_set_debug_buffer.restype = None
     lib.sdpa_b200_set_debug_buffer.argtypes = [c_void_p]
     _lib = lib

@@ -12,6 +12,8 @@
 // warp shuffles.
 #include <cuda_bf16.h>
 
+#include <mutex>
+
 #include "kernels.h"
 #include "ptx_sm100.cuh"
 
@@ -428,3 +430,132 @@ int launch_fwd_decode(const sdpa_b200_params& p, void* workspace, size_t workspa
 }
 
 }  // namespace sdpa_b200
+
+// ---------------------------------------------------------------------------------------
+// Decode without any caller- or library-allocated scratch memory.
+//
+// Some callers may not allocate device memory at the point where they need attention: code
+// running inside a memory-pool callback or an allocator hook, a serving loop whose memory plan
+// was frozen at start-up, or a process that has handed the whole device to another allocator.
+// For them the split-KV partials live in a fixed array that is part of this library's image;
+// every GPU that loads the library carries those SDPA_B200_STATIC_SCRATCH_BYTES until exit.
+//
+// The array name below is only a host-side handle: in host code it is not a device address and
+// must never be handed to a kernel. The real address is asked from the runtime with
+// cudaGetSymbolAddress, once per device, with that device current, on the first call made on
+// that device (so make that first call outside any stream capture). Nothing is allocated or
+// freed here, and no library routine that allocates is called.
+//
+// All calls on a device share the one array and it keeps whatever the previous call left in
+// it. That is harmless for this kernel pair - every (row, split) slot the merge kernel reads is
+// written by the split kernel of the same call first, so nothing has to start at zero - but two
+// calls whose kernels overlap on the GPU (different streams, no ordering) race on it.
+// ---------------------------------------------------------------------------------------
+namespace sdpa_b200 {
+namespace {
+
+static __device__ __align__(256) unsigned char g_decode_static_scratch[SDPA_B200_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices] = {};
+std::mutex g_static_scratch_mutex;
+
+// Device address of the static array on the current device (looked up once per device).
+int static_scratch_address(void** out) {
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    (void)cudaGetLastError();
+    set_error("decode_static: cannot identify the current device");
+    return SDPA_B200_NO_DEVICE;
+  }
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    err = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
+    if (err != cudaSuccess || ptr == nullptr) {
+      (void)cudaGetLastError();
+      set_error("decode_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(err));
+      return SDPA_B200_LAUNCH_FAILED;
+    }
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return SDPA_B200_OK;
+}
+
+}  // namespace
+}  // namespace sdpa_b200
+
+extern "C" SDPA_B200_API int sdpa_b200_decode_static(const sdpa_b200_params* p, void* stream) {
+  using namespace sdpa_b200;
+  int st = validate_forward_call(p);
+  if (st != SDPA_B200_OK) return st;
+  if (p->cu_seqlens_q != nullptr || p->max_seqlen_q != 1) {
+    set_error("decode_static takes dense tensors with seqlen_q == 1 (got %d)", p->max_seqlen_q);
+    return SDPA_B200_UNSUPPORTED;
+  }
+  const int splits = choose_splits(*p);
+  const size_t rows = static_cast<size_t>(p->batch) * p->heads_q * splits;
+  const size_t need = rows * sizeof(float) * (kD + 1);
+  if (need > SDPA_B200_STATIC_SCRATCH_BYTES) {
+    set_error("decode_static: batch %d x heads_q %d x %d splits needs %zu bytes of split partials, more than the "
+              "%u bytes built into the library; lower num_splits or use sdpa_b200_fwd with a workspace",
+              p->batch, p->heads_q, splits, need, static_cast<unsigned>(SDPA_B200_STATIC_SCRATCH_BYTES));
+    return SDPA_B200_INVALID_ARG;
+  }
+  void* scratch = nullptr;
+  st = static_scratch_address(&scratch);
+  if (st != SDPA_B200_OK) return st;
+
+  DecodeParams d;
+  d.q = static_cast<const __nv_bfloat16*>(p->q);
+  d.k = static_cast<const __nv_bfloat16*>(p->k);
+  d.v = static_cast<const __nv_bfloat16*>(p->v);
+  d.out = static_cast<__nv_bfloat16*>(p->out);
+  d.lse = p->lse;
+  d.part_o = static_cast<float*>(scratch);
+  d.part_lse = d.part_o + rows * kD;
+  d.q_batch_stride = p->q_batch_stride;
+  d.q_head_stride = p->q_head_stride;
+  d.k_batch_stride = p->k_batch_stride;
+  d.k_head_stride = p->k_head_stride;
+  d.k_row_stride = p->k_row_stride;
+  d.v_batch_stride = p->v_batch_stride;
+  d.v_head_stride = p->v_head_stride;
+  d.v_row_stride = p->v_row_stride;
+  d.o_batch_stride = p->o_batch_stride;
+  d.o_head_stride = p->o_head_stride;
+  d.heads_q = p->heads_q;
+  d.heads_kv = p->heads_kv;
+  d.group = p->heads_q / p->heads_kv;
+  d.chunks = (d.group + 15) / 16;
+  d.len_k = p->max_seqlen_k;
+  d.num_splits = splits;
+  const int kps = (p->max_seqlen_k + splits - 1) / splits;
+  d.keys_per_split = ((kps + 63) / 64) * 64;
+  d.scale_log2 = p->softmax_scale * 1.4426950408889634f;
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  dim3 grid(splits, p->heads_kv * d.chunks, p->batch);
+  if (d.group > 8) decode_splitkv_kernel<true><<<grid, kDecThreads, 0, s>>>(d);
+  else decode_splitkv_kernel<false><<<grid, kDecThreads, 0, s>>>(d);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("decode_static: launch failed: %s", cudaGetErrorString(err));
+    return SDPA_B200_LAUNCH_FAILED;
+  }
+  count_launch();
+  if (splits > 1) {
+    const int nrows = p->batch * p->heads_q;
+    decode_combine_kernel<<<(nrows + 3) / 4, 128, 0, s>>>(d, nrows);
+    err = cudaGetLastError();
+    if (err != cudaSuccess) {
+      set_error("decode_static merge: launch failed: %s", cudaGetErrorString(err));
+      return SDPA_B200_LAUNCH_FAILED;
+    }
+    count_launch();
+  }
+  return SDPA_B200_OK;
+}
+

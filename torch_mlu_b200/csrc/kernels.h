@@ -33,6 +33,10 @@ size_t decode_workspace_bytes(const sdpa_b200_params& p, int* num_splits_out);
 int launch_fwd_decode(const sdpa_b200_params& p, void* workspace, size_t workspace_bytes,
                       cudaStream_t stream);
 
+// Argument and device checks of the forward entry point, for entry points defined outside
+// sdpa_api.cu. Returns an SDPA_B200_* status and sets the error text.
+int validate_forward_call(const sdpa_b200_params* p);
+
 // Backward: delta pre-pass + dK/dV kernel + dQ kernel.
 size_t bwd_workspace_bytes(const sdpa_b200_params& p);
 int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_bytes,

@@ -217,6 +217,13 @@ bool use_decode(const sdpa_b200_params* p) {
 float* g_debug_buffer = nullptr;  // test hook, see sdpa_b200_set_debug_buffer
 
 }  // namespace
+
+int validate_forward_call(const sdpa_b200_params* p) {
+  int st = validate_common(p);
+  if (st != SDPA_B200_OK) return st;
+  return check_device();
+}
+
 }  // namespace sdpa_b200
 
 using namespace sdpa_b200;
