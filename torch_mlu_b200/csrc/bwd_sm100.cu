@@ -13,10 +13,10 @@
 //      which later turns their P into exact zeros).
 //   2. bwd_tile_kernel<kModeDKDV>: one CTA per (batch, kv head, 128-key block). K and V tiles
 //      stay in shared memory; (Q, dO) tiles stream through a 2-stage TMA ring. Per Q tile:
-//      S^T = K Q^T and dP^T = V dO^T on tcgen05 into TMEM, the compute warpgroup (thread = key
-//      row = TMEM lane) forms P^T and dS^T, writes them back to TMEM as bf16, and two more
-//      MMAs with the TMEM operand accumulate dV += P^T dO and dK += dS^T Q (the streamed tiles
-//      are re-read in place as MN-major operands).
+//      S^T = K Q^T and dP^T = V dO^T on tcgen05 into TMEM, two compute warpgroups (thread = key
+//      row = TMEM lane, one warpgroup per 64-query half of the tile) form P^T and dS^T, write
+//      them back to TMEM as bf16, and MMAs with the TMEM operand accumulate dV += P^T dO and
+//      dK += dS^T Q half by half (the streamed tiles are re-read in place as MN-major operands).
 //   3. bwd_tile_kernel<kModeDQ>: one CTA per (batch, query head, 128-query block); Q and dO
 //      stay, (K, V) stream; S = Q K^T, dP = dO V^T, dS -> TMEM, dQ += dS K.
 // TMEM: T1 [0,128) T2 [128,256) ACC1 [256,384) ACC2 [384,512).
@@ -32,7 +32,7 @@ constexpr int kTile = 128;  // rows per tile (queries or keys) and head_dim
 constexpr uint32_t kTileBytes = kTile * kTile * 2;
 constexpr uint32_t kHalfBytes = kTileBytes / 2;
 constexpr int kStages = 2;
-constexpr int kThreads = 192;  // warps 0-3 compute, warp 4 TMA, warp 5 MMA
+constexpr int kThreads = 320;  // warps 0-3 / 4-7 compute (column halves), warp 8 TMA, warp 9 MMA
 constexpr int kModeDKDV = 0;
 constexpr int kModeDQ = 1;
 
@@ -44,8 +44,8 @@ constexpr uint32_t kBarXFull = 0;
 constexpr uint32_t kBarYFull = 8;
 constexpr uint32_t kBarYEmpty = kBarYFull + 8 * kStages;
 constexpr uint32_t kBarTFull = kBarYEmpty + 8 * kStages;
-constexpr uint32_t kBarPFull = kBarTFull + 8;
-constexpr uint32_t kBarAccFull = kBarPFull + 8;
+constexpr uint32_t kBarPFull = kBarTFull + 8;  // 2: one per column half
+constexpr uint32_t kBarAccFull = kBarPFull + 16;
 constexpr uint32_t kSmemTmemPtr = kBarAccFull + 8;
 constexpr uint32_t kSmemAbort = kSmemTmemPtr + 4;
 constexpr uint32_t kSmemBytes = kSmemBar + 256 + 1024;
@@ -73,19 +73,24 @@ constexpr uint32_t kIdescTS = umma_idesc_bf16(kTile, kTile, false, true);
 
 // T = X Y^T, contraction over head_dim, both operands K-major in shared memory
 __device__ __forceinline__ void issue_xyT(uint32_t t, uint32_t x_smem, uint32_t y_smem) {
+  const uint32_t a_lo = umma_desc_lo_kmajor(x_smem);
+  const uint32_t b_lo = umma_desc_lo_kmajor(y_smem);
+  umma_ss_lo<kIdescSS, false>(t, a_lo, b_lo);
 #pragma unroll
-  for (int ks = 0; ks < kTile / 16; ++ks) {
-    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-    umma_ss(t, umma_desc_kmajor(x_smem + off), umma_desc_kmajor(y_smem + off), kIdescSS, ks > 0 ? 1u : 0u);
+  for (int ks = 1; ks < kTile / 16; ++ks) {
+    const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+    umma_ss_lo<kIdescSS, true>(t, a_lo + off, b_lo + off);
   }
 }
 
-// ACC (+)= W Y, W bf16 in TMEM (lane = row), contraction over the 128 rows of the Y tile
-__device__ __forceinline__ void issue_wy(uint32_t acc, uint32_t w_tmem, uint32_t y_smem, bool accumulate) {
+// ACC (+)= W Y over rows [64*half, 64*half + 64) of the Y tile. W (bf16, lane = stationary row)
+// for those rows sits in the first 32 columns of the half's own 64-column score region.
+__device__ __forceinline__ void issue_wy_half(uint32_t acc, uint32_t t, uint32_t y_smem, int half, bool accumulate) {
+  const uint32_t b_lo = umma_desc_lo_mnmajor(y_smem, kHalfBytes);
 #pragma unroll
-  for (int ks = 0; ks < kTile / 16; ++ks) {
-    umma_ts(acc, w_tmem + ks * 8, umma_desc_mnmajor(y_smem + ks * 2048, kHalfBytes), kIdescTS,
-            (accumulate || ks > 0) ? 1u : 0u);
+  for (int i = 0; i < 4; ++i) {
+    const int ks = half * 4 + i;
+    umma_ts_lo<kIdescTS>(acc, t + half * 64 + i * 8, b_lo + ks * (2048 >> 4), (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 
@@ -152,6 +157,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     mbar_init(bar + kBarTFull, 1);
     mbar_init(bar + kBarPFull, kTile);
+    mbar_init(bar + kBarPFull + 8, kTile);
     mbar_init(bar + kBarAccFull, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -167,7 +173,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem_base = *tmem_ptr_smem;
   const uint32_t t1 = tmem_base, t2 = tmem_base + 128, acc1 = tmem_base + 256, acc2 = tmem_base + 384;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && n_items > 0) {
       const CUtensorMap* tmx1 = (kMode == kModeDKDV) ? &tm_k : &tm_q;
@@ -206,7 +212,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tma_load_4d(dst + kTileBytes + kHalfBytes, tmy2, full, 64, row, hy, bcoord);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && n_items > 0) {
       bool ok = mbar_wait(bar + kBarXFull, 0, abort_flag);
@@ -222,24 +228,31 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         issue_xyT(t1, base + kSmemX, y1);
         issue_xyT(t2, base + kSmemX + kTileBytes, y2);
         umma_commit(bar + kBarTFull);
-        ok = mbar_wait(bar + kBarPFull, i & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after_sync();
-        if (kMode == kModeDKDV) {
-          issue_wy(acc1, t1, y2, i > 0);  // dV += P^T dO
-          issue_wy(acc2, t2, y1, i > 0);  // dK += dS^T Q
-        } else {
-          issue_wy(acc1, t2, y1, i > 0);  // dQ += dS K
+        // the two compute warpgroups finish their 64 streamed rows independently
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          ok = mbar_wait(bar + kBarPFull + 8 * half, i & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          if (kMode == kModeDKDV) {
+            issue_wy_half(acc1, t1, y2, half, i > 0);  // dV += P^T dO
+            issue_wy_half(acc2, t2, y1, half, i > 0);  // dK += dS^T Q
+          } else {
+            issue_wy_half(acc1, t2, y1, half, i > 0);  // dQ += dS K
+          }
         }
+        if (!ok) break;
         umma_commit(bar + kBarYEmpty + 8 * s);
         if (i == n_items - 1) umma_commit(bar + kBarAccFull);
       }
     }
-  } else {
-    // ------------------------------------------------------------------ compute warpgroup
-    const int r = warp * 32 + lane;  // stationary row in the tile = TMEM lane
-    const int xr = x0 + r;           // key index (dK/dV) or query index (dQ) within the sequence
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ compute warpgroups
+    // warps 0-3 own streamed columns [0,64) of every stationary row, warps 4-7 columns [64,128)
+    const int half = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;  // stationary row in the tile = TMEM lane
+    const int xr = x0 + r;                 // key index (dK/dV) or query index (dQ) within the sequence
+    const uint32_t lane_base = (static_cast<uint32_t>((warp & 3) * 32) << 16) + half * 64;
     const float c = p.scale_log2;
     bool ok = true;
     float my_lse2 = 0.f, my_delta = 0.f;
@@ -273,7 +286,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (p.is_causal) j_hi = min(j_hi, xr + causal_off + 1 - y0);
       }
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t a[32], d[32];
         tmem_ld_x32(t1 + lane_base + cc * 32, a);
         tmem_ld_x32(t2 + lane_base + cc * 32, d);
@@ -284,7 +297,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           float pv[2], dsv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int j = cc * 32 + 2 * j2 + e;
+            const int j = half * 64 + cc * 32 + 2 * j2 + e;
             const float l2 = (kMode == kModeDKDV) ? vec_lse[j] : my_lse2;
             const float dl = (kMode == kModeDKDV) ? vec_delta[j] : my_delta;
             float pr = ex2_approx(fmaf(__uint_as_float(a[2 * j2 + e]), c, -l2));
@@ -300,7 +313,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(bar + kBarPFull);
+      mbar_arrive(bar + kBarPFull + 8 * half);
     }
 
     // ---- epilogue: accumulators -> scale -> bf16 -> global
@@ -334,7 +347,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           acc = acc2;
         }
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
+        for (int cc = 0; cc < 2; ++cc) {
           uint32_t v[32];
           if (n_items > 0) {
             tmem_ld_x32(acc + lane_base + cc * 32, v);
@@ -344,7 +357,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int j = 0; j < 32; ++j) v[j] = 0u;
           }
           if (valid) {
-            uint4* o4 = reinterpret_cast<uint4*>(dst + cc * 32);
+            uint4* o4 = reinterpret_cast<uint4*>(dst + half * 64 + cc * 32);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 w;
