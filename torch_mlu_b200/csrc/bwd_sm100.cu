@@ -19,7 +19,9 @@
 //      dK += dS^T Q half by half (the streamed tiles are re-read in place as MN-major operands).
 //   3. bwd_tile_kernel<kModeDQ>: one CTA per (batch, query head, 128-query block); Q and dO
 //      stay, (K, V) stream; S = Q K^T, dP = dO V^T, dS -> TMEM, dQ += dS K.
-// TMEM: T1 [0,128) T2 [128,256) ACC1 [256,384) ACC2 [384,512).
+// TMEM: T1 [0,128) T2 [128,256) ACC1 [256,384) ACC2 [384,512). T1/T2 swap roles every item (scores
+// vs dP); the bf16 P and dS of an item both live in its score buffer, which frees the dP buffer
+// for the next item's scores while the accumulation MMAs of this item are still running.
 #include <cuda_bf16.h>
 
 #include "kernels.h"
@@ -43,8 +45,9 @@ constexpr uint32_t kSmemBar = kSmemVec + kStages * 1024;
 constexpr uint32_t kBarXFull = 0;
 constexpr uint32_t kBarYFull = 8;
 constexpr uint32_t kBarYEmpty = kBarYFull + 8 * kStages;
-constexpr uint32_t kBarTFull = kBarYEmpty + 8 * kStages;
-constexpr uint32_t kBarPFull = kBarTFull + 8;  // 2: one per column half
+constexpr uint32_t kBarSFull = kBarYEmpty + 8 * kStages;   // first score GEMM (X1 Y1^T) of an item done
+constexpr uint32_t kBarDFull = kBarSFull + 8;              // second score GEMM (X2 Y2^T) done
+constexpr uint32_t kBarPFull = kBarDFull + 8;  // 2: one per column half
 constexpr uint32_t kBarAccFull = kBarPFull + 16;
 constexpr uint32_t kSmemTmemPtr = kBarAccFull + 8;
 constexpr uint32_t kSmemAbort = kSmemTmemPtr + 4;
@@ -84,13 +87,13 @@ __device__ __forceinline__ void issue_xyT(uint32_t t, uint32_t x_smem, uint32_t 
 }
 
 // ACC (+)= W Y over rows [64*half, 64*half + 64) of the Y tile. W (bf16, lane = stationary row)
-// for those rows sits in the first 32 columns of the half's own 64-column score region.
-__device__ __forceinline__ void issue_wy_half(uint32_t acc, uint32_t t, uint32_t y_smem, int half, bool accumulate) {
+// for those rows starts at TMEM column `w` (32 columns).
+__device__ __forceinline__ void issue_wy_half(uint32_t acc, uint32_t w, uint32_t y_smem, int half, bool accumulate) {
   const uint32_t b_lo = umma_desc_lo_mnmajor(y_smem, kHalfBytes);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int ks = half * 4 + i;
-    umma_ts_lo<kIdescTS>(acc, t + half * 64 + i * 8, b_lo + ks * (2048 >> 4), (accumulate || ks > 0) ? 1u : 0u);
+    umma_ts_lo<kIdescTS>(acc, w + i * 8, b_lo + ks * (2048 >> 4), (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 
@@ -155,7 +158,8 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(bar + kBarYFull + 8 * s, 1);
       mbar_init(bar + kBarYEmpty + 8 * s, 1);
     }
-    mbar_init(bar + kBarTFull, 1);
+    mbar_init(bar + kBarSFull, 1);
+    mbar_init(bar + kBarDFull, 1);
     mbar_init(bar + kBarPFull, kTile);
     mbar_init(bar + kBarPFull + 8, kTile);
     mbar_init(bar + kBarAccFull, 1);
@@ -215,35 +219,57 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && n_items > 0) {
+      // Score buffers swap roles every item: item i keeps S in T[i&1] and dP in T[(i&1)^1]. The
+      // compute warpgroups put BOTH bf16 results (P and dS) into the S buffer, so the dP buffer is
+      // free as soon as it has been read and takes the next item's S right away: that GEMM, and
+      // the exponentials that need only S, run under this item's accumulation MMAs.
+      const uint32_t tbuf[2] = {t1, t2};
+      const uint32_t x1 = base + kSmemX, x2 = base + kSmemX + kTileBytes;
       bool ok = mbar_wait(bar + kBarXFull, 0, abort_flag);
+      ok = ok && mbar_wait(bar + kBarYFull, 0, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_xyT(tbuf[0], x1, base + kSmemY);
+        umma_commit(bar + kBarSFull);
+        issue_xyT(tbuf[1], x2, base + kSmemY + kTileBytes);
+        umma_commit(bar + kBarDFull);
+      }
       for (int i = 0; ok && i < n_items; ++i) {
         const int s = i % kStages;
         const uint32_t y1 = base + kSmemY + s * 2 * kTileBytes;
         const uint32_t y2 = y1 + kTileBytes;
-        ok = mbar_wait(bar + kBarYFull + 8 * s, (i / kStages) & 1, abort_flag);
+        const uint32_t sbuf = tbuf[i & 1], dbuf = tbuf[(i & 1) ^ 1];
+        const bool more = i + 1 < n_items;
+        const int sn = (i + 1) % kStages;
+        const uint32_t y1n = base + kSmemY + sn * 2 * kTileBytes;
+        // both halves of dP(i) have been read once both warpgroups have signalled
+        ok = mbar_wait(bar + kBarPFull, i & 1, abort_flag) && mbar_wait(bar + kBarPFull + 8, i & 1, abort_flag);
         if (!ok) break;
+        if (more) {
+          ok = mbar_wait(bar + kBarYFull + 8 * sn, ((i + 1) / kStages) & 1, abort_flag);
+          if (!ok) break;
+        }
         tc_fence_after_sync();
-        // T1 = X1 Y1^T, T2 = X2 Y2^T (issued after the previous item's TMEM-operand MMAs, so
-        // the bf16 tiles those read from T1/T2 are consumed before being overwritten)
-        issue_xyT(t1, base + kSmemX, y1);
-        issue_xyT(t2, base + kSmemX + kTileBytes, y2);
-        umma_commit(bar + kBarTFull);
-        // the two compute warpgroups finish their 64 streamed rows independently
+        if (more) {
+          issue_xyT(dbuf, x1, y1n);  // S(i+1) into the buffer dP(i) has just left
+          umma_commit(bar + kBarSFull);
+        }
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          ok = mbar_wait(bar + kBarPFull + 8 * half, i & 1, abort_flag);
-          if (!ok) break;
-          tc_fence_after_sync();
           if (kMode == kModeDKDV) {
-            issue_wy_half(acc1, t1, y2, half, i > 0);  // dV += P^T dO
-            issue_wy_half(acc2, t2, y1, half, i > 0);  // dK += dS^T Q
+            issue_wy_half(acc1, sbuf + half * 64, y2, half, i > 0);       // dV += P^T dO
+            issue_wy_half(acc2, sbuf + half * 64 + 32, y1, half, i > 0);  // dK += dS^T Q
           } else {
-            issue_wy_half(acc1, t2, y1, half, i > 0);  // dQ += dS K
+            issue_wy_half(acc1, sbuf + half * 64 + 32, y1, half, i > 0);  // dQ += dS K
           }
         }
-        if (!ok) break;
         umma_commit(bar + kBarYEmpty + 8 * s);
-        if (i == n_items - 1) umma_commit(bar + kBarAccFull);
+        if (more) {
+          issue_xyT(sbuf, x2, y1n + kTileBytes);  // dP(i+1), after the MMAs that read P(i), dS(i)
+          umma_commit(bar + kBarDFull);
+        } else {
+          umma_commit(bar + kBarAccFull);
+        }
       }
     }
   } else if (warp < 8) {
@@ -265,7 +291,9 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int s = i % kStages;
       const int hi = i / tiles_per_head;
       const int y0 = (y_lo + (i - hi * tiles_per_head)) * kTile;
-      ok = mbar_wait(bar + kBarTFull, i & 1, abort_flag);
+      const uint32_t sbuf = ((i & 1) ? t2 : t1) + lane_base;
+      const uint32_t dbuf = ((i & 1) ? t1 : t2) + lane_base;
+      ok = mbar_wait(bar + kBarSFull, i & 1, abort_flag);
       if (!ok) break;
       if (kMode == kModeDKDV) {
         // the per-query vectors arrive with the stage's bulk copies; observe that barrier directly
@@ -273,7 +301,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (!ok) break;
       }
       tc_fence_after_sync();
-      const float* vec_lse = reinterpret_cast<const float*>(smem + kSmemVec + s * 1024);
+      const float* vec_lse = reinterpret_cast<const float*>(smem + kSmemVec + s * 1024) + half * 64;
       const float* vec_delta = vec_lse + 128;
       // visibility of element (row xr, column y0 + j)
       //   dK/dV: key xr, query y0+j : visible iff xr <= y0 + j + off  <=>  j >= xr - off - y0
@@ -285,31 +313,47 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         j_hi = len_k - y0;
         if (p.is_causal) j_hi = min(j_hi, xr + causal_off + 1 - y0);
       }
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t a[32], d[32];
-        tmem_ld_x32(t1 + lane_base + cc * 32, a);
-        tmem_ld_x32(t2 + lane_base + cc * 32, d);
+      j_lo -= half * 64;  // relative to this thread's 64 columns
+      j_hi -= half * 64;
+
+      // phase 1 (needs S only): P = exp2(S c - lse2), masked
+      float pr[64];
+      {
+        uint32_t a[64];
+        tmem_ld_x32_at<0>(sbuf, a);
+        tmem_ld_x32_at<32>(sbuf + 32, a);
         tmem_wait_ld();
-        uint32_t pw[16], dw[16];
 #pragma unroll
-        for (int j2 = 0; j2 < 16; ++j2) {
-          float pv[2], dsv[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int j = half * 64 + cc * 32 + 2 * j2 + e;
-            const float l2 = (kMode == kModeDKDV) ? vec_lse[j] : my_lse2;
-            const float dl = (kMode == kModeDKDV) ? vec_delta[j] : my_delta;
-            float pr = ex2_approx(fmaf(__uint_as_float(a[2 * j2 + e]), c, -l2));
-            pr = (j >= j_lo && j < j_hi) ? pr : 0.f;
-            pv[e] = pr;
-            dsv[e] = pr * (__uint_as_float(d[2 * j2 + e]) - dl);
-          }
-          pw[j2] = pack_bf16x2(pv[0], pv[1]);
-          dw[j2] = pack_bf16x2(dsv[0], dsv[1]);
+        for (int j = 0; j < 64; ++j) {
+          const float l2 = (kMode == kModeDKDV) ? vec_lse[j] : my_lse2;
+          const float e = ex2_approx(fmaf(__uint_as_float(a[j]), c, -l2));
+          pr[j] = (j >= j_lo && j < j_hi) ? e : 0.f;
         }
-        if (kMode == kModeDKDV) tmem_st_x16(t1 + lane_base + cc * 16, pw);
-        tmem_st_x16(t2 + lane_base + cc * 16, dw);
+      }
+      // phase 2 (needs dP): dS = P o (dP - delta); both bf16 results go into the S buffer
+      ok = mbar_wait(bar + kBarDFull, i & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after_sync();
+      {
+        uint32_t d[64];
+        tmem_ld_x32_at<0>(dbuf, d);
+        tmem_ld_x32_at<32>(dbuf + 32, d);
+        tmem_wait_ld();
+        uint32_t pw[32], dw[32];
+#pragma unroll
+        for (int j2 = 0; j2 < 32; ++j2) {
+          const float dl0 = (kMode == kModeDKDV) ? vec_delta[2 * j2] : my_delta;
+          const float dl1 = (kMode == kModeDKDV) ? vec_delta[2 * j2 + 1] : my_delta;
+          pw[j2] = pack_bf16x2(pr[2 * j2], pr[2 * j2 + 1]);
+          dw[j2] = pack_bf16x2(pr[2 * j2] * (__uint_as_float(d[2 * j2]) - dl0),
+                               pr[2 * j2 + 1] * (__uint_as_float(d[2 * j2 + 1]) - dl1));
+        }
+        if (kMode == kModeDKDV) {
+          tmem_st_x16(sbuf, pw);
+          tmem_st_x16(sbuf + 16, pw + 16);
+        }
+        tmem_st_x16(sbuf + 32, dw);
+        tmem_st_x16(sbuf + 48, dw + 16);
       }
       tmem_wait_st();
       tc_fence_before_sync();
