@@ -19,9 +19,10 @@
 //      dK += dS^T Q half by half (the streamed tiles are re-read in place as MN-major operands).
 //   3. bwd_tile_kernel<kModeDQ>: one CTA per (batch, query head, 128-query block); Q and dO
 //      stay, (K, V) stream; S = Q K^T, dP = dO V^T, dS -> TMEM, dQ += dS K.
-// TMEM: T1 [0,128) T2 [128,256) ACC1 [256,384) ACC2 [384,512). T1/T2 swap roles every item (scores
-// vs dP); the bf16 P and dS of an item both live in its score buffer, which frees the dP buffer
-// for the next item's scores while the accumulation MMAs of this item are still running.
+// TMEM: T1 [0,128) T2 [128,256) ACC1 [256,384) ACC2 [384,512). The bf16 P and dS of an item both
+// live in the item's score buffer, so the buffer that held dP is free as soon as it has been read;
+// the MMA issuer uses that (and, for dQ, the unused ACC2) to run the next item's score GEMMs and
+// exponentials under the current item's accumulation MMAs (buffer schedule at the issuer).
 #include <cuda_bf16.h>
 
 #include "kernels.h"
@@ -33,25 +34,30 @@ namespace {
 constexpr int kTile = 128;  // rows per tile (queries or keys) and head_dim
 constexpr uint32_t kTileBytes = kTile * kTile * 2;
 constexpr uint32_t kHalfBytes = kTileBytes / 2;
-constexpr int kStages = 2;
+// Ring of 32 KB streamed tiles Y1(0), Y2(0), Y1(1), Y2(1), ...: 4 slots for dK/dV (which also stages
+// the per-query vectors), 5 for dQ so that K(i+2) can land while item i is still accumulating.
+constexpr int kMaxStages = 5;
+__host__ __device__ constexpr int stages_for(int mode) { return mode == 1 ? 5 : 4; }
 constexpr int kThreads = 320;  // warps 0-3 / 4-7 compute (column halves), warp 8 TMA, warp 9 MMA
 constexpr int kModeDKDV = 0;
 constexpr int kModeDQ = 1;
 
 constexpr uint32_t kSmemX = 0;                                   // stationary pair, 64 KB
-constexpr uint32_t kSmemY = 2 * kTileBytes;                      // kStages x 64 KB
-constexpr uint32_t kSmemVec = kSmemY + kStages * 2 * kTileBytes; // kStages x (lse2[128], delta[128])
-constexpr uint32_t kSmemBar = kSmemVec + kStages * 1024;
+constexpr uint32_t kSmemY = 2 * kTileBytes;                      // stages x 32 KB
+__host__ __device__ constexpr uint32_t smem_vec_off(int mode) { return kSmemY + stages_for(mode) * kTileBytes; }
+// per-slot (lse2[128], delta[128]), dK/dV only
+__host__ __device__ constexpr uint32_t smem_bar_off(int mode) { return smem_vec_off(mode) + (mode == 1 ? 0 : stages_for(mode) * 1024); }
+__host__ __device__ constexpr uint32_t smem_bytes_for(int mode) { return smem_bar_off(mode) + 256 + 1024; }
 constexpr uint32_t kBarXFull = 0;
 constexpr uint32_t kBarYFull = 8;
-constexpr uint32_t kBarYEmpty = kBarYFull + 8 * kStages;
-constexpr uint32_t kBarSFull = kBarYEmpty + 8 * kStages;   // first score GEMM (X1 Y1^T) of an item done
-constexpr uint32_t kBarDFull = kBarSFull + 8;              // second score GEMM (X2 Y2^T) done
-constexpr uint32_t kBarPFull = kBarDFull + 8;  // 2: one per column half
+constexpr uint32_t kBarYEmpty = kBarYFull + 8 * kMaxStages;
+constexpr uint32_t kBarSFull = kBarYEmpty + 8 * kMaxStages;   // 2: first score GEMM (X1 Y1^T) of an item done
+constexpr uint32_t kBarDFull = kBarSFull + 16;             // second score GEMM (X2 Y2^T) done
+constexpr uint32_t kBarDFree = kBarDFull + 8;              // 2: a column half has read dP out of TMEM
+constexpr uint32_t kBarPFull = kBarDFree + 16;             // 2: a column half has stored P / dS
 constexpr uint32_t kBarAccFull = kBarPFull + 16;
 constexpr uint32_t kSmemTmemPtr = kBarAccFull + 8;
 constexpr uint32_t kSmemAbort = kSmemTmemPtr + 4;
-constexpr uint32_t kSmemBytes = kSmemBar + 256 + 1024;
 
 struct BwdKernelParams {
   const float* lse2;   // padded [batch, heads_q, lq_pad]
@@ -114,6 +120,9 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* smem = smem_raw + (base - raw_addr);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  constexpr int kStages = stages_for(kMode);
+  constexpr uint32_t kSmemVec = smem_vec_off(kMode);
+  constexpr uint32_t kSmemBar = smem_bar_off(kMode);
 
   // grid: x = stationary row block (heaviest first), y = head (kv head for dK/dV), z = batch
   const int b = blockIdx.z;
@@ -159,7 +168,10 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(bar + kBarYEmpty + 8 * s, 1);
     }
     mbar_init(bar + kBarSFull, 1);
+    mbar_init(bar + kBarSFull + 8, 1);
     mbar_init(bar + kBarDFull, 1);
+    mbar_init(bar + kBarDFree, kTile);
+    mbar_init(bar + kBarDFree + 8, kTile);
     mbar_init(bar + kBarPFull, kTile);
     mbar_init(bar + kBarPFull + 8, kTile);
     mbar_init(bar + kBarAccFull, 1);
@@ -191,69 +203,96 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tma_load_4d(base + kSmemX + kHalfBytes, tmx1, bar + kBarXFull, 64, x_row, hx, bcoord);
       tma_load_4d(base + kSmemX + kTileBytes, tmx2, bar + kBarXFull, 0, x_row, hx, bcoord);
       tma_load_4d(base + kSmemX + kTileBytes + kHalfBytes, tmx2, bar + kBarXFull, 64, x_row, hx, bcoord);
-      for (int i = 0; i < n_items; ++i) {
-        const int s = i % kStages;
-        const uint32_t use = static_cast<uint32_t>(i / kStages);
+      for (int idx = 0; idx < 2 * n_items; ++idx) {  // ring tile idx: Y1(idx/2) if even, Y2(idx/2) if odd
+        const int i = idx >> 1;
+        const int s = idx % kStages;
+        const uint32_t use = static_cast<uint32_t>(idx / kStages);
         if (!mbar_wait(bar + kBarYEmpty + 8 * s, (use & 1u) ^ 1u, abort_flag)) break;
         const int hi = i / tiles_per_head;
         const int yt = y_lo + (i - hi * tiles_per_head);
         // dK/dV streams the query heads of this KV head; dQ streams the KV head of this query head
         const int hy = (kMode == kModeDKDV) ? hx * p.kv_group + hi : hx / p.kv_group;
         const uint32_t full = bar + kBarYFull + 8 * s;
-        const uint32_t dst = base + kSmemY + s * 2 * kTileBytes;
+        const uint32_t dst = base + kSmemY + s * kTileBytes;
         const int row = y_off + yt * kTile;
-        if (kMode == kModeDKDV) {
-          mbar_arrive_expect_tx(full, 2 * kTileBytes + 1024);
+        const bool first = (idx & 1) == 0;
+        if (kMode == kModeDKDV && first) {
+          mbar_arrive_expect_tx(full, kTileBytes + 1024);
           const size_t vec = (static_cast<size_t>(b) * p.heads_q + hy) * p.lq_pad + static_cast<size_t>(yt) * kTile;
           bulk_load_1d(base + kSmemVec + s * 1024, p.lse2 + vec, 512, full);
           bulk_load_1d(base + kSmemVec + s * 1024 + 512, p.delta + vec, 512, full);
         } else {
-          mbar_arrive_expect_tx(full, 2 * kTileBytes);
+          mbar_arrive_expect_tx(full, kTileBytes);
         }
-        tma_load_4d(dst, tmy1, full, 0, row, hy, bcoord);
-        tma_load_4d(dst + kHalfBytes, tmy1, full, 64, row, hy, bcoord);
-        tma_load_4d(dst + kTileBytes, tmy2, full, 0, row, hy, bcoord);
-        tma_load_4d(dst + kTileBytes + kHalfBytes, tmy2, full, 64, row, hy, bcoord);
+        const CUtensorMap* tm = first ? tmy1 : tmy2;
+        tma_load_4d(dst, tm, full, 0, row, hy, bcoord);
+        tma_load_4d(dst + kHalfBytes, tm, full, 64, row, hy, bcoord);
       }
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && n_items > 0) {
-      // Score buffers swap roles every item: item i keeps S in T[i&1] and dP in T[(i&1)^1]. The
-      // compute warpgroups put BOTH bf16 results (P and dS) into the S buffer, so the dP buffer is
-      // free as soon as it has been read and takes the next item's S right away: that GEMM, and
-      // the exponentials that need only S, run under this item's accumulation MMAs.
-      const uint32_t tbuf[2] = {t1, t2};
+      // Where the score GEMMs of item i land:
+      //   dK/dV: S(i) in T[i&1], dP(i) in T[(i&1)^1]. The compute warpgroups put BOTH bf16 results
+      //          (P and dS) into the S buffer, so the dP buffer is free once it has been read and
+      //          takes S(i+1) right away; dP(i+1) follows the accumulation MMAs into the S buffer.
+      //   dQ:    ACC2 is unused, so S alternates between T1 and ACC2 and dP always uses T2: S(i+2)
+      //          is issued right behind the accumulation of item i, dP(i+1) as soon as dP(i) is read.
+      // Either way the next item's scores and exponentials run under this item's accumulation.
       const uint32_t x1 = base + kSmemX, x2 = base + kSmemX + kTileBytes;
-      bool ok = mbar_wait(bar + kBarXFull, 0, abort_flag);
-      ok = ok && mbar_wait(bar + kBarYFull, 0, abort_flag);
+      auto s_buf = [&](int i) { return kMode == kModeDKDV ? ((i & 1) ? t2 : t1) : ((i & 1) ? acc2 : t1); };
+      auto d_buf = [&](int i) { return kMode == kModeDKDV ? ((i & 1) ? t1 : t2) : t2; };
+      auto s_bar = [&](int i) { return bar + kBarSFull + (kMode == kModeDQ ? 8 * (i & 1) : 0); };
+      auto y_slot = [&](int idx) { return base + kSmemY + (idx % kStages) * kTileBytes; };
+      auto y_wait = [&](int idx) { return mbar_wait(bar + kBarYFull + 8 * (idx % kStages), (idx / kStages) & 1, abort_flag); };
+      auto y_free = [&](int idx) { umma_commit(bar + kBarYEmpty + 8 * (idx % kStages)); };
+      bool ok = mbar_wait(bar + kBarXFull, 0, abort_flag) && y_wait(0);
       if (ok) {
         tc_fence_after_sync();
-        issue_xyT(tbuf[0], x1, base + kSmemY);
-        umma_commit(bar + kBarSFull);
-        issue_xyT(tbuf[1], x2, base + kSmemY + kTileBytes);
+        issue_xyT(s_buf(0), x1, y_slot(0));
+        umma_commit(s_bar(0));
+      }
+      ok = ok && y_wait(1);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_xyT(d_buf(0), x2, y_slot(1));
         umma_commit(bar + kBarDFull);
+        if (kMode == kModeDQ) y_free(1);  // V(0) is only read by dP(0)
+      }
+      if (kMode == kModeDQ && ok && n_items > 1) {
+        ok = y_wait(2);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_xyT(s_buf(1), x1, y_slot(2));
+          umma_commit(s_bar(1));
+        }
       }
       for (int i = 0; ok && i < n_items; ++i) {
-        const int s = i % kStages;
-        const uint32_t y1 = base + kSmemY + s * 2 * kTileBytes;
-        const uint32_t y2 = y1 + kTileBytes;
-        const uint32_t sbuf = tbuf[i & 1], dbuf = tbuf[(i & 1) ^ 1];
+        const uint32_t y1 = y_slot(2 * i), y2 = y_slot(2 * i + 1);
+        const uint32_t sbuf = s_buf(i);
         const bool more = i + 1 < n_items;
-        const int sn = (i + 1) % kStages;
-        const uint32_t y1n = base + kSmemY + sn * 2 * kTileBytes;
-        // both halves of dP(i) have been read once both warpgroups have signalled
-        ok = mbar_wait(bar + kBarPFull, i & 1, abort_flag) && mbar_wait(bar + kBarPFull + 8, i & 1, abort_flag);
+        // dP(i) has left TMEM once both column halves have read it
+        ok = mbar_wait(bar + kBarDFree, i & 1, abort_flag) && mbar_wait(bar + kBarDFree + 8, i & 1, abort_flag);
         if (!ok) break;
         if (more) {
-          ok = mbar_wait(bar + kBarYFull + 8 * sn, ((i + 1) / kStages) & 1, abort_flag);
-          if (!ok) break;
+          if (kMode == kModeDKDV) {
+            ok = y_wait(2 * i + 2);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_xyT(d_buf(i), x1, y_slot(2 * i + 2));  // S(i+1) into the buffer dP(i) has just left
+            umma_commit(s_bar(i + 1));
+          } else {
+            ok = y_wait(2 * i + 3);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_xyT(t2, x2, y_slot(2 * i + 3));  // dP(i+1)
+            umma_commit(bar + kBarDFull);
+            y_free(2 * i + 3);  // V(i+1) is only read by dP(i+1)
+          }
         }
+        ok = mbar_wait(bar + kBarPFull, i & 1, abort_flag) && mbar_wait(bar + kBarPFull + 8, i & 1, abort_flag);
+        if (!ok) break;
         tc_fence_after_sync();
-        if (more) {
-          issue_xyT(dbuf, x1, y1n);  // S(i+1) into the buffer dP(i) has just left
-          umma_commit(bar + kBarSFull);
-        }
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           if (kMode == kModeDKDV) {
@@ -263,12 +302,23 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             issue_wy_half(acc1, sbuf + half * 64 + 32, y1, half, i > 0);  // dQ += dS K
           }
         }
-        umma_commit(bar + kBarYEmpty + 8 * s);
-        if (more) {
-          issue_xyT(sbuf, x2, y1n + kTileBytes);  // dP(i+1), after the MMAs that read P(i), dS(i)
-          umma_commit(bar + kBarDFull);
-        } else {
-          umma_commit(bar + kBarAccFull);
+        y_free(2 * i);
+        if (kMode == kModeDKDV) y_free(2 * i + 1);
+        if (i == n_items - 1) umma_commit(bar + kBarAccFull);
+        if (kMode == kModeDKDV) {
+          if (more) {
+            ok = y_wait(2 * i + 3);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_xyT(sbuf, x2, y_slot(2 * i + 3));  // dP(i+1), behind the MMAs reading P(i), dS(i)
+            umma_commit(bar + kBarDFull);
+          }
+        } else if (i + 2 < n_items) {
+          ok = y_wait(2 * i + 4);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_xyT(sbuf, x1, y_slot(2 * i + 4));  // S(i+2), behind the MMAs reading dS(i)
+          umma_commit(s_bar(i + 2));
         }
       }
     }
@@ -288,16 +338,17 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       my_delta = p.delta[vec];
     }
     for (int i = 0; i < n_items; ++i) {
-      const int s = i % kStages;
+      const int s = (2 * i) % kStages;  // ring slot of Y1(i), which carries the per-query vectors
       const int hi = i / tiles_per_head;
       const int y0 = (y_lo + (i - hi * tiles_per_head)) * kTile;
-      const uint32_t sbuf = ((i & 1) ? t2 : t1) + lane_base;
-      const uint32_t dbuf = ((i & 1) ? t1 : t2) + lane_base;
-      ok = mbar_wait(bar + kBarSFull, i & 1, abort_flag);
+      const uint32_t sbuf = (kMode == kModeDKDV ? ((i & 1) ? t2 : t1) : ((i & 1) ? acc2 : t1)) + lane_base;
+      const uint32_t dbuf = (kMode == kModeDKDV ? ((i & 1) ? t1 : t2) : t2) + lane_base;
+      ok = mbar_wait(bar + kBarSFull + (kMode == kModeDQ ? 8 * (i & 1) : 0), (kMode == kModeDQ ? (i >> 1) : i) & 1,
+                     abort_flag);
       if (!ok) break;
       if (kMode == kModeDKDV) {
         // the per-query vectors arrive with the stage's bulk copies; observe that barrier directly
-        ok = mbar_wait(bar + kBarYFull + 8 * s, (i / kStages) & 1, abort_flag);
+        ok = mbar_wait(bar + kBarYFull + 8 * s, ((2 * i) / kStages) & 1, abort_flag);
         if (!ok) break;
       }
       tc_fence_after_sync();
@@ -316,7 +367,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       j_lo -= half * 64;  // relative to this thread's 64 columns
       j_hi -= half * 64;
 
-      // phase 1 (needs S only): P = exp2(S c - lse2), masked
+      // phase 1 (needs S only): P = exp2(S c - lse2), masked; its bf16 copy goes back at once
       float pr[64];
       {
         uint32_t a[64];
@@ -329,8 +380,15 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           const float e = ex2_approx(fmaf(__uint_as_float(a[j]), c, -l2));
           pr[j] = (j >= j_lo && j < j_hi) ? e : 0.f;
         }
+        if (kMode == kModeDKDV) {
+          uint32_t pw[32];
+#pragma unroll
+          for (int j2 = 0; j2 < 32; ++j2) pw[j2] = pack_bf16x2(pr[2 * j2], pr[2 * j2 + 1]);
+          tmem_st_x16(sbuf, pw);
+          tmem_st_x16(sbuf + 16, pw + 16);
+        }
       }
-      // phase 2 (needs dP): dS = P o (dP - delta); both bf16 results go into the S buffer
+      // phase 2 (needs dP): dS = P o (dP - delta) into the second half of this thread's columns
       ok = mbar_wait(bar + kBarDFull, i & 1, abort_flag);
       if (!ok) break;
       tc_fence_after_sync();
@@ -339,18 +397,15 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_ld_x32_at<0>(dbuf, d);
         tmem_ld_x32_at<32>(dbuf + 32, d);
         tmem_wait_ld();
-        uint32_t pw[32], dw[32];
+        tc_fence_before_sync();
+        mbar_arrive(bar + kBarDFree + 8 * half);  // the dP buffer may be overwritten
+        uint32_t dw[32];
 #pragma unroll
         for (int j2 = 0; j2 < 32; ++j2) {
           const float dl0 = (kMode == kModeDKDV) ? vec_delta[2 * j2] : my_delta;
           const float dl1 = (kMode == kModeDKDV) ? vec_delta[2 * j2 + 1] : my_delta;
-          pw[j2] = pack_bf16x2(pr[2 * j2], pr[2 * j2 + 1]);
           dw[j2] = pack_bf16x2(pr[2 * j2] * (__uint_as_float(d[2 * j2]) - dl0),
                                pr[2 * j2 + 1] * (__uint_as_float(d[2 * j2 + 1]) - dl1));
-        }
-        if (kMode == kModeDKDV) {
-          tmem_st_x16(sbuf, pw);
-          tmem_st_x16(sbuf + 16, pw + 16);
         }
         tmem_st_x16(sbuf + 32, dw);
         tmem_st_x16(sbuf + 48, dw + 16);
@@ -575,17 +630,20 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
 
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e1 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDKDV>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    cudaError_t e2 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e1 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDKDV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          smem_bytes_for(kModeDKDV));
+    cudaError_t e2 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          smem_bytes_for(kModeDQ));
     if (e1 != cudaSuccess || e2 != cudaSuccess) {
-      set_error("backward: cudaFuncSetAttribute(%u bytes smem) failed", kSmemBytes);
+      set_error("backward: cudaFuncSetAttribute(%u / %u bytes smem) failed", smem_bytes_for(kModeDKDV),
+                smem_bytes_for(kModeDQ));
       return SDPA_B200_LAUNCH_FAILED;
     }
     attr_done = true;
   }
 
   kp.num_row_blocks = (p.max_seqlen_k + kTile - 1) / kTile;
-  bwd_tile_kernel<kModeDKDV><<<dim3(kp.num_row_blocks, p.heads_kv, p.batch), kThreads, kSmemBytes, stream>>>(
+  bwd_tile_kernel<kModeDKDV><<<dim3(kp.num_row_blocks, p.heads_kv, p.batch), kThreads, smem_bytes_for(kModeDKDV), stream>>>(
       tm_q, tm_k, tm_v, tm_do, kp);
   err = cudaGetLastError();
   if (err != cudaSuccess) {
@@ -594,7 +652,7 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   }
   count_launch();
   kp.num_row_blocks = (p.max_seqlen_q + kTile - 1) / kTile;
-  bwd_tile_kernel<kModeDQ><<<dim3(kp.num_row_blocks, p.heads_q, p.batch), kThreads, kSmemBytes, stream>>>(
+  bwd_tile_kernel<kModeDQ><<<dim3(kp.num_row_blocks, p.heads_q, p.batch), kThreads, smem_bytes_for(kModeDQ), stream>>>(
       tm_q, tm_k, tm_v, tm_do, kp);
   err = cudaGetLastError();
   if (err != cudaSuccess) {
