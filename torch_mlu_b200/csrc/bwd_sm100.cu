@@ -243,9 +243,20 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       auto s_buf = [&](int i) { return kMode == kModeDKDV ? ((i & 1) ? t2 : t1) : ((i & 1) ? acc2 : t1); };
       auto d_buf = [&](int i) { return kMode == kModeDKDV ? ((i & 1) ? t1 : t2) : t2; };
       auto s_bar = [&](int i) { return bar + kBarSFull + (kMode == kModeDQ ? 8 * (i & 1) : 0); };
-      auto y_slot = [&](int idx) { return base + kSmemY + (idx % kStages) * kTileBytes; };
-      auto y_wait = [&](int idx) { return mbar_wait(bar + kBarYFull + 8 * (idx % kStages), (idx / kStages) & 1, abort_flag); };
-      auto y_free = [&](int idx) { umma_commit(bar + kBarYEmpty + 8 * (idx % kStages)); };
+      // ring position of tile 2i, kept incrementally (no division in the issue loop): slot = (2i) mod
+      // kStages, lap = (2i) / kStages. Tiles 2i + k, k < kStages, follow from it with one wrap.
+      int ring_slot = 0, ring_lap = 0;
+      auto pos = [&](int k, int& slot, int& lap) {
+        slot = ring_slot + k;
+        lap = ring_lap;
+        if (slot >= kStages) { slot -= kStages; ++lap; }
+      };
+      auto y_slot_k = [&](int k) { int sl, lp; pos(k, sl, lp); return base + kSmemY + sl * kTileBytes; };
+      auto y_wait_k = [&](int k) { int sl, lp; pos(k, sl, lp); return mbar_wait(bar + kBarYFull + 8 * sl, lp & 1, abort_flag); };
+      auto y_free_k = [&](int k) { int sl, lp; pos(k, sl, lp); umma_commit(bar + kBarYEmpty + 8 * sl); };
+      auto y_slot = [&](int idx) { return y_slot_k(idx); };  // prologue only (item 0: idx == k)
+      auto y_wait = [&](int idx) { return y_wait_k(idx); };
+      auto y_free = [&](int idx) { y_free_k(idx); };
       bool ok = mbar_wait(bar + kBarXFull, 0, abort_flag) && y_wait(0);
       if (ok) {
         tc_fence_after_sync();
@@ -268,7 +279,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       for (int i = 0; ok && i < n_items; ++i) {
-        const uint32_t y1 = y_slot(2 * i), y2 = y_slot(2 * i + 1);
+        const uint32_t y1 = y_slot_k(0), y2 = y_slot_k(1);
         const uint32_t sbuf = s_buf(i);
         const bool more = i + 1 < n_items;
         // dP(i) has left TMEM once both column halves have read it
@@ -276,18 +287,18 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (!ok) break;
         if (more) {
           if (kMode == kModeDKDV) {
-            ok = y_wait(2 * i + 2);
+            ok = y_wait_k(2);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_xyT(d_buf(i), x1, y_slot(2 * i + 2));  // S(i+1) into the buffer dP(i) has just left
+            issue_xyT(d_buf(i), x1, y_slot_k(2));  // S(i+1) into the buffer dP(i) has just left
             umma_commit(s_bar(i + 1));
           } else {
-            ok = y_wait(2 * i + 3);
+            ok = y_wait_k(3);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_xyT(t2, x2, y_slot(2 * i + 3));  // dP(i+1)
+            issue_xyT(t2, x2, y_slot_k(3));  // dP(i+1)
             umma_commit(bar + kBarDFull);
-            y_free(2 * i + 3);  // V(i+1) is only read by dP(i+1)
+            y_free_k(3);  // V(i+1) is only read by dP(i+1)
           }
         }
         ok = mbar_wait(bar + kBarPFull, i & 1, abort_flag) && mbar_wait(bar + kBarPFull + 8, i & 1, abort_flag);
@@ -302,24 +313,26 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             issue_wy_half(acc1, sbuf + half * 64 + 32, y1, half, i > 0);  // dQ += dS K
           }
         }
-        y_free(2 * i);
-        if (kMode == kModeDKDV) y_free(2 * i + 1);
+        y_free_k(0);
+        if (kMode == kModeDKDV) y_free_k(1);
         if (i == n_items - 1) umma_commit(bar + kBarAccFull);
         if (kMode == kModeDKDV) {
           if (more) {
-            ok = y_wait(2 * i + 3);
+            ok = y_wait_k(3);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_xyT(sbuf, x2, y_slot(2 * i + 3));  // dP(i+1), behind the MMAs reading P(i), dS(i)
+            issue_xyT(sbuf, x2, y_slot_k(3));  // dP(i+1), behind the MMAs reading P(i), dS(i)
             umma_commit(bar + kBarDFull);
           }
         } else if (i + 2 < n_items) {
-          ok = y_wait(2 * i + 4);
+          ok = y_wait_k(4);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_xyT(sbuf, x1, y_slot(2 * i + 4));  // S(i+2), behind the MMAs reading dS(i)
+          issue_xyT(sbuf, x1, y_slot_k(4));  // S(i+2), behind the MMAs reading dS(i)
           umma_commit(s_bar(i + 2));
         }
+        ring_slot += 2;
+        if (ring_slot >= kStages) { ring_slot -= kStages; ++ring_lap; }
       }
     }
   } else if (warp < 8) {
