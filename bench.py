@@ -39,7 +39,7 @@ WORKLOAD = "bf16 causal prefill forward B=4 Hq=Hkv=32 L=4096 D=128 (seed 1)"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram bytes per launch of the prefill kernel on the headline workload, from the ncu capture
 # summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES = {"prefill_c2": 5.04e8}  # 2 x 252 MB measured at half the batch (traffic scales with batch)
+NCU_TRAFFIC_BYTES = {"prefill_c2": 5.34e8}  # 2 x 267 MB measured at half the batch (traffic scales with batch)
 
 
 def load_peaks():
@@ -128,7 +128,7 @@ def dist_env():
 # ------------------------------------------------------------------------------------------
 # CPU reference arm
 # ------------------------------------------------------------------------------------------
-def cpu_reference_sample(budget_s: float = 12.0, max_reps: int = 40):
+def cpu_reference_sample(budget_s: float = 12.0, max_reps: int = 400):
     """Times torch CPU fused SDPA (fp32) on one batch element of the headline workload
     (B=1, H=32, L=4096, D=128, causal: 1/4 of a step), repeated for about `budget_s` seconds.
     Returns (info, best seconds per repetition, FLOP per repetition)."""
