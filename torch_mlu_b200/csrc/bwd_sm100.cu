@@ -73,6 +73,7 @@ struct BwdKernelParams {
   int64_t dv_batch_stride, dv_head_stride, dv_row_stride;
   int seqlen_q, seqlen_k, heads_q, heads_kv, kv_group, lq_pad;
   int num_row_blocks;  // blocks of 128 stationary rows (keys for dK/dV, queries for dQ)
+  int num_bh, heads_x, heads_per_wave;  // CTA order, see the top of bwd_tile_kernel
   float scale, scale_log2;
   int is_causal;
 };
@@ -124,9 +125,23 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr uint32_t kSmemVec = smem_vec_off(kMode);
   constexpr uint32_t kSmemBar = smem_bar_off(kMode);
 
-  // grid: x = stationary row block (heaviest first), y = head (kv head for dK/dV), z = batch
-  const int b = blockIdx.z;
-  const int hx = blockIdx.y;
+  // CTA order (1-D grid): (batch, head) pairs in groups of `heads_per_wave` whose streamed tensors
+  // fit L2 together; inside a group the 128-row blocks go heaviest first across all its heads
+  // (dK/dV: key block 0 sees every query; dQ: the last query block sees every key), so the launch
+  // ends on its lightest blocks.
+  int b, hx, xb;
+  {
+    const int per_group = p.heads_per_wave * p.num_row_blocks;
+    const int grp = blockIdx.x / per_group;
+    const int w = blockIdx.x - grp * per_group;
+    const int size = min(p.heads_per_wave, p.num_bh - grp * p.heads_per_wave);
+    const int rank = w / size;
+    const int bh = grp * p.heads_per_wave + (w - rank * size);
+    if (rank >= p.num_row_blocks) return;  // padding slots of a short last group
+    xb = (kMode == kModeDKDV) ? rank : p.num_row_blocks - 1 - rank;
+    b = bh / p.heads_x;
+    hx = bh - b * p.heads_x;
+  }
   int q_off = 0, k_off = 0, len_q = p.seqlen_q, len_k = p.seqlen_k, bcoord = b;
   if (p.cu_q != nullptr) {
     q_off = p.cu_q[b];
@@ -137,8 +152,6 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   const int causal_off = len_k - len_q;
   const int len_x = (kMode == kModeDKDV) ? len_k : len_q;
-  // dK/dV: block 0 sees every query (heaviest) -> ascending; dQ: last block heaviest -> descending
-  const int xb = (kMode == kModeDKDV) ? static_cast<int>(blockIdx.x) : p.num_row_blocks - 1 - static_cast<int>(blockIdx.x);
   const int x0 = xb * kTile;
   if (x0 >= len_x) return;
 
@@ -655,8 +668,21 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
     attr_done = true;
   }
 
+  // heads per group: streamed bytes per head (q + dO of the group, or k + v) within ~48 MB of L2
+  auto set_order = [&](int heads_x, int rows_streamed, int streams_per_head) {
+    kp.heads_x = heads_x;
+    kp.num_bh = p.batch * heads_x;
+    const double bytes = 2.0 * rows_streamed * p.head_dim * 2 * streams_per_head;
+    int hpw = static_cast<int>((48.0 * 1024 * 1024) / bytes);
+    hpw = hpw < 1 ? 1 : (hpw > 32 ? 32 : hpw);
+    if (hpw > kp.num_bh) hpw = kp.num_bh;
+    kp.heads_per_wave = hpw;
+    const int groups = (kp.num_bh + hpw - 1) / hpw;
+    return groups * hpw * kp.num_row_blocks;
+  };
   kp.num_row_blocks = (p.max_seqlen_k + kTile - 1) / kTile;
-  bwd_tile_kernel<kModeDKDV><<<dim3(kp.num_row_blocks, p.heads_kv, p.batch), kThreads, smem_bytes_for(kModeDKDV), stream>>>(
+  const int grid_dkdv = set_order(p.heads_kv, p.max_seqlen_q, kp.kv_group);
+  bwd_tile_kernel<kModeDKDV><<<dim3(grid_dkdv), kThreads, smem_bytes_for(kModeDKDV), stream>>>(
       tm_q, tm_k, tm_v, tm_do, kp);
   err = cudaGetLastError();
   if (err != cudaSuccess) {
@@ -665,7 +691,8 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   }
   count_launch();
   kp.num_row_blocks = (p.max_seqlen_q + kTile - 1) / kTile;
-  bwd_tile_kernel<kModeDQ><<<dim3(kp.num_row_blocks, p.heads_q, p.batch), kThreads, smem_bytes_for(kModeDQ), stream>>>(
+  const int grid_dq = set_order(p.heads_q, p.max_seqlen_k, 1);
+  bwd_tile_kernel<kModeDQ><<<dim3(grid_dq), kThreads, smem_bytes_for(kModeDQ), stream>>>(
       tm_q, tm_k, tm_v, tm_do, kp);
   err = cudaGetLastError();
   if (err != cudaSuccess) {
