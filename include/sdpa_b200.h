@@ -157,6 +157,18 @@ SDPA_B200_API int sdpa_b200_read_device_status(const void* workspace, void* stre
 #define SDPA_B200_STATIC_SCRATCH_BYTES (16u << 20)
 SDPA_B200_API int sdpa_b200_decode_static(const sdpa_b200_params* p, void* stream);
 
+/* Folds one partial attention result into an fp32 accumulator by the logsumexp rule (the combine
+ * step of ring / context-parallel prefill; no counterpart in the reference, whose attention is
+ * single-device):  lse' = log(exp(lse_acc) + exp(lse_part)),
+ *                  o_acc' = o_acc*exp(lse_acc - lse') + o_part*exp(lse_part - lse').
+ * o_acc [batch, heads, rows, 128] fp32 and lse_acc / lse_part [batch, heads, rows] fp32 are
+ * contiguous; o_part is bf16 with the given element strides (the `out` of sdpa_b200_fwd).
+ * Start an accumulator with lse_acc = -inf (o_acc may be uninitialised). */
+SDPA_B200_API int sdpa_b200_merge_partial(float* o_acc, float* lse_acc, const void* o_part, const float* lse_part,
+                                          int32_t batch, int32_t heads, int32_t rows, int32_t head_dim,
+                                          int64_t part_batch_stride, int64_t part_head_stride,
+                                          int64_t part_row_stride, void* stream);
+
 /* How many of this library's kernels the calling process has launched so far. */
 SDPA_B200_API uint64_t sdpa_b200_launch_count(void);
 

@@ -1,0 +1,47 @@
+"""Launched by torchrun (one rank per GPU): ring prefill and batch x head sharding over NCCL,
+each rank checking its own slice against the CPU oracle. Used by tests/test_ring_gpu.py when the
+machine has at least two GPUs:
+    torchrun --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 tests/run_multigpu_ring.py
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from oracle import sdpa_oracle as orc  # noqa: E402
+from torch_mlu_b200 import ring, sharding  # noqa: E402
+
+
+def main():
+    rank, local, world = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    g = torch.Generator().manual_seed(17)
+    B, Hq, Hkv, Ls = 1, 8, 2, 512
+    L = world * Ls
+    q = torch.randn(B, Hq, L, 128, generator=g).bfloat16()
+    k = torch.randn(B, Hkv, L, 128, generator=g).bfloat16()
+    v = torch.randn(B, Hkv, L, 128, generator=g).bfloat16()
+    sl = slice(rank * Ls, (rank + 1) * Ls)
+    for causal in (False, True):
+        out, lse = ring.ring_prefill(q[:, :, sl].to(dev), k[:, :, sl].to(dev), v[:, :, sl].to(dev), is_causal=causal)
+        torch.cuda.synchronize()
+        o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=causal)
+        orc.assert_close_bf16(out, o_ref[:, :, sl], f"ring out rank {rank} causal={causal}")
+        orc.assert_close_lse(lse, l_ref[:, :, sl], max_abs=2e-5)
+    out, lse, _ = sharding.sdpa_batch_head_sharded(q.to(dev), k.to(dev), v.to(dev), is_causal=True)
+    torch.cuda.synchronize()
+    o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=True)
+    orc.assert_close_bf16(out, o_ref, f"sharded out rank {rank}")
+    orc.assert_close_lse(lse, l_ref)
+    dist.barrier()
+    if rank == 0:
+        print(f"multigpu ring ok: world {world}")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

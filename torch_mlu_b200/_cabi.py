@@ -27,6 +27,7 @@ EXPORTED_SYMBOLS = (
     "sdpa_b200_bwd",
     "sdpa_b200_read_device_status",
     "sdpa_b200_decode_static",
+    "sdpa_b200_merge_partial",
     "sdpa_b200_launch_count",
 )
 STATIC_SCRATCH_BYTES = 16 << 20
@@ -94,6 +95,9 @@ def load() -> ctypes.CDLL:
     lib.sdpa_b200_read_device_status.argtypes = [c_void_p, c_void_p, POINTER(c_int)]
     lib.sdpa_b200_decode_static.restype = c_int
     lib.sdpa_b200_decode_static.argtypes = [POINTER(SdpaParams), c_void_p]
+    lib.sdpa_b200_merge_partial.restype = c_int
+    lib.sdpa_b200_merge_partial.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
+                                            c_int64, c_int64, c_int64, c_void_p]
     lib.sdpa_b200_set_debug_buffer.restype = None
     lib.sdpa_b200_set_debug_buffer.argtypes = [c_void_p]
     _lib = lib

@@ -1,0 +1,84 @@
+"""Ring / context-parallel prefill for sequences too long for one GPU's share of the work.
+
+Every rank owns a contiguous slice of the sequence: its queries stay put, the key/value slices
+travel around the ring (``batch_isend_irecv`` over NCCL: each hop lands in this GPU's own memory
+before any kernel reads it). At every hop the local forward kernel produces a partial
+(out, logsumexp) for (local queries x visiting keys) and ``merge_partial`` folds it into an fp32
+accumulator by the logsumexp rule. Causal masking falls out of the slice order: a visiting slice
+from an earlier rank is fully visible, the rank's own slice is the usual lower triangle, slices
+from later ranks are skipped (but still forwarded).
+
+The reference has no such path (its attention is single-device; P2P lives in
+ProcessGroupCNCL::send/recv, process_group_cncl.cpp:2526-2552).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _cabi
+
+
+def merge_partial(o_acc: torch.Tensor, lse_acc: torch.Tensor, o_part: torch.Tensor, lse_part: torch.Tensor) -> None:
+    """In-place logsumexp fold of a bf16 partial [B,H,L,128] (any strides) into the fp32
+    accumulator (contiguous [B,H,L,128], lse [B,H,L]). CUDA only."""
+    assert o_acc.is_cuda and o_acc.dtype == torch.float32 and o_acc.is_contiguous()
+    assert lse_acc.dtype == torch.float32 and lse_acc.is_contiguous() and lse_part.is_contiguous()
+    assert o_part.dtype == torch.bfloat16 and o_part.stride(-1) == 1
+    B, H, L, D = o_acc.shape
+    lib = _cabi.load()
+    st = lib.sdpa_b200_merge_partial(o_acc.data_ptr(), lse_acc.data_ptr(), o_part.data_ptr(), lse_part.data_ptr(), B, H, L, D,
+                                     o_part.stride(0), o_part.stride(1), o_part.stride(2),
+                                     torch.cuda.current_stream().cuda_stream)
+    _cabi.check(st, "sdpa_b200_merge_partial")
+
+
+def merge_partial_reference(o_acc, lse_acc, o_part, lse_part) -> None:
+    """The same fold in plain torch (host-side logic tests on CPU ranks)."""
+    lp = torch.where(torch.isposinf(lse_part), torch.full_like(lse_part, float("-inf")), lse_part)
+    new = torch.logaddexp(lse_acc, lp)
+    wa = torch.where(torch.isneginf(new), torch.zeros_like(new), torch.exp(lse_acc - new))
+    wp = torch.where(torch.isneginf(new), torch.zeros_like(new), torch.exp(lp - new))
+    o_acc.copy_(torch.where(wa.unsqueeze(-1) == 0, torch.zeros_like(o_acc), o_acc * wa.unsqueeze(-1)) + o_part.float() * wp.unsqueeze(-1))
+    lse_acc.copy_(new)
+
+
+def ring_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal: bool, scale: Optional[float] = None,
+                 group=None, attention_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None
+                 ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """q [B,Hq,Ls,D], k/v [B,Hkv,Ls,D]: this rank's slice (rank r owns rows [r*Ls, (r+1)*Ls)).
+    Returns (out [B,Hq,Ls,D] in q's dtype, lse [B,Hq,Ls] fp32) for the local queries over the
+    whole sequence. ``attention_fn(q, k, v, is_causal=, scale=) -> (out, lse)`` and ``merge_fn``
+    default to this library's kernels."""
+    if attention_fn is None:
+        from . import ops
+        attention_fn = ops.gqa_prefill
+    if merge_fn is None:
+        merge_fn = merge_partial
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    B, Hq, Ls, D = q.shape
+    o_acc = torch.empty((B, Hq, Ls, D), dtype=torch.float32, device=q.device)
+    lse_acc = torch.full((B, Hq, Ls), float("-inf"), dtype=torch.float32, device=q.device)
+    k_cur, v_cur = k.contiguous(), v.contiguous()
+    send_to = dist.get_global_rank(group, (rank + 1) % world) if group is not None else (rank + 1) % world
+    recv_from = dist.get_global_rank(group, (rank - 1) % world) if group is not None else (rank - 1) % world
+    for step in range(world):
+        src = (rank - step) % world  # owner of the slice now visiting
+        reqs = []
+        if step + 1 < world:
+            k_next, v_next = torch.empty_like(k_cur), torch.empty_like(v_cur)
+            ops_list = [dist.P2POp(dist.isend, k_cur, send_to, group), dist.P2POp(dist.isend, v_cur, send_to, group),
+                        dist.P2POp(dist.irecv, k_next, recv_from, group), dist.P2POp(dist.irecv, v_next, recv_from, group)]
+            reqs = dist.batch_isend_irecv(ops_list)
+        if not is_causal or src <= rank:
+            o_part, lse_part = attention_fn(q, k_cur, v_cur, is_causal=bool(is_causal and src == rank), scale=scale)
+            merge_fn(o_acc, lse_acc, o_part, lse_part.contiguous())
+        for r in reqs:
+            r.wait()
+        if step + 1 < world:
+            k_cur, v_cur = k_next, v_next
+    lse = torch.where(torch.isneginf(lse_acc), torch.full_like(lse_acc, float("inf")), lse_acc)
+    return o_acc.to(q.dtype), lse
