@@ -35,7 +35,7 @@ def rand(shape, seed):
     return torch.randn(shape, generator=g).bfloat16()
 
 
-@pytest.mark.parametrize("path", [p for p in GOLDEN if "d128" in p], ids=lambda p: os.path.basename(p)[14:-4])
+@pytest.mark.parametrize("path", GOLDEN, ids=lambda p: os.path.basename(p)[14:-4])
 def test_forward_matches_reference_golden(cuda_device, native_lib, path):
     g = load_golden(path)
     before = _cabi.launch_count()
@@ -62,6 +62,30 @@ def test_forward_matches_reference_golden(cuda_device, native_lib, path):
 def test_forward_dense_shapes(cuda_device, native_lib, B, Hq, Hkv, Lq, Lk, causal):
     q, k, v = rand((B, Hq, Lq, 128), 1), rand((B, Hkv, Lk, 128), 2), rand((B, Hkv, Lk, 128), 3)
     check_dense(cuda_device, q, k, v, causal)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Lq,Lk,causal", [
+    (2, 4, 4, 512, 512, True),
+    (1, 8, 2, 300, 700, True),
+    (1, 2, 2, 257, 255, False),
+    (1, 1, 1, 1, 1, True),
+])
+def test_forward_head_dim_64(cuda_device, native_lib, B, Hq, Hkv, Lq, Lk, causal):
+    g = torch.Generator().manual_seed(4)
+    q = torch.randn((B, Hq, Lq, 64), generator=g).bfloat16()
+    k = torch.randn((B, Hkv, Lk, 64), generator=g).bfloat16()
+    v = torch.randn((B, Hkv, Lk, 64), generator=g).bfloat16()
+    check_dense(cuda_device, q, k, v, causal)
+
+
+def test_config1_on_gpu_with_bf16_rounded_inputs(cuda_device, native_lib):
+    """BASELINE config 1 (B2 H8 L256 D64 non-causal, seed 0, scale 1/8) is the reference's own fp32
+    CPU case; the GPU path is bf16, so it runs on the bf16-rounded copies of the same inputs and is
+    compared with the CPU reference on those copies."""
+    c = workloads.config1_cpu_reference()
+    q, k, v = c.q.bfloat16(), c.k.bfloat16(), c.v.bfloat16()
+    out, lse = check_dense(cuda_device, q, k, v, False, scale=c.softmax_scale)
+    assert out.shape == (2, 8, 256, 64) and lse.shape == (2, 8, 256)
 
 
 def test_forward_scale_and_layouts(cuda_device, native_lib):

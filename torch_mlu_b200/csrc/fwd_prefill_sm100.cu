@@ -27,9 +27,9 @@ namespace {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockN = 128;
-constexpr int kHeadDim = 128;
+constexpr int kMaxHeadDim = 128;  // shared-memory slots are sized for it; head_dim 64 uses half of each
 constexpr int kStages = 4;
-constexpr uint32_t kTileBytes = kBlockN * kHeadDim * 2;  // 32768
+constexpr uint32_t kTileBytes = kBlockN * kMaxHeadDim * 2;  // 32768: one shared-memory slot
 constexpr uint32_t kHalfBytes = kTileBytes / 2;          // one 64-column TMA box
 constexpr int kNumThreads = 384;  // 3 warpgroups; warps 10-11 idle
 constexpr int kProducerWarp = 8;
@@ -76,31 +76,34 @@ constexpr int kStampBase = 2 * 128 * 260;
   } while (0)
 
 constexpr uint32_t kIdescQK = umma_idesc_bf16(kBlockM, kBlockN, false, false);
-constexpr uint32_t kIdescPV = umma_idesc_bf16(kBlockM, kHeadDim, false, true);
+template <int kD>
+constexpr uint32_t kIdescPV = umma_idesc_bf16(kBlockM, kD, false, true);
 
+template <int kD>
 __device__ __forceinline__ void issue_qk(uint32_t t_s, uint32_t q_smem, uint32_t k_smem) {
   const uint32_t a_lo = umma_desc_lo_kmajor(q_smem);
   const uint32_t b_lo = umma_desc_lo_kmajor(k_smem);
   umma_ss_lo<kIdescQK, false>(t_s, a_lo, b_lo);
 #pragma unroll
-  for (int ks = 1; ks < kHeadDim / 16; ++ks) {
+  for (int ks = 1; ks < kD / 16; ++ks) {
     const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
     umma_ss_lo<kIdescQK, true>(t_s, a_lo + off, b_lo + off);
   }
 }
 
 // O_t (+)= P_t V for keys [64*half, 64*half + 64) of the block: four K = 16 steps
+template <int kD>
 __device__ __forceinline__ void issue_pv_half(uint32_t t_o, uint32_t t_p, uint32_t v_smem, int half,
                                               bool accumulate) {
   const uint32_t b_lo = umma_desc_lo_mnmajor(v_smem, kHalfBytes);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int ks = half * 4 + i;
-    umma_ts_lo<kIdescPV>(t_o, t_p + ks * 8, b_lo + ks * (2048 >> 4), (accumulate || ks > 0) ? 1u : 0u);
+    umma_ts_lo<kIdescPV<kD>>(t_o, t_p + ks * 8, b_lo + ks * (2048 >> 4), (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 
-template <bool kDebug>
+template <bool kDebug, int kD>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k,
@@ -192,13 +195,14 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
       const int hk = h / p.kv_group;
-      mbar_arrive_expect_tx(bar + kBarQFull, 2 * kTileBytes);
+      constexpr uint32_t kLoadBytes = kBlockN * kD * 2;  // bytes one Q/K/V tile brings in
+      mbar_arrive_expect_tx(bar + kBarQFull, 2 * kLoadBytes);
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         const uint32_t dst = base + kSmemQ + t * kTileBytes;
         tma_load_4d(dst, &tm_q, bar + kBarQFull, 0, q_off + m0 + t * kBlockM, h, bcoord);
-        tma_load_4d(dst + kHalfBytes, &tm_q, bar + kBarQFull, 64, q_off + m0 + t * kBlockM, h,
-                    bcoord);
+        if (kD > 64)
+          tma_load_4d(dst + kHalfBytes, &tm_q, bar + kBarQFull, 64, q_off + m0 + t * kBlockM, h, bcoord);
       }
       for (int i = 0; i < 2 * n_iter; ++i) {  // ring item i: K(i/2) if even, V(i/2) if odd
         const int s = i % kStages;
@@ -208,9 +212,9 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint32_t dst = base + kSmemKV + s * kTileBytes;
         const CUtensorMap* tm = (i & 1) ? &tm_v : &tm_k;
         const int row = k_off + (i >> 1) * kBlockN;
-        mbar_arrive_expect_tx(full, kTileBytes);
+        mbar_arrive_expect_tx(full, kLoadBytes);
         tma_load_4d(dst, tm, full, 0, row, hk, bcoord);
-        tma_load_4d(dst + kHalfBytes, tm, full, 64, row, hk, bcoord);
+        if (kD > 64) tma_load_4d(dst + kHalfBytes, tm, full, 64, row, hk, bcoord);
       }
     }
   } else if (warp == kMmaWarp) {
@@ -227,7 +231,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (nblk[t] > 0) {
-            issue_qk(t_s[t], q_smem[t], base + kSmemKV);
+            issue_qk<kD>(t_s[t], q_smem[t], base + kSmemKV);
             umma_commit(bar + kBarSFull + 8 * t);
           }
         }
@@ -253,12 +257,12 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
             if (!ok) break;
             SDPA_STAMP(2, j, 1 + 3 * t);
             tc_fence_after_sync();
-            issue_pv_half(t_o[t], t_s[t], v_smem, 0, j > 0);
+            issue_pv_half<kD>(t_o[t], t_s[t], v_smem, 0, j > 0);
             ok = mbar_wait(bar + kBarPFull + 16 * t + 8, j & 1, abort_flag);
             if (!ok) break;
             if (t == 0) SDPA_STAMP(2, j, 7);
             tc_fence_after_sync();
-            issue_pv_half(t_o[t], t_s[t], v_smem, 1, true);
+            issue_pv_half<kD>(t_o[t], t_s[t], v_smem, 1, true);
             umma_commit(bar + kBarOFull + 8 * t);
           }
           if (t == 1) umma_commit(bar + kBarKVEmpty + 8 * sv);
@@ -270,7 +274,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
           SDPA_STAMP(2, j, 2 + 3 * t);
           if (j + 1 < nblk[t]) {
-            issue_qk(t_s[t], q_smem[t], k_smem);
+            issue_qk<kD>(t_s[t], q_smem[t], k_smem);
             umma_commit(bar + kBarSFull + 8 * t);
           }
           SDPA_STAMP(2, j, 3 + 3 * t);
@@ -359,7 +363,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
           if (!ok) break;
           tc_fence_after_sync();
 #pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
+          for (int cc = 0; cc < kD / 32; ++cc) {
             uint32_t r[32];
             tmem_ld_x32(t_o + cc * 32, r);
             tmem_wait_ld();
@@ -423,7 +427,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
         lse_ptr = p.lse + (static_cast<int64_t>(b) * p.heads_q + h) * p.seqlen_q + row;
       }
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
+      for (int cc = 0; cc < kD / 32; ++cc) {
         uint32_t r[32];
         if (my_blocks > 0) {
           tmem_ld_x32(t_o + cc * 32, r);
@@ -510,7 +514,8 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
   kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   kp.is_causal = p.is_causal;
 
-  auto kernel = debug ? fwd_prefill_kernel<true> : fwd_prefill_kernel<false>;
+  auto kernel = p.head_dim == 64 ? fwd_prefill_kernel<false, 64>
+                                 : (debug ? fwd_prefill_kernel<true, 128> : fwd_prefill_kernel<false, 128>);
   cudaError_t err =
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (err != cudaSuccess) {
