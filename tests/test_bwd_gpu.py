@@ -35,7 +35,7 @@ def check_grads(got, want, names=("dq", "dk", "dv")):
         orc.assert_close_grad_bf16(g, w, name)
 
 
-@pytest.mark.parametrize("path", [p for p in GOLDEN if "d128" in p], ids=lambda p: os.path.basename(p)[14:-4])
+@pytest.mark.parametrize("path", GOLDEN, ids=lambda p: os.path.basename(p)[14:-4])
 def test_backward_matches_reference_golden(cuda_device, native_lib, path):
     g = load_golden(path)
     out, lse, dq, dk, dv = run_fwd_bwd(cuda_device, g["q"], g["k"], g["v"], g["dout"], g["causal"], g["scale"])
@@ -62,6 +62,22 @@ def test_backward_dense_shapes(cuda_device, native_lib, B, Hq, Hkv, Lq, Lk, caus
     o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=causal)
     want = orc.cpu_sdpa_backward(dout, q, k, v, o_ref, l_ref, causal=causal)
     check_grads((dq, dk, dv), want)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Lq,Lk,causal", [
+    (2, 4, 4, 512, 512, True),
+    (1, 8, 2, 300, 700, True),
+    (1, 2, 2, 257, 255, False),
+])
+def test_backward_head_dim_64(cuda_device, native_lib, B, Hq, Hkv, Lq, Lk, causal):
+    g = torch.Generator().manual_seed(6)
+    q = torch.randn((B, Hq, Lq, 64), generator=g).bfloat16()
+    k = torch.randn((B, Hkv, Lk, 64), generator=g).bfloat16()
+    v = torch.randn((B, Hkv, Lk, 64), generator=g).bfloat16()
+    dout = torch.randn((B, Hq, Lq, 64), generator=g).bfloat16()
+    out, lse, dq, dk, dv = run_fwd_bwd(cuda_device, q, k, v, dout, causal)
+    o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=causal)
+    check_grads((dq, dk, dv), orc.cpu_sdpa_backward(dout, q, k, v, o_ref, l_ref, causal=causal))
 
 
 def test_backward_reference_operator_surface_and_scale(cuda_device, native_lib):

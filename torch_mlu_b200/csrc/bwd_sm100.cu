@@ -31,8 +31,8 @@
 namespace sdpa_b200 {
 namespace {
 
-constexpr int kTile = 128;  // rows per tile (queries or keys) and head_dim
-constexpr uint32_t kTileBytes = kTile * kTile * 2;
+constexpr int kTile = 128;  // rows per tile (queries or keys)
+constexpr uint32_t kTileBytes = kTile * 128 * 2;  // one shared-memory slot (head_dim 64 uses half of it)
 constexpr uint32_t kHalfBytes = kTileBytes / 2;
 // Ring of 32 KB streamed tiles Y1(0), Y2(0), Y1(1), Y2(1), ...: 4 slots for dK/dV (which also stages
 // the per-query vectors), 5 for dQ so that K(i+2) can land while item i is still accumulating.
@@ -79,15 +79,17 @@ struct BwdKernelParams {
 };
 
 constexpr uint32_t kIdescSS = umma_idesc_bf16(kTile, kTile, false, false);
-constexpr uint32_t kIdescTS = umma_idesc_bf16(kTile, kTile, false, true);
+template <int kD>
+constexpr uint32_t kIdescTS = umma_idesc_bf16(kTile, kD, false, true);
 
 // T = X Y^T, contraction over head_dim, both operands K-major in shared memory
+template <int kD>
 __device__ __forceinline__ void issue_xyT(uint32_t t, uint32_t x_smem, uint32_t y_smem) {
   const uint32_t a_lo = umma_desc_lo_kmajor(x_smem);
   const uint32_t b_lo = umma_desc_lo_kmajor(y_smem);
   umma_ss_lo<kIdescSS, false>(t, a_lo, b_lo);
 #pragma unroll
-  for (int ks = 1; ks < kTile / 16; ++ks) {
+  for (int ks = 1; ks < kD / 16; ++ks) {
     const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
     umma_ss_lo<kIdescSS, true>(t, a_lo + off, b_lo + off);
   }
@@ -95,12 +97,13 @@ __device__ __forceinline__ void issue_xyT(uint32_t t, uint32_t x_smem, uint32_t 
 
 // ACC (+)= W Y over rows [64*half, 64*half + 64) of the Y tile. W (bf16, lane = stationary row)
 // for those rows starts at TMEM column `w` (32 columns).
+template <int kD>
 __device__ __forceinline__ void issue_wy_half(uint32_t acc, uint32_t w, uint32_t y_smem, int half, bool accumulate) {
   const uint32_t b_lo = umma_desc_lo_mnmajor(y_smem, kHalfBytes);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int ks = half * 4 + i;
-    umma_ts_lo<kIdescTS>(acc, w + i * 8, b_lo + ks * (2048 >> 4), (accumulate || ks > 0) ? 1u : 0u);
+    umma_ts_lo<kIdescTS<kD>>(acc, w + i * 8, b_lo + ks * (2048 >> 4), (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 
@@ -110,7 +113,7 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src,
                : "memory");
 }
 
-template <int kMode>
+template <int kMode, int kD>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -211,11 +214,12 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const CUtensorMap* tmy2 = (kMode == kModeDKDV) ? &tm_do : &tm_v;
       const int x_row = ((kMode == kModeDKDV) ? k_off : q_off) + x0;
       const int y_off = (kMode == kModeDKDV) ? q_off : k_off;
-      mbar_arrive_expect_tx(bar + kBarXFull, 2 * kTileBytes);
+      constexpr uint32_t kLoadBytes = kTile * kD * 2;  // bytes one tile brings in
+      mbar_arrive_expect_tx(bar + kBarXFull, 2 * kLoadBytes);
       tma_load_4d(base + kSmemX, tmx1, bar + kBarXFull, 0, x_row, hx, bcoord);
-      tma_load_4d(base + kSmemX + kHalfBytes, tmx1, bar + kBarXFull, 64, x_row, hx, bcoord);
+      if (kD > 64) tma_load_4d(base + kSmemX + kHalfBytes, tmx1, bar + kBarXFull, 64, x_row, hx, bcoord);
       tma_load_4d(base + kSmemX + kTileBytes, tmx2, bar + kBarXFull, 0, x_row, hx, bcoord);
-      tma_load_4d(base + kSmemX + kTileBytes + kHalfBytes, tmx2, bar + kBarXFull, 64, x_row, hx, bcoord);
+      if (kD > 64) tma_load_4d(base + kSmemX + kTileBytes + kHalfBytes, tmx2, bar + kBarXFull, 64, x_row, hx, bcoord);
       for (int idx = 0; idx < 2 * n_items; ++idx) {  // ring tile idx: Y1(idx/2) if even, Y2(idx/2) if odd
         const int i = idx >> 1;
         const int s = idx % kStages;
@@ -230,16 +234,16 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int row = y_off + yt * kTile;
         const bool first = (idx & 1) == 0;
         if (kMode == kModeDKDV && first) {
-          mbar_arrive_expect_tx(full, kTileBytes + 1024);
+          mbar_arrive_expect_tx(full, kLoadBytes + 1024);
           const size_t vec = (static_cast<size_t>(b) * p.heads_q + hy) * p.lq_pad + static_cast<size_t>(yt) * kTile;
           bulk_load_1d(base + kSmemVec + s * 1024, p.lse2 + vec, 512, full);
           bulk_load_1d(base + kSmemVec + s * 1024 + 512, p.delta + vec, 512, full);
         } else {
-          mbar_arrive_expect_tx(full, kTileBytes);
+          mbar_arrive_expect_tx(full, kLoadBytes);
         }
         const CUtensorMap* tm = first ? tmy1 : tmy2;
         tma_load_4d(dst, tm, full, 0, row, hy, bcoord);
-        tma_load_4d(dst + kHalfBytes, tm, full, 64, row, hy, bcoord);
+        if (kD > 64) tma_load_4d(dst + kHalfBytes, tm, full, 64, row, hy, bcoord);
       }
     }
   } else if (warp == 9) {
@@ -273,13 +277,13 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       bool ok = mbar_wait(bar + kBarXFull, 0, abort_flag) && y_wait(0);
       if (ok) {
         tc_fence_after_sync();
-        issue_xyT(s_buf(0), x1, y_slot(0));
+        issue_xyT<kD>(s_buf(0), x1, y_slot(0));
         umma_commit(s_bar(0));
       }
       ok = ok && y_wait(1);
       if (ok) {
         tc_fence_after_sync();
-        issue_xyT(d_buf(0), x2, y_slot(1));
+        issue_xyT<kD>(d_buf(0), x2, y_slot(1));
         umma_commit(bar + kBarDFull);
         if (kMode == kModeDQ) y_free(1);  // V(0) is only read by dP(0)
       }
@@ -287,7 +291,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ok = y_wait(2);
         if (ok) {
           tc_fence_after_sync();
-          issue_xyT(s_buf(1), x1, y_slot(2));
+          issue_xyT<kD>(s_buf(1), x1, y_slot(2));
           umma_commit(s_bar(1));
         }
       }
@@ -303,13 +307,13 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             ok = y_wait_k(2);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_xyT(d_buf(i), x1, y_slot_k(2));  // S(i+1) into the buffer dP(i) has just left
+            issue_xyT<kD>(d_buf(i), x1, y_slot_k(2));  // S(i+1) into the buffer dP(i) has just left
             umma_commit(s_bar(i + 1));
           } else {
             ok = y_wait_k(3);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_xyT(t2, x2, y_slot_k(3));  // dP(i+1)
+            issue_xyT<kD>(t2, x2, y_slot_k(3));  // dP(i+1)
             umma_commit(bar + kBarDFull);
             y_free_k(3);  // V(i+1) is only read by dP(i+1)
           }
@@ -320,10 +324,10 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           if (kMode == kModeDKDV) {
-            issue_wy_half(acc1, sbuf + half * 64, y2, half, i > 0);       // dV += P^T dO
-            issue_wy_half(acc2, sbuf + half * 64 + 32, y1, half, i > 0);  // dK += dS^T Q
+            issue_wy_half<kD>(acc1, sbuf + half * 64, y2, half, i > 0);       // dV += P^T dO
+            issue_wy_half<kD>(acc2, sbuf + half * 64 + 32, y1, half, i > 0);  // dK += dS^T Q
           } else {
-            issue_wy_half(acc1, sbuf + half * 64 + 32, y1, half, i > 0);  // dQ += dS K
+            issue_wy_half<kD>(acc1, sbuf + half * 64 + 32, y1, half, i > 0);  // dQ += dS K
           }
         }
         y_free_k(0);
@@ -334,14 +338,14 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             ok = y_wait_k(3);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_xyT(sbuf, x2, y_slot_k(3));  // dP(i+1), behind the MMAs reading P(i), dS(i)
+            issue_xyT<kD>(sbuf, x2, y_slot_k(3));  // dP(i+1), behind the MMAs reading P(i), dS(i)
             umma_commit(bar + kBarDFull);
           }
         } else if (i + 2 < n_items) {
           ok = y_wait_k(4);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_xyT(sbuf, x1, y_slot_k(4));  // S(i+2), behind the MMAs reading dS(i)
+          issue_xyT<kD>(sbuf, x1, y_slot_k(4));  // S(i+2), behind the MMAs reading dS(i)
           umma_commit(s_bar(i + 2));
         }
         ring_slot += 2;
@@ -472,17 +476,18 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           acc = acc2;
         }
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
+        // this warpgroup converts head_dim columns [half * kD/2, (half + 1) * kD/2)
+        for (int cc = 0; cc < kD / 64; ++cc) {
           uint32_t v[32];
           if (n_items > 0) {
-            tmem_ld_x32(acc + lane_base + cc * 32, v);
+            tmem_ld_x32(acc + (lane_base - half * 64) + half * (kD / 2) + cc * 32, v);
             tmem_wait_ld();
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0u;
           }
           if (valid) {
-            uint4* o4 = reinterpret_cast<uint4*>(dst + half * 64 + cc * 32);
+            uint4* o4 = reinterpret_cast<uint4*>(dst + half * (kD / 2) + cc * 32);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 w;
@@ -518,7 +523,7 @@ struct PreParams {
   const int32_t* cu_q;
   int64_t o_batch_stride, o_head_stride, o_row_stride;
   int64_t do_batch_stride, do_head_stride, do_row_stride;
-  int seqlen_q, total_q, heads_q, lq_pad;
+  int seqlen_q, total_q, heads_q, lq_pad, head_dim;
 };
 
 __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreParams p) {
@@ -551,8 +556,11 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreParams p) 
     dout = p.dout + b * p.do_batch_stride + h * p.do_head_stride + static_cast<int64_t>(row) * p.do_row_stride;
     lse = p.lse[(static_cast<size_t>(b) * p.heads_q + h) * p.seqlen_q + row];
   }
-  const uint2 ov = *reinterpret_cast<const uint2*>(o + lane * 4);
-  const uint2 dv = *reinterpret_cast<const uint2*>(dout + lane * 4);
+  uint2 ov = make_uint2(0u, 0u), dv = make_uint2(0u, 0u);
+  if (lane * 4 < p.head_dim) {
+    ov = *reinterpret_cast<const uint2*>(o + lane * 4);
+    dv = *reinterpret_cast<const uint2*>(dout + lane * 4);
+  }
   const __nv_bfloat162 o0 = *reinterpret_cast<const __nv_bfloat162*>(&ov.x);
   const __nv_bfloat162 o1 = *reinterpret_cast<const __nv_bfloat162*>(&ov.y);
   const __nv_bfloat162 d0 = *reinterpret_cast<const __nv_bfloat162*>(&dv.x);
@@ -600,6 +608,7 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   pre.total_q = p.total_q;
   pre.heads_q = p.heads_q;
   pre.lq_pad = lq_pad;
+  pre.head_dim = p.head_dim;
   bwd_preprocess_kernel<<<dim3(lq_pad / 8, p.heads_q, p.batch), 256, 0, stream>>>(pre);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {
@@ -656,10 +665,16 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
 
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e1 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDKDV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e1 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDKDV, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           smem_bytes_for(kModeDKDV));
-    cudaError_t e2 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e2 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDQ, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           smem_bytes_for(kModeDQ));
+    if (e1 == cudaSuccess)
+      e1 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDKDV, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                smem_bytes_for(kModeDKDV));
+    if (e2 == cudaSuccess)
+      e2 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDQ, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                smem_bytes_for(kModeDQ));
     if (e1 != cudaSuccess || e2 != cudaSuccess) {
       set_error("backward: cudaFuncSetAttribute(%u / %u bytes smem) failed", smem_bytes_for(kModeDKDV),
                 smem_bytes_for(kModeDQ));
@@ -682,8 +697,10 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   };
   kp.num_row_blocks = (p.max_seqlen_k + kTile - 1) / kTile;
   const int grid_dkdv = set_order(p.heads_kv, p.max_seqlen_q, kp.kv_group);
-  bwd_tile_kernel<kModeDKDV><<<dim3(grid_dkdv), kThreads, smem_bytes_for(kModeDKDV), stream>>>(
-      tm_q, tm_k, tm_v, tm_do, kp);
+  if (p.head_dim == 64)
+    bwd_tile_kernel<kModeDKDV, 64><<<dim3(grid_dkdv), kThreads, smem_bytes_for(kModeDKDV), stream>>>(tm_q, tm_k, tm_v, tm_do, kp);
+  else
+    bwd_tile_kernel<kModeDKDV, 128><<<dim3(grid_dkdv), kThreads, smem_bytes_for(kModeDKDV), stream>>>(tm_q, tm_k, tm_v, tm_do, kp);
   err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("backward dK/dV: launch failed: %s", cudaGetErrorString(err));
@@ -692,8 +709,10 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   count_launch();
   kp.num_row_blocks = (p.max_seqlen_q + kTile - 1) / kTile;
   const int grid_dq = set_order(p.heads_q, p.max_seqlen_k, 1);
-  bwd_tile_kernel<kModeDQ><<<dim3(grid_dq), kThreads, smem_bytes_for(kModeDQ), stream>>>(
-      tm_q, tm_k, tm_v, tm_do, kp);
+  if (p.head_dim == 64)
+    bwd_tile_kernel<kModeDQ, 64><<<dim3(grid_dq), kThreads, smem_bytes_for(kModeDQ), stream>>>(tm_q, tm_k, tm_v, tm_do, kp);
+  else
+    bwd_tile_kernel<kModeDQ, 128><<<dim3(grid_dq), kThreads, smem_bytes_for(kModeDQ), stream>>>(tm_q, tm_k, tm_v, tm_do, kp);
   err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("backward dQ: launch failed: %s", cudaGetErrorString(err));

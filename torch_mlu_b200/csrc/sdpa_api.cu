@@ -130,7 +130,7 @@ int validate_common(const sdpa_b200_params* p) {
     return SDPA_B200_INVALID_ARG;
   }
   if (p->head_dim != 128 && p->head_dim != 64) {
-    set_error("this build has kernels for head_dim 128 (all paths) and 64 (prefill forward) only (got %d)", p->head_dim);
+    set_error("this build has kernels for head_dim 128 (all paths) and 64 (prefill forward and backward) only (got %d)", p->head_dim);
     return SDPA_B200_UNSUPPORTED;
   }
   if (!(p->softmax_scale > 0.f) || !(p->softmax_scale < 3.0e38f)) {
@@ -304,10 +304,6 @@ int sdpa_b200_fwd(const sdpa_b200_params* p, void* workspace, size_t workspace_b
 int sdpa_b200_bwd(const sdpa_b200_params* p, void* workspace, size_t workspace_bytes, void* stream) {
   int st = validate_common(p);
   if (st != SDPA_B200_OK) return st;
-  if (p->head_dim != 128) {
-    set_error("the backward kernels are built for head_dim 128 only (got %d)", p->head_dim);
-    return SDPA_B200_UNSUPPORTED;
-  }
   const bool varlen = p->cu_seqlens_q != nullptr;
   if ((st = check_tensor("dout", p->dout, p->do_batch_stride, p->do_head_stride, p->do_row_stride, varlen,
                          p->batch, p->heads_q)) != SDPA_B200_OK)
