@@ -32,6 +32,19 @@ def test_decode_matches_oracle(cuda_device, native_lib, B, Hq, Hkv, Lk, splits):
     orc.assert_close_lse(lse, l_ref)
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,Lk,splits", [(2, 8, 2, 1000, 4), (1, 32, 2, 777, 3), (1, 4, 4, 4096, 0)])
+def test_decode_head_dim_64(cuda_device, native_lib, B, Hq, Hkv, Lk, splits):
+    g = torch.Generator().manual_seed(8)
+    q = torch.randn((B, Hq, 1, 64), generator=g).bfloat16()
+    k = torch.randn((B, Hkv, Lk, 64), generator=g).bfloat16()
+    v = torch.randn((B, Hkv, Lk, 64), generator=g).bfloat16()
+    dev = cuda_device
+    out, lse = ops.decode_attention(q.to(dev), k.to(dev), v.to(dev), num_splits=splits)
+    o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=False)
+    orc.assert_close_bf16(out, o_ref, "out")
+    orc.assert_close_lse(lse, l_ref)
+
+
 def test_decode_auto_dispatch_and_strided_cache(cuda_device, native_lib):
     """Lq == 1 reaches the decode kernel through the dense op too; the cache may be a
     [B, L, H, D] buffer viewed as [B, H, L, D]."""

@@ -23,7 +23,7 @@ namespace {
 constexpr int kDecWarps = 4;
 constexpr int kDecThreads = kDecWarps * 32;
 constexpr int kKeysPerStep = 16;  // keys one warp handles per loop iteration
-constexpr int kD = 128;
+constexpr int kMaxD = 128;  // head_dim 64 and 128 are built
 constexpr int kMaxSplits = 128;
 
 struct DecodeParams {
@@ -32,13 +32,13 @@ struct DecodeParams {
   const __nv_bfloat16* v;
   __nv_bfloat16* out;
   float* lse;
-  float* part_o;    // [batch, heads_q, splits, 128] fp32, normalised per split
+  float* part_o;    // [batch, heads_q, splits, head_dim] fp32, normalised per split
   float* part_lse;  // [batch, heads_q, splits] fp32, log2 domain
   int64_t q_batch_stride, q_head_stride;
   int64_t k_batch_stride, k_head_stride, k_row_stride;
   int64_t v_batch_stride, v_head_stride, v_row_stride;
   int64_t o_batch_stride, o_head_stride;
-  int heads_q, heads_kv, group, chunks, len_k, num_splits, keys_per_split;
+  int heads_q, heads_kv, group, chunks, len_k, num_splits, keys_per_split, head_dim;
   float scale_log2;
 };
 
@@ -90,6 +90,7 @@ __device__ __forceinline__ float quad_sum(float x) {
 }
 
 // Shared scratch for the 4-warp merge: per warp 16 rows x (128 O + m + l).
+template <int kD>
 struct DecodeSmem {
   float o[kDecWarps][16][kD];
   float m[kDecWarps][16];
@@ -97,9 +98,13 @@ struct DecodeSmem {
 };
 
 // kHi: the GQA group has more than 8 query heads, so fragment rows 8-15 are in use too.
-template <bool kHi>
+template <bool kHi, int kD>
 __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const DecodeParams p) {
-  __shared__ DecodeSmem sm;
+  __shared__ DecodeSmem<kD> sm;
+  constexpr int kKSteps = kD / 16;   // MMAs over head_dim for Q K^T
+  constexpr int kLoads = kD / 32;    // 16-byte K loads per thread and key
+  constexpr int kHalves = kD / 64;   // 64-column halves of V / O
+  constexpr int kNBlocks = kD / 8;   // 8-column output blocks of P V
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2;  // fragment row (query head within the chunk) / key within a block
@@ -115,11 +120,11 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
   const int k_end = min(p.len_k, k_begin + p.keys_per_split);
 
   // ---- Q fragments. MMA i (0..7) contracts over d = (i/2)*32 + 8t + 4(i&1) + {0,1 | 2,3}.
-  uint32_t qa[8][4];
+  uint32_t qa[kKSteps][4];
   {
     const __nv_bfloat16* qb = p.q + b * p.q_batch_stride;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < kKSteps; ++i) {
       const int d0 = (i >> 1) * 32 + 8 * t + 4 * (i & 1);
       uint2 lo = make_uint2(0u, 0u), hi = make_uint2(0u, 0u);
       if (g < nheads) lo = *reinterpret_cast<const uint2*>(qb + (head0 + g) * p.q_head_stride + d0);
@@ -135,21 +140,21 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
   const __nv_bfloat16* vbase = p.v + b * p.v_batch_stride + hkv * p.v_head_stride;
   const int last_key = p.len_k - 1;
 
-  float o[16][4];
+  float o[kNBlocks][4];
 #pragma unroll
-  for (int nb = 0; nb < 16; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f;
+  for (int nb = 0; nb < kNBlocks; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f;
   float m_lo = -INFINITY, m_hi = kHi ? -INFINITY : 0.f;  // running max (log2 domain) of rows g and g+8
   float l_lo = 0.f, l_hi = 0.f;              // this thread's share of the running sums
   const float c = p.scale_log2;
 
-  uint4 kbuf[2][4];
+  uint4 kbuf[2][kLoads];
   auto load_k = [&](int key0) {
 #pragma unroll
     for (int blk = 0; blk < 2; ++blk) {
       const int key = min(key0 + blk * 8 + g, last_key);
       const __nv_bfloat16* row = kbase + static_cast<int64_t>(key) * p.k_row_stride + 8 * t;
 #pragma unroll
-      for (int l4 = 0; l4 < 4; ++l4) kbuf[blk][l4] = ld_stream_16(row + l4 * 32);
+      for (int l4 = 0; l4 < kLoads; ++l4) kbuf[blk][l4] = ld_stream_16(row + l4 * 32);
     }
   };
 
@@ -157,11 +162,11 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
   if (key0 < k_end) load_k(key0);
   for (; key0 < k_end; key0 += kDecWarps * kKeysPerStep) {
     // ---- V rows of this step: keys 2t, 2t+1, 2t+8, 2t+9 at d = half*64 + 8g .. +7
-    uint4 vbuf[2][4];
+    uint4 vbuf[kHalves][4];
     {
       const int r0 = key0 + 2 * t;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      for (int half = 0; half < kHalves; ++half) {
         const __nv_bfloat16* col = vbase + half * 64 + 8 * g;
         vbuf[half][0] = ld_stream_16(col + static_cast<int64_t>(min(r0, last_key)) * p.v_row_stride);
         vbuf[half][1] = ld_stream_16(col + static_cast<int64_t>(min(r0 + 1, last_key)) * p.v_row_stride);
@@ -175,7 +180,7 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
     for (int blk = 0; blk < 2; ++blk) {
       s[blk][0] = s[blk][1] = s[blk][2] = s[blk][3] = 0.f;
 #pragma unroll
-      for (int l4 = 0; l4 < 4; ++l4) {
+      for (int l4 = 0; l4 < kLoads; ++l4) {
         const uint4 w = kbuf[blk][l4];
         mma_rows<kHi>(s[blk], qa[2 * l4], w.x, w.y);
         mma_rows<kHi>(s[blk], qa[2 * l4 + 1], w.z, w.w);
@@ -202,7 +207,7 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
       l_lo *= a_lo;
       l_hi *= a_hi;
 #pragma unroll
-      for (int nb = 0; nb < 16; ++nb) {
+      for (int nb = 0; nb < kNBlocks; ++nb) {
         o[nb][0] *= a_lo;
         o[nb][1] *= a_lo;
         if (kHi) {
@@ -230,7 +235,7 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
 
     // ---- O += P V. n-block (half, q) covers d = half*64 + 8*n + q for fragment column n.
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
+    for (int half = 0; half < kHalves; ++half) {
       const uint32_t x0[4] = {vbuf[half][0].x, vbuf[half][0].y, vbuf[half][0].z, vbuf[half][0].w};
       const uint32_t x1[4] = {vbuf[half][1].x, vbuf[half][1].y, vbuf[half][1].z, vbuf[half][1].w};
       const uint32_t x2[4] = {vbuf[half][2].x, vbuf[half][2].y, vbuf[half][2].z, vbuf[half][2].w};
@@ -257,7 +262,7 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
     sm.l[warp][g + 8] = l_hi;
   }
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
+  for (int half = 0; half < kHalves; ++half) {
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       const int nb = half * 8 + q;
@@ -272,8 +277,8 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
   }
   __syncthreads();
 
-  const int d = threadIdx.x;  // 128 threads <-> 128 output columns
-  for (int r = 0; r < nheads; ++r) {
+  const int d = threadIdx.x;  // thread <-> output column (threads beyond head_dim idle)
+  for (int r = 0; d < kD && r < nheads; ++r) {
     float mm = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, sm.m[w][r]);
@@ -302,6 +307,7 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
 
 // One warp per (batch, query head): merge the per-split partials.
 __global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeParams p, int rows) {
+  const int kD = p.head_dim;
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp_global >= rows) return;
@@ -325,7 +331,8 @@ __global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeParams 
 
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   const float inv = (sum > 0.f) ? 1.f / sum : 0.f;
-  for (int s = 0; s < p.num_splits; ++s) {
+  const bool active = lane * 4 < kD;
+  for (int s = 0; active && s < p.num_splits; ++s) {
     const float v = pl[s];
     const float w = (v == -INFINITY) ? 0.f : exp2f(v - mx) * inv;
     const float4 x = *reinterpret_cast<const float4*>(po + static_cast<int64_t>(s) * kD + lane * 4);
@@ -334,11 +341,23 @@ __global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeParams 
     acc.z += w * x.z;
     acc.w += w * x.w;
   }
-  __nv_bfloat16* dst = p.out + b * p.o_batch_stride + hq * p.o_head_stride + lane * 4;
-  uint2 packed = make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
-  *reinterpret_cast<uint2*>(dst) = packed;
+  if (active) {
+    __nv_bfloat16* dst = p.out + b * p.o_batch_stride + hq * p.o_head_stride + lane * 4;
+    uint2 packed = make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
+    *reinterpret_cast<uint2*>(dst) = packed;
+  }
   if (lane == 0)
     p.lse[warp_global] = (sum > 0.f) ? (mx + log2f(sum)) * 0.6931471805599453f : INFINITY;
+}
+
+void launch_decode_kernel(const DecodeParams& d, dim3 grid, cudaStream_t stream) {
+  if (d.head_dim == 64) {
+    if (d.group > 8) decode_splitkv_kernel<true, 64><<<grid, kDecThreads, 0, stream>>>(d);
+    else decode_splitkv_kernel<false, 64><<<grid, kDecThreads, 0, stream>>>(d);
+  } else {
+    if (d.group > 8) decode_splitkv_kernel<true, 128><<<grid, kDecThreads, 0, stream>>>(d);
+    else decode_splitkv_kernel<false, 128><<<grid, kDecThreads, 0, stream>>>(d);
+  }
 }
 
 int choose_splits(const sdpa_b200_params& p) {
@@ -362,7 +381,7 @@ size_t decode_workspace_bytes(const sdpa_b200_params& p, int* num_splits_out) {
   if (num_splits_out) *num_splits_out = splits;
   if (splits == 1) return 0;
   const size_t rows = static_cast<size_t>(p.batch) * p.heads_q * splits;
-  return rows * sizeof(float) * (kD + 1) + 256;
+  return rows * sizeof(float) * (p.head_dim + 1) + 256;
 }
 
 int launch_fwd_decode(const sdpa_b200_params& p, void* workspace, size_t workspace_bytes,
@@ -386,7 +405,7 @@ int launch_fwd_decode(const sdpa_b200_params& p, void* workspace, size_t workspa
   const size_t rows = static_cast<size_t>(p.batch) * p.heads_q * splits;
   float* ws = reinterpret_cast<float*>(static_cast<char*>(workspace) + kWorkspaceHeaderBytes);
   d.part_o = ws;
-  d.part_lse = ws + rows * kD;
+  d.part_lse = ws + rows * p.head_dim;
   d.q_batch_stride = p.q_batch_stride;
   d.q_head_stride = p.q_head_stride;
   d.k_batch_stride = p.k_batch_stride;
@@ -403,13 +422,13 @@ int launch_fwd_decode(const sdpa_b200_params& p, void* workspace, size_t workspa
   d.chunks = (d.group + 15) / 16;
   d.len_k = p.max_seqlen_k;
   d.num_splits = splits;
+  d.head_dim = p.head_dim;
   const int kps = (p.max_seqlen_k + splits - 1) / splits;
   d.keys_per_split = ((kps + 63) / 64) * 64;  // whole 4-warp steps
   d.scale_log2 = p.softmax_scale * 1.4426950408889634f;
 
   dim3 grid(splits, p.heads_kv * d.chunks, p.batch);
-  if (d.group > 8) decode_splitkv_kernel<true><<<grid, kDecThreads, 0, stream>>>(d);
-  else decode_splitkv_kernel<false><<<grid, kDecThreads, 0, stream>>>(d);
+  launch_decode_kernel(d, grid, stream);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("decode: launch failed: %s", cudaGetErrorString(err));
@@ -497,7 +516,7 @@ extern "C" SDPA_B200_API int sdpa_b200_decode_static(const sdpa_b200_params* p, 
   }
   const int splits = choose_splits(*p);
   const size_t rows = static_cast<size_t>(p->batch) * p->heads_q * splits;
-  const size_t need = rows * sizeof(float) * (kD + 1);
+  const size_t need = rows * sizeof(float) * (p->head_dim + 1);
   if (need > SDPA_B200_STATIC_SCRATCH_BYTES) {
     set_error("decode_static: batch %d x heads_q %d x %d splits needs %zu bytes of split partials, more than the "
               "%u bytes built into the library; lower num_splits or use sdpa_b200_fwd with a workspace",
@@ -515,7 +534,7 @@ extern "C" SDPA_B200_API int sdpa_b200_decode_static(const sdpa_b200_params* p, 
   d.out = static_cast<__nv_bfloat16*>(p->out);
   d.lse = p->lse;
   d.part_o = static_cast<float*>(scratch);
-  d.part_lse = d.part_o + rows * kD;
+  d.part_lse = d.part_o + rows * p->head_dim;
   d.q_batch_stride = p->q_batch_stride;
   d.q_head_stride = p->q_head_stride;
   d.k_batch_stride = p->k_batch_stride;
@@ -532,14 +551,14 @@ extern "C" SDPA_B200_API int sdpa_b200_decode_static(const sdpa_b200_params* p, 
   d.chunks = (d.group + 15) / 16;
   d.len_k = p->max_seqlen_k;
   d.num_splits = splits;
+  d.head_dim = p->head_dim;
   const int kps = (p->max_seqlen_k + splits - 1) / splits;
   d.keys_per_split = ((kps + 63) / 64) * 64;
   d.scale_log2 = p->softmax_scale * 1.4426950408889634f;
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   dim3 grid(splits, p->heads_kv * d.chunks, p->batch);
-  if (d.group > 8) decode_splitkv_kernel<true><<<grid, kDecThreads, 0, s>>>(d);
-  else decode_splitkv_kernel<false><<<grid, kDecThreads, 0, s>>>(d);
+  launch_decode_kernel(d, grid, s);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("decode_static: launch failed: %s", cudaGetErrorString(err));

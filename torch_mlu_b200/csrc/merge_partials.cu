@@ -16,12 +16,12 @@ namespace sdpa_b200 {
 namespace {
 
 struct MergeParams {
-  float* o_acc;               // [batch, heads, rows, 128] fp32, contiguous
+  float* o_acc;               // [batch, heads, rows, head_dim] fp32, contiguous
   float* lse_acc;             // [batch, heads, rows] fp32, contiguous
   const __nv_bfloat16* o_part;
   const float* lse_part;      // [batch, heads, rows] fp32, contiguous
   int64_t p_batch_stride, p_head_stride, p_row_stride;  // o_part element strides
-  int batch, heads, rows;
+  int batch, heads, rows, head_dim;
 };
 
 __global__ void __launch_bounds__(256) merge_partial_kernel(const MergeParams p) {
@@ -44,7 +44,9 @@ __global__ void __launch_bounds__(256) merge_partial_kernel(const MergeParams p)
     wa = ea / sum;
     wp = ep / sum;
   }
-  float4* acc = reinterpret_cast<float4*>(p.o_acc + row_id * 128) + lane;
+  if (lane == 0) p.lse_acc[row_id] = ln;
+  if (lane * 4 >= p.head_dim) return;
+  float4* acc = reinterpret_cast<float4*>(p.o_acc + row_id * p.head_dim) + lane;
   const uint2 pv = *reinterpret_cast<const uint2*>(p.o_part + b * p.p_batch_stride + h * p.p_head_stride +
                                                    static_cast<int64_t>(r) * p.p_row_stride + lane * 4);
   const __nv_bfloat162 p01 = *reinterpret_cast<const __nv_bfloat162*>(&pv.x);
@@ -56,7 +58,6 @@ __global__ void __launch_bounds__(256) merge_partial_kernel(const MergeParams p)
   a.z = (wa == 0.f ? 0.f : a.z * wa) + __bfloat162float(p23.x) * wp;
   a.w = (wa == 0.f ? 0.f : a.w * wa) + __bfloat162float(p23.y) * wp;
   *acc = a;
-  if (lane == 0) p.lse_acc[row_id] = ln;
 }
 
 }  // namespace
@@ -71,8 +72,8 @@ extern "C" SDPA_B200_API int sdpa_b200_merge_partial(float* o_acc, float* lse_ac
     set_error("merge_partial: NULL pointer");
     return SDPA_B200_INVALID_ARG;
   }
-  if (head_dim != 128) {
-    set_error("merge_partial: this build handles head_dim 128 only (got %d)", head_dim);
+  if (head_dim != 128 && head_dim != 64) {
+    set_error("merge_partial: this build handles head_dim 64 and 128 only (got %d)", head_dim);
     return SDPA_B200_UNSUPPORTED;
   }
   if (batch <= 0 || heads <= 0 || rows <= 0 || part_row_stride % 4 != 0 || part_head_stride % 4 != 0 ||
@@ -91,6 +92,7 @@ extern "C" SDPA_B200_API int sdpa_b200_merge_partial(float* o_acc, float* lse_ac
   m.batch = batch;
   m.heads = heads;
   m.rows = rows;
+  m.head_dim = head_dim;
   const int64_t total = static_cast<int64_t>(batch) * heads * rows;
   merge_partial_kernel<<<static_cast<unsigned>((total + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(m);
   cudaError_t err = cudaGetLastError();

@@ -130,7 +130,7 @@ int validate_common(const sdpa_b200_params* p) {
     return SDPA_B200_INVALID_ARG;
   }
   if (p->head_dim != 128 && p->head_dim != 64) {
-    set_error("this build has kernels for head_dim 128 (all paths) and 64 (prefill forward and backward) only (got %d)", p->head_dim);
+    set_error("this build has kernels for head_dim 128 and 64 only (got %d)", p->head_dim);
     return SDPA_B200_UNSUPPORTED;
   }
   if (!(p->softmax_scale > 0.f) || !(p->softmax_scale < 3.0e38f)) {
@@ -290,10 +290,6 @@ int sdpa_b200_fwd(const sdpa_b200_params* p, void* workspace, size_t workspace_b
   if (use_decode(p)) {
     if (p->cu_seqlens_q != nullptr) {
       set_error("the decode kernel takes dense tensors only");
-      return SDPA_B200_UNSUPPORTED;
-    }
-    if (p->head_dim != 128) {
-      set_error("the decode kernel is built for head_dim 128 only (got %d)", p->head_dim);
       return SDPA_B200_UNSUPPORTED;
     }
     return launch_fwd_decode(*p, workspace, workspace_bytes, s);
