@@ -51,7 +51,7 @@
 extern "C" {
 #endif
 
-#define SDPA_B200_VERSION 100
+#define SDPA_B200_VERSION 101
 
 #if defined(__GNUC__)
 #define SDPA_B200_API __attribute__((visibility("default")))
@@ -69,7 +69,8 @@ enum {
   SDPA_B200_NO_DEVICE = 5       /* not an sm_100 device / no CUDA driver */
 };
 
-enum { SDPA_B200_BF16 = 0 }; /* element type of q, k, v, out and gradients */
+enum { SDPA_B200_BF16 = 0, SDPA_B200_F16 = 1 }; /* element type of q, k, v, out and gradients (the reference
+                                                   takes the same two: sdp_utils.h:433-455) */
 
 /* kernel selection for the forward entry point */
 enum {
@@ -119,7 +120,7 @@ typedef struct sdpa_b200_params {
   float softmax_scale; /* > 0; the reference default is 1/sqrt(head_dim), sdp_utils.h:40-47 */
   float dropout_p;     /* must be 0 */
   int32_t is_causal;
-  int32_t dtype;      /* SDPA_B200_BF16 */
+  int32_t dtype;      /* SDPA_B200_BF16 or SDPA_B200_F16 */
   int32_t kernel;     /* SDPA_B200_KERNEL_* (forward only) */
   int32_t num_splits; /* decode: 0 = choose; otherwise the number of KV splits */
   int32_t reserved[4]; /* zero */
@@ -161,12 +162,13 @@ SDPA_B200_API int sdpa_b200_decode_static(const sdpa_b200_params* p, void* strea
  * step of ring / context-parallel prefill; no counterpart in the reference, whose attention is
  * single-device):  lse' = log(exp(lse_acc) + exp(lse_part)),
  *                  o_acc' = o_acc*exp(lse_acc - lse') + o_part*exp(lse_part - lse').
- * o_acc [batch, heads, rows, 128] fp32 and lse_acc / lse_part [batch, heads, rows] fp32 are
- * contiguous; o_part is bf16 with the given element strides (the `out` of sdpa_b200_fwd).
+ * o_acc [batch, heads, rows, head_dim] fp32 and lse_acc / lse_part [batch, heads, rows] fp32 are
+ * contiguous; o_part is bf16 or f16 (`dtype`) with the given element strides (the `out` of
+ * sdpa_b200_fwd).
  * Start an accumulator with lse_acc = -inf (o_acc may be uninitialised). */
 SDPA_B200_API int sdpa_b200_merge_partial(float* o_acc, float* lse_acc, const void* o_part, const float* lse_part,
                                           int32_t batch, int32_t heads, int32_t rows, int32_t head_dim,
-                                          int64_t part_batch_stride, int64_t part_head_stride,
+                                          int32_t dtype, int64_t part_batch_stride, int64_t part_head_stride,
                                           int64_t part_row_stride, void* stream);
 
 /* How many of this library's kernels the calling process has launched so far. */

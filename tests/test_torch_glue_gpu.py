@@ -95,3 +95,26 @@ def test_glue_rejects_what_the_reference_rejects(cuda_device, native_lib):
         torch.ops.b200_sdpa._scaled_dot_product_flash_attention(q, q, q, 0.5)
     with pytest.raises(RuntimeError, match="head_dim 128"):
         torch.ops.b200_sdpa._scaled_dot_product_flash_attention(q[..., :32], q[..., :32], q[..., :32])
+
+
+@pytest.mark.parametrize("amp_dtype", [torch.bfloat16, torch.float16])
+def test_autocast_casts_fp32_inputs_like_the_reference(cuda_device, native_lib, amp_dtype):
+    """aten/autocast_mode.cpp:147 puts _scaled_dot_product_flash_attention on the
+    lower_precision_fp list: fp32 inputs run in the autocast dtype, gradients come back in fp32."""
+    torch_glue.load()
+    dev = cuda_device
+    g = torch.Generator().manual_seed(11)
+    q, k, v, do = (torch.randn((1, 2, 256, 128), generator=g) for _ in range(4))
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    with torch.autocast("cuda", dtype=amp_dtype):
+        out = torch.ops.b200_sdpa._scaled_dot_product_flash_attention(qd, kd, vd, 0.0, True, False)[0]
+    assert out.dtype == amp_dtype
+    out.backward(do.to(dev).to(amp_dtype))
+    assert qd.grad.dtype == torch.float32
+    ql, kl, vl, dl = (t.to(amp_dtype) for t in (q, k, v, do))
+    o_ref, l_ref = orc.cpu_sdpa_forward(ql, kl, vl, causal=True)
+    dq, dk, dv = orc.cpu_sdpa_backward(dl, ql, kl, vl, o_ref, l_ref, causal=True)
+    orc.assert_close_bf16(out, o_ref, "out")
+    orc.assert_close_grad_bf16(qd.grad, dq, "dq")
+    orc.assert_close_grad_bf16(kd.grad, dk, "dk")
+    orc.assert_close_grad_bf16(vd.grad, dv, "dv")

@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(LIB_DIR, "libsdpa_b200.so")
 
 OK, INVALID_ARG, UNSUPPORTED, LAUNCH_FAILED, DEVICE_TIMEOUT, NO_DEVICE = range(6)
 KERNEL_AUTO, KERNEL_PREFILL, KERNEL_DECODE = 0, 1, 2
-DTYPE_BF16 = 0
+DTYPE_BF16, DTYPE_F16 = 0, 1
 
 # every symbol include/sdpa_b200.h declares
 EXPORTED_SYMBOLS = (
@@ -97,7 +97,7 @@ def load() -> ctypes.CDLL:
     lib.sdpa_b200_decode_static.argtypes = [POINTER(SdpaParams), c_void_p]
     lib.sdpa_b200_merge_partial.restype = c_int
     lib.sdpa_b200_merge_partial.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
-                                            c_int64, c_int64, c_int64, c_void_p]
+                                            c_int32, c_int64, c_int64, c_int64, c_void_p]
     lib.sdpa_b200_set_debug_buffer.restype = None
     lib.sdpa_b200_set_debug_buffer.argtypes = [c_void_p]
     _lib = lib

@@ -62,9 +62,9 @@ constexpr uint32_t kSmemAbort = kSmemTmemPtr + 4;
 struct BwdKernelParams {
   const float* lse2;   // padded [batch, heads_q, lq_pad]
   const float* delta;  // padded [batch, heads_q, lq_pad]
-  __nv_bfloat16* dq;
-  __nv_bfloat16* dk;
-  __nv_bfloat16* dv;
+  uint16_t* dq;  // bf16 or f16 bits
+  uint16_t* dk;
+  uint16_t* dv;
   const int32_t* cu_q;
   const int32_t* cu_k;
   uint32_t* status;
@@ -78,32 +78,33 @@ struct BwdKernelParams {
   int is_causal;
 };
 
-constexpr uint32_t kIdescSS = umma_idesc_bf16(kTile, kTile, false, false);
-template <int kD>
-constexpr uint32_t kIdescTS = umma_idesc_bf16(kTile, kD, false, true);
+template <bool kF16>
+constexpr uint32_t kIdescSS = umma_idesc_16(kTile, kTile, false, false, kF16);
+template <int kD, bool kF16>
+constexpr uint32_t kIdescTS = umma_idesc_16(kTile, kD, false, true, kF16);
 
 // T = X Y^T, contraction over head_dim, both operands K-major in shared memory
-template <int kD>
+template <int kD, bool kF16>
 __device__ __forceinline__ void issue_xyT(uint32_t t, uint32_t x_smem, uint32_t y_smem) {
   const uint32_t a_lo = umma_desc_lo_kmajor(x_smem);
   const uint32_t b_lo = umma_desc_lo_kmajor(y_smem);
-  umma_ss_lo<kIdescSS, false>(t, a_lo, b_lo);
+  umma_ss_lo<kIdescSS<kF16>, false>(t, a_lo, b_lo);
 #pragma unroll
   for (int ks = 1; ks < kD / 16; ++ks) {
     const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-    umma_ss_lo<kIdescSS, true>(t, a_lo + off, b_lo + off);
+    umma_ss_lo<kIdescSS<kF16>, true>(t, a_lo + off, b_lo + off);
   }
 }
 
 // ACC (+)= W Y over rows [64*half, 64*half + 64) of the Y tile. W (bf16, lane = stationary row)
 // for those rows starts at TMEM column `w` (32 columns).
-template <int kD>
+template <int kD, bool kF16>
 __device__ __forceinline__ void issue_wy_half(uint32_t acc, uint32_t w, uint32_t y_smem, int half, bool accumulate) {
   const uint32_t b_lo = umma_desc_lo_mnmajor(y_smem, kHalfBytes);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int ks = half * 4 + i;
-    umma_ts_lo<kIdescTS<kD>>(acc, w + i * 8, b_lo + ks * (2048 >> 4), (accumulate || ks > 0) ? 1u : 0u);
+    umma_ts_lo<kIdescTS<kD, kF16>>(acc, w + i * 8, b_lo + ks * (2048 >> 4), (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 
@@ -113,7 +114,7 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src,
                : "memory");
 }
 
-template <int kMode, int kD>
+template <int kMode, int kD, bool kF16>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -277,13 +278,13 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       bool ok = mbar_wait(bar + kBarXFull, 0, abort_flag) && y_wait(0);
       if (ok) {
         tc_fence_after_sync();
-        issue_xyT<kD>(s_buf(0), x1, y_slot(0));
+        issue_xyT<kD, kF16>(s_buf(0), x1, y_slot(0));
         umma_commit(s_bar(0));
       }
       ok = ok && y_wait(1);
       if (ok) {
         tc_fence_after_sync();
-        issue_xyT<kD>(d_buf(0), x2, y_slot(1));
+        issue_xyT<kD, kF16>(d_buf(0), x2, y_slot(1));
         umma_commit(bar + kBarDFull);
         if (kMode == kModeDQ) y_free(1);  // V(0) is only read by dP(0)
       }
@@ -291,7 +292,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ok = y_wait(2);
         if (ok) {
           tc_fence_after_sync();
-          issue_xyT<kD>(s_buf(1), x1, y_slot(2));
+          issue_xyT<kD, kF16>(s_buf(1), x1, y_slot(2));
           umma_commit(s_bar(1));
         }
       }
@@ -307,13 +308,13 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             ok = y_wait_k(2);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_xyT<kD>(d_buf(i), x1, y_slot_k(2));  // S(i+1) into the buffer dP(i) has just left
+            issue_xyT<kD, kF16>(d_buf(i), x1, y_slot_k(2));  // S(i+1) into the buffer dP(i) has just left
             umma_commit(s_bar(i + 1));
           } else {
             ok = y_wait_k(3);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_xyT<kD>(t2, x2, y_slot_k(3));  // dP(i+1)
+            issue_xyT<kD, kF16>(t2, x2, y_slot_k(3));  // dP(i+1)
             umma_commit(bar + kBarDFull);
             y_free_k(3);  // V(i+1) is only read by dP(i+1)
           }
@@ -324,10 +325,10 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           if (kMode == kModeDKDV) {
-            issue_wy_half<kD>(acc1, sbuf + half * 64, y2, half, i > 0);       // dV += P^T dO
-            issue_wy_half<kD>(acc2, sbuf + half * 64 + 32, y1, half, i > 0);  // dK += dS^T Q
+            issue_wy_half<kD, kF16>(acc1, sbuf + half * 64, y2, half, i > 0);       // dV += P^T dO
+            issue_wy_half<kD, kF16>(acc2, sbuf + half * 64 + 32, y1, half, i > 0);  // dK += dS^T Q
           } else {
-            issue_wy_half<kD>(acc1, sbuf + half * 64 + 32, y1, half, i > 0);  // dQ += dS K
+            issue_wy_half<kD, kF16>(acc1, sbuf + half * 64 + 32, y1, half, i > 0);  // dQ += dS K
           }
         }
         y_free_k(0);
@@ -338,14 +339,14 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             ok = y_wait_k(3);
             if (!ok) break;
             tc_fence_after_sync();
-            issue_xyT<kD>(sbuf, x2, y_slot_k(3));  // dP(i+1), behind the MMAs reading P(i), dS(i)
+            issue_xyT<kD, kF16>(sbuf, x2, y_slot_k(3));  // dP(i+1), behind the MMAs reading P(i), dS(i)
             umma_commit(bar + kBarDFull);
           }
         } else if (i + 2 < n_items) {
           ok = y_wait_k(4);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_xyT<kD>(sbuf, x1, y_slot_k(4));  // S(i+2), behind the MMAs reading dS(i)
+          issue_xyT<kD, kF16>(sbuf, x1, y_slot_k(4));  // S(i+2), behind the MMAs reading dS(i)
           umma_commit(s_bar(i + 2));
         }
         ring_slot += 2;
@@ -413,7 +414,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (kMode == kModeDKDV) {
           uint32_t pw[32];
 #pragma unroll
-          for (int j2 = 0; j2 < 32; ++j2) pw[j2] = pack_bf16x2(pr[2 * j2], pr[2 * j2 + 1]);
+          for (int j2 = 0; j2 < 32; ++j2) pw[j2] = pack_16x2<kF16>(pr[2 * j2], pr[2 * j2 + 1]);
           tmem_st_x16(sbuf, pw);
           tmem_st_x16(sbuf + 16, pw + 16);
         }
@@ -434,7 +435,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int j2 = 0; j2 < 32; ++j2) {
           const float dl0 = (kMode == kModeDKDV) ? vec_delta[2 * j2] : my_delta;
           const float dl1 = (kMode == kModeDKDV) ? vec_delta[2 * j2 + 1] : my_delta;
-          dw[j2] = pack_bf16x2(pr[2 * j2] * (__uint_as_float(d[2 * j2]) - dl0),
+          dw[j2] = pack_16x2<kF16>(pr[2 * j2] * (__uint_as_float(d[2 * j2]) - dl0),
                                pr[2 * j2 + 1] * (__uint_as_float(d[2 * j2 + 1]) - dl1));
         }
         tmem_st_x16(sbuf + 32, dw);
@@ -453,7 +454,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int n_out = (kMode == kModeDKDV) ? 2 : 1;
 #pragma unroll
       for (int which = 0; which < n_out; ++which) {
-        __nv_bfloat16* dst;
+        uint16_t* dst;
         float mul;
         uint32_t acc;
         if (kMode == kModeDQ) {
@@ -491,10 +492,10 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 w;
-              w.x = pack_bf16x2(__uint_as_float(v[8 * j + 0]) * mul, __uint_as_float(v[8 * j + 1]) * mul);
-              w.y = pack_bf16x2(__uint_as_float(v[8 * j + 2]) * mul, __uint_as_float(v[8 * j + 3]) * mul);
-              w.z = pack_bf16x2(__uint_as_float(v[8 * j + 4]) * mul, __uint_as_float(v[8 * j + 5]) * mul);
-              w.w = pack_bf16x2(__uint_as_float(v[8 * j + 6]) * mul, __uint_as_float(v[8 * j + 7]) * mul);
+              w.x = pack_16x2<kF16>(__uint_as_float(v[8 * j + 0]) * mul, __uint_as_float(v[8 * j + 1]) * mul);
+              w.y = pack_16x2<kF16>(__uint_as_float(v[8 * j + 2]) * mul, __uint_as_float(v[8 * j + 3]) * mul);
+              w.z = pack_16x2<kF16>(__uint_as_float(v[8 * j + 4]) * mul, __uint_as_float(v[8 * j + 5]) * mul);
+              w.w = pack_16x2<kF16>(__uint_as_float(v[8 * j + 6]) * mul, __uint_as_float(v[8 * j + 7]) * mul);
               o4[j] = w;
             }
           }
@@ -515,8 +516,8 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // delta[row] = sum_d dO[row,d] * O[row,d]; lse2[row] = lse[row] * log2(e). One warp per row,
 // rows padded to lq_pad per (batch, head): padding rows get lse2 = +inf, delta = 0.
 struct PreParams {
-  const __nv_bfloat16* out;
-  const __nv_bfloat16* dout;
+  const uint16_t* out;
+  const uint16_t* dout;
   const float* lse;
   float* lse2;
   float* delta;
@@ -526,6 +527,7 @@ struct PreParams {
   int seqlen_q, total_q, heads_q, lq_pad, head_dim;
 };
 
+template <bool kF16>
 __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * 8 + warp;  // row within the padded sequence
@@ -544,8 +546,8 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreParams p) 
     }
     return;
   }
-  const __nv_bfloat16* o;
-  const __nv_bfloat16* dout;
+  const uint16_t* o;
+  const uint16_t* dout;
   float lse;
   if (p.cu_q != nullptr) {
     o = p.out + static_cast<int64_t>(q_off + row) * p.o_row_stride + h * p.o_head_stride;
@@ -561,18 +563,44 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreParams p) 
     ov = *reinterpret_cast<const uint2*>(o + lane * 4);
     dv = *reinterpret_cast<const uint2*>(dout + lane * 4);
   }
-  const __nv_bfloat162 o0 = *reinterpret_cast<const __nv_bfloat162*>(&ov.x);
-  const __nv_bfloat162 o1 = *reinterpret_cast<const __nv_bfloat162*>(&ov.y);
-  const __nv_bfloat162 d0 = *reinterpret_cast<const __nv_bfloat162*>(&dv.x);
-  const __nv_bfloat162 d1 = *reinterpret_cast<const __nv_bfloat162*>(&dv.y);
-  float acc = __bfloat162float(o0.x) * __bfloat162float(d0.x) + __bfloat162float(o0.y) * __bfloat162float(d0.y) +
-              __bfloat162float(o1.x) * __bfloat162float(d1.x) + __bfloat162float(o1.y) * __bfloat162float(d1.y);
+  const float2 o0 = unpack_16x2<kF16>(ov.x), o1 = unpack_16x2<kF16>(ov.y);
+  const float2 d0 = unpack_16x2<kF16>(dv.x), d1 = unpack_16x2<kF16>(dv.y);
+  float acc = o0.x * d0.x + o0.y * d0.y + o1.x * d1.x + o1.y * d1.y;
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (lane == 0) {
     p.lse2[dst] = lse * 1.4426950408889634f;  // +inf stays +inf
     p.delta[dst] = acc;
   }
+}
+
+using TileKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                            const BwdKernelParams);
+
+template <int kMode>
+TileKernel pick_tile_kernel(int head_dim, bool f16) {
+  if (head_dim == 64) return f16 ? bwd_tile_kernel<kMode, 64, true> : bwd_tile_kernel<kMode, 64, false>;
+  return f16 ? bwd_tile_kernel<kMode, 128, true> : bwd_tile_kernel<kMode, 128, false>;
+}
+
+int launch_tile_kernel(int mode, int head_dim, bool f16, int grid, cudaStream_t stream, const CUtensorMap& tm_q,
+                       const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_do,
+                       const BwdKernelParams& kp) {
+  TileKernel kernel = mode == kModeDKDV ? pick_tile_kernel<kModeDKDV>(head_dim, f16) : pick_tile_kernel<kModeDQ>(head_dim, f16);
+  const uint32_t smem = smem_bytes_for(mode);
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (err != cudaSuccess) {
+    set_error("backward: cudaFuncSetAttribute(%u bytes smem): %s", smem, cudaGetErrorString(err));
+    return SDPA_B200_LAUNCH_FAILED;
+  }
+  kernel<<<dim3(grid), kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_do, kp);
+  err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("backward %s: launch failed: %s", mode == kModeDKDV ? "dK/dV" : "dQ", cudaGetErrorString(err));
+    return SDPA_B200_LAUNCH_FAILED;
+  }
+  count_launch();
+  return SDPA_B200_OK;
 }
 
 int lq_padded(const sdpa_b200_params& p) { return ((p.max_seqlen_q + kTile - 1) / kTile) * kTile; }
@@ -585,6 +613,7 @@ size_t bwd_workspace_bytes(const sdpa_b200_params& p) {
 
 int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
   (void)workspace_bytes;
+  const bool f16 = p.dtype == SDPA_B200_F16;
   const bool varlen = p.cu_seqlens_q != nullptr;
   const int lq_pad = lq_padded(p);
   const size_t vec_elems = static_cast<size_t>(p.batch) * p.heads_q * lq_pad;
@@ -592,8 +621,8 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   float* delta = lse2 + vec_elems;
 
   PreParams pre;
-  pre.out = static_cast<const __nv_bfloat16*>(p.out);
-  pre.dout = static_cast<const __nv_bfloat16*>(p.dout);
+  pre.out = static_cast<const uint16_t*>(p.out);
+  pre.dout = static_cast<const uint16_t*>(p.dout);
   pre.lse = p.lse;
   pre.lse2 = lse2;
   pre.delta = delta;
@@ -609,7 +638,10 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   pre.heads_q = p.heads_q;
   pre.lq_pad = lq_pad;
   pre.head_dim = p.head_dim;
-  bwd_preprocess_kernel<<<dim3(lq_pad / 8, p.heads_q, p.batch), 256, 0, stream>>>(pre);
+  if (f16)
+    bwd_preprocess_kernel<true><<<dim3(lq_pad / 8, p.heads_q, p.batch), 256, 0, stream>>>(pre);
+  else
+    bwd_preprocess_kernel<false><<<dim3(lq_pad / 8, p.heads_q, p.batch), 256, 0, stream>>>(pre);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("backward preprocess: launch failed: %s", cudaGetErrorString(err));
@@ -622,25 +654,25 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   const int64_t rows_k = varlen ? p.total_k : p.max_seqlen_k;
   const int64_t nb = varlen ? 1 : p.batch;
   int st;
-  if ((st = make_tensor_map_bf16(&tm_q, p.q, p.head_dim, rows_q, p.heads_q, nb, p.q_row_stride, p.q_head_stride,
+  if ((st = make_tensor_map_16(f16, &tm_q, p.q, p.head_dim, rows_q, p.heads_q, nb, p.q_row_stride, p.q_head_stride,
                                  p.q_batch_stride, kTile)) != SDPA_B200_OK)
     return st;
-  if ((st = make_tensor_map_bf16(&tm_k, p.k, p.head_dim, rows_k, p.heads_kv, nb, p.k_row_stride, p.k_head_stride,
+  if ((st = make_tensor_map_16(f16, &tm_k, p.k, p.head_dim, rows_k, p.heads_kv, nb, p.k_row_stride, p.k_head_stride,
                                  p.k_batch_stride, kTile)) != SDPA_B200_OK)
     return st;
-  if ((st = make_tensor_map_bf16(&tm_v, p.v, p.head_dim, rows_k, p.heads_kv, nb, p.v_row_stride, p.v_head_stride,
+  if ((st = make_tensor_map_16(f16, &tm_v, p.v, p.head_dim, rows_k, p.heads_kv, nb, p.v_row_stride, p.v_head_stride,
                                  p.v_batch_stride, kTile)) != SDPA_B200_OK)
     return st;
-  if ((st = make_tensor_map_bf16(&tm_do, p.dout, p.head_dim, rows_q, p.heads_q, nb, p.do_row_stride,
+  if ((st = make_tensor_map_16(f16, &tm_do, p.dout, p.head_dim, rows_q, p.heads_q, nb, p.do_row_stride,
                                  p.do_head_stride, p.do_batch_stride, kTile)) != SDPA_B200_OK)
     return st;
 
   BwdKernelParams kp;
   kp.lse2 = lse2;
   kp.delta = delta;
-  kp.dq = static_cast<__nv_bfloat16*>(p.dq);
-  kp.dk = static_cast<__nv_bfloat16*>(p.dk);
-  kp.dv = static_cast<__nv_bfloat16*>(p.dv);
+  kp.dq = static_cast<uint16_t*>(p.dq);
+  kp.dk = static_cast<uint16_t*>(p.dk);
+  kp.dv = static_cast<uint16_t*>(p.dv);
   kp.cu_q = p.cu_seqlens_q;
   kp.cu_k = p.cu_seqlens_k;
   kp.status = static_cast<uint32_t*>(workspace);
@@ -663,26 +695,6 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   kp.is_causal = p.is_causal;
 
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e1 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDKDV, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          smem_bytes_for(kModeDKDV));
-    cudaError_t e2 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDQ, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          smem_bytes_for(kModeDQ));
-    if (e1 == cudaSuccess)
-      e1 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDKDV, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                smem_bytes_for(kModeDKDV));
-    if (e2 == cudaSuccess)
-      e2 = cudaFuncSetAttribute(bwd_tile_kernel<kModeDQ, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                smem_bytes_for(kModeDQ));
-    if (e1 != cudaSuccess || e2 != cudaSuccess) {
-      set_error("backward: cudaFuncSetAttribute(%u / %u bytes smem) failed", smem_bytes_for(kModeDKDV),
-                smem_bytes_for(kModeDQ));
-      return SDPA_B200_LAUNCH_FAILED;
-    }
-    attr_done = true;
-  }
-
   // heads per group: streamed bytes per head (q + dO of the group, or k + v) within ~48 MB of L2
   auto set_order = [&](int heads_x, int rows_streamed, int streams_per_head) {
     kp.heads_x = heads_x;
@@ -697,29 +709,12 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   };
   kp.num_row_blocks = (p.max_seqlen_k + kTile - 1) / kTile;
   const int grid_dkdv = set_order(p.heads_kv, p.max_seqlen_q, kp.kv_group);
-  if (p.head_dim == 64)
-    bwd_tile_kernel<kModeDKDV, 64><<<dim3(grid_dkdv), kThreads, smem_bytes_for(kModeDKDV), stream>>>(tm_q, tm_k, tm_v, tm_do, kp);
-  else
-    bwd_tile_kernel<kModeDKDV, 128><<<dim3(grid_dkdv), kThreads, smem_bytes_for(kModeDKDV), stream>>>(tm_q, tm_k, tm_v, tm_do, kp);
-  err = cudaGetLastError();
-  if (err != cudaSuccess) {
-    set_error("backward dK/dV: launch failed: %s", cudaGetErrorString(err));
-    return SDPA_B200_LAUNCH_FAILED;
-  }
-  count_launch();
+  if ((st = launch_tile_kernel(kModeDKDV, p.head_dim, f16, grid_dkdv, stream, tm_q, tm_k, tm_v, tm_do, kp)) !=
+      SDPA_B200_OK)
+    return st;
   kp.num_row_blocks = (p.max_seqlen_q + kTile - 1) / kTile;
   const int grid_dq = set_order(p.heads_q, p.max_seqlen_k, 1);
-  if (p.head_dim == 64)
-    bwd_tile_kernel<kModeDQ, 64><<<dim3(grid_dq), kThreads, smem_bytes_for(kModeDQ), stream>>>(tm_q, tm_k, tm_v, tm_do, kp);
-  else
-    bwd_tile_kernel<kModeDQ, 128><<<dim3(grid_dq), kThreads, smem_bytes_for(kModeDQ), stream>>>(tm_q, tm_k, tm_v, tm_do, kp);
-  err = cudaGetLastError();
-  if (err != cudaSuccess) {
-    set_error("backward dQ: launch failed: %s", cudaGetErrorString(err));
-    return SDPA_B200_LAUNCH_FAILED;
-  }
-  count_launch();
-  return SDPA_B200_OK;
+  return launch_tile_kernel(kModeDQ, p.head_dim, f16, grid_dq, stream, tm_q, tm_k, tm_v, tm_do, kp);
 }
 
 }  // namespace sdpa_b200

@@ -27,10 +27,10 @@ constexpr int kMaxD = 128;  // head_dim 64 and 128 are built
 constexpr int kMaxSplits = 128;
 
 struct DecodeParams {
-  const __nv_bfloat16* q;
-  const __nv_bfloat16* k;
-  const __nv_bfloat16* v;
-  __nv_bfloat16* out;
+  const uint16_t* q;  // bf16 or f16 bits (f16 != 0)
+  const uint16_t* k;
+  const uint16_t* v;
+  uint16_t* out;
   float* lse;
   float* part_o;    // [batch, heads_q, splits, head_dim] fp32, normalised per split
   float* part_lse;  // [batch, heads_q, splits] fp32, log2 domain
@@ -40,6 +40,7 @@ struct DecodeParams {
   int64_t o_batch_stride, o_head_stride;
   int heads_q, heads_kv, group, chunks, len_k, num_splits, keys_per_split, head_dim;
   float scale_log2;
+  int f16;
 };
 
 __device__ __forceinline__ uint4 ld_stream_16(const void* p) {
@@ -50,31 +51,47 @@ __device__ __forceinline__ uint4 ld_stream_16(const void* p) {
   return r;
 }
 
+template <bool kF16>
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                           uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
-      "{%8, %9}, {%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  if constexpr (kF16)
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+        "{%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  else
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+        "{%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 // Same MMA when only fragment rows 0-7 carry query heads: rows 8-15 of A are zero, so their
 // accumulators are constants and need no live registers.
+template <bool kF16>
 __device__ __forceinline__ void mma_16816_lo(float& c0, float& c1, uint32_t a0, uint32_t a2,
                                              uint32_t b0, uint32_t b1) {
   float d2, d3;
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %5}, "
-      "{%7, %8}, {%0, %1, %9, %9};"
-      : "+f"(c0), "+f"(c1), "=f"(d2), "=f"(d3)
-      : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.f));
+  if constexpr (kF16)
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %5}, "
+        "{%7, %8}, {%0, %1, %9, %9};"
+        : "+f"(c0), "+f"(c1), "=f"(d2), "=f"(d3)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.f));
+  else
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %5}, "
+        "{%7, %8}, {%0, %1, %9, %9};"
+        : "+f"(c0), "+f"(c1), "=f"(d2), "=f"(d3)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.f));
 }
 
-template <bool kHi>
+template <bool kHi, bool kF16>
 __device__ __forceinline__ void mma_rows(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  if constexpr (kHi) mma_16816(c, a[0], a[1], a[2], a[3], b0, b1);
-  else mma_16816_lo(c[0], c[1], a[0], a[2], b0, b1);
+  if constexpr (kHi) mma_16816<kF16>(c, a[0], a[1], a[2], a[3], b0, b1);
+  else mma_16816_lo<kF16>(c[0], c[1], a[0], a[2], b0, b1);
 }
 
 __device__ __forceinline__ float quad_max(float x) {
@@ -98,7 +115,7 @@ struct DecodeSmem {
 };
 
 // kHi: the GQA group has more than 8 query heads, so fragment rows 8-15 are in use too.
-template <bool kHi, int kD>
+template <bool kHi, int kD, bool kF16>
 __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const DecodeParams p) {
   __shared__ DecodeSmem<kD> sm;
   constexpr int kKSteps = kD / 16;   // MMAs over head_dim for Q K^T
@@ -122,7 +139,7 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
   // ---- Q fragments. MMA i (0..7) contracts over d = (i/2)*32 + 8t + 4(i&1) + {0,1 | 2,3}.
   uint32_t qa[kKSteps][4];
   {
-    const __nv_bfloat16* qb = p.q + b * p.q_batch_stride;
+    const uint16_t* qb = p.q + b * p.q_batch_stride;
 #pragma unroll
     for (int i = 0; i < kKSteps; ++i) {
       const int d0 = (i >> 1) * 32 + 8 * t + 4 * (i & 1);
@@ -136,8 +153,8 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
     }
   }
 
-  const __nv_bfloat16* kbase = p.k + b * p.k_batch_stride + hkv * p.k_head_stride;
-  const __nv_bfloat16* vbase = p.v + b * p.v_batch_stride + hkv * p.v_head_stride;
+  const uint16_t* kbase = p.k + b * p.k_batch_stride + hkv * p.k_head_stride;
+  const uint16_t* vbase = p.v + b * p.v_batch_stride + hkv * p.v_head_stride;
   const int last_key = p.len_k - 1;
 
   float o[kNBlocks][4];
@@ -152,7 +169,7 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
 #pragma unroll
     for (int blk = 0; blk < 2; ++blk) {
       const int key = min(key0 + blk * 8 + g, last_key);
-      const __nv_bfloat16* row = kbase + static_cast<int64_t>(key) * p.k_row_stride + 8 * t;
+      const uint16_t* row = kbase + static_cast<int64_t>(key) * p.k_row_stride + 8 * t;
 #pragma unroll
       for (int l4 = 0; l4 < kLoads; ++l4) kbuf[blk][l4] = ld_stream_16(row + l4 * 32);
     }
@@ -167,7 +184,7 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
       const int r0 = key0 + 2 * t;
 #pragma unroll
       for (int half = 0; half < kHalves; ++half) {
-        const __nv_bfloat16* col = vbase + half * 64 + 8 * g;
+        const uint16_t* col = vbase + half * 64 + 8 * g;
         vbuf[half][0] = ld_stream_16(col + static_cast<int64_t>(min(r0, last_key)) * p.v_row_stride);
         vbuf[half][1] = ld_stream_16(col + static_cast<int64_t>(min(r0 + 1, last_key)) * p.v_row_stride);
         vbuf[half][2] = ld_stream_16(col + static_cast<int64_t>(min(r0 + 8, last_key)) * p.v_row_stride);
@@ -182,8 +199,8 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
 #pragma unroll
       for (int l4 = 0; l4 < kLoads; ++l4) {
         const uint4 w = kbuf[blk][l4];
-        mma_rows<kHi>(s[blk], qa[2 * l4], w.x, w.y);
-        mma_rows<kHi>(s[blk], qa[2 * l4 + 1], w.z, w.w);
+        mma_rows<kHi, kF16>(s[blk], qa[2 * l4], w.x, w.y);
+        mma_rows<kHi, kF16>(s[blk], qa[2 * l4 + 1], w.z, w.w);
       }
     }
     const int next = key0 + kDecWarps * kKeysPerStep;
@@ -228,10 +245,10 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
       l_lo += pr[blk][0] + pr[blk][1];
       l_hi += pr[blk][2] + pr[blk][3];
     }
-    const uint32_t pa0 = pack_bf16x2(pr[0][0], pr[0][1]);  // row g,   keys 2t, 2t+1
-    const uint32_t pa1 = pack_bf16x2(pr[0][2], pr[0][3]);  // row g+8
-    const uint32_t pa2 = pack_bf16x2(pr[1][0], pr[1][1]);  // row g,   keys 8+2t, 9+2t
-    const uint32_t pa3 = pack_bf16x2(pr[1][2], pr[1][3]);  // row g+8
+    const uint32_t pa0 = pack_16x2<kF16>(pr[0][0], pr[0][1]);  // row g,   keys 2t, 2t+1
+    const uint32_t pa1 = pack_16x2<kF16>(pr[0][2], pr[0][3]);  // row g+8
+    const uint32_t pa2 = pack_16x2<kF16>(pr[1][0], pr[1][1]);  // row g,   keys 8+2t, 9+2t
+    const uint32_t pa3 = pack_16x2<kF16>(pr[1][2], pr[1][3]);  // row g+8
 
     // ---- O += P V. n-block (half, q) covers d = half*64 + 8*n + q for fragment column n.
 #pragma unroll
@@ -246,7 +263,7 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
         const uint32_t b0 = __byte_perm(x0[q >> 1], x1[q >> 1], sel);
         const uint32_t b1 = __byte_perm(x2[q >> 1], x3[q >> 1], sel);
         const uint32_t pa[4] = {pa0, pa1, pa2, pa3};
-        mma_rows<kHi>(o[half * 8 + q], pa, b0, b1);
+        mma_rows<kHi, kF16>(o[half * 8 + q], pa, b0, b1);
       }
     }
   }
@@ -294,7 +311,7 @@ __global__ void __launch_bounds__(kDecThreads, 3) decode_splitkv_kernel(const De
     const float inv = (ll > 0.f) ? 1.f / ll : 0.f;
     const float lse2 = (ll > 0.f) ? mm + log2f(ll) : -INFINITY;
     if (p.num_splits == 1) {
-      p.out[b * p.o_batch_stride + hq * p.o_head_stride + d] = __float2bfloat16_rn(acc * inv);
+      p.out[b * p.o_batch_stride + hq * p.o_head_stride + d] = to_16<kF16>(acc * inv);
       if (d == 0)
         p.lse[static_cast<int64_t>(b) * p.heads_q + hq] = (ll > 0.f) ? lse2 * 0.6931471805599453f : INFINITY;
     } else {
@@ -342,21 +359,28 @@ __global__ void __launch_bounds__(128) decode_combine_kernel(const DecodeParams 
     acc.w += w * x.w;
   }
   if (active) {
-    __nv_bfloat16* dst = p.out + b * p.o_batch_stride + hq * p.o_head_stride + lane * 4;
-    uint2 packed = make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
+    uint16_t* dst = p.out + b * p.o_batch_stride + hq * p.o_head_stride + lane * 4;
+    const uint2 packed = p.f16 ? make_uint2(pack_f16x2(acc.x, acc.y), pack_f16x2(acc.z, acc.w))
+                               : make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
     *reinterpret_cast<uint2*>(dst) = packed;
   }
   if (lane == 0)
     p.lse[warp_global] = (sum > 0.f) ? (mx + log2f(sum)) * 0.6931471805599453f : INFINITY;
 }
 
+template <int kD, bool kF16>
+void launch_decode_kernel_t(const DecodeParams& d, dim3 grid, cudaStream_t stream) {
+  if (d.group > 8) decode_splitkv_kernel<true, kD, kF16><<<grid, kDecThreads, 0, stream>>>(d);
+  else decode_splitkv_kernel<false, kD, kF16><<<grid, kDecThreads, 0, stream>>>(d);
+}
+
 void launch_decode_kernel(const DecodeParams& d, dim3 grid, cudaStream_t stream) {
   if (d.head_dim == 64) {
-    if (d.group > 8) decode_splitkv_kernel<true, 64><<<grid, kDecThreads, 0, stream>>>(d);
-    else decode_splitkv_kernel<false, 64><<<grid, kDecThreads, 0, stream>>>(d);
+    if (d.f16) launch_decode_kernel_t<64, true>(d, grid, stream);
+    else launch_decode_kernel_t<64, false>(d, grid, stream);
   } else {
-    if (d.group > 8) decode_splitkv_kernel<true, 128><<<grid, kDecThreads, 0, stream>>>(d);
-    else decode_splitkv_kernel<false, 128><<<grid, kDecThreads, 0, stream>>>(d);
+    if (d.f16) launch_decode_kernel_t<128, true>(d, grid, stream);
+    else launch_decode_kernel_t<128, false>(d, grid, stream);
   }
 }
 
@@ -397,10 +421,10 @@ int launch_fwd_decode(const sdpa_b200_params& p, void* workspace, size_t workspa
     return SDPA_B200_INVALID_ARG;
   }
   DecodeParams d;
-  d.q = static_cast<const __nv_bfloat16*>(p.q);
-  d.k = static_cast<const __nv_bfloat16*>(p.k);
-  d.v = static_cast<const __nv_bfloat16*>(p.v);
-  d.out = static_cast<__nv_bfloat16*>(p.out);
+  d.q = static_cast<const uint16_t*>(p.q);
+  d.k = static_cast<const uint16_t*>(p.k);
+  d.v = static_cast<const uint16_t*>(p.v);
+  d.out = static_cast<uint16_t*>(p.out);
   d.lse = p.lse;
   const size_t rows = static_cast<size_t>(p.batch) * p.heads_q * splits;
   float* ws = reinterpret_cast<float*>(static_cast<char*>(workspace) + kWorkspaceHeaderBytes);
@@ -426,6 +450,7 @@ int launch_fwd_decode(const sdpa_b200_params& p, void* workspace, size_t workspa
   const int kps = (p.max_seqlen_k + splits - 1) / splits;
   d.keys_per_split = ((kps + 63) / 64) * 64;  // whole 4-warp steps
   d.scale_log2 = p.softmax_scale * 1.4426950408889634f;
+  d.f16 = p.dtype == SDPA_B200_F16;
 
   dim3 grid(splits, p.heads_kv * d.chunks, p.batch);
   launch_decode_kernel(d, grid, stream);
@@ -528,10 +553,10 @@ extern "C" SDPA_B200_API int sdpa_b200_decode_static(const sdpa_b200_params* p, 
   if (st != SDPA_B200_OK) return st;
 
   DecodeParams d;
-  d.q = static_cast<const __nv_bfloat16*>(p->q);
-  d.k = static_cast<const __nv_bfloat16*>(p->k);
-  d.v = static_cast<const __nv_bfloat16*>(p->v);
-  d.out = static_cast<__nv_bfloat16*>(p->out);
+  d.q = static_cast<const uint16_t*>(p->q);
+  d.k = static_cast<const uint16_t*>(p->k);
+  d.v = static_cast<const uint16_t*>(p->v);
+  d.out = static_cast<uint16_t*>(p->out);
   d.lse = p->lse;
   d.part_o = static_cast<float*>(scratch);
   d.part_lse = d.part_o + rows * p->head_dim;
@@ -555,6 +580,7 @@ extern "C" SDPA_B200_API int sdpa_b200_decode_static(const sdpa_b200_params* p, 
   const int kps = (p->max_seqlen_k + splits - 1) / splits;
   d.keys_per_split = ((kps + 63) / 64) * 64;
   d.scale_log2 = p->softmax_scale * 1.4426950408889634f;
+  d.f16 = p->dtype == SDPA_B200_F16;
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   dim3 grid(splits, p->heads_kv * d.chunks, p->batch);

@@ -3,7 +3,7 @@
 // Replaces the device work behind mha_varlen_fwd -> cnnlFlashAttentionForward_v2
 // (torch_mlu/csrc/aten/operators/cnnl/internal/FlashAttention_internal.cpp:231-258):
 //   O = softmax(scale * Q K^T + causal mask) V,  LSE = logsumexp(scale * Q K^T)
-// for bf16 Q/K/V with head_dim 128, dense or packed-varlen, GQA by head broadcast.
+// for bf16 or f16 Q/K/V with head_dim 64 or 128, dense or packed-varlen, GQA by head broadcast.
 //
 // One CTA owns 256 query rows of one (batch, head): two 128-row Q tiles. Roles:
 //   warps 0-3  softmax warpgroup for Q tile 0  (thread = one query row = one TMEM lane)
@@ -12,7 +12,7 @@
 //   warp  9    MMA issuer: S_t = Q_t K^T and O_t += P_t V on tcgen05, accumulators in TMEM
 //   warps 10-11 idle; they complete the third warpgroup so it can hand its registers to the
 //              softmax warpgroups (setmaxnreg), which hold a whole 128-column S row per thread
-// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t (bf16, 64
+// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t (16-bit, 64
 // columns) overwrites the front of S_t once the softmax thread holds the whole S row in
 // registers. The two Q tiles ping-pong: while one warpgroup exponentiates, the tensor core
 // runs the other tile's GEMMs. Online softmax works in the log2 domain; O is rescaled lazily
@@ -52,7 +52,7 @@ constexpr uint32_t kSmemUsed = kSmemBar + 256;
 constexpr uint32_t kSmemBytes = kSmemUsed + 1024;  // slack for manual 1024-byte alignment
 
 struct FwdKernelParams {
-  __nv_bfloat16* out;
+  uint16_t* out;  // bf16 or f16 bits
   float* lse;
   float* debug;
   const int32_t* cu_q;
@@ -75,35 +75,36 @@ constexpr int kStampBase = 2 * 128 * 260;
       p.debug[kStampBase + ((role) * 24 + (iter)) * 8 + (ev)] = static_cast<float>(clock64() - t_start); \
   } while (0)
 
-constexpr uint32_t kIdescQK = umma_idesc_bf16(kBlockM, kBlockN, false, false);
-template <int kD>
-constexpr uint32_t kIdescPV = umma_idesc_bf16(kBlockM, kD, false, true);
+template <bool kF16>
+constexpr uint32_t kIdescQK = umma_idesc_16(kBlockM, kBlockN, false, false, kF16);
+template <int kD, bool kF16>
+constexpr uint32_t kIdescPV = umma_idesc_16(kBlockM, kD, false, true, kF16);
 
-template <int kD>
+template <int kD, bool kF16>
 __device__ __forceinline__ void issue_qk(uint32_t t_s, uint32_t q_smem, uint32_t k_smem) {
   const uint32_t a_lo = umma_desc_lo_kmajor(q_smem);
   const uint32_t b_lo = umma_desc_lo_kmajor(k_smem);
-  umma_ss_lo<kIdescQK, false>(t_s, a_lo, b_lo);
+  umma_ss_lo<kIdescQK<kF16>, false>(t_s, a_lo, b_lo);
 #pragma unroll
   for (int ks = 1; ks < kD / 16; ++ks) {
     const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-    umma_ss_lo<kIdescQK, true>(t_s, a_lo + off, b_lo + off);
+    umma_ss_lo<kIdescQK<kF16>, true>(t_s, a_lo + off, b_lo + off);
   }
 }
 
 // O_t (+)= P_t V for keys [64*half, 64*half + 64) of the block: four K = 16 steps
-template <int kD>
+template <int kD, bool kF16>
 __device__ __forceinline__ void issue_pv_half(uint32_t t_o, uint32_t t_p, uint32_t v_smem, int half,
                                               bool accumulate) {
   const uint32_t b_lo = umma_desc_lo_mnmajor(v_smem, kHalfBytes);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int ks = half * 4 + i;
-    umma_ts_lo<kIdescPV<kD>>(t_o, t_p + ks * 8, b_lo + ks * (2048 >> 4), (accumulate || ks > 0) ? 1u : 0u);
+    umma_ts_lo<kIdescPV<kD, kF16>>(t_o, t_p + ks * 8, b_lo + ks * (2048 >> 4), (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 
-template <bool kDebug, int kD>
+template <bool kDebug, int kD, bool kF16>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k,
@@ -231,7 +232,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (nblk[t] > 0) {
-            issue_qk<kD>(t_s[t], q_smem[t], base + kSmemKV);
+            issue_qk<kD, kF16>(t_s[t], q_smem[t], base + kSmemKV);
             umma_commit(bar + kBarSFull + 8 * t);
           }
         }
@@ -257,12 +258,12 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
             if (!ok) break;
             SDPA_STAMP(2, j, 1 + 3 * t);
             tc_fence_after_sync();
-            issue_pv_half<kD>(t_o[t], t_s[t], v_smem, 0, j > 0);
+            issue_pv_half<kD, kF16>(t_o[t], t_s[t], v_smem, 0, j > 0);
             ok = mbar_wait(bar + kBarPFull + 16 * t + 8, j & 1, abort_flag);
             if (!ok) break;
             if (t == 0) SDPA_STAMP(2, j, 7);
             tc_fence_after_sync();
-            issue_pv_half<kD>(t_o[t], t_s[t], v_smem, 1, true);
+            issue_pv_half<kD, kF16>(t_o[t], t_s[t], v_smem, 1, true);
             umma_commit(bar + kBarOFull + 8 * t);
           }
           if (t == 1) umma_commit(bar + kBarKVEmpty + 8 * sv);
@@ -274,7 +275,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
           SDPA_STAMP(2, j, 2 + 3 * t);
           if (j + 1 < nblk[t]) {
-            issue_qk<kD>(t_s[t], q_smem[t], k_smem);
+            issue_qk<kD, kF16>(t_s[t], q_smem[t], k_smem);
             umma_commit(bar + kBarSFull + 8 * t);
           }
           SDPA_STAMP(2, j, 3 + 3 * t);
@@ -386,7 +387,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
           const float2 x = fma2(make_float2(s[cc * 16 + 2 * i], s[cc * 16 + 2 * i + 1]), c2, nm2);
           const float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
           if (i & 1) lb = add2(lb, pr); else la = add2(la, pr);
-          pk[i] = pack_bf16x2(pr.x, pr.y);
+          pk[i] = pack_16x2<kF16>(pr.x, pr.y);
         }
         if (cc == 4) {
           // keys 0-63 of P were stored one chunk of arithmetic ago, so this wait is short:
@@ -410,13 +411,13 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       SDPA_STAMP(t, j, 4);
     }
 
-    // ---- epilogue: O / l -> bf16, LSE
+    // ---- epilogue: O / l -> 16-bit, LSE
     if (ok && my_blocks > 0) ok = mbar_wait(bar_o, (my_blocks - 1) & 1, abort_flag);
     if (ok && row_lo < len_q) {
       tc_fence_after_sync();
       const bool valid = row < len_q;
       const float inv_l = (l_run > 0.f) ? 1.f / l_run : 0.f;
-      __nv_bfloat16* orow;
+      uint16_t* orow;
       float* lse_ptr;
       if (p.cu_q != nullptr) {
         orow = p.out + static_cast<int64_t>(q_off + row) * p.o_row_stride + h * p.o_head_stride;
@@ -445,7 +446,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i)
-          w[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
+          w[i] = pack_16x2<kF16>(__uint_as_float(r[2 * i]) * inv_l, __uint_as_float(r[2 * i + 1]) * inv_l);
         if (valid) {
           uint4* dst = reinterpret_cast<uint4*>(orow + cc * 32);
 #pragma unroll
@@ -486,18 +487,18 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
   const int64_t rows_q = varlen ? p.total_q : p.max_seqlen_q;
   const int64_t rows_k = varlen ? p.total_k : p.max_seqlen_k;
   const int64_t nb = varlen ? 1 : p.batch;
-  st = make_tensor_map_bf16(&tm_q, p.q, p.head_dim, rows_q, p.heads_q, nb, p.q_row_stride,
+  st = make_tensor_map_16(p.dtype == SDPA_B200_F16, &tm_q, p.q, p.head_dim, rows_q, p.heads_q, nb, p.q_row_stride,
                             p.q_head_stride, p.q_batch_stride, kBlockM);
   if (st != SDPA_B200_OK) return st;
-  st = make_tensor_map_bf16(&tm_k, p.k, p.head_dim, rows_k, p.heads_kv, nb, p.k_row_stride,
+  st = make_tensor_map_16(p.dtype == SDPA_B200_F16, &tm_k, p.k, p.head_dim, rows_k, p.heads_kv, nb, p.k_row_stride,
                             p.k_head_stride, p.k_batch_stride, kBlockN);
   if (st != SDPA_B200_OK) return st;
-  st = make_tensor_map_bf16(&tm_v, p.v, p.head_dim, rows_k, p.heads_kv, nb, p.v_row_stride,
+  st = make_tensor_map_16(p.dtype == SDPA_B200_F16, &tm_v, p.v, p.head_dim, rows_k, p.heads_kv, nb, p.v_row_stride,
                             p.v_head_stride, p.v_batch_stride, kBlockN);
   if (st != SDPA_B200_OK) return st;
 
   FwdKernelParams kp;
-  kp.out = static_cast<__nv_bfloat16*>(p.out);
+  kp.out = static_cast<uint16_t*>(p.out);
   kp.lse = p.lse;
   kp.debug = debug;
   kp.cu_q = p.cu_seqlens_q;
@@ -514,8 +515,11 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
   kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   kp.is_causal = p.is_causal;
 
-  auto kernel = p.head_dim == 64 ? fwd_prefill_kernel<false, 64>
-                                 : (debug ? fwd_prefill_kernel<true, 128> : fwd_prefill_kernel<false, 128>);
+  const bool f16 = p.dtype == SDPA_B200_F16;
+  auto kernel = p.head_dim == 64
+                    ? (f16 ? fwd_prefill_kernel<false, 64, true> : fwd_prefill_kernel<false, 64, false>)
+                    : (f16 ? fwd_prefill_kernel<false, 128, true>
+                           : (debug ? fwd_prefill_kernel<true, 128, false> : fwd_prefill_kernel<false, 128, false>));
   cudaError_t err =
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (err != cudaSuccess) {

@@ -17,11 +17,11 @@ constexpr size_t kWorkspaceHeaderBytes = 256;
 void set_error(const char* fmt, ...);
 void count_launch(int n = 1);
 
-// Builds a 4-D bf16 tensor map {head_dim, rows, heads, batch} with a {64, box_rows, 1, 1}
-// box and 128-byte swizzle. Strides are in ELEMENTS. Returns an SDPA_B200_* status.
-int make_tensor_map_bf16(CUtensorMap* map, const void* base, int head_dim, int64_t rows,
-                         int64_t heads, int64_t batch, int64_t row_stride, int64_t head_stride,
-                         int64_t batch_stride, int box_rows);
+// Builds a 4-D tensor map over 16-bit elements (f16 or bf16) {head_dim, rows, heads, batch} with a
+// {64, box_rows, 1, 1} box and 128-byte swizzle. Strides are in ELEMENTS. Returns an SDPA_B200_* status.
+int make_tensor_map_16(bool f16, CUtensorMap* map, const void* base, int head_dim, int64_t rows,
+                       int64_t heads, int64_t batch, int64_t row_stride, int64_t head_stride,
+                       int64_t batch_stride, int box_rows);
 
 // Prefill forward (TMA + tcgen05). `debug` (nullable, device) receives per-row dumps of the
 // first CTA when the library is asked for them by the test hook.

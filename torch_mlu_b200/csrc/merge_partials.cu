@@ -4,13 +4,12 @@
 // the logsumexp mha_varlen_fwd returns (FlashAttention_internal.cpp:129): for each query row
 //   lse' = log(exp(lse_acc) + exp(lse_part))
 //   o_acc' = o_acc * exp(lse_acc - lse') + o_part * exp(lse_part - lse')
-// with o_acc in fp32 (so that many blocks can be folded without bf16 re-rounding), o_part the
-// bf16 output of sdpa_b200_fwd. A row whose partial saw no key (lse_part = +inf, the library's
+// with o_acc in fp32 (so that many blocks can be folded without 16-bit re-rounding), o_part the
+// bf16 / f16 output of sdpa_b200_fwd. A row whose partial saw no key (lse_part = +inf, the library's
 // convention) contributes nothing; an accumulator that has seen no key yet holds lse_acc = -inf.
 // HBM-bound elementwise kernel: one warp per row, 128-bit accesses.
-#include <cuda_bf16.h>
-
 #include "kernels.h"
+#include "ptx_sm100.cuh"
 
 namespace sdpa_b200 {
 namespace {
@@ -18,12 +17,13 @@ namespace {
 struct MergeParams {
   float* o_acc;               // [batch, heads, rows, head_dim] fp32, contiguous
   float* lse_acc;             // [batch, heads, rows] fp32, contiguous
-  const __nv_bfloat16* o_part;
+  const uint16_t* o_part;     // bf16 or f16 bits
   const float* lse_part;      // [batch, heads, rows] fp32, contiguous
   int64_t p_batch_stride, p_head_stride, p_row_stride;  // o_part element strides
   int batch, heads, rows, head_dim;
 };
 
+template <bool kF16>
 __global__ void __launch_bounds__(256) merge_partial_kernel(const MergeParams p) {
   const int lane = threadIdx.x & 31;
   const int64_t row_id = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
@@ -49,14 +49,13 @@ __global__ void __launch_bounds__(256) merge_partial_kernel(const MergeParams p)
   float4* acc = reinterpret_cast<float4*>(p.o_acc + row_id * p.head_dim) + lane;
   const uint2 pv = *reinterpret_cast<const uint2*>(p.o_part + b * p.p_batch_stride + h * p.p_head_stride +
                                                    static_cast<int64_t>(r) * p.p_row_stride + lane * 4);
-  const __nv_bfloat162 p01 = *reinterpret_cast<const __nv_bfloat162*>(&pv.x);
-  const __nv_bfloat162 p23 = *reinterpret_cast<const __nv_bfloat162*>(&pv.y);
+  const float2 p01 = unpack_16x2<kF16>(pv.x), p23 = unpack_16x2<kF16>(pv.y);
   float4 a = *acc;
   // wa == 0 also covers the uninitialised first fold (lse_acc = -inf): the old contents are ignored
-  a.x = (wa == 0.f ? 0.f : a.x * wa) + __bfloat162float(p01.x) * wp;
-  a.y = (wa == 0.f ? 0.f : a.y * wa) + __bfloat162float(p01.y) * wp;
-  a.z = (wa == 0.f ? 0.f : a.z * wa) + __bfloat162float(p23.x) * wp;
-  a.w = (wa == 0.f ? 0.f : a.w * wa) + __bfloat162float(p23.y) * wp;
+  a.x = (wa == 0.f ? 0.f : a.x * wa) + p01.x * wp;
+  a.y = (wa == 0.f ? 0.f : a.y * wa) + p01.y * wp;
+  a.z = (wa == 0.f ? 0.f : a.z * wa) + p23.x * wp;
+  a.w = (wa == 0.f ? 0.f : a.w * wa) + p23.y * wp;
   *acc = a;
 }
 
@@ -65,12 +64,17 @@ __global__ void __launch_bounds__(256) merge_partial_kernel(const MergeParams p)
 
 extern "C" SDPA_B200_API int sdpa_b200_merge_partial(float* o_acc, float* lse_acc, const void* o_part,
                                                      const float* lse_part, int32_t batch, int32_t heads,
-                                                     int32_t rows, int32_t head_dim, int64_t part_batch_stride,
+                                                     int32_t rows, int32_t head_dim, int32_t dtype,
+                                                     int64_t part_batch_stride,
                                                      int64_t part_head_stride, int64_t part_row_stride, void* stream) {
   using namespace sdpa_b200;
   if (o_acc == nullptr || lse_acc == nullptr || o_part == nullptr || lse_part == nullptr) {
     set_error("merge_partial: NULL pointer");
     return SDPA_B200_INVALID_ARG;
+  }
+  if (dtype != SDPA_B200_BF16 && dtype != SDPA_B200_F16) {
+    set_error("merge_partial: o_part must be bf16 or f16 (dtype code %d)", dtype);
+    return SDPA_B200_UNSUPPORTED;
   }
   if (head_dim != 128 && head_dim != 64) {
     set_error("merge_partial: this build handles head_dim 64 and 128 only (got %d)", head_dim);
@@ -84,7 +88,7 @@ extern "C" SDPA_B200_API int sdpa_b200_merge_partial(float* o_acc, float* lse_ac
   MergeParams m;
   m.o_acc = o_acc;
   m.lse_acc = lse_acc;
-  m.o_part = static_cast<const __nv_bfloat16*>(o_part);
+  m.o_part = static_cast<const uint16_t*>(o_part);
   m.lse_part = lse_part;
   m.p_batch_stride = part_batch_stride;
   m.p_head_stride = part_head_stride;
@@ -94,7 +98,9 @@ extern "C" SDPA_B200_API int sdpa_b200_merge_partial(float* o_acc, float* lse_ac
   m.rows = rows;
   m.head_dim = head_dim;
   const int64_t total = static_cast<int64_t>(batch) * heads * rows;
-  merge_partial_kernel<<<static_cast<unsigned>((total + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(m);
+  const unsigned grid = static_cast<unsigned>((total + 7) / 8);
+  if (dtype == SDPA_B200_F16) merge_partial_kernel<true><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(m);
+  else merge_partial_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(m);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("merge_partial: launch failed: %s", cudaGetErrorString(err));

@@ -103,6 +103,32 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+// The kernels are templated on the 16-bit storage type: kF16 = true is IEEE half, false is bf16.
+template <bool kF16>
+__device__ __forceinline__ uint32_t pack_16x2(float lo, float hi) {
+  return kF16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
+}
+// packed pair -> two fp32 (x = low half)
+template <bool kF16>
+__device__ __forceinline__ float2 unpack_16x2(uint32_t w) {
+  if (kF16) {
+    float2 r;
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.f32.f16 %0, lo;\n\tcvt.f32.f16 %1, hi;\n\t}\n"
+        : "=f"(r.x), "=f"(r.y)
+        : "r"(w));
+    return r;
+  }
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <bool kF16>
+__device__ __forceinline__ uint16_t to_16(float x) {
+  return static_cast<uint16_t>(pack_16x2<kF16>(x, 0.f) & 0xffffu);
+}
 
 // ---------------------------------------------------------------------------------------
 // mbarrier
@@ -331,12 +357,12 @@ __device__ __forceinline__ uint64_t umma_desc_mnmajor(uint32_t smem_addr, uint32
   return umma_smem_desc(smem_addr, mn_chunk_stride, 1024);
 }
 
-// Instruction descriptor for kind::f16 with bf16 A/B and fp32 D.
-//   bits [4,6) D format (1 = f32), [7,10) A format (1 = bf16), [10,13) B format (1 = bf16),
+// Instruction descriptor for kind::f16 with 16-bit A/B (f16 when `f16`, else bf16) and fp32 D.
+//   bits [4,6) D format (1 = f32), [7,10) A format (0 = f16, 1 = bf16), [10,13) B format (same),
 //   bit 15 A major (1 = MN), bit 16 B major (1 = MN), bits [17,23) N >> 3, bits [24,29) M >> 4.
-__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, bool a_mn_major,
-                                                       bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+__host__ __device__ constexpr uint32_t umma_idesc_16(int M, int N, bool a_mn_major, bool b_mn_major,
+                                                     bool f16) {
+  return (1u << 4) | (f16 ? 0u : ((1u << 7) | (1u << 10))) | (static_cast<uint32_t>(a_mn_major) << 15) |
          (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
          (static_cast<uint32_t>(M >> 4) << 24);
 }

@@ -45,9 +45,9 @@ void set_error(const char* fmt, ...) {
 
 void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
 
-int make_tensor_map_bf16(CUtensorMap* map, const void* base, int head_dim, int64_t rows,
-                         int64_t heads, int64_t batch, int64_t row_stride, int64_t head_stride,
-                         int64_t batch_stride, int box_rows) {
+int make_tensor_map_16(bool f16, CUtensorMap* map, const void* base, int head_dim, int64_t rows,
+                       int64_t heads, int64_t batch, int64_t row_stride, int64_t head_stride,
+                       int64_t batch_stride, int box_rows) {
   EncodeTiledFn encode = get_encode_fn();
   if (encode == nullptr) {
     set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
@@ -63,7 +63,7 @@ int make_tensor_map_bf16(CUtensorMap* map, const void* base, int head_dim, int64
                            static_cast<cuuint64_t>(batch_stride) * 2};
   cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box,
+  CUresult r = encode(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box,
                       estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -108,8 +108,8 @@ int validate_common(const sdpa_b200_params* p) {
     set_error("params is NULL");
     return SDPA_B200_INVALID_ARG;
   }
-  if (p->dtype != SDPA_B200_BF16) {
-    set_error("only bf16 q/k/v are supported (dtype code %d)", p->dtype);
+  if (p->dtype != SDPA_B200_BF16 && p->dtype != SDPA_B200_F16) {
+    set_error("q/k/v must be bf16 or f16 (dtype code %d)", p->dtype);
     return SDPA_B200_UNSUPPORTED;
   }
   if (p->dropout_p != 0.f) {

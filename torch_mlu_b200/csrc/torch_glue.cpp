@@ -12,6 +12,7 @@
 // attention.cpp:124-129, 260-269): strides go straight into sdpa_b200_params. torch supplies
 // device memory (outputs, workspace) and the current stream only.
 #include <ATen/ATen.h>
+#include <ATen/autocast_mode.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
@@ -33,9 +34,8 @@ void check_status(int st, const char* what) {
 // FlashAttention_internal.cpp:73-108: device, dtype and last-dim stride checks
 void check_input(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, " must be on a CUDA device (this path has no CPU fallback)");
-  TORCH_CHECK(t.scalar_type() == at::kBFloat16,
-              "FlashAttention only support fp16 and bf16 data type; this build implements bf16 (", name, " is ",
-              t.scalar_type(), ")");
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16 || t.scalar_type() == at::kHalf,
+              "FlashAttention only support fp16 and bf16 data type (", name, " is ", t.scalar_type(), ")");
   TORCH_CHECK(t.stride(-1) == 1, "Input tensor must have contiguous last dimension (", name, ")");
 }
 
@@ -65,7 +65,9 @@ void base_params(sdpa_b200_params& p, const Tensor& q, const Tensor& k, const Te
   p.lse = lse.data_ptr<float>();
   p.softmax_scale = static_cast<float>(scale);
   p.is_causal = causal ? 1 : 0;
-  p.dtype = SDPA_B200_BF16;
+  TORCH_CHECK(k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type(),
+              "query, key, and value must have the same dtype");
+  p.dtype = q.scalar_type() == at::kHalf ? SDPA_B200_F16 : SDPA_B200_BF16;
   p.kernel = SDPA_B200_KERNEL_AUTO;
 }
 
@@ -373,6 +375,35 @@ void remove_aten_overrides() { g_aten_overrides.reset(); }
 
 int64_t launch_count() { return static_cast<int64_t>(sdpa_b200_launch_count()); }
 
+// ------------------------------------------------ autocast (aten/autocast_mode.cpp:147: lower_precision_fp)
+// Under torch.autocast("cuda") fp32 query/key/value are cast to the autocast dtype (fp16 or bf16)
+// before the kernels run, as the reference does for _scaled_dot_product_flash_attention.
+Tensor to_autocast_dtype(const Tensor& t) {
+  return at::autocast::cached_cast(at::autocast::get_autocast_dtype(at::kCUDA), t, c10::DeviceType::CUDA);
+}
+
+std::tuple<Tensor, Tensor, Tensor, Tensor, int64_t, int64_t, Tensor, Tensor, Tensor> autocast_sdpa_flash(
+    const Tensor& q, const Tensor& k, const Tensor& v, double dropout_p, bool is_causal, bool return_debug_mask,
+    c10::optional<double> scale) {
+  c10::impl::ExcludeDispatchKeyGuard no_autocast(c10::DispatchKey::AutocastCUDA);
+  static auto op = c10::Dispatcher::singleton()
+                       .findSchemaOrThrow("b200_sdpa::_scaled_dot_product_flash_attention", "")
+                       .typed<decltype(autocast_sdpa_flash)>();
+  return op.call(to_autocast_dtype(q), to_autocast_dtype(k), to_autocast_dtype(v), dropout_p, is_causal,
+                 return_debug_mask, scale);
+}
+
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> autocast_flash_forward(
+    const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& cu_q, const Tensor& cu_k, int64_t max_q,
+    int64_t max_k, double dropout_p, bool is_causal, bool return_debug_mask, c10::optional<double> scale) {
+  c10::impl::ExcludeDispatchKeyGuard no_autocast(c10::DispatchKey::AutocastCUDA);
+  static auto op = c10::Dispatcher::singleton()
+                       .findSchemaOrThrow("b200_sdpa::_flash_attention_forward", "")
+                       .typed<decltype(autocast_flash_forward)>();
+  return op.call(to_autocast_dtype(q), to_autocast_dtype(k), to_autocast_dtype(v), cu_q, cu_k, max_q, max_k, dropout_p,
+                 is_causal, return_debug_mask, scale);
+}
+
 }  // namespace
 
 TORCH_LIBRARY(b200_sdpa, m) {
@@ -392,6 +423,11 @@ TORCH_LIBRARY(b200_sdpa, m) {
   m.def("_install_aten_overrides() -> ()", install_aten_overrides);
   m.def("_remove_aten_overrides() -> ()", remove_aten_overrides);
   m.def("_launch_count() -> int", launch_count);
+}
+
+TORCH_LIBRARY_IMPL(b200_sdpa, AutocastCUDA, m) {
+  m.impl("_scaled_dot_product_flash_attention", autocast_sdpa_flash);
+  m.impl("_flash_attention_forward", autocast_flash_forward);
 }
 
 TORCH_LIBRARY_IMPL(b200_sdpa, CUDA, m) {

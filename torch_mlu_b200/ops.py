@@ -53,9 +53,9 @@ def _check_inputs(*tensors: torch.Tensor) -> None:
     for t in tensors:
         _check(t.is_cuda, "Input tensor must be on a CUDA device (this path has no CPU fallback)")
         # FlashAttention_internal.cpp:74-80
-        _check(t.dtype == torch.bfloat16,
-               "FlashAttention only support fp16 and bf16 data type; this build implements bf16 "
-               f"(got {t.dtype})")
+        _check(t.dtype in (torch.bfloat16, torch.float16),
+               f"FlashAttention only support fp16 and bf16 data type (got {t.dtype})")
+        _check(t.dtype == tensors[0].dtype, "query, key, and value must have the same dtype")
         # FlashAttention_internal.cpp:100-108
         _check(t.stride(-1) == 1, "Input tensor must have contiguous last dimension")
 
@@ -153,7 +153,7 @@ def _dense_params(query, key, value, out, lse, is_causal, scale, kernel=_cabi.KE
     p.softmax_scale = scale
     p.dropout_p = 0.0
     p.is_causal = int(bool(is_causal))
-    p.dtype = _cabi.DTYPE_BF16
+    p.dtype = _cabi.DTYPE_F16 if query.dtype == torch.float16 else _cabi.DTYPE_BF16
     p.kernel = kernel
     p.num_splits = num_splits
     return p
@@ -246,7 +246,7 @@ def _varlen_params(query, key, value, out, lse, cu_q, cu_k, max_q, max_k, is_cau
     p.softmax_scale = scale
     p.dropout_p = 0.0
     p.is_causal = int(bool(is_causal))
-    p.dtype = _cabi.DTYPE_BF16
+    p.dtype = _cabi.DTYPE_F16 if query.dtype == torch.float16 else _cabi.DTYPE_BF16
     p.kernel = _cabi.KERNEL_PREFILL
     return p
 

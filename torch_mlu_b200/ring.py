@@ -23,14 +23,15 @@ from . import _cabi
 
 
 def merge_partial(o_acc: torch.Tensor, lse_acc: torch.Tensor, o_part: torch.Tensor, lse_part: torch.Tensor) -> None:
-    """In-place logsumexp fold of a bf16 partial [B,H,L,128] (any strides) into the fp32
-    accumulator (contiguous [B,H,L,128], lse [B,H,L]). CUDA only."""
+    """In-place logsumexp fold of a bf16 / f16 partial [B,H,L,D] (any strides) into the fp32
+    accumulator (contiguous [B,H,L,D], lse [B,H,L]). CUDA only."""
     assert o_acc.is_cuda and o_acc.dtype == torch.float32 and o_acc.is_contiguous()
     assert lse_acc.dtype == torch.float32 and lse_acc.is_contiguous() and lse_part.is_contiguous()
-    assert o_part.dtype == torch.bfloat16 and o_part.stride(-1) == 1
+    assert o_part.dtype in (torch.bfloat16, torch.float16) and o_part.stride(-1) == 1
     B, H, L, D = o_acc.shape
     lib = _cabi.load()
     st = lib.sdpa_b200_merge_partial(o_acc.data_ptr(), lse_acc.data_ptr(), o_part.data_ptr(), lse_part.data_ptr(), B, H, L, D,
+                                     _cabi.DTYPE_F16 if o_part.dtype == torch.float16 else _cabi.DTYPE_BF16,
                                      o_part.stride(0), o_part.stride(1), o_part.stride(2),
                                      torch.cuda.current_stream().cuda_stream)
     _cabi.check(st, "sdpa_b200_merge_partial")

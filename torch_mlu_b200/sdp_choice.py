@@ -8,7 +8,7 @@ and math is disabled, every constraint is re-run in debug mode (warnings) and
 ``RuntimeError("No available kernel.  Aborting execution.")`` is raised. What differs on purpose:
 there is one fused backend here (flash; the memory-efficient kernel is not built), and the
 MLU-occupancy heuristics of sdp_utils.h:479-524 (500-series check, split condition, valid-data
-ratio) are replaced by what this build needs: an sm_100 CUDA device, bf16, head_dim 64 or 128.
+ratio) are replaced by what this build needs: an sm_100 CUDA device, head_dim 64 or 128.
 """
 from __future__ import annotations
 
@@ -107,9 +107,9 @@ def _check_fused_kernel_device_support(q, k, v, mask, debug):  # stands where sd
     return True
 
 
-def _check_tensor_dtype(q, k, v, mask, debug):  # sdp_utils.h:433-455 with this build's dtype list
-    if not (q.dtype == k.dtype == v.dtype == torch.bfloat16):
-        _warn(debug, "Expected query, key and value to all be of dtype: {BFloat16}. Got "
+def _check_tensor_dtype(q, k, v, mask, debug):  # sdp_utils.h:433-455
+    if not (q.dtype == k.dtype == v.dtype and q.dtype in (torch.float16, torch.bfloat16)):
+        _warn(debug, "Expected query, key and value to all be of dtype: {Half, BFloat16}. Got "
                      f"Query dtype: {q.dtype}, Key dtype: {k.dtype}, and Value dtype: {v.dtype} instead.")
         return False
     return True
