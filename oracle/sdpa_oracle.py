@@ -235,3 +235,35 @@ def assert_close_lse(got, want, name: str = "lse", max_abs: float = LSE_MAX_ABS)
     mx = float(d.max()) if d.numel() else 0.0
     assert mx <= max_abs, f"{name}: max-abs {mx:.3e} (limit {max_abs})"
     return mx
+
+
+# ------------------------------------------------------------------ the reference tests' own rule
+# test/torch_ops/test_scaled_dot_product_attention.py:165-204: the fused kernel may deviate from
+# the high-precision result by at most `fudge` times what the SAME math evaluated in the low
+# precision dtype deviates, with per-dtype floors.
+_DEFAULT_ATOL = {torch.float16: 1e-3, torch.bfloat16: 1e-3, torch.float32: 1e-5}
+_DEFAULT_RTOL = {torch.float16: 1e-3, torch.bfloat16: 1.6e-2, torch.float32: 1.3e-6}
+
+
+def reference_tolerances(true_value: torch.Tensor, lowp_value: torch.Tensor, fudge: float = 2.0) -> Tuple[float, float]:
+    dt = lowp_value.dtype
+    dev = true_value.double() - lowp_value.double()
+    atol = float(dev.abs().max())
+    rel = torch.nan_to_num((dev / true_value.double()).abs(), nan=_DEFAULT_RTOL[dt])
+    rtol = float(rel.max())
+    atol = fudge * max(atol, _DEFAULT_ATOL[dt])
+    rtol = fudge * max(rtol, _DEFAULT_RTOL[dt])
+    if rtol > 1e30:
+        rtol = _DEFAULT_RTOL[dt]
+    return atol, rtol
+
+
+def assert_close_reference_rule(got, true_value, lowp_value, name: str, fudge: float = 2.0):
+    """got: the kernel's result; true_value: fp32/fp64 math; lowp_value: the same math in got's dtype."""
+    atol, rtol = reference_tolerances(true_value, lowp_value, fudge)
+    g = got.detach().cpu().double()
+    t = true_value.double()
+    bad = (g - t).abs() > atol + rtol * t.abs()
+    assert not bool(bad.any()), (f"{name}: {int(bad.sum())} elements outside atol {atol:.3e} rtol {rtol:.3e} "
+                                 f"(max-abs error {float((g - t).abs().max()):.3e})")
+    return atol, rtol

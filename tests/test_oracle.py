@@ -107,3 +107,18 @@ def test_fully_masked_rows_follow_library_convention():
         out, lse = fn(q, k, v, causal=True)
         assert torch.all(out[0, 0, :2] == 0) and torch.all(torch.isinf(lse[0, 0, :2]) & (lse[0, 0, :2] > 0))
         assert torch.isfinite(lse[0, 0, 2:]).all()
+
+
+def test_reference_tolerance_rule_floors_and_fudge():
+    """reference_tolerances restates get_tolerances
+    (test/torch_ops/test_scaled_dot_product_attention.py:188-204)."""
+    true = torch.tensor([1.0, 2.0, 4.0])
+    lowp = torch.tensor([1.0, 2.0, 4.0]).bfloat16()
+    atol, rtol = orc.reference_tolerances(true, lowp)          # no deviation: the per-dtype floors x 2
+    assert atol == pytest.approx(2e-3) and rtol == pytest.approx(3.2e-2)
+    lowp = torch.tensor([1.0, 2.0, 4.5]).bfloat16()
+    atol, rtol = orc.reference_tolerances(true, lowp, fudge=4)
+    assert atol == pytest.approx(4 * 0.5) and rtol == pytest.approx(4 * 0.125)
+    orc.assert_close_reference_rule(torch.tensor([1.0, 2.0, 5.0]), true, lowp, "x", fudge=4)
+    with pytest.raises(AssertionError):
+        orc.assert_close_reference_rule(torch.tensor([1.0, 2.0, 9.0]), true, lowp, "x")

@@ -50,7 +50,8 @@ def build_native(verbose: bool = False, force: bool = False) -> str:
         o = os.path.join(OBJ_DIR, src.replace(".cu", ".o"))
         objs.append(o)
         if force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hdr):
-            cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-c", s, "-o", o]
+            # SDPA_B200_NVCC_EXTRA: extra compile flags, e.g. -DSDPA_BWD_STAMPS for a profiling build
+            cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("SDPA_B200_NVCC_EXTRA", "").split(), "-I", INCLUDE, "-c", s, "-o", o]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)

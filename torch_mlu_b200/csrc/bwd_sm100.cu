@@ -25,6 +25,8 @@
 // exponentials under the current item's accumulation MMAs (buffer schedule at the issuer).
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+
 #include "kernels.h"
 #include "ptx_sm100.cuh"
 
@@ -53,8 +55,8 @@ constexpr uint32_t kBarYFull = 8;
 constexpr uint32_t kBarYEmpty = kBarYFull + 8 * kMaxStages;
 constexpr uint32_t kBarSFull = kBarYEmpty + 8 * kMaxStages;   // 2: first score GEMM (X1 Y1^T) of an item done
 constexpr uint32_t kBarDFull = kBarSFull + 16;             // second score GEMM (X2 Y2^T) done
-constexpr uint32_t kBarDFree = kBarDFull + 8;              // 2: a column half has read dP out of TMEM
-constexpr uint32_t kBarPFull = kBarDFree + 16;             // 2: a column half has stored P / dS
+constexpr uint32_t kBarDFree = kBarDFull + 8;              // all compute warps have read dP out of TMEM
+constexpr uint32_t kBarPFull = kBarDFree + 16;             // all compute warps have stored P / dS
 constexpr uint32_t kBarAccFull = kBarPFull + 16;
 constexpr uint32_t kSmemTmemPtr = kBarAccFull + 8;
 constexpr uint32_t kSmemAbort = kSmemTmemPtr + 4;
@@ -76,7 +78,22 @@ struct BwdKernelParams {
   int num_bh, heads_x, heads_per_wave;  // CTA order, see the top of bwd_tile_kernel
   float scale, scale_log2;
   int is_causal;
+#ifdef SDPA_BWD_STAMPS
+  float* stamps;  // [mode 2][role 4][item 24][event 8] SM cycles since CTA start, one CTA per mode
+#endif
 };
+
+// Profiling builds (-DSDPA_BWD_STAMPS) time-stamp pipeline events of one CTA per kernel; role 0/1 =
+// lane 0 of the first warp of each compute warpgroup, roles 2 and 3 = the MMA issuer.
+#ifdef SDPA_BWD_STAMPS
+#define BWD_STAMP(role, item, ev)                                                                       \
+  do {                                                                                                  \
+    if (stamp_on && (item) < 24)                                                                        \
+      p.stamps[((kMode * 4 + (role)) * 24 + (item)) * 8 + (ev)] = static_cast<float>(clock64() - t_start); \
+  } while (0)
+#else
+#define BWD_STAMP(role, item, ev) do {} while (0)
+#endif
 
 template <bool kF16>
 constexpr uint32_t kIdescSS = umma_idesc_16(kTile, kTile, false, false, kF16);
@@ -187,10 +204,8 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(bar + kBarSFull, 1);
     mbar_init(bar + kBarSFull + 8, 1);
     mbar_init(bar + kBarDFull, 1);
-    mbar_init(bar + kBarDFree, kTile);
-    mbar_init(bar + kBarDFree + 8, kTile);
-    mbar_init(bar + kBarPFull, kTile);
-    mbar_init(bar + kBarPFull + 8, kTile);
+    mbar_init(bar + kBarDFree, 8);  // one arrival per compute warp
+    mbar_init(bar + kBarPFull, 8);
     mbar_init(bar + kBarAccFull, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -205,6 +220,13 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
   const uint32_t t1 = tmem_base, t2 = tmem_base + 128, acc1 = tmem_base + 256, acc2 = tmem_base + 384;
+#ifdef SDPA_BWD_STAMPS
+  const long long t_start = clock64();
+  // a long-running block of batch 0, head 0 (non-causal: any; causal: the heaviest)
+  const bool stamp_on = p.stamps != nullptr && b == 0 && hx == 0 &&
+                        xb == ((kMode == kModeDKDV) ? 0 : p.num_row_blocks - 1) && (lane == 0) &&
+                        (warp == 0 || warp == 4 || warp == 9);
+#endif
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
@@ -223,9 +245,25 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (kD > 64) tma_load_4d(base + kSmemX + kTileBytes + kHalfBytes, tmx2, bar + kBarXFull, 64, x_row, hx, bcoord);
       for (int idx = 0; idx < 2 * n_items; ++idx) {  // ring tile idx: Y1(idx/2) if even, Y2(idx/2) if odd
         const int i = idx >> 1;
-        const int s = idx % kStages;
-        const uint32_t use = static_cast<uint32_t>(idx / kStages);
-        if (!mbar_wait(bar + kBarYEmpty + 8 * s, (use & 1u) ^ 1u, abort_flag)) break;
+        int s = idx % kStages;
+        uint32_t use = static_cast<uint32_t>(idx / kStages);
+        if (kMode == kModeDQ) {  // K ring: slots 0-2, V ring: slots 3-4
+          s = (idx & 1) ? 3 + (i & 1) : i % 3;
+          use = static_cast<uint32_t>((idx & 1) ? (i >> 1) : i / 3);
+        }
+        // Slot reuse. dK/dV: the pair of slots of item i - 2 is released by one commit behind its
+        // accumulation GEMMs. dQ has no release commits (they cost the issuer time): V(i) reuses the
+        // slot of V(i-2), whose only reader dP(i-2) is tracked by the dP-full barrier; K(i) reuses the
+        // slot of K(i-3), last read by dQ(i-3), which precedes S(i-1) in the tensor pipe, so the
+        // score-full barrier of S(i-1) covers it. Neither barrier can run a second phase ahead,
+        // because the GEMM of that later phase needs a tile this loop has not loaded yet.
+        if (kMode == kModeDKDV) {
+          if (!mbar_wait(bar + kBarYEmpty + 8 * (s & ~1), (use & 1u) ^ 1u, abort_flag)) break;
+        } else if (idx & 1) {
+          if (i >= 2 && !mbar_wait(bar + kBarDFull, (i - 2) & 1, abort_flag)) break;
+        } else {
+          if (i >= 3 && !mbar_wait(bar + kBarSFull + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag)) break;
+        }
         const int hi = i / tiles_per_head;
         const int yt = y_lo + (i - hi * tiles_per_head);
         // dK/dV streams the query heads of this KV head; dQ streams the KV head of this query head
@@ -263,18 +301,31 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       auto s_bar = [&](int i) { return bar + kBarSFull + (kMode == kModeDQ ? 8 * (i & 1) : 0); };
       // ring position of tile 2i, kept incrementally (no division in the issue loop): slot = (2i) mod
       // kStages, lap = (2i) / kStages. Tiles 2i + k, k < kStages, follow from it with one wrap.
-      int ring_slot = 0, ring_lap = 0;
+      // dQ splits its five slots into a K ring (slots 0-2) and a V ring (slots 3-4): a K tile lives
+      // from its score GEMM to its accumulation GEMM two items later, a V tile only for one GEMM, so a
+      // shared round-robin would free the slot V(i+1) needs too late to hide the load latency.
+      int ring_slot = 0, ring_lap = 0;  // dK/dV: position of tile 2i; dQ: i mod 3 and i / 3
+      int item = 0;
       auto pos = [&](int k, int& slot, int& lap) {
-        slot = ring_slot + k;
-        lap = ring_lap;
-        if (slot >= kStages) { slot -= kStages; ++lap; }
+        if (kMode == kModeDKDV) {
+          slot = ring_slot + k;
+          lap = ring_lap;
+          if (slot >= kStages) { slot -= kStages; ++lap; }
+        } else if ((k & 1) == 0) {  // K(item + k/2)
+          slot = ring_slot + (k >> 1);
+          lap = ring_lap;
+          if (slot >= 3) { slot -= 3; ++lap; }
+        } else {  // V(item + k/2)
+          const int j = item + (k >> 1);
+          slot = 3 + (j & 1);
+          lap = j >> 1;
+        }
       };
       auto y_slot_k = [&](int k) { int sl, lp; pos(k, sl, lp); return base + kSmemY + sl * kTileBytes; };
       auto y_wait_k = [&](int k) { int sl, lp; pos(k, sl, lp); return mbar_wait(bar + kBarYFull + 8 * sl, lp & 1, abort_flag); };
       auto y_free_k = [&](int k) { int sl, lp; pos(k, sl, lp); umma_commit(bar + kBarYEmpty + 8 * sl); };
       auto y_slot = [&](int idx) { return y_slot_k(idx); };  // prologue only (item 0: idx == k)
       auto y_wait = [&](int idx) { return y_wait_k(idx); };
-      auto y_free = [&](int idx) { y_free_k(idx); };
       bool ok = mbar_wait(bar + kBarXFull, 0, abort_flag) && y_wait(0);
       if (ok) {
         tc_fence_after_sync();
@@ -286,7 +337,6 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tc_fence_after_sync();
         issue_xyT<kD, kF16>(d_buf(0), x2, y_slot(1));
         umma_commit(bar + kBarDFull);
-        if (kMode == kModeDQ) y_free(1);  // V(0) is only read by dP(0)
       }
       if (kMode == kModeDQ && ok && n_items > 1) {
         ok = y_wait(2);
@@ -300,27 +350,34 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const uint32_t y1 = y_slot_k(0), y2 = y_slot_k(1);
         const uint32_t sbuf = s_buf(i);
         const bool more = i + 1 < n_items;
+        BWD_STAMP(2, i, 0);
         // dP(i) has left TMEM once both column halves have read it
-        ok = mbar_wait(bar + kBarDFree, i & 1, abort_flag) && mbar_wait(bar + kBarDFree + 8, i & 1, abort_flag);
+        ok = mbar_wait(bar + kBarDFree, i & 1, abort_flag);
         if (!ok) break;
+        BWD_STAMP(2, i, 1);
         if (more) {
           if (kMode == kModeDKDV) {
             ok = y_wait_k(2);
             if (!ok) break;
+            BWD_STAMP(3, i, 0);
             tc_fence_after_sync();
             issue_xyT<kD, kF16>(d_buf(i), x1, y_slot_k(2));  // S(i+1) into the buffer dP(i) has just left
+            BWD_STAMP(3, i, 1);
             umma_commit(s_bar(i + 1));
           } else {
             ok = y_wait_k(3);
             if (!ok) break;
+            BWD_STAMP(3, i, 0);
             tc_fence_after_sync();
             issue_xyT<kD, kF16>(t2, x2, y_slot_k(3));  // dP(i+1)
+            BWD_STAMP(3, i, 1);
             umma_commit(bar + kBarDFull);
-            y_free_k(3);  // V(i+1) is only read by dP(i+1)
           }
         }
-        ok = mbar_wait(bar + kBarPFull, i & 1, abort_flag) && mbar_wait(bar + kBarPFull + 8, i & 1, abort_flag);
+        BWD_STAMP(2, i, 2);
+        ok = mbar_wait(bar + kBarPFull, i & 1, abort_flag);
         if (!ok) break;
+        BWD_STAMP(2, i, 3);
         tc_fence_after_sync();
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
@@ -330,27 +387,39 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           } else {
             issue_wy_half<kD, kF16>(acc1, sbuf + half * 64 + 32, y1, half, i > 0);  // dQ += dS K
           }
+          BWD_STAMP(3, i, 3 + half);
         }
-        y_free_k(0);
-        if (kMode == kModeDKDV) y_free_k(1);
+        if (kMode == kModeDKDV) y_free_k(0);  // releases the slot pair Q(i), dO(i)
+        BWD_STAMP(2, i, 4);
         if (i == n_items - 1) umma_commit(bar + kBarAccFull);
         if (kMode == kModeDKDV) {
           if (more) {
             ok = y_wait_k(3);
             if (!ok) break;
+            BWD_STAMP(3, i, 5);
             tc_fence_after_sync();
             issue_xyT<kD, kF16>(sbuf, x2, y_slot_k(3));  // dP(i+1), behind the MMAs reading P(i), dS(i)
+            BWD_STAMP(3, i, 6);
             umma_commit(bar + kBarDFull);
           }
         } else if (i + 2 < n_items) {
           ok = y_wait_k(4);
           if (!ok) break;
+          BWD_STAMP(3, i, 5);
           tc_fence_after_sync();
           issue_xyT<kD, kF16>(sbuf, x1, y_slot_k(4));  // S(i+2), behind the MMAs reading dS(i)
+          BWD_STAMP(3, i, 6);
           umma_commit(s_bar(i + 2));
         }
-        ring_slot += 2;
-        if (ring_slot >= kStages) { ring_slot -= kStages; ++ring_lap; }
+        BWD_STAMP(2, i, 5);
+        ++item;
+        if (kMode == kModeDKDV) {
+          ring_slot += 2;
+          if (ring_slot >= kStages) { ring_slot -= kStages; ++ring_lap; }
+        } else if (++ring_slot == 3) {
+          ring_slot = 0;
+          ++ring_lap;
+        }
       }
     }
   } else if (warp < 8) {
@@ -374,15 +443,18 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int y0 = (y_lo + (i - hi * tiles_per_head)) * kTile;
       const uint32_t sbuf = (kMode == kModeDKDV ? ((i & 1) ? t2 : t1) : ((i & 1) ? acc2 : t1)) + lane_base;
       const uint32_t dbuf = (kMode == kModeDKDV ? ((i & 1) ? t1 : t2) : t2) + lane_base;
+      BWD_STAMP(half, i, 0);
+      // `ok` is made warp-uniform after every wait: the warp-level arrivals below need all 32 lanes
       ok = mbar_wait(bar + kBarSFull + (kMode == kModeDQ ? 8 * (i & 1) : 0), (kMode == kModeDQ ? (i >> 1) : i) & 1,
                      abort_flag);
-      if (!ok) break;
       if (kMode == kModeDKDV) {
         // the per-query vectors arrive with the stage's bulk copies; observe that barrier directly
-        ok = mbar_wait(bar + kBarYFull + 8 * s, ((2 * i) / kStages) & 1, abort_flag);
-        if (!ok) break;
+        ok = ok && mbar_wait(bar + kBarYFull + 8 * s, ((2 * i) / kStages) & 1, abort_flag);
       }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       tc_fence_after_sync();
+      BWD_STAMP(half, i, 1);
       const float* vec_lse = reinterpret_cast<const float*>(smem + kSmemVec + s * 1024) + half * 64;
       const float* vec_delta = vec_lse + 128;
       // visibility of element (row xr, column y0 + j)
@@ -405,11 +477,21 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_ld_x32_at<0>(sbuf, a);
         tmem_ld_x32_at<32>(sbuf + 32, a);
         tmem_wait_ld();
+        BWD_STAMP(half, i, 2);
+        // only tiles on the causal diagonal or past the end of the keys need the element mask
+        if (__any_sync(0xffffffffu, j_lo > 0 || j_hi < 64)) {
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          const float l2 = (kMode == kModeDKDV) ? vec_lse[j] : my_lse2;
-          const float e = ex2_approx(fmaf(__uint_as_float(a[j]), c, -l2));
-          pr[j] = (j >= j_lo && j < j_hi) ? e : 0.f;
+          for (int j = 0; j < 64; ++j) {
+            const float l2 = (kMode == kModeDKDV) ? vec_lse[j] : my_lse2;
+            const float e = ex2_approx(fmaf(__uint_as_float(a[j]), c, -l2));
+            pr[j] = (j >= j_lo && j < j_hi) ? e : 0.f;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) {
+            const float l2 = (kMode == kModeDKDV) ? vec_lse[j] : my_lse2;
+            pr[j] = ex2_approx(fmaf(__uint_as_float(a[j]), c, -l2));
+          }
         }
         if (kMode == kModeDKDV) {
           uint32_t pw[32];
@@ -420,16 +502,20 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       // phase 2 (needs dP): dS = P o (dP - delta) into the second half of this thread's columns
-      ok = mbar_wait(bar + kBarDFull, i & 1, abort_flag);
+      BWD_STAMP(half, i, 3);
+      ok = __all_sync(0xffffffffu, mbar_wait(bar + kBarDFull, i & 1, abort_flag));
       if (!ok) break;
       tc_fence_after_sync();
+      BWD_STAMP(half, i, 4);
       {
         uint32_t d[64];
         tmem_ld_x32_at<0>(dbuf, d);
         tmem_ld_x32_at<32>(dbuf + 32, d);
         tmem_wait_ld();
         tc_fence_before_sync();
-        mbar_arrive(bar + kBarDFree + 8 * half);  // the dP buffer may be overwritten
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar + kBarDFree);  // the dP buffer may be overwritten
+        BWD_STAMP(half, i, 5);
         uint32_t dw[32];
 #pragma unroll
         for (int j2 = 0; j2 < 32; ++j2) {
@@ -441,9 +527,12 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_st_x16(sbuf + 32, dw);
         tmem_st_x16(sbuf + 48, dw + 16);
       }
+      BWD_STAMP(half, i, 6);
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(bar + kBarPFull + 8 * half);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar + kBarPFull);
+      BWD_STAMP(half, i, 7);
     }
 
     // ---- epilogue: accumulators -> scale -> bf16 -> global
@@ -694,6 +783,12 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   kp.scale = p.softmax_scale;
   kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   kp.is_causal = p.is_causal;
+#ifdef SDPA_BWD_STAMPS
+  {
+    const char* env = getenv("SDPA_BWD_STAMPS_PTR");
+    kp.stamps = env ? reinterpret_cast<float*>(strtoull(env, nullptr, 10)) : nullptr;
+  }
+#endif
 
   // heads per group: streamed bytes per head (q + dO of the group, or k + v) within ~48 MB of L2
   auto set_order = [&](int heads_x, int rows_streamed, int streams_per_head) {

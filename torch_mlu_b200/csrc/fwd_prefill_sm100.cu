@@ -168,8 +168,8 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar + kBarSFull + 8 * t, 1);
-      mbar_init(bar + kBarPFull + 16 * t, kBlockM);
-      mbar_init(bar + kBarPFull + 16 * t + 8, kBlockM);
+      mbar_init(bar + kBarPFull + 16 * t, 4);  // one arrival per softmax warp
+      mbar_init(bar + kBarPFull + 16 * t + 8, 4);
       mbar_init(bar + kBarOFull + 8 * t, 1);
     }
     *abort_flag = 0;
@@ -309,7 +309,8 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
 
     for (int j = 0; j < my_blocks; ++j) {
       const int n0 = j * kBlockN;
-      ok = mbar_wait(bar_s, j & 1, abort_flag);
+      // warp-uniform, because the arrivals below are made by one lane on behalf of its warp
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_s, j & 1, abort_flag));
       if (!ok) break;
       const bool stamp_on = stamp_cta && row_in_tile == 0;
       SDPA_STAMP(t, j, 0);
@@ -360,7 +361,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
           m_run = m_new;
           l_run *= alpha;
           // O_t still receives PV(j-1); wait for it before touching the accumulator
-          ok = mbar_wait(bar_o, (j - 1) & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, mbar_wait(bar_o, (j - 1) & 1, abort_flag));
           if (!ok) break;
           tc_fence_after_sync();
 #pragma unroll
@@ -394,7 +395,8 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
           // let the MMA warp start on them while the rest of the row is exponentiated
           tmem_wait_st();
           tc_fence_before_sync();
-          mbar_arrive(bar_p);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_p);
         }
         // P_t overwrites the front of S_t: 8 columns = 16 keys per store
         asm volatile(
@@ -407,7 +409,8 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       SDPA_STAMP(t, j, 3);
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(bar_p + 8);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p + 8);
       SDPA_STAMP(t, j, 4);
     }
 
