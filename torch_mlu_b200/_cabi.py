@@ -98,8 +98,6 @@ def load() -> ctypes.CDLL:
     lib.sdpa_b200_merge_partial.restype = c_int
     lib.sdpa_b200_merge_partial.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                             c_int32, c_int64, c_int64, c_int64, c_void_p]
-    lib.sdpa_b200_set_debug_buffer.restype = None
-    lib.sdpa_b200_set_debug_buffer.argtypes = [c_void_p]
     _lib = lib
     return lib
 

@@ -252,17 +252,21 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           use = static_cast<uint32_t>((idx & 1) ? (i >> 1) : i / 3);
         }
         // Slot reuse. dK/dV: the pair of slots of item i - 2 is released by one commit behind its
-        // accumulation GEMMs. dQ has no release commits (they cost the issuer time): V(i) reuses the
-        // slot of V(i-2), whose only reader dP(i-2) is tracked by the dP-full barrier; K(i) reuses the
-        // slot of K(i-3), last read by dQ(i-3), which precedes S(i-1) in the tensor pipe, so the
-        // score-full barrier of S(i-1) covers it. Neither barrier can run a second phase ahead,
-        // because the GEMM of that later phase needs a tile this loop has not loaded yet.
+        // accumulation GEMMs. dQ has no release commits (they cost the issuer time) and watches a
+        // barrier the GEMMs signal anyway: the score-full barrier of S(i-1), waited for before K(i).
+        //   K(i) reuses the slot of K(i-3), last read by dQ(i-3); V(i) reuses the slot of V(i-2), read
+        //   by dP(i-2) only. Both GEMMs are issued before S(i-1) (prologue: S0 dP0 S1; item j: dP(j+1)
+        //   dQ(j) S(j+2)) and the tensor pipe runs in order, so "S(i-1) done" covers both slots; V(i)
+        //   is loaded right behind K(i) and needs no wait of its own.
+        //   A parity wait can only tell "this phase is over" from "it is not" while the barrier is at
+        //   most one phase further on. That holds here: the next phase of this barrier is S(i+1), and
+        //   S(i+1) needs K(i+1), which this loop loads later. (The dP-full barrier would NOT do for
+        //   V(i): dP(i-1) can finish as well before the producer looks, and two phases on the parity
+        //   reads "not yet" again.)
         if (kMode == kModeDKDV) {
           if (!mbar_wait(bar + kBarYEmpty + 8 * (s & ~1), (use & 1u) ^ 1u, abort_flag)) break;
-        } else if (idx & 1) {
-          if (i >= 2 && !mbar_wait(bar + kBarDFull, (i - 2) & 1, abort_flag)) break;
-        } else {
-          if (i >= 3 && !mbar_wait(bar + kBarSFull + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag)) break;
+        } else if ((idx & 1) == 0 && i >= 2) {
+          if (!mbar_wait(bar + kBarSFull + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag)) break;
         }
         const int hi = i / tiles_per_head;
         const int yt = y_lo + (i - hi * tiles_per_head);
@@ -284,6 +288,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tma_load_4d(dst, tm, full, 0, row, hy, bcoord);
         if (kD > 64) tma_load_4d(dst + kHalfBytes, tm, full, 64, row, hy, bcoord);
       }
+      drain_after_abort(abort_flag);
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer

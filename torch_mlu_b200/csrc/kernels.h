@@ -23,10 +23,11 @@ int make_tensor_map_16(bool f16, CUtensorMap* map, const void* base, int head_di
                        int64_t heads, int64_t batch, int64_t row_stride, int64_t head_stride,
                        int64_t batch_stride, int box_rows);
 
-// Prefill forward (TMA + tcgen05). `debug` (nullable, device) receives per-row dumps of the
-// first CTA when the library is asked for them by the test hook.
-int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t stream,
-                       float* debug);
+// Prefill forward (TMA + tcgen05), a persistent kernel with one CTA per SM.
+int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t stream);
+
+// Number of SMs of the current device (cached per device), <= 0 on error.
+int sm_count();
 
 // Split-KV decode forward. Workspace layout is private to decode_splitkv.cu.
 size_t decode_workspace_bytes(const sdpa_b200_params& p, int* num_splits_out);

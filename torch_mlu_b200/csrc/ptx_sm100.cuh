@@ -191,6 +191,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   }
 }
 
+// After a time-out the CTA must not return while copies it started or MMAs it issued are still in
+// flight (they would land in shared memory / TMEM that already belongs to another CTA). One thread
+// calls this before the tear-down barrier; the rest of the CTA waits for it there. 200 us covers any
+// copy or MMA that is still going to finish at all.
+__device__ __forceinline__ void drain_after_abort(volatile uint32_t* abort_flag) {
+  if (*abort_flag == 0) return;
+  const uint64_t t0 = global_timer_ns();
+  while (global_timer_ns() - t0 < 200000ull) {
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // TMA (tiled bulk tensor copies; CTA-local destination, no multicast)
 // ---------------------------------------------------------------------------------------
@@ -394,6 +405,45 @@ __device__ __forceinline__ void umma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint3
 }
 
 // D[tmem] (+)= A[tmem] * B[smem]
+// The same two issue forms with the per-MMA offsets as compile-time immediates that are added INSIDE
+// the asm block. Written as `a_lo + off` in C++, the sums are loop invariants the compiler hoists out
+// of the issue loop - sixteen or more live registers in a thread that only has a few dozen.
+template <uint32_t kIdesc, uint32_t kOffA, uint32_t kOffB, bool kAccumulate>
+__device__ __forceinline__ void umma_ss_off(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b32 ra, rb;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "add.u32 ra, %1, %6;\n\t"
+      "add.u32 rb, %2, %7;\n\t"
+      "mov.b64 da, {ra, %3};\n\t"
+      "mov.b64 db, {rb, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kDescHiSw128), "r"(kIdesc), "r"(kAccumulate ? 1u : 0u), "n"(kOffA),
+      "n"(kOffB)
+      : "memory");
+}
+
+template <uint32_t kIdesc, uint32_t kOffA, uint32_t kOffB>
+__device__ __forceinline__ void umma_ts_off(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b32 ra, rb;\n\t"
+      ".reg .b64 db;\n\t"
+      "add.u32 ra, %1, %6;\n\t"
+      "add.u32 rb, %2, %7;\n\t"
+      "mov.b64 db, {rb, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [ra], db, %4, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(kDescHiSw128), "r"(kIdesc), "r"(accumulate), "n"(kOffA), "n"(kOffB)
+      : "memory");
+}
+
 template <uint32_t kIdesc>
 __device__ __forceinline__ void umma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t accumulate) {
   asm volatile(

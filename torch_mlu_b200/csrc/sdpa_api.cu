@@ -214,9 +214,21 @@ bool use_decode(const sdpa_b200_params* p) {
   return p->cu_seqlens_q == nullptr && p->max_seqlen_q == 1;
 }
 
-float* g_debug_buffer = nullptr;  // test hook, see sdpa_b200_set_debug_buffer
-
 }  // namespace
+
+int sm_count() {
+  static std::mutex mu;
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
 
 int validate_forward_call(const sdpa_b200_params* p) {
   int st = validate_common(p);
@@ -294,7 +306,7 @@ int sdpa_b200_fwd(const sdpa_b200_params* p, void* workspace, size_t workspace_b
     }
     return launch_fwd_decode(*p, workspace, workspace_bytes, s);
   }
-  return launch_fwd_prefill(*p, workspace, s, g_debug_buffer);
+  return launch_fwd_prefill(*p, workspace, s);
 }
 
 int sdpa_b200_bwd(const sdpa_b200_params* p, void* workspace, size_t workspace_bytes, void* stream) {
@@ -342,10 +354,5 @@ int sdpa_b200_read_device_status(const void* workspace, void* stream, int* devic
   *device_status = static_cast<int>(word);
   return SDPA_B200_OK;
 }
-
-// Test hook (not declared in the public header): a device buffer of 2*128*260 floats that
-// receives, for the first CTA of the next prefill launches, each row's raw first S tile,
-// its un-normalised O accumulator and its running (max, sum). Pass NULL to switch it off.
-SDPA_B200_API void sdpa_b200_set_debug_buffer(float* device_buffer) { g_debug_buffer = device_buffer; }
 
 }  // extern "C"
