@@ -65,11 +65,15 @@ constexpr uint32_t kBarOFree = kBarOFull + 16;             // 2: the epilogue ha
 constexpr uint32_t kBarQFree = kBarOFree + 16;             // the unit's last QK^T has read the Q tiles
 constexpr uint32_t kBarUnitFull = kBarQFree + 8;           // kUnitRing: the scheduler has written the entry
 constexpr uint32_t kBarUnitEmpty = kBarUnitFull + 16;      // kUnitRing: every reader has copied the entry
-constexpr uint32_t kSmemTmemPtr = kBarUnitEmpty + 16;
+constexpr uint32_t kBarStageFree = kBarUnitEmpty + 16;     // 2: the warpgroup's staging buffer may be rewritten
+constexpr uint32_t kBarStageFull = kBarStageFree + 16;     // 2: all four warps have written their rows
+constexpr uint32_t kSmemTmemPtr = kBarStageFull + 16;
 constexpr uint32_t kSmemAbort = kSmemTmemPtr + 4;
 constexpr uint32_t kSmemUnits = 256;  // offset of the Unit ring from kSmemBar (2 x 64 bytes)
-constexpr uint32_t kSmemStash = 512;   // per softmax thread: output row and lse pointers of the current unit
-constexpr uint32_t kSmemUsed = kSmemBar + 512 + 256 * 16;
+constexpr uint32_t kSmemStash = 512;   // per softmax warp: the unit's coordinates for the epilogue (8 x 32 bytes)
+constexpr uint32_t kSmemStage = kSmemBar + 1024;  // 2 x 16 KB: one 64-column half of an O tile per softmax warpgroup
+constexpr uint32_t kStageBytes = kBlockM * 128;
+constexpr uint32_t kSmemUsed = kSmemStage + 2 * kStageBytes;
 constexpr uint32_t kSmemBytes = kSmemUsed + 1024;  // slack for manual 1024-byte alignment
 
 struct FwdKernelParams {
@@ -255,7 +259,8 @@ template <int kD, bool kF16>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_v, const FwdKernelParams p) {
+                   const __grid_constant__ CUtensorMap tm_v,
+                   const __grid_constant__ CUtensorMap tm_o, const FwdKernelParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -280,6 +285,8 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       mbar_init(bar + kBarPFull + 16 * t + 8, 4);
       mbar_init(bar + kBarOFull + 8 * t, 1);
       mbar_init(bar + kBarOFree + 8 * t, 4);
+      mbar_init(bar + kBarStageFree + 8 * t, 1);
+      mbar_init(bar + kBarStageFull + 8 * t, 4);
     }
     for (int e = 0; e < kUnitRing; ++e) {
       mbar_init(bar + kBarUnitFull + 8 * e, 1);
@@ -471,7 +478,8 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t bar_o = bar + kBarOFull + 8 * t;
     const float c = p.scale_log2;
     const float neg_inf = -INFINITY;
-    uint32_t cnt = 0;  // key blocks this tile has processed so far (phase of the S/P/O barriers)
+    uint32_t cnt = 0;     // key blocks this tile has processed so far (phase of the S/P/O barriers)
+    uint32_t st_cnt = 0;  // 64-column output stores this warpgroup has staged so far
     uint32_t ucnt = 0;
     bool ok = true;
 
@@ -479,24 +487,32 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       Unit u;
       ok = read_unit(smem, bar, n, true, abort_flag, u);
       if (!ok || u.done) break;
-      // everything the block loop and the epilogue need from the unit, so that `u` dies here
+      // everything the block loop needs from the unit, so that `u` dies here; what only the epilogue
+      // needs waits in shared memory (one slot per warp), not in registers
       const int row_lo = u.m0 + t * kBlockM;
       const int row = row_lo + row_in_tile;
       const int my_blocks = u.nblk[t];
-      const bool valid = row < u.len_q;
-      uint16_t* orow;
-      float* lse_ptr;
-      if (p.cu_q != nullptr) {
-        orow = p.out + static_cast<int64_t>(u.q_off + row) * p.o_row_stride + u.h * p.o_head_stride;
-        lse_ptr = p.lse + static_cast<int64_t>(u.h) * p.total_q + u.q_off + row;
-      } else {
-        orow = p.out + u.b * p.o_batch_stride + u.h * p.o_head_stride + static_cast<int64_t>(row) * p.o_row_stride;
-        lse_ptr = p.lse + (static_cast<int64_t>(u.b) * p.heads_q + u.h) * p.seqlen_q + row;
+      int* info = reinterpret_cast<int*>(smem + kSmemBar + kSmemStash) + 8 * warp;
+      if (lane == 0) {
+        info[0] = u.q_off;
+        info[1] = u.h;
+        info[2] = u.b;
+        info[3] = u.len_q;
       }
+      __syncwarp();
       if (u.n_iter == 0) {
         // no key is visible to any row of the unit (causal with more queries than keys): the other
         // roles skip it, the rows get out = 0 and lse = +inf
-        if (valid) {
+        if (row < u.len_q) {
+          uint16_t* orow;
+          float* lse_ptr;
+          if (p.cu_q != nullptr) {
+            orow = p.out + static_cast<int64_t>(u.q_off + row) * p.o_row_stride + u.h * p.o_head_stride;
+            lse_ptr = p.lse + static_cast<int64_t>(u.h) * p.total_q + u.q_off + row;
+          } else {
+            orow = p.out + u.b * p.o_batch_stride + u.h * p.o_head_stride + static_cast<int64_t>(row) * p.o_row_stride;
+            lse_ptr = p.lse + (static_cast<int64_t>(u.b) * p.heads_q + u.h) * p.seqlen_q + row;
+          }
           uint4* dst = reinterpret_cast<uint4*>(orow);
 #pragma unroll
           for (int i = 0; i < kD / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -508,11 +524,6 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       // keys at index >= col_limit are invisible to this row; blocks reaching past mask_from need the mask
       const int col_limit = p.is_causal ? min(len_k, row + u.causal_off + 1) : len_k;
       const int mask_from = p.is_causal ? min(len_k, row_lo + u.causal_off + 1) : len_k;
-      // The epilogue's pointers wait in shared memory, not in registers, while the block loop runs
-      // (a null output pointer marks a row past the end of the sequence).
-      uint64_t* stash = reinterpret_cast<uint64_t*>(smem + kSmemBar + kSmemStash) + 2 * threadIdx.x;
-      stash[0] = valid ? reinterpret_cast<uint64_t>(orow) : 0ull;
-      stash[1] = reinterpret_cast<uint64_t>(lse_ptr);
 
       float m_run = neg_inf;
       float l_run = 0.f;
@@ -622,7 +633,8 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
         if (!ok) break;
       }
       if (row_in_tile == 0) FWD_STAMP(t, ucnt, 3);
-      if (my_blocks > 0 || __any_sync(0xffffffffu, stash[0] != 0ull)) {
+      const int u_q_off = info[0], u_h = info[1], u_b = info[2], u_len_q = info[3];
+      if (row_lo < u_len_q) {
         tc_fence_after_sync();
         const float inv_l = (l_run > 0.f) ? 1.f / l_run : 0.f;
         uint32_t w[kD / 2];
@@ -646,13 +658,52 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
         __syncwarp();
         if (lane == 0) mbar_arrive(bar + kBarOFree + 8 * t);
         if (row_in_tile == 0) FWD_STAMP(t, ucnt, 4);
-        uint16_t* out_row = reinterpret_cast<uint16_t*>(stash[0]);
-        if (out_row != nullptr) {
-          uint4* dst = reinterpret_cast<uint4*>(out_row);
+        const bool valid = row < u_len_q;
+        // A whole 128-row tile goes out as TMA stores (64 columns at a time through a 16 KB staging
+        // buffer per warpgroup): asynchronous and fully coalesced. Dense tensors are clipped by the
+        // tensor map; a packed (varlen) tile that ends inside its sequence's last rows would spill
+        // into the next sequence, so it is written row by row from registers instead.
+        if (p.cu_q == nullptr || row_lo + kBlockM <= u_len_q) {
+          // (mbarriers with bounded waits rather than bar.sync: a warp that has given up must not
+          // leave the other three waiting for it forever)
+          uint8_t* stage = smem + kSmemStage + t * kStageBytes + row_in_tile * 128;
+#pragma unroll
+          for (int half = 0; half < kD / 64; ++half, ++st_cnt) {
+            if (row_in_tile == 0) {
+              tma_store_wait_read();  // the previous store has left the buffer
+              mbar_arrive(bar + kBarStageFree + 8 * t);
+            }
+            ok = __all_sync(0xffffffffu, mbar_wait(bar + kBarStageFree + 8 * t, st_cnt & 1, abort_flag));
+            if (!ok) break;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+              *reinterpret_cast<uint4*>(stage + ((ch ^ (row_in_tile & 7)) << 4)) =
+                  make_uint4(w[half * 32 + 4 * ch], w[half * 32 + 4 * ch + 1], w[half * 32 + 4 * ch + 2],
+                             w[half * 32 + 4 * ch + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar + kBarStageFull + 8 * t);
+            if (row_in_tile == 0) {
+              if (mbar_wait(bar + kBarStageFull + 8 * t, st_cnt & 1, abort_flag)) {
+                tma_store_4d(&tm_o, base + kSmemStage + t * kStageBytes, half * 64, u_q_off + row_lo, u_h,
+                             p.cu_q != nullptr ? 0 : u_b);
+                tma_store_commit();
+              }
+            }
+          }
+          if (!ok) break;
+        } else if (valid) {
+          uint4* dst = reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(u_q_off + row) * p.o_row_stride +
+                                                u_h * p.o_head_stride);
 #pragma unroll
           for (int i = 0; i < kD / 8; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        }
+        if (valid) {
+          float* lse_ptr = (p.cu_q != nullptr)
+                               ? p.lse + static_cast<int64_t>(u_h) * p.total_q + u_q_off + row
+                               : p.lse + (static_cast<int64_t>(u_b) * p.heads_q + u_h) * p.seqlen_q + row;
           const float kLn2 = 0.6931471805599453f;
-          *reinterpret_cast<float*>(stash[1]) = (l_run > 0.f) ? (m_run + log2f(l_run)) * kLn2 : INFINITY;
+          *lse_ptr = (l_run > 0.f) ? (m_run + log2f(l_run)) * kLn2 : INFINITY;
         }
       } else {
         __syncwarp();
@@ -662,6 +713,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       cnt += my_blocks;
       ++ucnt;
     }
+    if (row_in_tile == 0) tma_store_wait_all();  // the CTA's shared memory must outlive its stores
   }
 
   // ------------------------------------------------------------------ tear-down
@@ -679,7 +731,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
 int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t stream) {
   const bool varlen = p.cu_seqlens_q != nullptr;
   const bool f16 = p.dtype == SDPA_B200_F16;
-  CUtensorMap tm_q, tm_k, tm_v;
+  CUtensorMap tm_q, tm_k, tm_v, tm_o;
   int st;
   const int64_t rows_q = varlen ? p.total_q : p.max_seqlen_q;
   const int64_t rows_k = varlen ? p.total_k : p.max_seqlen_k;
@@ -692,6 +744,9 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
   if (st != SDPA_B200_OK) return st;
   st = make_tensor_map_16(f16, &tm_v, p.v, p.head_dim, rows_k, p.heads_kv, nb, p.v_row_stride,
                           p.v_head_stride, p.v_batch_stride, kBlockN);
+  if (st != SDPA_B200_OK) return st;
+  st = make_tensor_map_16(f16, &tm_o, p.out, p.head_dim, rows_q, p.heads_q, nb, p.o_row_stride,
+                          p.o_head_stride, p.o_batch_stride, kBlockM);
   if (st != SDPA_B200_OK) return st;
 
   FwdKernelParams kp;
@@ -745,7 +800,7 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
   }
   // one persistent CTA per SM (shared memory and TMEM allow no second one)
   dim3 grid(kp.num_slots < sms ? kp.num_slots : sms, 1, 1);
-  kernel<<<grid, kNumThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, kp);
+  kernel<<<grid, kNumThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, kp);
   err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("prefill: launch failed: %s", cudaGetErrorString(err));
