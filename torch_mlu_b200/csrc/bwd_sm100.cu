@@ -607,7 +607,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, SDPA_B200_DEVICE_TIMEOUT);
 }
 
-// delta[row] = sum_d dO[row,d] * O[row,d]; lse2[row] = lse[row] * log2(e). One warp per row,
+// delta[row] = sum_d dO[row,d] * O[row,d]; lse2[row] = lse[row] * log2(e);
 // rows padded to lq_pad per (batch, head): padding rows get lse2 = +inf, delta = 0.
 struct PreParams {
   const uint16_t* out;
@@ -621,52 +621,71 @@ struct PreParams {
   int seqlen_q, total_q, heads_q, lq_pad, head_dim;
 };
 
+// 16 bytes (8 elements) per thread and head_dim / 8 threads per row; a 256-thread block covers 64 rows of
+// the padded sequence in up to four passes whose loads are all issued before the first use.
+constexpr int kPreRows = 64;
 template <bool kF16>
 __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreParams p) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = blockIdx.x * 8 + warp;  // row within the padded sequence
-  const int h = blockIdx.y, b = blockIdx.z;
-  if (row >= p.lq_pad) return;
+  // heads vary fastest across the grid: with the usual [batch, row, head, dim] memory order the blocks
+  // that run together then read neighbouring 256-byte pieces of the same rows
+  const int h = blockIdx.x, b = blockIdx.z;
+  const int tpr = p.head_dim >> 3;          // threads per row: 16 (head_dim 128) or 8 (64)
+  const int rows_per_pass = 256 / tpr;      // 16 or 32
+  const int passes = kPreRows / rows_per_pass;  // 4 or 2
+  const int sub = threadIdx.x % tpr;
+  const int r_in_pass = threadIdx.x / tpr;
   int q_off = 0, len_q = p.seqlen_q;
   if (p.cu_q != nullptr) {
     q_off = p.cu_q[b];
     len_q = p.cu_q[b + 1] - q_off;
   }
-  const size_t dst = (static_cast<size_t>(b) * p.heads_q + h) * p.lq_pad + row;
-  if (row >= len_q) {
-    if (lane == 0) {
-      p.lse2[dst] = INFINITY;
-      p.delta[dst] = 0.f;
-    }
-    return;
-  }
-  const uint16_t* o;
-  const uint16_t* dout;
-  float lse;
-  if (p.cu_q != nullptr) {
-    o = p.out + static_cast<int64_t>(q_off + row) * p.o_row_stride + h * p.o_head_stride;
-    dout = p.dout + static_cast<int64_t>(q_off + row) * p.do_row_stride + h * p.do_head_stride;
-    lse = p.lse[static_cast<size_t>(h) * p.total_q + q_off + row];
-  } else {
-    o = p.out + b * p.o_batch_stride + h * p.o_head_stride + static_cast<int64_t>(row) * p.o_row_stride;
-    dout = p.dout + b * p.do_batch_stride + h * p.do_head_stride + static_cast<int64_t>(row) * p.do_row_stride;
-    lse = p.lse[(static_cast<size_t>(b) * p.heads_q + h) * p.seqlen_q + row];
-  }
-  uint2 ov = make_uint2(0u, 0u), dv = make_uint2(0u, 0u);
-  if (lane * 4 < p.head_dim) {
-    ov = *reinterpret_cast<const uint2*>(o + lane * 4);
-    dv = *reinterpret_cast<const uint2*>(dout + lane * 4);
-  }
-  const float2 o0 = unpack_16x2<kF16>(ov.x), o1 = unpack_16x2<kF16>(ov.y);
-  const float2 d0 = unpack_16x2<kF16>(dv.x), d1 = unpack_16x2<kF16>(dv.y);
-  float acc = o0.x * d0.x + o0.y * d0.y + o1.x * d1.x + o1.y * d1.y;
+  uint4 ov[4], dv[4];
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) {
-    p.lse2[dst] = lse * 1.4426950408889634f;  // +inf stays +inf
-    p.delta[dst] = acc;
+  for (int ps = 0; ps < 4; ++ps) {
+    ov[ps] = make_uint4(0u, 0u, 0u, 0u);
+    dv[ps] = make_uint4(0u, 0u, 0u, 0u);
+    const int row = blockIdx.y * kPreRows + ps * rows_per_pass + r_in_pass;
+    if (ps < passes && row < len_q) {
+      const uint16_t* o;
+      const uint16_t* dout;
+      if (p.cu_q != nullptr) {
+        o = p.out + static_cast<int64_t>(q_off + row) * p.o_row_stride + h * p.o_head_stride;
+        dout = p.dout + static_cast<int64_t>(q_off + row) * p.do_row_stride + h * p.do_head_stride;
+      } else {
+        o = p.out + b * p.o_batch_stride + h * p.o_head_stride + static_cast<int64_t>(row) * p.o_row_stride;
+        dout = p.dout + b * p.do_batch_stride + h * p.do_head_stride + static_cast<int64_t>(row) * p.do_row_stride;
+      }
+      ov[ps] = *reinterpret_cast<const uint4*>(o + sub * 8);
+      dv[ps] = *reinterpret_cast<const uint4*>(dout + sub * 8);
+    }
+  }
+#pragma unroll
+  for (int ps = 0; ps < 4; ++ps) {
+    if (ps >= passes) break;
+    const int row = blockIdx.y * kPreRows + ps * rows_per_pass + r_in_pass;
+    const float2 o0 = unpack_16x2<kF16>(ov[ps].x), o1 = unpack_16x2<kF16>(ov[ps].y);
+    const float2 o2 = unpack_16x2<kF16>(ov[ps].z), o3 = unpack_16x2<kF16>(ov[ps].w);
+    const float2 d0 = unpack_16x2<kF16>(dv[ps].x), d1 = unpack_16x2<kF16>(dv[ps].y);
+    const float2 d2 = unpack_16x2<kF16>(dv[ps].z), d3 = unpack_16x2<kF16>(dv[ps].w);
+    float acc = (o0.x * d0.x + o0.y * d0.y) + (o1.x * d1.x + o1.y * d1.y) + (o2.x * d2.x + o2.y * d2.y) +
+                (o3.x * d3.x + o3.y * d3.y);
+    // the tpr threads of a row are consecutive lanes of one warp
+    for (int off = tpr >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (sub == 0 && row < p.lq_pad) {
+      const size_t dst = (static_cast<size_t>(b) * p.heads_q + h) * p.lq_pad + row;
+      if (row < len_q) {
+        const float lse = (p.cu_q != nullptr) ? p.lse[static_cast<size_t>(h) * p.total_q + q_off + row]
+                                              : p.lse[(static_cast<size_t>(b) * p.heads_q + h) * p.seqlen_q + row];
+        p.lse2[dst] = lse * 1.4426950408889634f;  // +inf stays +inf
+        p.delta[dst] = acc;
+      } else {
+        p.lse2[dst] = INFINITY;
+        p.delta[dst] = 0.f;
+      }
+    }
   }
 }
+
 
 using TileKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
                             const BwdKernelParams);
@@ -733,9 +752,9 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   pre.lq_pad = lq_pad;
   pre.head_dim = p.head_dim;
   if (f16)
-    bwd_preprocess_kernel<true><<<dim3(lq_pad / 8, p.heads_q, p.batch), 256, 0, stream>>>(pre);
+    bwd_preprocess_kernel<true><<<dim3(p.heads_q, lq_pad / kPreRows, p.batch), 256, 0, stream>>>(pre);
   else
-    bwd_preprocess_kernel<false><<<dim3(lq_pad / 8, p.heads_q, p.batch), 256, 0, stream>>>(pre);
+    bwd_preprocess_kernel<false><<<dim3(p.heads_q, lq_pad / kPreRows, p.batch), 256, 0, stream>>>(pre);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("backward preprocess: launch failed: %s", cudaGetErrorString(err));
