@@ -447,18 +447,29 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       // ------------------------------------------------------------------ unit scheduler
       if (lane == 0) {
         bool ok = true;
+        // Claiming ahead hides the claim (atomic + decode) and lets the producer prefetch the next Q
+        // tiles, but near the end of the list a unit claimed early by a busy CTA is a unit an idle CTA
+        // cannot take. For the last two rounds of the grid the scheduler therefore claims late: only
+        // once the last QK^T of the unit it published before has been issued (the Q-free barrier).
+        bool lazy = false;
+        bool last_runs = false;  // the unit published last has key blocks (and so a Q-free phase)
+        uint32_t ucnt = 0;       // such units published so far
         for (uint32_t n = 0; ok; ++n) {
           const uint32_t e = n % kUnitRing;
           ok = mbar_wait(bar + kBarUnitEmpty + 8 * e, ((n / kUnitRing) & 1u) ^ 1u, abort_flag);
+          if (ok && lazy && last_runs) ok = mbar_wait(bar + kBarQFree, (ucnt - 1) & 1, abort_flag);
           if (!ok) break;
           Unit u;
           u.done = 1;
           for (;;) {
             const int slot = static_cast<int>(atomicAdd(p.unit_counter, 1u));
             if (slot >= p.num_slots) break;
+            if (slot >= p.num_slots - 2 * static_cast<int>(gridDim.x)) lazy = true;
             if (decode_unit(p, slot, u)) break;  // padding slots and row-less units are skipped
             u.done = 1;
           }
+          last_runs = !u.done && u.n_iter > 0;
+          if (last_runs) ++ucnt;
           write_unit(smem, e, u);
           mbar_arrive(bar + kBarUnitFull + 8 * e);  // release: the entry is visible to whoever sees the phase
           if (u.done) break;
