@@ -40,7 +40,7 @@ constexpr uint32_t kHalfBytes = kTileBytes / 2;
 // the per-query vectors), 5 for dQ so that K(i+2) can land while item i is still accumulating.
 constexpr int kMaxStages = 5;
 __host__ __device__ constexpr int stages_for(int mode) { return mode == 1 ? 5 : 4; }
-constexpr int kThreads = 320;  // warps 0-3 / 4-7 compute (column halves), warp 8 TMA, warp 9 MMA
+constexpr int kThreads = 352;  // warps 0-3 / 4-7 compute (column halves), warp 8 TMA, warps 9 and 10 MMA issuers
 constexpr int kModeDKDV = 0;
 constexpr int kModeDQ = 1;
 
@@ -58,7 +58,10 @@ constexpr uint32_t kBarDFull = kBarSFull + 16;             // second score GEMM 
 constexpr uint32_t kBarDFree = kBarDFull + 8;              // all compute warps have read dP out of TMEM
 constexpr uint32_t kBarPFull = kBarDFree + 16;             // all compute warps have stored P / dS
 constexpr uint32_t kBarAccFull = kBarPFull + 16;
-constexpr uint32_t kSmemTmemPtr = kBarAccFull + 8;
+constexpr uint32_t kBarP1Full = kBarAccFull + 8;           // dK/dV: all compute warps have stored P (dS still to come)
+constexpr uint32_t kBarWFree = kBarP1Full + 8;             // 2 (item parity): the accumulation GEMMs have read P / dS
+constexpr uint32_t kBarSIssued = kBarWFree + 16;           // dK/dV: the next item's score GEMM is in the pipe
+constexpr uint32_t kSmemTmemPtr = kBarSIssued + 8;
 constexpr uint32_t kSmemAbort = kSmemTmemPtr + 4;
 
 struct BwdKernelParams {
@@ -206,6 +209,10 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(bar + kBarDFull, 1);
     mbar_init(bar + kBarDFree, 8);  // one arrival per compute warp
     mbar_init(bar + kBarPFull, 8);
+    mbar_init(bar + kBarP1Full, 8);
+    mbar_init(bar + kBarWFree, 1);
+    mbar_init(bar + kBarWFree + 8, 1);
+    mbar_init(bar + kBarSIssued, 1);
     mbar_init(bar + kBarAccFull, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -225,7 +232,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // a long-running block of batch 0, head 0 (non-causal: any; causal: the heaviest)
   const bool stamp_on = p.stamps != nullptr && b == 0 && hx == 0 &&
                         xb == ((kMode == kModeDKDV) ? 0 : p.num_row_blocks - 1) && (lane == 0) &&
-                        (warp == 0 || warp == 4 || warp == 9);
+                        (warp == 0 || warp == 4 || warp == 9 || warp == 10);
 #endif
 
   if (warp == 8) {
@@ -255,9 +262,10 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // accumulation GEMMs. dQ has no release commits (they cost the issuer time) and watches a
         // barrier the GEMMs signal anyway: the score-full barrier of S(i-1), waited for before K(i).
         //   K(i) reuses the slot of K(i-3), last read by dQ(i-3); V(i) reuses the slot of V(i-2), read
-        //   by dP(i-2) only. Both GEMMs are issued before S(i-1) (prologue: S0 dP0 S1; item j: dP(j+1)
-        //   dQ(j) S(j+2)) and the tensor pipe runs in order, so "S(i-1) done" covers both slots; V(i)
-        //   is loaded right behind K(i) and needs no wait of its own.
+        //   by dP(i-2) only. S(i-1) overwrites the buffer of dS(i-3), so its issuer has waited for
+        //   dQ(i-3) (`W free`), and it issues dP(i-2) before S(i-1) itself (prologue: S0 dP0 S1; item j:
+        //   dP(j+1), S(j+2)); the tensor pipe keeps the order of one thread's MMAs. So "S(i-1) done"
+        //   covers both slots; V(i) is loaded right behind K(i) and needs no wait of its own.
         //   A parity wait can only tell "this phase is over" from "it is not" while the barrier is at
         //   most one phase further on. That holds here: the next phase of this barrier is S(i+1), and
         //   S(i+1) needs K(i+1), which this loop loads later. (The dP-full barrier would NOT do for
@@ -290,15 +298,25 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       drain_after_abort(abort_flag);
     }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == 9 || warp == 10) {
+    // ------------------------------------------------------------------ MMA issuers
+    // One thread needs ~50-65 cycles to issue an MMA and ~70 for every barrier wait or commit, about
+    // as long as the tensor pipe needs to execute it, and an item has 24 (dQ) or 32 (dK/dV) MMAs
+    // plus half a dozen waits: a single issuer is the bottleneck. So two threads issue:
+    //   warp 9  the score GEMMs   S = X1 Y1^T, dP = X2 Y2^T            (operands in shared memory)
+    //   warp 10 the accumulations dV += P^T dO, dK += dS^T Q / dQ += dS K (A operand in TMEM)
+    // What the in-order pipe would guarantee between the two groups is a barrier here: `W free`
+    // (warp 10 commits it behind an item's accumulation MMAs; warp 9 waits for it before a score GEMM
+    // overwrites that item's P / dS buffer). There is one per item parity, so that the barrier a wait
+    // looks at cannot be a whole phase further on: its next phase belongs to item i+2, whose scores
+    // only exist after this wait.
     if (lane == 0 && n_items > 0) {
       // Where the score GEMMs of item i land:
-      //   dK/dV: S(i) in T[i&1], dP(i) in T[(i&1)^1]. The compute warpgroups put BOTH bf16 results
+      //   dK/dV: S(i) in T[i&1], dP(i) in T[(i&1)^1]. The compute warpgroups put BOTH 16-bit results
       //          (P and dS) into the S buffer, so the dP buffer is free once it has been read and
-      //          takes S(i+1) right away; dP(i+1) follows the accumulation MMAs into the S buffer.
+      //          takes S(i+1) right away; dP(i+1) goes into the S buffer behind the accumulations.
       //   dQ:    ACC2 is unused, so S alternates between T1 and ACC2 and dP always uses T2: S(i+2)
-      //          is issued right behind the accumulation of item i, dP(i+1) as soon as dP(i) is read.
+      //          follows the accumulation of item i, dP(i+1) goes out as soon as dP(i) is read.
       // Either way the next item's scores and exponentials run under this item's accumulation.
       const uint32_t x1 = base + kSmemX, x2 = base + kSmemX + kTileBytes;
       auto s_buf = [&](int i) { return kMode == kModeDKDV ? ((i & 1) ? t2 : t1) : ((i & 1) ? acc2 : t1); };
@@ -326,97 +344,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           lap = j >> 1;
         }
       };
-      auto y_slot_k = [&](int k) { int sl, lp; pos(k, sl, lp); return base + kSmemY + sl * kTileBytes; };
-      auto y_wait_k = [&](int k) { int sl, lp; pos(k, sl, lp); return mbar_wait(bar + kBarYFull + 8 * sl, lp & 1, abort_flag); };
-      auto y_free_k = [&](int k) { int sl, lp; pos(k, sl, lp); umma_commit(bar + kBarYEmpty + 8 * sl); };
-      auto y_slot = [&](int idx) { return y_slot_k(idx); };  // prologue only (item 0: idx == k)
-      auto y_wait = [&](int idx) { return y_wait_k(idx); };
-      bool ok = mbar_wait(bar + kBarXFull, 0, abort_flag) && y_wait(0);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_xyT<kD, kF16>(s_buf(0), x1, y_slot(0));
-        umma_commit(s_bar(0));
-      }
-      ok = ok && y_wait(1);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_xyT<kD, kF16>(d_buf(0), x2, y_slot(1));
-        umma_commit(bar + kBarDFull);
-      }
-      if (kMode == kModeDQ && ok && n_items > 1) {
-        ok = y_wait(2);
-        if (ok) {
-          tc_fence_after_sync();
-          issue_xyT<kD, kF16>(s_buf(1), x1, y_slot(2));
-          umma_commit(s_bar(1));
-        }
-      }
-      for (int i = 0; ok && i < n_items; ++i) {
-        const uint32_t y1 = y_slot_k(0), y2 = y_slot_k(1);
-        const uint32_t sbuf = s_buf(i);
-        const bool more = i + 1 < n_items;
-        BWD_STAMP(2, i, 0);
-        // dP(i) has left TMEM once both column halves have read it
-        ok = mbar_wait(bar + kBarDFree, i & 1, abort_flag);
-        if (!ok) break;
-        BWD_STAMP(2, i, 1);
-        if (more) {
-          if (kMode == kModeDKDV) {
-            ok = y_wait_k(2);
-            if (!ok) break;
-            BWD_STAMP(3, i, 0);
-            tc_fence_after_sync();
-            issue_xyT<kD, kF16>(d_buf(i), x1, y_slot_k(2));  // S(i+1) into the buffer dP(i) has just left
-            BWD_STAMP(3, i, 1);
-            umma_commit(s_bar(i + 1));
-          } else {
-            ok = y_wait_k(3);
-            if (!ok) break;
-            BWD_STAMP(3, i, 0);
-            tc_fence_after_sync();
-            issue_xyT<kD, kF16>(t2, x2, y_slot_k(3));  // dP(i+1)
-            BWD_STAMP(3, i, 1);
-            umma_commit(bar + kBarDFull);
-          }
-        }
-        BWD_STAMP(2, i, 2);
-        ok = mbar_wait(bar + kBarPFull, i & 1, abort_flag);
-        if (!ok) break;
-        BWD_STAMP(2, i, 3);
-        tc_fence_after_sync();
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          if (kMode == kModeDKDV) {
-            issue_wy_half<kD, kF16>(acc1, sbuf + half * 64, y2, half, i > 0);       // dV += P^T dO
-            issue_wy_half<kD, kF16>(acc2, sbuf + half * 64 + 32, y1, half, i > 0);  // dK += dS^T Q
-          } else {
-            issue_wy_half<kD, kF16>(acc1, sbuf + half * 64 + 32, y1, half, i > 0);  // dQ += dS K
-          }
-          BWD_STAMP(3, i, 3 + half);
-        }
-        if (kMode == kModeDKDV) y_free_k(0);  // releases the slot pair Q(i), dO(i)
-        BWD_STAMP(2, i, 4);
-        if (i == n_items - 1) umma_commit(bar + kBarAccFull);
-        if (kMode == kModeDKDV) {
-          if (more) {
-            ok = y_wait_k(3);
-            if (!ok) break;
-            BWD_STAMP(3, i, 5);
-            tc_fence_after_sync();
-            issue_xyT<kD, kF16>(sbuf, x2, y_slot_k(3));  // dP(i+1), behind the MMAs reading P(i), dS(i)
-            BWD_STAMP(3, i, 6);
-            umma_commit(bar + kBarDFull);
-          }
-        } else if (i + 2 < n_items) {
-          ok = y_wait_k(4);
-          if (!ok) break;
-          BWD_STAMP(3, i, 5);
-          tc_fence_after_sync();
-          issue_xyT<kD, kF16>(sbuf, x1, y_slot_k(4));  // S(i+2), behind the MMAs reading dS(i)
-          BWD_STAMP(3, i, 6);
-          umma_commit(s_bar(i + 2));
-        }
-        BWD_STAMP(2, i, 5);
+      auto advance = [&]() {
         ++item;
         if (kMode == kModeDKDV) {
           ring_slot += 2;
@@ -424,6 +352,119 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         } else if (++ring_slot == 3) {
           ring_slot = 0;
           ++ring_lap;
+        }
+      };
+      auto y_slot_k = [&](int k) { int sl, lp; pos(k, sl, lp); return base + kSmemY + sl * kTileBytes; };
+      auto y_wait_k = [&](int k) { int sl, lp; pos(k, sl, lp); return mbar_wait(bar + kBarYFull + 8 * sl, lp & 1, abort_flag); };
+      auto y_free_k = [&](int k) { int sl, lp; pos(k, sl, lp); umma_commit(bar + kBarYEmpty + 8 * sl); };
+      bool ok = true;
+      if (warp == 9) {
+        // ---------------- score GEMMs
+        ok = mbar_wait(bar + kBarXFull, 0, abort_flag) && y_wait_k(0);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_xyT<kD, kF16>(s_buf(0), x1, y_slot_k(0));
+          umma_commit(s_bar(0));
+        }
+        ok = ok && y_wait_k(1);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_xyT<kD, kF16>(d_buf(0), x2, y_slot_k(1));
+          umma_commit(bar + kBarDFull);
+        }
+        if (kMode == kModeDQ && ok && n_items > 1) {
+          ok = y_wait_k(2);
+          if (ok) {
+            tc_fence_after_sync();
+            issue_xyT<kD, kF16>(s_buf(1), x1, y_slot_k(2));
+            umma_commit(s_bar(1));
+          }
+        }
+        for (int i = 0; ok && i < n_items; ++i, advance()) {
+          const uint32_t sbuf = s_buf(i);
+          const bool more = i + 1 < n_items;
+          BWD_STAMP(2, i, 0);
+          // dP(i) has left TMEM once all compute warps have read it
+          ok = mbar_wait(bar + kBarDFree, i & 1, abort_flag);
+          if (!ok) break;
+          BWD_STAMP(2, i, 1);
+          if (kMode == kModeDKDV) {
+            if (!more) {
+              mbar_arrive(bar + kBarSIssued);
+              continue;
+            }
+            ok = y_wait_k(2);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_xyT<kD, kF16>(d_buf(i), x1, y_slot_k(2));  // S(i+1) into the buffer dP(i) has just left
+            umma_commit(s_bar(i + 1));
+            // S(i+1) is what the compute warps wait for; dK(i) is not urgent. The other issuer holds
+            // dK(i) back until this arrival, so the two GEMMs do not share the pipe MMA by MMA.
+            mbar_arrive(bar + kBarSIssued);
+            BWD_STAMP(2, i, 2);
+            ok = mbar_wait(bar + kBarWFree + 8 * (i & 1), (i >> 1) & 1, abort_flag) && y_wait_k(3);
+            if (!ok) break;
+            BWD_STAMP(2, i, 3);
+            tc_fence_after_sync();
+            issue_xyT<kD, kF16>(sbuf, x2, y_slot_k(3));  // dP(i+1) into the buffer P(i), dS(i) have left
+            umma_commit(bar + kBarDFull);
+            BWD_STAMP(2, i, 4);
+          } else {
+            if (more) {
+              ok = y_wait_k(3);
+              if (!ok) break;
+              tc_fence_after_sync();
+              issue_xyT<kD, kF16>(t2, x2, y_slot_k(3));  // dP(i+1)
+              umma_commit(bar + kBarDFull);
+            }
+            BWD_STAMP(2, i, 2);
+            if (i + 2 < n_items) {
+              ok = mbar_wait(bar + kBarWFree + 8 * (i & 1), (i >> 1) & 1, abort_flag) && y_wait_k(4);
+              if (!ok) break;
+              BWD_STAMP(2, i, 3);
+              tc_fence_after_sync();
+              issue_xyT<kD, kF16>(sbuf, x1, y_slot_k(4));  // S(i+2) into the buffer dS(i) has left
+              umma_commit(s_bar(i + 2));
+              BWD_STAMP(2, i, 4);
+            }
+          }
+        }
+      } else {
+        // ---------------- accumulation GEMMs
+        ok = mbar_wait(bar + kBarXFull, 0, abort_flag);
+        for (int i = 0; ok && i < n_items; ++i, advance()) {
+          const uint32_t y1 = y_slot_k(0), y2 = y_slot_k(1);
+          const uint32_t sbuf = s_buf(i);
+          // the tiles have landed long ago (the other issuer has used them); this wait makes the
+          // copies visible to this thread's MMAs as well
+          ok = y_wait_k(0) && (kMode == kModeDQ || y_wait_k(1));
+          if (!ok) break;
+          if (kMode == kModeDKDV) {
+            // dV needs P only, which is stored a whole dS pass before the item is complete
+            ok = mbar_wait(bar + kBarP1Full, i & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_wy_half<kD, kF16>(acc1, sbuf, y2, 0, i > 0);       // dV += P^T dO
+            issue_wy_half<kD, kF16>(acc1, sbuf + 64, y2, 1, true);
+          }
+          BWD_STAMP(3, i, 0);
+          ok = mbar_wait(bar + kBarPFull, i & 1, abort_flag);
+          if (!ok) break;
+          BWD_STAMP(3, i, 1);
+          tc_fence_after_sync();
+          if (kMode == kModeDKDV) {
+            ok = mbar_wait(bar + kBarSIssued, i & 1, abort_flag);
+            if (!ok) break;
+            issue_wy_half<kD, kF16>(acc2, sbuf + 32, y1, 0, i > 0);  // dK += dS^T Q
+            issue_wy_half<kD, kF16>(acc2, sbuf + 96, y1, 1, true);
+            y_free_k(0);  // releases the slot pair Q(i), dO(i)
+          } else {
+            issue_wy_half<kD, kF16>(acc1, sbuf + 32, y1, 0, i > 0);  // dQ += dS K
+            issue_wy_half<kD, kF16>(acc1, sbuf + 96, y1, 1, true);
+          }
+          umma_commit(bar + kBarWFree + 8 * (i & 1));
+          if (i == n_items - 1) umma_commit(bar + kBarAccFull);
+          BWD_STAMP(3, i, 2);
         }
       }
     }
@@ -504,6 +545,10 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           for (int j2 = 0; j2 < 32; ++j2) pw[j2] = pack_16x2<kF16>(pr[2 * j2], pr[2 * j2 + 1]);
           tmem_st_x16(sbuf, pw);
           tmem_st_x16(sbuf + 16, pw + 16);
+          tmem_wait_st();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar + kBarP1Full);
         }
       }
       // phase 2 (needs dP): dS = P o (dP - delta) into the second half of this thread's columns
