@@ -39,7 +39,7 @@ WORKLOAD = "bf16 causal prefill forward B=4 Hq=Hkv=32 L=4096 D=128 (seed 1)"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram bytes per launch of the prefill kernel on the headline workload, from the ncu capture
 # summarised in profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES = {"prefill_c2": 5.34e8}  # 2 x 267 MB measured at half the batch (traffic scales with batch)
+NCU_TRAFFIC_BYTES = {"prefill_c2": 6.32e8}  # 2 x 316 MB measured at half the batch (traffic scales with batch)
 
 
 def load_peaks():
