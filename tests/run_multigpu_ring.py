@@ -32,6 +32,12 @@ def main():
         o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=causal)
         orc.assert_close_bf16(out, o_ref[:, :, sl], f"ring out rank {rank} causal={causal}")
         orc.assert_close_lse(lse, l_ref[:, :, sl], max_abs=2e-5)
+    take = lambda t: ring.zigzag_take(t, rank, world)
+    out, lse = ring.ring_prefill(take(q).to(dev), take(k).to(dev), take(v).to(dev), is_causal=True, layout="zigzag")
+    torch.cuda.synchronize()
+    o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=True)
+    orc.assert_close_bf16(out, take(o_ref), f"zig-zag ring out rank {rank}")
+    orc.assert_close_lse(lse, take(l_ref), max_abs=2e-5)
     out, lse, _ = sharding.sdpa_batch_head_sharded(q.to(dev), k.to(dev), v.to(dev), is_causal=True)
     torch.cuda.synchronize()
     o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=True)

@@ -40,6 +40,12 @@ def _worker(rank, world, port, out_dir):
                                      attention_fn=_attn, merge_fn=ring.merge_partial_reference)
         o_ref, l_ref = orc.attention_math(q, k, v, causal=causal)
         results[causal] = (float((out - o_ref[:, :, sl]).abs().max()), float((lse - l_ref[:, :, sl]).abs().max()))
+    # zig-zag layout (causal): rank r owns chunks r and 2*world-1-r
+    take = lambda t: ring.zigzag_take(t, rank, world)
+    out, lse = ring.ring_prefill(take(q).float(), take(k).float(), take(v).float(), is_causal=True,
+                                 attention_fn=_attn, merge_fn=ring.merge_partial_reference, layout="zigzag")
+    o_ref, l_ref = orc.attention_math(q, k, v, causal=True)
+    results["zigzag"] = (float((out - take(o_ref)).abs().max()), float((lse - take(l_ref)).abs().max()))
     torch.save(results, os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
@@ -52,6 +58,20 @@ def test_ring_prefill_matches_full_attention_world3(tmp_path):
         res = torch.load(tmp_path / f"r{r}.pt")
         for causal, (eo, el) in res.items():
             assert eo < 2e-5 and el < 2e-5, (r, causal, eo, el)
+
+
+def test_zigzag_rows_cover_the_sequence_once_and_balance_the_causal_work():
+    world, L = 4, 64
+    seen = torch.zeros(L, dtype=torch.int32)
+    work = []
+    for r in range(world):
+        lo, hi = ring.zigzag_rows(r, world, L)
+        seen[lo] += 1
+        seen[hi] += 1
+        rows = torch.cat([torch.arange(L)[lo], torch.arange(L)[hi]])
+        work.append(int((rows + 1).sum()))  # visible keys per query under a causal mask
+    assert bool((seen == 1).all())
+    assert max(work) - min(work) == 0
 
 
 def test_merge_reference_handles_empty_partials():
