@@ -8,6 +8,8 @@ reference operator it stands for (torch-2.1 schemas, codegen/mlu_functions.yaml:
 * ``_flash_attention_forward``                      <- cnnl__flash_attention_forward (attention.cpp:161-203)
 * ``_scaled_dot_product_flash_attention_backward``  <- attention.cpp:205-297
 * ``_flash_attention_backward``                     <- cnnl__flash_attention_backward (attention.cpp:299-348)
+* ``_scaled_dot_product_efficient_attention[_backward]`` <- attention.cpp:350-391, 510-600, for calls without an
+  additive bias (top-left causal convention)
 
 Unlike the reference wrappers, nothing is re-packed: tensors go to the kernels with their
 strides (any [B,H,L,D] / [B,L,H,D] view with unit head_dim stride), so the five
@@ -225,6 +227,71 @@ def _scaled_dot_product_flash_attention_backward(grad_out, query, key, value, ou
     if grad_out.stride(-1) != 1:
         grad_out = grad_out.contiguous()
     return _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, calculate_scale(query, scale))
+
+
+# --------------------------------------------------------------------------------------
+# memory-efficient operator surface (bias-free subset)
+# --------------------------------------------------------------------------------------
+def _scaled_dot_product_efficient_attention(query, key, value, attn_bias, compute_log_sumexp: bool,
+                                            dropout_p: float = 0.0, is_causal: bool = False, *,
+                                            scale: Optional[float] = None):
+    """(output, log_sumexp, philox_seed, philox_offset), attention.cpp:350-391, for ``attn_bias=None``.
+
+    The reference runs this operator on the same device kernel as the flash operator; what differs at
+    this level is the causal convention: ``CausalFromTopLeft`` (sdp_utils.h:32-37, attention.cpp:369-371)
+    instead of the flash operator's bottom-right alignment. With Lq == Lk the two coincide; otherwise
+    the top-left mask is rebuilt from what the kernels offer: keys past Lq are invisible to every row
+    (Lq < Lk), and rows past Lk see every key (Lq > Lk). An additive bias is not built: it is refused.
+    ``log_sumexp`` is [B,H,Lq] fp32, or empty when ``compute_log_sumexp`` is false.
+    """
+    _check(attn_bias is None, "attn_bias is not supported: the additive-bias kernels are not built in this library")
+    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
+    sc = calculate_scale(query, scale)
+    Lq, Lk = query.size(2), key.size(2)
+    if not is_causal or Lq == Lk:
+        out, lse = _dense_forward(query, key, value, is_causal, sc, allow_gqa=False)
+    elif Lq < Lk:
+        out, lse = _dense_forward(query, key[:, :, :Lq], value[:, :, :Lq], True, sc, allow_gqa=False)
+    else:
+        o1, l1 = _dense_forward(query[:, :, :Lk], key, value, True, sc, allow_gqa=False)
+        o2, l2 = _dense_forward(query[:, :, Lk:], key, value, False, sc, allow_gqa=False)
+        out = torch.cat([o1.transpose(1, 2), o2.transpose(1, 2)], dim=1).transpose(1, 2)
+        lse = torch.cat([l1, l2], dim=2)
+    if not compute_log_sumexp:
+        lse = lse.new_empty((query.size(0), query.size(1), 0))
+    seed, offset = _philox_placeholders(query)
+    return out, lse, seed, offset
+
+
+def _scaled_dot_product_efficient_attention_backward(grad_out, query, key, value, attn_bias, out, logsumexp,
+                                                     philox_seed, philox_offset, dropout_p: float,
+                                                     grad_input_mask, is_causal: bool = False, *,
+                                                     scale: Optional[float] = None):
+    """(grad_q, grad_k, grad_v, grad_bias), attention.cpp:510-600, for a call made without bias; grad_bias
+    is an empty tensor. Needs the log_sumexp of a forward call with ``compute_log_sumexp=True``."""
+    _check(attn_bias is None or attn_bias.numel() == 0,
+           "attn_bias is not supported: the additive-bias kernels are not built in this library")
+    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
+    _check(logsumexp.size(-1) == query.size(2), "log_sumexp is empty: run the forward with compute_log_sumexp=True")
+    sc = calculate_scale(query, scale)
+    if grad_out.stride(-1) != 1:
+        grad_out = grad_out.contiguous()
+    Lq, Lk = query.size(2), key.size(2)
+    if not is_causal or Lq == Lk:
+        dq, dk, dv = _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, sc)
+    elif Lq < Lk:
+        dq, dk_a, dv_a = _dense_backward(grad_out, query, key[:, :, :Lq], value[:, :, :Lq], out, logsumexp, True, sc)
+        dk, dv = torch.zeros_like(key), torch.zeros_like(value)
+        dk[:, :, :Lq] = dk_a
+        dv[:, :, :Lq] = dv_a
+    else:
+        l1, l2 = logsumexp[:, :, :Lk].contiguous(), logsumexp[:, :, Lk:].contiguous()
+        dq1, dk1, dv1 = _dense_backward(grad_out[:, :, :Lk], query[:, :, :Lk], key, value, out[:, :, :Lk], l1, True, sc)
+        dq2, dk2, dv2 = _dense_backward(grad_out[:, :, Lk:], query[:, :, Lk:], key, value, out[:, :, Lk:], l2, False, sc)
+        dq = torch.cat([dq1.transpose(1, 2), dq2.transpose(1, 2)], dim=1).transpose(1, 2)
+        dk = (dk1.float() + dk2.float()).to(key.dtype)
+        dv = (dv1.float() + dv2.float()).to(value.dtype)
+    return dq, dk, dv, query.new_empty((0,))
 
 
 # --------------------------------------------------------------------------------------

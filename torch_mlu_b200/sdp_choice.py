@@ -6,8 +6,8 @@ Same decision procedure and the same warning / error texts for the constraints t
 (sdp_utils.h:99-455): backends in priority order, each with a constraint list; if none qualifies
 and math is disabled, every constraint is re-run in debug mode (warnings) and
 ``RuntimeError("No available kernel.  Aborting execution.")`` is raised. What differs on purpose:
-there is one fused backend here (flash; the memory-efficient kernel is not built), and the
-MLU-occupancy heuristics of sdp_utils.h:479-524 (500-series check, split condition, valid-data
+both fused backends run the same kernels here (the memory-efficient one without its additive bias, so
+it refuses an attn_mask like flash does), and the MLU-occupancy heuristics of sdp_utils.h:479-524 (500-series check, split condition, valid-data
 ratio) are replaced by what this build needs: an sm_100 CUDA device, head_dim 64 or 128.
 """
 from __future__ import annotations
@@ -133,21 +133,57 @@ def use_flash_attention(query, key, value, attn_mask=None, debug: bool = False) 
     return all(c(query, key, value, attn_mask, debug) for c in _FLASH_CONSTRAINTS)
 
 
+def _check_runtime_disabled_mem_efficient(q, k, v, mask, debug):  # sdp_utils.h:111-123
+    if not backends.mem_efficient_sdp_enabled():
+        _warn(debug, "Memory efficient attention has been runtime disabled.")
+        return False
+    return True
+
+
+def _check_no_bias_for_mem_efficient(q, k, v, mask, debug):
+    if mask is not None:
+        _warn(debug, "The memory efficient kernel of this library is built without the additive bias: "
+                     "it does not support non-null attn_mask.")
+        return False
+    return True
+
+
+_MEM_EFFICIENT_CONSTRAINTS = (
+    _check_runtime_disabled_mem_efficient,
+    _check_tensor_shapes,
+    _check_batch_size_and_num_heads,
+    _check_no_bias_for_mem_efficient,
+    _check_head_dim_size,
+    _check_nonzero_sequence_lengths,
+    _check_last_dim_stride_equals_1,
+    _check_fused_kernel_device_support,
+    _check_tensor_dtype,
+)
+
+
+def use_mem_efficient_attention(query, key, value, attn_mask=None, debug: bool = False) -> bool:
+    """sdp_utils.cpp:74-95."""
+    return all(c(query, key, value, attn_mask, debug) for c in _MEM_EFFICIENT_CONSTRAINTS)
+
+
 def _fused_sdp_choice(query, key, value, attn_mask=None, dropout_p: float = 0.0, is_causal: bool = False,
                       *, scale: Optional[float] = None) -> int:
     """Returns the SDPBackend value (int) the call would use, or raises like the reference."""
     if not (backends.math_sdp_enabled() or backends.flash_sdp_enabled() or backends.mem_efficient_sdp_enabled()):
         return int(SDPBackend.ERROR)
+    # priority order of sdp_utils.cpp:28-31: flash, memory efficient, math
     if dropout_p == 0.0 and use_flash_attention(query, key, value, attn_mask, False):
         return int(SDPBackend.FLASH_ATTENTION)
+    if dropout_p == 0.0 and use_mem_efficient_attention(query, key, value, attn_mask, False):
+        return int(SDPBackend.EFFICIENT_ATTENTION)
     if backends.math_sdp_enabled():
         return int(SDPBackend.MATH)
     # nothing qualifies: say why, then fail (sdp_utils.cpp:134-146)
     warnings.warn("Memory efficient kernel not used because:", UserWarning, stacklevel=2)
-    warnings.warn("The memory efficient attention kernel is not built in this library.", UserWarning, stacklevel=2)
-    warnings.warn("Flash attention kernel not used because:", UserWarning, stacklevel=2)
     if dropout_p != 0.0:
-        warnings.warn("Flash attention in this build does not support dropout.", UserWarning, stacklevel=2)
+        warnings.warn("The fused kernels of this build do not support dropout.", UserWarning, stacklevel=2)
+    use_mem_efficient_attention(query, key, value, attn_mask, True)
+    warnings.warn("Flash attention kernel not used because:", UserWarning, stacklevel=2)
     use_flash_attention(query, key, value, attn_mask, True)
     raise RuntimeError("No available kernel.  Aborting execution.")
 
@@ -160,10 +196,20 @@ def scaled_dot_product_attention(query, key, value, attn_mask=None, dropout_p: f
     choice = _fused_sdp_choice(query, key, value, attn_mask, dropout_p, is_causal, scale=scale)
     if choice == int(SDPBackend.ERROR):
         raise RuntimeError("No viable backend for scaled_dot_product_attention was found.")
-    if choice == int(SDPBackend.FLASH_ATTENTION):
+    if choice == int(SDPBackend.FLASH_ATTENTION) or (
+            choice == int(SDPBackend.EFFICIENT_ATTENTION) and (not is_causal or query.size(-2) == key.size(-2))):
+        # same kernels, same mask when Lq == Lk: the registered operator also carries autograd
         from . import torch_glue
         torch_glue.load()
         return torch.ops.b200_sdpa._scaled_dot_product_flash_attention(query, key, value, dropout_p, is_causal, False,
                                                                        scale=scale)[0]
+    if choice == int(SDPBackend.EFFICIENT_ATTENTION):
+        # top-left causal mask with Lq != Lk: forward only through the operator mirror
+        if torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value)):
+            raise RuntimeError("the memory efficient backend with is_causal and Lq != Lk has no autograd here; "
+                               "call ops._scaled_dot_product_efficient_attention[_backward] directly")
+        from . import ops
+        return ops._scaled_dot_product_efficient_attention(query, key, value, None, False, dropout_p, is_causal,
+                                                           scale=scale)[0]
     return torch.ops.aten._scaled_dot_product_attention_math(query, key, value, attn_mask, dropout_p, is_causal,
                                                              scale=scale)[0]
