@@ -33,6 +33,13 @@
 namespace sdpa_b200 {
 namespace {
 
+#ifndef SDPA_BWD_POLY_DKDV
+#define SDPA_BWD_POLY_DKDV 2  // of every 4 column pairs, how many use the polynomial 2^x (dK/dV kernel)
+#endif
+#ifndef SDPA_BWD_POLY_DQ
+#define SDPA_BWD_POLY_DQ 1    // the same for the dQ kernel
+#endif
+
 constexpr int kTile = 128;  // rows per tile (queries or keys)
 constexpr uint32_t kTileBytes = kTile * 128 * 2;  // one shared-memory slot (head_dim 64 uses half of it)
 constexpr uint32_t kHalfBytes = kTileBytes / 2;
@@ -524,20 +531,31 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_ld_x32_at<32>(sbuf + 32, a);
         tmem_wait_ld();
         BWD_STAMP(half, i, 2);
+        // x = S c - lse2. In the dK/dV kernel this pass sits on the critical chain (score GEMM ->
+        // exponentials -> dP read -> next score GEMM) and the exponential unit alone would bound it, so
+        // kPolyOf4 of every four column pairs take their 2^x from the FMA pipe (exp2_poly3_x2). The dQ
+        // kernel's compute warps are bound by issue slots as much as by the exponential unit; there one
+        // pair in four is the measured optimum (two of four already cost time), here two of four.
+        constexpr int kPolyOf4 = (kMode == kModeDKDV) ? SDPA_BWD_POLY_DKDV : SDPA_BWD_POLY_DQ;
+#pragma unroll
+        for (int j = 0; j < 64; j += 2) {
+          const float l0 = (kMode == kModeDKDV) ? vec_lse[j] : my_lse2;
+          const float l1 = (kMode == kModeDKDV) ? vec_lse[j + 1] : my_lse2;
+          const float x0 = fmaf(__uint_as_float(a[j]), c, -l0);
+          const float x1 = fmaf(__uint_as_float(a[j + 1]), c, -l1);
+          if (((j >> 1) & 3) < kPolyOf4) {
+            const float2 e = exp2_poly3_x2(make_float2(x0, x1));
+            pr[j] = e.x;
+            pr[j + 1] = e.y;
+          } else {
+            pr[j] = ex2_approx(x0);
+            pr[j + 1] = ex2_approx(x1);
+          }
+        }
         // only tiles on the causal diagonal or past the end of the keys need the element mask
         if (__any_sync(0xffffffffu, j_lo > 0 || j_hi < 64)) {
 #pragma unroll
-          for (int j = 0; j < 64; ++j) {
-            const float l2 = (kMode == kModeDKDV) ? vec_lse[j] : my_lse2;
-            const float e = ex2_approx(fmaf(__uint_as_float(a[j]), c, -l2));
-            pr[j] = (j >= j_lo && j < j_hi) ? e : 0.f;
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 64; ++j) {
-            const float l2 = (kMode == kModeDKDV) ? vec_lse[j] : my_lse2;
-            pr[j] = ex2_approx(fmaf(__uint_as_float(a[j]), c, -l2));
-          }
+          for (int j = 0; j < 64; ++j) pr[j] = (j >= j_lo && j < j_hi) ? pr[j] : 0.f;
         }
         if (kMode == kModeDKDV) {
           uint32_t pw[32];
