@@ -68,7 +68,8 @@ constexpr uint32_t kBarAccFull = kBarPFull + 16;
 constexpr uint32_t kBarP1Full = kBarAccFull + 8;           // dK/dV: all compute warps have stored P (dS still to come)
 constexpr uint32_t kBarWFree = kBarP1Full + 8;             // 2 (item parity): the accumulation GEMMs have read P / dS
 constexpr uint32_t kBarSIssued = kBarWFree + 16;           // dK/dV: the next item's score GEMM is in the pipe
-constexpr uint32_t kSmemTmemPtr = kBarSIssued + 8;
+constexpr uint32_t kBarEpiFull = kBarSIssued + 8;           // all compute warps have staged their output rows
+constexpr uint32_t kSmemTmemPtr = kBarEpiFull + 8;
 constexpr uint32_t kSmemAbort = kSmemTmemPtr + 4;
 
 struct BwdKernelParams {
@@ -145,8 +146,12 @@ template <int kMode, int kD, bool kF16>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                const __grid_constant__ CUtensorMap tm_o1, const __grid_constant__ CUtensorMap tm_o2,
                 const BwdKernelParams p) {
   extern __shared__ uint8_t smem_raw[];
+#ifdef SDPA_BWD_STAMPS
+  const long long t_entry = clock64();
+#endif
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw_addr);
@@ -220,6 +225,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(bar + kBarWFree, 1);
     mbar_init(bar + kBarWFree + 8, 1);
     mbar_init(bar + kBarSIssued, 1);
+    mbar_init(bar + kBarEpiFull, 8);
     mbar_init(bar + kBarAccFull, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -367,12 +373,17 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       bool ok = true;
       if (warp == 9) {
         // ---------------- score GEMMs
+#ifdef SDPA_BWD_STAMPS
+        if (stamp_on) p.stamps[((kMode * 4 + 2) * 24 + 23) * 8 + 0] = static_cast<float>(t_start - t_entry);
+#endif
         ok = mbar_wait(bar + kBarXFull, 0, abort_flag) && y_wait_k(0);
+        BWD_STAMP(2, 23, 1);
         if (ok) {
           tc_fence_after_sync();
           issue_xyT<kD, kF16>(s_buf(0), x1, y_slot_k(0));
           umma_commit(s_bar(0));
         }
+        BWD_STAMP(2, 23, 2);
         ok = ok && y_wait_k(1);
         if (ok) {
           tc_fence_after_sync();
@@ -472,6 +483,8 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           umma_commit(bar + kBarWFree + 8 * (i & 1));
           if (i == n_items - 1) umma_commit(bar + kBarAccFull);
           BWD_STAMP(3, i, 2);
+          if (i == 0) BWD_STAMP(3, 23, 0);
+          if (i == n_items - 1) BWD_STAMP(3, 23, 1);
         }
       }
     }
@@ -603,11 +616,18 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       BWD_STAMP(half, i, 7);
     }
 
-    // ---- epilogue: accumulators -> scale -> bf16 -> global
+    // ---- epilogue: accumulators -> scale -> 16-bit -> global
     if (ok && n_items > 0) ok = mbar_wait(bar + kBarAccFull, 0, abort_flag);
+    BWD_STAMP(half, 23, 0);
     if (ok) {
       tc_fence_after_sync();
       const bool valid = xr < len_x;
+      // A whole 128-row tile leaves through shared memory and TMA stores (the ring slots are idle by
+      // now): coalesced and asynchronous, where row-wise stores from registers - 128 bytes per thread,
+      // every lane on another row - kept the load/store unit busy for ~4000 cycles per CTA. Dense
+      // tensors are clipped by the tensor map; a packed (varlen) tile that ends inside its sequence's
+      // last rows would spill into the next sequence and is written row by row instead.
+      const bool use_tma = (p.cu_q == nullptr) || (x0 + kTile <= len_x);
       const int n_out = (kMode == kModeDKDV) ? 2 : 1;
 #pragma unroll
       for (int which = 0; which < n_out; ++which) {
@@ -644,29 +664,59 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0u;
           }
-          if (valid) {
-            uint4* o4 = reinterpret_cast<uint4*>(dst + half * (kD / 2) + cc * 32);
+          uint4 w[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint4 w;
-              w.x = pack_16x2<kF16>(__uint_as_float(v[8 * j + 0]) * mul, __uint_as_float(v[8 * j + 1]) * mul);
-              w.y = pack_16x2<kF16>(__uint_as_float(v[8 * j + 2]) * mul, __uint_as_float(v[8 * j + 3]) * mul);
-              w.z = pack_16x2<kF16>(__uint_as_float(v[8 * j + 4]) * mul, __uint_as_float(v[8 * j + 5]) * mul);
-              w.w = pack_16x2<kF16>(__uint_as_float(v[8 * j + 6]) * mul, __uint_as_float(v[8 * j + 7]) * mul);
-              o4[j] = w;
+          for (int j = 0; j < 4; ++j) {
+            w[j].x = pack_16x2<kF16>(__uint_as_float(v[8 * j + 0]) * mul, __uint_as_float(v[8 * j + 1]) * mul);
+            w[j].y = pack_16x2<kF16>(__uint_as_float(v[8 * j + 2]) * mul, __uint_as_float(v[8 * j + 3]) * mul);
+            w[j].z = pack_16x2<kF16>(__uint_as_float(v[8 * j + 4]) * mul, __uint_as_float(v[8 * j + 5]) * mul);
+            w[j].w = pack_16x2<kF16>(__uint_as_float(v[8 * j + 6]) * mul, __uint_as_float(v[8 * j + 7]) * mul);
+          }
+          const int col = half * (kD / 2) + cc * 32;  // first of this thread's 32 columns
+          if (use_tma) {
+            // output tile `which` is staged in ring slot `which`: two 64-column halves of 128-byte rows
+            // in the 128-byte-swizzled layout the tensor map expects
+            uint8_t* row = smem + kSmemY + which * kTileBytes + (col >> 6) * kHalfBytes + r * 128;
+            const int chunk0 = (col & 63) >> 3;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(row + (((chunk0 + j) ^ (r & 7)) << 4)) = w[j];
+          } else if (valid) {
+            uint4* o4 = reinterpret_cast<uint4*>(dst + col);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) o4[j] = w[j];
+          }
+        }
+      }
+      if (use_tma) {
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar + kBarEpiFull);
+        if (threadIdx.x == 0) {
+          if (mbar_wait(bar + kBarEpiFull, 0, abort_flag)) {
+            const int row0 = ((kMode == kModeDKDV) ? k_off : q_off) + x0;
+#pragma unroll
+            for (int which = 0; which < n_out; ++which) {
+              const CUtensorMap* tm = (which == 0) ? &tm_o1 : &tm_o2;
+#pragma unroll
+              for (int ht = 0; ht < kD / 64; ++ht)
+                tma_store_4d(tm, base + kSmemY + which * kTileBytes + ht * kHalfBytes, ht * 64, row0, hx, bcoord);
             }
+            tma_store_commit();
+            tma_store_wait_all();  // the shared memory must outlive the stores
           }
         }
       }
     }
   }
 
+  if (warp < 8) BWD_STAMP(warp >> 2, 23, 1);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
+  if (warp == 0) BWD_STAMP(0, 23, 2);
   if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, SDPA_B200_DEVICE_TIMEOUT);
 }
 
@@ -751,7 +801,7 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreParams p) 
 
 
 using TileKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
-                            const BwdKernelParams);
+                            const CUtensorMap, const CUtensorMap, const BwdKernelParams);
 
 template <int kMode>
 TileKernel pick_tile_kernel(int head_dim, bool f16) {
@@ -761,7 +811,7 @@ TileKernel pick_tile_kernel(int head_dim, bool f16) {
 
 int launch_tile_kernel(int mode, int head_dim, bool f16, int grid, cudaStream_t stream, const CUtensorMap& tm_q,
                        const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_do,
-                       const BwdKernelParams& kp) {
+                       const CUtensorMap& tm_o1, const CUtensorMap& tm_o2, const BwdKernelParams& kp) {
   TileKernel kernel = mode == kModeDKDV ? pick_tile_kernel<kModeDKDV>(head_dim, f16) : pick_tile_kernel<kModeDQ>(head_dim, f16);
   const uint32_t smem = smem_bytes_for(mode);
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -769,7 +819,7 @@ int launch_tile_kernel(int mode, int head_dim, bool f16, int grid, cudaStream_t 
     set_error("backward: cudaFuncSetAttribute(%u bytes smem): %s", smem, cudaGetErrorString(err));
     return SDPA_B200_LAUNCH_FAILED;
   }
-  kernel<<<dim3(grid), kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_do, kp);
+  kernel<<<dim3(grid), kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_o1, tm_o2, kp);
   err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("backward %s: launch failed: %s", mode == kModeDKDV ? "dK/dV" : "dQ", cudaGetErrorString(err));
@@ -842,6 +892,16 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   if ((st = make_tensor_map_16(f16, &tm_do, p.dout, p.head_dim, rows_q, p.heads_q, nb, p.do_row_stride,
                                  p.do_head_stride, p.do_batch_stride, kTile)) != SDPA_B200_OK)
     return st;
+  CUtensorMap tm_dq, tm_dk, tm_dv;  // outputs, stored tile by tile from the epilogue's staging buffers
+  if ((st = make_tensor_map_16(f16, &tm_dq, p.dq, p.head_dim, rows_q, p.heads_q, nb, p.dq_row_stride, p.dq_head_stride,
+                                 p.dq_batch_stride, kTile)) != SDPA_B200_OK)
+    return st;
+  if ((st = make_tensor_map_16(f16, &tm_dk, p.dk, p.head_dim, rows_k, p.heads_kv, nb, p.dk_row_stride, p.dk_head_stride,
+                                 p.dk_batch_stride, kTile)) != SDPA_B200_OK)
+    return st;
+  if ((st = make_tensor_map_16(f16, &tm_dv, p.dv, p.head_dim, rows_k, p.heads_kv, nb, p.dv_row_stride, p.dv_head_stride,
+                                 p.dv_batch_stride, kTile)) != SDPA_B200_OK)
+    return st;
 
   BwdKernelParams kp;
   kp.lse2 = lse2;
@@ -891,12 +951,12 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   };
   kp.num_row_blocks = (p.max_seqlen_k + kTile - 1) / kTile;
   const int grid_dkdv = set_order(p.heads_kv, p.max_seqlen_q, kp.kv_group);
-  if ((st = launch_tile_kernel(kModeDKDV, p.head_dim, f16, grid_dkdv, stream, tm_q, tm_k, tm_v, tm_do, kp)) !=
+  if ((st = launch_tile_kernel(kModeDKDV, p.head_dim, f16, grid_dkdv, stream, tm_q, tm_k, tm_v, tm_do, tm_dv, tm_dk, kp)) !=
       SDPA_B200_OK)
     return st;
   kp.num_row_blocks = (p.max_seqlen_q + kTile - 1) / kTile;
   const int grid_dq = set_order(p.heads_q, p.max_seqlen_k, 1);
-  return launch_tile_kernel(kModeDQ, p.head_dim, f16, grid_dq, stream, tm_q, tm_k, tm_v, tm_do, kp);
+  return launch_tile_kernel(kModeDQ, p.head_dim, f16, grid_dq, stream, tm_q, tm_k, tm_v, tm_do, tm_dq, tm_dq, kp);
 }
 
 }  // namespace sdpa_b200
