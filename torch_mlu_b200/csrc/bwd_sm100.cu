@@ -210,60 +210,19 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kSmemBar + kSmemAbort);
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + kSmemBar + kSmemTmemPtr);
 
-  if (threadIdx.x == 0) {
-    mbar_init(bar + kBarXFull, 1);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar + kBarYFull + 8 * s, 1);
-      mbar_init(bar + kBarYEmpty + 8 * s, 1);
-    }
-    mbar_init(bar + kBarSFull, 1);
-    mbar_init(bar + kBarSFull + 8, 1);
-    mbar_init(bar + kBarDFull, 1);
-    mbar_init(bar + kBarDFree, 8);  // one arrival per compute warp
-    mbar_init(bar + kBarPFull, 8);
-    mbar_init(bar + kBarP1Full, 8);
-    mbar_init(bar + kBarWFree, 1);
-    mbar_init(bar + kBarWFree + 8, 1);
-    mbar_init(bar + kBarSIssued, 1);
-    mbar_init(bar + kBarEpiFull, 8);
-    mbar_init(bar + kBarAccFull, 1);
-    *abort_flag = 0;
-    fence_mbar_init();
-  }
-  if (warp == 0) {
-    __syncwarp();
-    tmem_alloc(base + kSmemBar + kSmemTmemPtr, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_ptr_smem;
-  const uint32_t t1 = tmem_base, t2 = tmem_base + 128, acc1 = tmem_base + 256, acc2 = tmem_base + 384;
-#ifdef SDPA_BWD_STAMPS
-  const long long t_start = clock64();
-  // a long-running block of batch 0, head 0 (non-causal: any; causal: the heaviest)
-  const bool stamp_on = p.stamps != nullptr && b == 0 && hx == 0 &&
-                        xb == ((kMode == kModeDKDV) ? 0 : p.num_row_blocks - 1) && (lane == 0) &&
-                        (warp == 0 || warp == 4 || warp == 9 || warp == 10);
-#endif
-
-  if (warp == 8) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && n_items > 0) {
-      const CUtensorMap* tmx1 = (kMode == kModeDKDV) ? &tm_k : &tm_q;
-      const CUtensorMap* tmx2 = (kMode == kModeDKDV) ? &tm_v : &tm_do;
-      const CUtensorMap* tmy1 = (kMode == kModeDKDV) ? &tm_q : &tm_k;
-      const CUtensorMap* tmy2 = (kMode == kModeDKDV) ? &tm_do : &tm_v;
-      const int x_row = ((kMode == kModeDKDV) ? k_off : q_off) + x0;
-      const int y_off = (kMode == kModeDKDV) ? q_off : k_off;
-      constexpr uint32_t kLoadBytes = kTile * kD * 2;  // bytes one tile brings in
-      mbar_arrive_expect_tx(bar + kBarXFull, 2 * kLoadBytes);
-      tma_load_4d(base + kSmemX, tmx1, bar + kBarXFull, 0, x_row, hx, bcoord);
-      if (kD > 64) tma_load_4d(base + kSmemX + kHalfBytes, tmx1, bar + kBarXFull, 64, x_row, hx, bcoord);
-      tma_load_4d(base + kSmemX + kTileBytes, tmx2, bar + kBarXFull, 0, x_row, hx, bcoord);
-      if (kD > 64) tma_load_4d(base + kSmemX + kTileBytes + kHalfBytes, tmx2, bar + kBarXFull, 64, x_row, hx, bcoord);
-      for (int idx = 0; idx < 2 * n_items; ++idx) {  // ring tile idx: Y1(idx/2) if even, Y2(idx/2) if odd
+  // TMA producer state. The producer thread also initialises the barriers and issues the first loads
+  // (the stationary pair and the first kPreloaded ring tiles, whose slots are free by construction)
+  // BEFORE the set-up barrier, so that their latency runs under the TMEM allocation.
+  const CUtensorMap* tmx1 = (kMode == kModeDKDV) ? &tm_k : &tm_q;
+  const CUtensorMap* tmx2 = (kMode == kModeDKDV) ? &tm_v : &tm_do;
+  const CUtensorMap* tmy1 = (kMode == kModeDKDV) ? &tm_q : &tm_k;
+  const CUtensorMap* tmy2 = (kMode == kModeDKDV) ? &tm_do : &tm_v;
+  const int x_row = ((kMode == kModeDKDV) ? k_off : q_off) + x0;
+  const int y_off = (kMode == kModeDKDV) ? q_off : k_off;
+  constexpr uint32_t kLoadBytes = kTile * kD * 2;  // bytes one tile brings in
+  constexpr int kPreloaded = 4;
+  // ring tile idx: Y1(idx/2) if even, Y2(idx/2) if odd; false when a wait gave up
+  auto load_tile = [&](int idx) -> bool {
         const int i = idx >> 1;
         int s = idx % kStages;
         uint32_t use = static_cast<uint32_t>(idx / kStages);
@@ -285,9 +244,9 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         //   V(i): dP(i-1) can finish as well before the producer looks, and two phases on the parity
         //   reads "not yet" again.)
         if (kMode == kModeDKDV) {
-          if (!mbar_wait(bar + kBarYEmpty + 8 * (s & ~1), (use & 1u) ^ 1u, abort_flag)) break;
+          if (!mbar_wait(bar + kBarYEmpty + 8 * (s & ~1), (use & 1u) ^ 1u, abort_flag)) return false;
         } else if ((idx & 1) == 0 && i >= 2) {
-          if (!mbar_wait(bar + kBarSFull + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag)) break;
+          if (!mbar_wait(bar + kBarSFull + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag)) return false;
         }
         const int hi = i / tiles_per_head;
         const int yt = y_lo + (i - hi * tiles_per_head);
@@ -308,7 +267,60 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const CUtensorMap* tm = first ? tmy1 : tmy2;
         tma_load_4d(dst, tm, full, 0, row, hy, bcoord);
         if (kD > 64) tma_load_4d(dst + kHalfBytes, tm, full, 64, row, hy, bcoord);
-      }
+    return true;
+  };
+
+  if (warp == 8 && lane == 0) {
+    mbar_init(bar + kBarXFull, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar + kBarYFull + 8 * s, 1);
+      mbar_init(bar + kBarYEmpty + 8 * s, 1);
+    }
+    mbar_init(bar + kBarSFull, 1);
+    mbar_init(bar + kBarSFull + 8, 1);
+    mbar_init(bar + kBarDFull, 1);
+    mbar_init(bar + kBarDFree, 8);  // one arrival per compute warp
+    mbar_init(bar + kBarPFull, 8);
+    mbar_init(bar + kBarP1Full, 8);
+    mbar_init(bar + kBarWFree, 1);
+    mbar_init(bar + kBarWFree + 8, 1);
+    mbar_init(bar + kBarSIssued, 1);
+    mbar_init(bar + kBarEpiFull, 8);
+    mbar_init(bar + kBarAccFull, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    if (n_items > 0) {
+      mbar_arrive_expect_tx(bar + kBarXFull, 2 * kLoadBytes);
+      tma_load_4d(base + kSmemX, tmx1, bar + kBarXFull, 0, x_row, hx, bcoord);
+      if (kD > 64) tma_load_4d(base + kSmemX + kHalfBytes, tmx1, bar + kBarXFull, 64, x_row, hx, bcoord);
+      tma_load_4d(base + kSmemX + kTileBytes, tmx2, bar + kBarXFull, 0, x_row, hx, bcoord);
+      if (kD > 64) tma_load_4d(base + kSmemX + kTileBytes + kHalfBytes, tmx2, bar + kBarXFull, 64, x_row, hx, bcoord);
+      for (int idx = 0; idx < kPreloaded && idx < 2 * n_items; ++idx) load_tile(idx);
+    }
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(base + kSmemBar + kSmemTmemPtr, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  const uint32_t t1 = tmem_base, t2 = tmem_base + 128, acc1 = tmem_base + 256, acc2 = tmem_base + 384;
+#ifdef SDPA_BWD_STAMPS
+  const long long t_start = clock64();
+  // a long-running block of batch 0, head 0 (non-causal: any; causal: the heaviest)
+  const bool stamp_on = p.stamps != nullptr && b == 0 && hx == 0 &&
+                        xb == ((kMode == kModeDKDV) ? 0 : p.num_row_blocks - 1) && (lane == 0) &&
+                        (warp == 0 || warp == 4 || warp == 9 || warp == 10);
+#endif
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer (rest of the ring)
+    if (lane == 0 && n_items > 0) {
+      for (int idx = kPreloaded; idx < 2 * n_items; ++idx)
+        if (!load_tile(idx)) break;
       drain_after_abort(abort_flag);
     }
   } else if (warp == 9 || warp == 10) {
