@@ -271,6 +271,11 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   };
 
   if (warp == 8 && lane == 0) {
+    // descriptor fetches run under the barrier initialisation
+    tma_prefetch_desc(tmx1);
+    tma_prefetch_desc(tmy1);
+    tma_prefetch_desc(tmx2);
+    tma_prefetch_desc(tmy2);
     mbar_init(bar + kBarXFull, 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar + kBarYFull + 8 * s, 1);
@@ -714,7 +719,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 tma_store_4d(tm, base + kSmemY + which * kTileBytes + ht * kHalfBytes, ht * 64, row0, hx, bcoord);
             }
             tma_store_commit();
-            tma_store_wait_all();  // the shared memory must outlive the stores
+            tma_store_wait_read();  // the shared memory must outlive the stores' reads of it
           }
         }
       }

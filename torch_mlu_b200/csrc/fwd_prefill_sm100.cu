@@ -724,7 +724,7 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       cnt += my_blocks;
       ++ucnt;
     }
-    if (row_in_tile == 0) tma_store_wait_all();  // the CTA's shared memory must outlive its stores
+    if (row_in_tile == 0) tma_store_wait_read();  // the CTA's shared memory must outlive its stores' reads of it
   }
 
   // ------------------------------------------------------------------ tear-down
