@@ -80,7 +80,7 @@ def test_workspace_query_and_validation_codes(native_lib):
     expect(lambda p: setattr(p, "heads_kv", 3), _cabi.INVALID_ARG, "must divide number of heads in query")
     expect(lambda p: setattr(p, "head_dim", 100), _cabi.INVALID_ARG, "multiple of 8")
     expect(lambda p: setattr(p, "head_dim", 264), _cabi.INVALID_ARG, "at most 256")
-    expect(lambda p: setattr(p, "head_dim", 96), _cabi.UNSUPPORTED, "head_dim 128")
+    expect(lambda p: setattr(p, "head_dim", 192), _cabi.UNSUPPORTED, "up to 128")
     expect(lambda p: setattr(p, "dropout_p", 0.1), _cabi.UNSUPPORTED, "dropout_p must be 0")
     expect(lambda p: setattr(p, "dtype", 3), _cabi.UNSUPPORTED, "bf16")
     expect(lambda p: setattr(p, "max_seqlen_k", 0), _cabi.INVALID_ARG, "sequence lengths must be positive")

@@ -89,6 +89,7 @@ struct BwdKernelParams {
   int num_bh, heads_x, heads_per_wave;  // CTA order, see the top of bwd_tile_kernel
   float scale, scale_log2;
   int is_causal;
+  int head_dim;  // <= kD (the kernels are built for 64 and 128 columns; TMA pads loads and clips stores)
 #ifdef SDPA_BWD_STAMPS
   float* stamps;  // [mode 2][role 4][item 24][event 8] SM cycles since CTA start, one CTA per mode
 #endif
@@ -700,7 +701,8 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           } else if (valid) {
             uint4* o4 = reinterpret_cast<uint4*>(dst + col);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) o4[j] = w[j];
+            for (int j = 0; j < 4; ++j)
+              if (col + 8 * j < p.head_dim) o4[j] = w[j];
           }
         }
       }
@@ -759,7 +761,7 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreParams p) 
   // heads vary fastest across the grid: with the usual [batch, row, head, dim] memory order the blocks
   // that run together then read neighbouring 256-byte pieces of the same rows
   const int h = blockIdx.x, b = blockIdx.z;
-  const int tpr = p.head_dim >> 3;          // threads per row: 16 (head_dim 128) or 8 (64)
+  const int tpr = p.head_dim <= 64 ? 8 : 16;  // threads per row (head dims in between leave lanes without data)
   const int rows_per_pass = 256 / tpr;      // 16 or 32
   const int passes = kPreRows / rows_per_pass;  // 4 or 2
   const int sub = threadIdx.x % tpr;
@@ -785,8 +787,10 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreParams p) 
         o = p.out + b * p.o_batch_stride + h * p.o_head_stride + static_cast<int64_t>(row) * p.o_row_stride;
         dout = p.dout + b * p.do_batch_stride + h * p.do_head_stride + static_cast<int64_t>(row) * p.do_row_stride;
       }
-      ov[ps] = *reinterpret_cast<const uint4*>(o + sub * 8);
-      dv[ps] = *reinterpret_cast<const uint4*>(dout + sub * 8);
+      if (sub * 8 < p.head_dim) {
+        ov[ps] = *reinterpret_cast<const uint4*>(o + sub * 8);
+        dv[ps] = *reinterpret_cast<const uint4*>(dout + sub * 8);
+      }
     }
   }
 #pragma unroll
@@ -822,7 +826,7 @@ using TileKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensor
 
 template <int kMode>
 TileKernel pick_tile_kernel(int head_dim, bool f16) {
-  if (head_dim == 64) return f16 ? bwd_tile_kernel<kMode, 64, true> : bwd_tile_kernel<kMode, 64, false>;
+  if (head_dim <= 64) return f16 ? bwd_tile_kernel<kMode, 64, true> : bwd_tile_kernel<kMode, 64, false>;
   return f16 ? bwd_tile_kernel<kMode, 128, true> : bwd_tile_kernel<kMode, 128, false>;
 }
 
@@ -945,6 +949,7 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   kp.kv_group = p.heads_q / p.heads_kv;
   kp.lq_pad = lq_pad;
   kp.scale = p.softmax_scale;
+  kp.head_dim = p.head_dim;
   kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   kp.is_causal = p.is_causal;
 #ifdef SDPA_BWD_STAMPS

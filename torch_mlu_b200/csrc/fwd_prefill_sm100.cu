@@ -3,7 +3,9 @@
 // Replaces the device work behind mha_varlen_fwd -> cnnlFlashAttentionForward_v2
 // (torch_mlu/csrc/aten/operators/cnnl/internal/FlashAttention_internal.cpp:231-258):
 //   O = softmax(scale * Q K^T + causal mask) V,  LSE = logsumexp(scale * Q K^T)
-// for bf16 or f16 Q/K/V with head_dim 64 or 128, dense or packed-varlen, GQA by head broadcast.
+// for bf16 or f16 Q/K/V with head_dim <= 128 (a multiple of 8), dense or packed-varlen, GQA by head
+// broadcast. The kernel is built for 64 and 128 columns; other head dims run in the next larger one:
+// TMA loads fill the missing columns with zeros and TMA stores clip them.
 //
 // A work unit is 256 query rows of one (batch, head): two 128-row Q tiles. One persistent CTA per SM
 // walks the unit list; its barriers, TMEM and K/V ring live across units, so the next unit's loads
@@ -85,6 +87,7 @@ struct FwdKernelParams {
   uint32_t* unit_counter;  // zeroed by the caller before the launch
   int64_t o_batch_stride, o_head_stride, o_row_stride;
   int seqlen_q, seqlen_k, total_q, heads_q, kv_group;
+  int head_dim;  // <= kD: the real row length, for the paths that write rows without TMA
   int num_m_blocks, num_bh, heads_per_wave, num_slots;  // work-unit order, see decode_unit()
   float scale_log2;
   int is_causal;
@@ -526,7 +529,8 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
           }
           uint4* dst = reinterpret_cast<uint4*>(orow);
 #pragma unroll
-          for (int i = 0; i < kD / 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+          for (int i = 0; i < kD / 8; ++i)
+            if (8 * i < p.head_dim) dst[i] = make_uint4(0u, 0u, 0u, 0u);
           *lse_ptr = INFINITY;
         }
         continue;
@@ -707,7 +711,8 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
           uint4* dst = reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(u_q_off + row) * p.o_row_stride +
                                                 u_h * p.o_head_stride);
 #pragma unroll
-          for (int i = 0; i < kD / 8; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+          for (int i = 0; i < kD / 8; ++i)
+            if (8 * i < p.head_dim) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
         }
         if (valid) {
           float* lse_ptr = (p.cu_q != nullptr)
@@ -775,6 +780,7 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
   kp.total_q = p.total_q;
   kp.heads_q = p.heads_q;
   kp.kv_group = p.heads_q / p.heads_kv;
+  kp.head_dim = p.head_dim;
   kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   kp.is_causal = p.is_causal;
 #ifdef SDPA_FWD_STAMPS
@@ -784,7 +790,7 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
   }
 #endif
 
-  auto kernel = p.head_dim == 64 ? (f16 ? fwd_prefill_kernel<64, true> : fwd_prefill_kernel<64, false>)
+  auto kernel = p.head_dim <= 64 ? (f16 ? fwd_prefill_kernel<64, true> : fwd_prefill_kernel<64, false>)
                                  : (f16 ? fwd_prefill_kernel<128, true> : fwd_prefill_kernel<128, false>);
   cudaError_t err =
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);

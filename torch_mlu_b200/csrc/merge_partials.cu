@@ -76,8 +76,8 @@ extern "C" SDPA_B200_API int sdpa_b200_merge_partial(float* o_acc, float* lse_ac
     set_error("merge_partial: o_part must be bf16 or f16 (dtype code %d)", dtype);
     return SDPA_B200_UNSUPPORTED;
   }
-  if (head_dim != 128 && head_dim != 64) {
-    set_error("merge_partial: this build handles head_dim 64 and 128 only (got %d)", head_dim);
+  if (head_dim <= 0 || head_dim > 128 || head_dim % 8 != 0) {
+    set_error("merge_partial: head_dim must be a multiple of 8 up to 128 (got %d)", head_dim);
     return SDPA_B200_UNSUPPORTED;
   }
   if (batch <= 0 || heads <= 0 || rows <= 0 || part_row_stride % 4 != 0 || part_head_stride % 4 != 0 ||

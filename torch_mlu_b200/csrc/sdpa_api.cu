@@ -129,8 +129,8 @@ int validate_common(const sdpa_b200_params* p) {
     set_error("head_dim must be a multiple of 8 and at most 256 (got %d)", p->head_dim);
     return SDPA_B200_INVALID_ARG;
   }
-  if (p->head_dim != 128 && p->head_dim != 64) {
-    set_error("this build has kernels for head_dim 128 and 64 only (got %d)", p->head_dim);
+  if (p->head_dim > 128) {
+    set_error("this build has kernels for head_dim up to 128 only (got %d)", p->head_dim);
     return SDPA_B200_UNSUPPORTED;
   }
   if (!(p->softmax_scale > 0.f) || !(p->softmax_scale < 3.0e38f)) {
@@ -211,7 +211,9 @@ int check_device() {
 bool use_decode(const sdpa_b200_params* p) {
   if (p->kernel == SDPA_B200_KERNEL_DECODE) return true;
   if (p->kernel == SDPA_B200_KERNEL_PREFILL) return false;
-  return p->cu_seqlens_q == nullptr && p->max_seqlen_q == 1;
+  // the streaming kernel reads whole 64- or 128-element rows; other head dims take the tile kernel,
+  // whose TMA loads pad the head dim with zeros
+  return p->cu_seqlens_q == nullptr && p->max_seqlen_q == 1 && (p->head_dim == 64 || p->head_dim == 128);
 }
 
 }  // namespace
@@ -302,6 +304,10 @@ int sdpa_b200_fwd(const sdpa_b200_params* p, void* workspace, size_t workspace_b
   if (use_decode(p)) {
     if (p->cu_seqlens_q != nullptr) {
       set_error("the decode kernel takes dense tensors only");
+      return SDPA_B200_UNSUPPORTED;
+    }
+    if (p->head_dim != 64 && p->head_dim != 128) {
+      set_error("the decode kernel is built for head_dim 64 and 128 only (got %d)", p->head_dim);
       return SDPA_B200_UNSUPPORTED;
     }
     return launch_fwd_decode(*p, workspace, workspace_bytes, s);

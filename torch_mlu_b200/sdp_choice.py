@@ -8,7 +8,7 @@ and math is disabled, every constraint is re-run in debug mode (warnings) and
 ``RuntimeError("No available kernel.  Aborting execution.")`` is raised. What differs on purpose:
 both fused backends run the same kernels here (the memory-efficient one without its additive bias, so
 it refuses an attn_mask like flash does), and the MLU-occupancy heuristics of sdp_utils.h:479-524 (500-series check, split condition, valid-data
-ratio) are replaced by what this build needs: an sm_100 CUDA device, head_dim 64 or 128.
+ratio) are replaced by what this build needs: an sm_100 CUDA device, head_dim at most 128.
 """
 from __future__ import annotations
 
@@ -101,8 +101,8 @@ def _check_fused_kernel_device_support(q, k, v, mask, debug):  # stands where sd
         _warn(debug, "The fused kernel only supports sm_100 (B200). Attempting to run on "
                      f"{torch.cuda.get_device_name(q.device)}.")
         return False
-    if q.size(-1) not in (64, 128):
-        _warn(debug, f"This build has fused kernels for head_dim 64 and 128 only. Got Query.size(-1): {q.size(-1)}.")
+    if q.size(-1) > 128:
+        _warn(debug, f"This build has fused kernels for head_dim up to 128 only. Got Query.size(-1): {q.size(-1)}.")
         return False
     return True
 
