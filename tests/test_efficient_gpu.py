@@ -58,3 +58,59 @@ def test_choice_prefers_flash_then_memory_efficient(cuda_device, native_lib):
         out = sdp_choice.scaled_dot_product_attention(q, q, q, is_causal=True)
     ref = F.scaled_dot_product_attention(q.float().cpu(), q.float().cpu(), q.float().cpu(), is_causal=True)
     orc.assert_close_bf16(out, ref, "out through the memory efficient choice")
+
+
+@pytest.mark.parametrize("mask_type,Lq,Lk", [(0, 300, 500), (1, 200, 456), (1, 456, 200), (2, 200, 456), (2, 384, 384)])
+def test_efficient_attention_forward_backward_pair(cuda_device, native_lib, mask_type, Lq, Lk):
+    """_efficient_attention_forward / _backward (attention.cpp:393-507, 579-727): [B, L, H, D] tensors, the three
+    custom mask types of sdp_utils.h:32-37, logsumexp as [H, B*Lq]."""
+    dev = cuda_device
+    B, H, D = 2, 3, 128
+    q, k, v, do = rand((B, Lq, H, D), 1), rand((B, Lk, H, D), 2), rand((B, Lk, H, D), 3), rand((B, Lq, H, D), 4)
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    out, lse, seed, off = ops._efficient_attention_forward(qd, kd, vd, None, None, None, None, 0.0, mask_type, True)
+    assert tuple(out.shape) == (B, H, Lq, D) and tuple(lse.shape) == (H, B * Lq)
+    out_blhd = out.transpose(1, 2)
+    dq, dk, dv, dbias = ops._efficient_attention_backward(do.to(dev), qd, kd, vd, None, out_blhd, None, None, Lk, Lq, lse, 0.0,
+                                                         seed, off, mask_type, False)
+    assert ops.device_status() == 0 and dbias.numel() == 0
+    assert tuple(dq.shape) == (B, Lq, H, D) and tuple(dk.shape) == (B, Lk, H, D) and tuple(dv.shape) == (B, Lk, H, D)
+    qf, kf, vf = (t.float().transpose(1, 2).detach().requires_grad_(True) for t in (q, k, v))
+    scores = torch.einsum("bhqd,bhkd->bhqk", qf, kf) / D ** 0.5
+    if mask_type == 1:
+        scores = scores.masked_fill(torch.ones(Lq, Lk, dtype=torch.bool).triu(1), float("-inf"))
+    elif mask_type == 2:
+        scores = scores.masked_fill(orc.causal_mask_bottom_right(Lq, Lk), float("-inf"))
+    l_ref = torch.logsumexp(scores, dim=-1)
+    dead = torch.isinf(l_ref)
+    attn = torch.softmax(scores, dim=-1).masked_fill(dead.unsqueeze(-1), 0.0)
+    ref = torch.einsum("bhqk,bhkd->bhqd", attn, vf)
+    ref.backward(do.float().transpose(1, 2))
+    orc.assert_close_bf16(out, ref.detach(), "out")
+    orc.assert_close_lse(lse.view(H, B, Lq).permute(1, 0, 2), l_ref.detach().masked_fill(dead, float("inf")))
+    orc.assert_close_grad_bf16(dq.transpose(1, 2), qf.grad, "dq")
+    orc.assert_close_grad_bf16(dk.transpose(1, 2), kf.grad, "dk")
+    orc.assert_close_grad_bf16(dv.transpose(1, 2), vf.grad, "dv")
+
+
+def test_efficient_attention_with_cu_seqlens(cuda_device, native_lib):
+    """cu_seqlens index the flattened B*L token axis (attention.cpp:435-470): two sequences of 200 and 256 tokens
+    inside a [2, 256] token grid; the tokens after the last offset belong to no sequence."""
+    dev = cuda_device
+    B, L, H, D = 2, 256, 2, 64
+    q, k, v, do = (rand((B, L, H, D), s) for s in (1, 2, 3, 4))
+    cu = [0, 200, 456]
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    out, lse, seed, off = ops._efficient_attention_forward(qd, kd, vd, None, cu_t, cu_t, 256, 0.0, 1, True)
+    dq, dk, dv, _ = ops._efficient_attention_backward(do.to(dev), qd, kd, vd, None, out.transpose(1, 2), cu_t, cu_t, 256, 256, lse,
+                                                     0.0, seed, off, 1, False)
+    assert ops.device_status() == 0
+    flat = lambda x: x.reshape(B * L, H, D)
+    o_ref, l_ref = orc.varlen_forward(flat(q), flat(k), flat(v), cu, cu, causal=True)
+    n = cu[-1]
+    orc.assert_close_bf16(flat(out.transpose(1, 2))[:n], o_ref, "out")
+    orc.assert_close_lse(lse[:, :n], l_ref)
+    want = orc.varlen_backward(flat(do)[:n], flat(q)[:n], flat(k)[:n], flat(v)[:n], cu, cu, causal=True)
+    for name, g, w in zip(("dq", "dk", "dv"), (dq, dk, dv), want):
+        orc.assert_close_grad_bf16(flat(g)[:n], w, name)

@@ -385,6 +385,101 @@ def _flash_attention_backward(grad_out, query, key, value, out, logsumexp, cum_s
 # --------------------------------------------------------------------------------------
 # decode (seqlen_q == 1, GQA allowed) - no reference counterpart
 # --------------------------------------------------------------------------------------
+# sdp::CustomMaskType (sdp_utils.h:32-37)
+NO_CUSTOM_MASK, CAUSAL_FROM_TOP_LEFT, CAUSAL_FROM_BOTTOM_RIGHT = 0, 1, 2
+
+
+def _efficient_attention_forward(query, key, value, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: Optional[int],
+                                 dropout_p: float, custom_mask_type: int, compute_log_sumexp: bool = False, *,
+                                 scale: Optional[float] = None, causal_diagonal=None, seqlen_k=None):
+    """(output, logsumexp, philox_seed, philox_offset), attention.cpp:393-507, without bias and dropout.
+
+    query is [B, Lq, H, D], key / value [B, Lk, H, D] (sequence before heads, unlike the sdp operators).
+    output comes back as the reference returns it: the [B, Lq, H, D] buffer viewed as [B, H, Lq, D]
+    (:503-506). logsumexp is [H, B*Lq] fp32 (mem_eff_fwd, FlashAttention_internal.cpp:603), empty unless
+    asked for. With cu_seqlens (int32 [B+1], offsets into the flattened B*L token axis, :435-470) the packed
+    kernels run; their causal mask is bottom-right aligned, so ``CausalFromTopLeft`` is taken there only
+    when both offset tensors are equal (the two alignments then coincide).
+    """
+    _check(query.dim() == 4 and key.dim() == 4 and value.dim() == 4, "query, key and value must be [B, L, H, D]")
+    _check(query.size(0) == key.size(0) == value.size(0), "batch sizes differ")
+    _check(key.size(1) == value.size(1), "key and value lengths differ")
+    _check(query.size(2) == key.size(2) == value.size(2), "numbers of heads differ")
+    _check(query.size(3) == key.size(3) == value.size(3), "head dims differ")
+    _check(bias is None, "bias is not supported: the additive-bias kernels are not built in this library")
+    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
+    _check(causal_diagonal is None and seqlen_k is None, "causal_diagonal and seqlen_k are not supported")
+    _check(custom_mask_type in (NO_CUSTOM_MASK, CAUSAL_FROM_TOP_LEFT, CAUSAL_FROM_BOTTOM_RIGHT),
+           f"unknown custom_mask_type {custom_mask_type}")
+    _check((cu_seqlens_q is None) == (cu_seqlens_k is None), "cu_seqlens_q and cu_seqlens_k must be given together")
+    B, Lq, H, D = query.shape
+    Lk = key.size(1)
+    sc = calculate_scale(query, scale)
+    seed, offset = _philox_placeholders(query)
+    if cu_seqlens_q is None:
+        q_t, k_t, v_t = query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2)
+        if custom_mask_type == CAUSAL_FROM_TOP_LEFT:
+            out, lse, _, _ = _scaled_dot_product_efficient_attention(q_t, k_t, v_t, None, True, 0.0, True, scale=sc)
+        else:
+            out, lse = _dense_forward(q_t, k_t, v_t, custom_mask_type == CAUSAL_FROM_BOTTOM_RIGHT, sc, allow_gqa=False)
+        lse = lse.permute(1, 0, 2).reshape(H, B * Lq)
+    else:
+        _check(cu_seqlens_q.dtype == torch.int32 and cu_seqlens_k.dtype == torch.int32, "cu_seqlens must have dtype int32")
+        _check(cu_seqlens_q.numel() == B + 1 and cu_seqlens_k.numel() == B + 1, "cu_seqlens must have batch + 1 entries")
+        if custom_mask_type == CAUSAL_FROM_TOP_LEFT:
+            _check(cu_seqlens_q is cu_seqlens_k or torch.equal(cu_seqlens_q, cu_seqlens_k),
+                   "CausalFromTopLeft with cu_seqlens needs equal query and key lengths in this library")
+        max_q = Lq if max_seqlen_q is None else int(max_seqlen_q)
+        out, lse, _, _, _ = _flash_attention_forward(
+            query.reshape(B * Lq, H, D), key.reshape(B * Lk, H, D), value.reshape(B * Lk, H, D), cu_seqlens_q.contiguous(),
+            cu_seqlens_k.contiguous(), max_q, Lk, 0.0, custom_mask_type != NO_CUSTOM_MASK, False, scale=sc)
+        out = out.view(B, Lq, H, D).transpose(1, 2)
+    if not compute_log_sumexp:
+        lse = lse.new_empty((0,))
+    return out, lse, seed, offset
+
+
+def _efficient_attention_backward(grad_out_, query, key, value, bias, out, cu_seqlens_q, cu_seqlens_k, max_seqlen_k: int,
+                                  max_seqlen_q: int, logsumexp, dropout_p: float, philox_seed, philox_offset,
+                                  custom_mask_type: int, bias_requires_grad: bool, *, scale: Optional[float] = None,
+                                  num_splits_key: Optional[int] = None):
+    """(grad_q [B,Lq,H,D], grad_k, grad_v [B,Lk,H,D], grad_bias), attention.cpp:579-727, for a forward call
+    made without bias; grad_bias is an empty tensor. ``out`` and ``grad_out_`` are [B, Lq, H, D] (any strides
+    with unit head-dim stride); ``logsumexp`` is the [H, B*Lq] tensor of the forward."""
+    _check(bias is None, "bias is not supported: the additive-bias kernels are not built in this library")
+    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
+    _check(query.dim() == 4 and grad_out_.dim() == 4 and out.dim() == 4, "tensors must be [B, L, H, D]")
+    _check((cu_seqlens_q is None) == (cu_seqlens_k is None), "cu_seqlens_q and cu_seqlens_k must be given together")
+    B, Lq, H, D = query.shape
+    Lk = key.size(1)
+    _check(tuple(logsumexp.shape) == (H, B * Lq), "logsumexp must be [heads, batch*seqlen_q]: run the forward with "
+                                                  "compute_log_sumexp=True")
+    sc = calculate_scale(query, scale)
+    empty_bias_grad = query.new_empty((0,))
+    if cu_seqlens_q is None:
+        t = lambda x: x.transpose(1, 2)
+        lse = logsumexp.view(H, B, Lq).permute(1, 0, 2).contiguous()
+        if custom_mask_type == CAUSAL_FROM_TOP_LEFT:
+            dq, dk, dv, _ = _scaled_dot_product_efficient_attention_backward(
+                t(grad_out_), t(query), t(key), t(value), None, t(out), lse, philox_seed, philox_offset, 0.0,
+                [True, True, True, False], True, scale=sc)
+        else:
+            go = t(grad_out_)
+            if go.stride(-1) != 1:
+                go = go.contiguous()
+            dq, dk, dv = _dense_backward(go, t(query), t(key), t(value), t(out), lse,
+                                         custom_mask_type == CAUSAL_FROM_BOTTOM_RIGHT, sc)
+        return t(dq), t(dk), t(dv), empty_bias_grad
+    if custom_mask_type == CAUSAL_FROM_TOP_LEFT:
+        _check(cu_seqlens_q is cu_seqlens_k or torch.equal(cu_seqlens_q, cu_seqlens_k),
+               "CausalFromTopLeft with cu_seqlens needs equal query and key lengths in this library")
+    dq, dk, dv = _flash_attention_backward(
+        grad_out_.reshape(B * Lq, H, D), query.reshape(B * Lq, H, D), key.reshape(B * Lk, H, D), value.reshape(B * Lk, H, D),
+        out.reshape(B * Lq, H, D), logsumexp.contiguous(), cu_seqlens_q.contiguous(), cu_seqlens_k.contiguous(),
+        int(max_seqlen_q), int(max_seqlen_k), 0.0, custom_mask_type != NO_CUSTOM_MASK, philox_seed, philox_offset, scale=sc)
+    return dq.view(B, Lq, H, D), dk.view(B, Lk, H, D), dv.view(B, Lk, H, D), empty_bias_grad
+
+
 def decode_attention(query, key_cache, value_cache, *, scale: Optional[float] = None, num_splits: int = 0):
     """query [B,Hq,1,D], key/value cache [B,Hkv,Lkv,D] -> (output [B,Hq,1,D], logsumexp [B,Hq,1]).
 
