@@ -54,7 +54,9 @@ def bf16_bits(t: torch.Tensor) -> np.ndarray:
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <checkout of Cambricon/torch_mlu>")
+    ref_root = sys.argv[1]
     attention_ref = load_reference_functions(ref_root)
     for idx, (name, B, Hq, Hkv, Lq, Lk, D, causal, scale) in enumerate(CASES):
         g = torch.Generator().manual_seed(1234 + idx)
