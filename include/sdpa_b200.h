@@ -51,7 +51,7 @@
 extern "C" {
 #endif
 
-#define SDPA_B200_VERSION 101
+#define SDPA_B200_VERSION 102
 
 #if defined(__GNUC__)
 #define SDPA_B200_API __attribute__((visibility("default")))
@@ -118,12 +118,15 @@ typedef struct sdpa_b200_params {
   int64_t dv_batch_stride, dv_head_stride, dv_row_stride;
 
   float softmax_scale; /* > 0; the reference default is 1/sqrt(head_dim), sdp_utils.h:40-47 */
-  float dropout_p;     /* must be 0 */
+  float dropout_p;     /* 0, or inside (0, 1) together with keep_rows / keep_cols (dense tensors only) */
   int32_t is_causal;
   int32_t dtype;      /* SDPA_B200_BF16 or SDPA_B200_F16 */
   int32_t kernel;     /* SDPA_B200_KERNEL_* (forward only) */
   int32_t num_splits; /* decode: 0 = choose; otherwise the number of KV splits */
-  int32_t reserved[4]; /* zero */
+  /* Dropout keep-masks written by sdpa_b200_dropout_keep_mask() for the same batch, heads_q and sequence
+   * lengths; both NULL when dropout_p == 0. The forward reads keep_rows; the backward reads both. */
+  const uint32_t* keep_rows;
+  const uint32_t* keep_cols;
 } sdpa_b200_params;
 
 SDPA_B200_API int sdpa_b200_version(void);
@@ -170,6 +173,19 @@ SDPA_B200_API int sdpa_b200_merge_partial(float* o_acc, float* lse_acc, const vo
                                           int32_t batch, int32_t heads, int32_t rows, int32_t head_dim,
                                           int32_t dtype, int64_t part_batch_stride, int64_t part_head_stride,
                                           int64_t part_row_stride, void* stream);
+
+/* Dropout pattern for one attention call, one bit per (query, key) pair, drawn from Philox4x32-10 with the
+ * given seed and offset (the reference draws it inside its device kernel from such a pair,
+ * FlashAttention_internal.cpp:190-214, and returns the pair so that the backward pass can repeat it; here the
+ * caller generates the masks again from the pair before calling sdpa_b200_bwd, or keeps them).
+ *   keep_rows: uint32 [batch*heads][Lq_pad][Lk_pad/32], bit (k & 31) of word (q, k >> 5) set = pair kept
+ *   keep_cols: uint32 [batch*heads][Lk_pad][Lq_pad/32], bit (q & 31) of word (k, q >> 5): the transpose
+ * Lq_pad / Lk_pad are the lengths rounded up to a multiple of 128; `heads` is heads_q. A pair is dropped with
+ * probability round(dropout_p * 256) / 256; kept probabilities are scaled by 1 / (1 - dropout_p) in the
+ * attention kernels. Only the low 32 bits of `offset` enter the counter. */
+SDPA_B200_API int sdpa_b200_dropout_keep_mask(uint64_t seed, uint64_t offset, float dropout_p, int32_t batch,
+                                              int32_t heads, int32_t seqlen_q, int32_t seqlen_k, uint32_t* keep_rows,
+                                              uint32_t* keep_cols, void* stream);
 
 /* How many of this library's kernels the calling process has launched so far. */
 SDPA_B200_API uint64_t sdpa_b200_launch_count(void);

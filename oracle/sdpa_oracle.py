@@ -267,3 +267,40 @@ def assert_close_reference_rule(got, true_value, lowp_value, name: str, fudge: f
     assert not bool(bad.any()), (f"{name}: {int(bad.sum())} elements outside atol {atol:.3e} rtol {rtol:.3e} "
                                  f"(max-abs error {float((g - t).abs().max()):.3e})")
     return atol, rtol
+
+
+# ------------------------------------------------------------------ dropout pattern
+def philox4x32_10(counter, key):
+    """Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC'11) on
+    numpy arrays: counter [..., 4] and key [..., 2] uint32 -> [..., 4] uint32."""
+    import numpy as np
+    c = [counter[..., i].astype(np.uint64) for i in range(4)]
+    k0 = np.uint64(key[0])
+    k1 = np.uint64(key[1])
+    mask = np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0 = np.uint64(0xD2511F53) * c[0]
+        p1 = np.uint64(0xCD9E8D57) * c[2]
+        hi0, lo0 = p0 >> np.uint64(32), p0 & mask
+        hi1, lo1 = p1 >> np.uint64(32), p1 & mask
+        c = [hi1 ^ c[1] ^ k0, lo1, hi0 ^ c[3] ^ k1, lo0]
+        k0 = (k0 + np.uint64(0x9E3779B9)) & mask
+        k1 = (k1 + np.uint64(0xBB67AE85)) & mask
+    return np.stack(c, axis=-1).astype(np.uint32)
+
+
+def dropout_keep_mask(seed: int, offset: int, dropout_p: float, batch: int, heads: int, seqlen_q: int, seqlen_k: int):
+    """bool [batch, heads, seqlen_q, seqlen_k], True = kept: the rule of the library's mask kernel restated.
+    counter = (key, query // 16, batch*heads_index, offset & 0xffffffff), key = (seed low, seed high); element
+    (q, k) is kept when byte (q % 16) of the 16 output bytes is >= round(dropout_p * 256)."""
+    import numpy as np
+    drop = min(255, max(0, int(dropout_p * 256.0 + 0.5)))
+    groups = (seqlen_q + 15) // 16
+    bh, g, k = np.meshgrid(np.arange(batch * heads, dtype=np.uint32), np.arange(groups, dtype=np.uint32),
+                           np.arange(seqlen_k, dtype=np.uint32), indexing="ij")
+    counter = np.stack([k, g, bh, np.full_like(k, offset & 0xFFFFFFFF)], axis=-1)
+    out = philox4x32_10(counter, (seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF))   # [BH, G, Lk, 4]
+    by = out.view(np.uint8).reshape(batch * heads, groups, seqlen_k, 16)            # little-endian bytes
+    keep = by >= drop                                                               # [BH, G, Lk, 16]
+    keep = keep.transpose(0, 1, 3, 2).reshape(batch * heads, groups * 16, seqlen_k)[:, :seqlen_q]
+    return torch.from_numpy(np.ascontiguousarray(keep)).reshape(batch, heads, seqlen_q, seqlen_k)

@@ -28,6 +28,7 @@ EXPORTED_SYMBOLS = (
     "sdpa_b200_read_device_status",
     "sdpa_b200_decode_static",
     "sdpa_b200_merge_partial",
+    "sdpa_b200_dropout_keep_mask",
     "sdpa_b200_launch_count",
 )
 STATIC_SCRATCH_BYTES = 16 << 20
@@ -52,7 +53,7 @@ class SdpaParams(ctypes.Structure):
         ("dv_batch_stride", c_int64), ("dv_head_stride", c_int64), ("dv_row_stride", c_int64),
         ("softmax_scale", c_float), ("dropout_p", c_float),
         ("is_causal", c_int32), ("dtype", c_int32), ("kernel", c_int32), ("num_splits", c_int32),
-        ("reserved", c_int32 * 4),
+        ("keep_rows", c_void_p), ("keep_cols", c_void_p),
     ]
 
 
@@ -98,6 +99,9 @@ def load() -> ctypes.CDLL:
     lib.sdpa_b200_merge_partial.restype = c_int
     lib.sdpa_b200_merge_partial.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                             c_int32, c_int64, c_int64, c_int64, c_void_p]
+    lib.sdpa_b200_dropout_keep_mask.restype = c_int
+    lib.sdpa_b200_dropout_keep_mask.argtypes = [c_uint64, c_uint64, c_float, c_int32, c_int32, c_int32, c_int32, c_void_p,
+                                                c_void_p, c_void_p]
     _lib = lib
     return lib
 

@@ -1,0 +1,137 @@
+// Dropout keep-masks for the attention kernels, one bit per (query, key) pair.
+//
+// The reference draws its dropout pattern inside the vendor kernel from a Philox seed / offset pair
+// (torch_mlu/csrc/aten/operators/cnnl/internal/FlashAttention_internal.cpp:190-214) and hands the pair to
+// the backward pass, which has to reproduce the pattern. Here the pattern is a separate, HBM-cheap
+// product: one bit per pair (Lq*Lk/8 bytes per head against 2*(Lq+Lk)*D of Q/K/V/O), written in both
+// orientations so that every attention kernel finds the bits of its thread's row in one aligned load:
+//   keep_rows [batch*heads][Lq_pad][Lk_pad/32]  bit (k & 31) of word (q, k >> 5): forward and dQ kernels
+//   keep_cols [batch*heads][Lk_pad][Lq_pad/32]  bit (q & 31) of word (k, q >> 5): dK/dV kernel
+// with Lq_pad, Lk_pad the lengths rounded up to 128 (a tile), so rows are 16-byte multiples and tiles
+// never read outside the array.
+//
+// Random stream: Philox4x32-10 (Salmon et al., SC'11). One call yields 16 bytes = the keep decisions of
+// 16 consecutive queries for one key: counter = (key, query / 16, batch*heads + head, offset), key =
+// the 64-bit seed. Element (q, k) is kept when byte (q & 15) of the output >= round(p * 256).
+#include "kernels.h"
+
+namespace sdpa_b200 {
+namespace {
+
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+    c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+    k.x += 0x9E3779B9u;
+    k.y += 0xBB67AE85u;
+  }
+  return c;
+}
+
+// 16 keep bits from 16 bytes: bit j set when byte j >= drop
+__device__ __forceinline__ uint32_t keep_bits16(uint4 r, uint32_t drop) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+  uint32_t bits = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) bits |= (((w[i] >> (8 * b)) & 0xffu) >= drop ? 1u : 0u) << (4 * i + b);
+  return bits;
+}
+
+struct MaskParams {
+  uint32_t* keep_rows;
+  uint32_t* keep_cols;
+  int lq_pad, lk_pad;
+  uint32_t seed_lo, seed_hi, offset, drop;
+};
+
+// One CTA (4 warps) per 128 x 128 tile of one head; warp w owns keys [32w, 32w + 32), lane = key.
+__global__ void __launch_bounds__(128) dropout_mask_kernel(const MaskParams p) {
+  __shared__ uint32_t rows[128][4];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t bh = blockIdx.z;
+  const int q0 = blockIdx.y * 128, k0 = blockIdx.x * 128;
+  const uint32_t k = k0 + warp * 32 + lane;
+  uint32_t col[4];
+#pragma unroll
+  for (int qb = 0; qb < 4; ++qb) {
+    const uint32_t g = (q0 + qb * 32) >> 4;  // first group of 16 queries
+    const uint32_t lo = keep_bits16(philox4x32_10(make_uint4(k, g, bh, p.offset), make_uint2(p.seed_lo, p.seed_hi)), p.drop);
+    const uint32_t hi = keep_bits16(philox4x32_10(make_uint4(k, g + 1, bh, p.offset), make_uint2(p.seed_lo, p.seed_hi)), p.drop);
+    col[qb] = lo | (hi << 16);
+  }
+  // key-major words: four consecutive words (128 queries) per key
+  *reinterpret_cast<uint4*>(p.keep_cols + (static_cast<size_t>(bh) * p.lk_pad + k) * (p.lq_pad >> 5) + (q0 >> 5)) =
+      make_uint4(col[0], col[1], col[2], col[3]);
+  // query-major words: transpose 32 x 32 bit blocks with ballots, gather the four key blocks of the
+  // tile in shared memory, then one 16-byte store per query row
+#pragma unroll
+  for (int qb = 0; qb < 4; ++qb) {
+    uint32_t mine = 0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const uint32_t w = __ballot_sync(0xffffffffu, (col[qb] >> j) & 1u);
+      if (lane == j) mine = w;
+    }
+    rows[qb * 32 + lane][warp] = mine;
+  }
+  __syncthreads();
+  const int q = q0 + threadIdx.x;
+  *reinterpret_cast<uint4*>(p.keep_rows + (static_cast<size_t>(bh) * p.lq_pad + q) * (p.lk_pad >> 5) + (k0 >> 5)) =
+      make_uint4(rows[threadIdx.x][0], rows[threadIdx.x][1], rows[threadIdx.x][2], rows[threadIdx.x][3]);
+}
+
+}  // namespace
+
+uint32_t dropout_drop_byte(float dropout_p) {
+  int d = static_cast<int>(dropout_p * 256.0f + 0.5f);
+  return static_cast<uint32_t>(d < 0 ? 0 : (d > 255 ? 255 : d));
+}
+
+}  // namespace sdpa_b200
+
+using namespace sdpa_b200;
+
+extern "C" SDPA_B200_API int sdpa_b200_dropout_keep_mask(uint64_t seed, uint64_t offset, float dropout_p, int32_t batch,
+                                                         int32_t heads, int32_t seqlen_q, int32_t seqlen_k,
+                                                         uint32_t* keep_rows, uint32_t* keep_cols, void* stream) {
+  if (keep_rows == nullptr || keep_cols == nullptr || (reinterpret_cast<uintptr_t>(keep_rows) & 15u) ||
+      (reinterpret_cast<uintptr_t>(keep_cols) & 15u)) {
+    set_error("dropout_keep_mask: keep_rows and keep_cols must be 16-byte aligned device pointers");
+    return SDPA_B200_INVALID_ARG;
+  }
+  if (batch <= 0 || heads <= 0 || seqlen_q <= 0 || seqlen_k <= 0 || static_cast<int64_t>(batch) * heads > 65535) {
+    set_error("dropout_keep_mask: sizes must be positive and batch*heads at most 65535 (got %d, %d, %d, %d)", batch, heads,
+              seqlen_q, seqlen_k);
+    return SDPA_B200_INVALID_ARG;
+  }
+  if (!(dropout_p > 0.f) || !(dropout_p < 1.f)) {
+    set_error("dropout_keep_mask: dropout_p must be inside (0, 1) (got %g)", static_cast<double>(dropout_p));
+    return SDPA_B200_INVALID_ARG;
+  }
+  MaskParams m;
+  m.keep_rows = keep_rows;
+  m.keep_cols = keep_cols;
+  m.lq_pad = (seqlen_q + 127) / 128 * 128;
+  m.lk_pad = (seqlen_k + 127) / 128 * 128;
+  m.seed_lo = static_cast<uint32_t>(seed);
+  m.seed_hi = static_cast<uint32_t>(seed >> 32);
+  m.offset = static_cast<uint32_t>(offset);
+  m.drop = dropout_drop_byte(dropout_p);
+  dim3 grid(m.lk_pad / 128, m.lq_pad / 128, batch * heads);
+  if (grid.y > 65535) {
+    set_error("dropout_keep_mask: seqlen_q too long (%d)", seqlen_q);
+    return SDPA_B200_INVALID_ARG;
+  }
+  dropout_mask_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(m);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("dropout_keep_mask: launch failed: %s", cudaGetErrorString(err));
+    return SDPA_B200_LAUNCH_FAILED;
+  }
+  count_launch();
+  return SDPA_B200_OK;
+}

@@ -38,6 +38,9 @@ int launch_fwd_decode(const sdpa_b200_params& p, void* workspace, size_t workspa
 // sdpa_api.cu. Returns an SDPA_B200_* status and sets the error text.
 int validate_forward_call(const sdpa_b200_params* p);
 
+// round(dropout_p * 256), the byte threshold of the dropout keep-masks (dropout_mask.cu)
+uint32_t dropout_drop_byte(float dropout_p);
+
 // Backward: delta pre-pass + dK/dV kernel + dQ kernel.
 size_t bwd_workspace_bytes(const sdpa_b200_params& p);
 int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_bytes,

@@ -151,11 +151,9 @@ int validate_common(const sdpa_b200_params* p) {
     set_error("varlen needs total_q and total_k > 0 (got %d, %d)", p->total_q, p->total_k);
     return SDPA_B200_INVALID_ARG;
   }
-  for (int i = 0; i < 4; ++i) {
-    if (p->reserved[i] != 0) {
-      set_error("reserved fields must be zero");
-      return SDPA_B200_INVALID_ARG;
-    }
+  if (p->dropout_p == 0.f && (p->keep_rows != nullptr || p->keep_cols != nullptr)) {
+    set_error("keep_rows / keep_cols must be NULL when dropout_p is 0");
+    return SDPA_B200_INVALID_ARG;
   }
   int st;
   if ((st = check_tensor("q", p->q, p->q_batch_stride, p->q_head_stride, p->q_row_stride, varlen, p->batch,

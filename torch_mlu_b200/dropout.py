@@ -1,0 +1,62 @@
+"""Dropout keep-masks for the attention operators (the C ABI's sdpa_b200_dropout_keep_mask).
+
+The reference returns a Philox (seed, offset) pair from its forward operators and replays it in the
+backward ones (FlashAttention_internal.cpp:190-214, 46-49). Here the pair selects a bit pattern that a small
+kernel writes once per call in two orientations; the attention kernels only read bits.
+"""
+from __future__ import annotations
+
+from typing import Tuple
+
+import torch
+
+from . import _cabi
+
+
+def padded(length: int) -> int:
+    return (length + 127) // 128 * 128
+
+
+class KeepMasks:
+    """keep_rows [B*H, Lq_pad, Lk_pad/32] and keep_cols [B*H, Lk_pad, Lq_pad/32] int32 words on the device."""
+
+    def __init__(self, seed: int, offset: int, dropout_p: float, batch: int, heads: int, seqlen_q: int, seqlen_k: int,
+                 device: torch.device):
+        if not (0.0 < dropout_p < 1.0):
+            raise ValueError(f"dropout_p must be inside (0, 1), got {dropout_p}")
+        self.shape = (batch, heads, seqlen_q, seqlen_k)
+        self.dropout_p = float(dropout_p)
+        self.seed, self.offset = int(seed), int(offset)
+        lq, lk = padded(seqlen_q), padded(seqlen_k)
+        self.rows = torch.empty((batch * heads, lq, lk // 32), dtype=torch.int32, device=device)
+        self.cols = torch.empty((batch * heads, lk, lq // 32), dtype=torch.int32, device=device)
+        lib = _cabi.load()
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream(device).cuda_stream
+            _cabi.check(lib.sdpa_b200_dropout_keep_mask(self.seed & (2 ** 64 - 1), self.offset & (2 ** 64 - 1), self.dropout_p,
+                                                        batch, heads, seqlen_q, seqlen_k, self.rows.data_ptr(),
+                                                        self.cols.data_ptr(), stream), "sdpa_b200_dropout_keep_mask")
+
+    def dense(self) -> torch.Tensor:
+        """bool [B, H, Lq, Lk], True = kept (what the reference's debug mask encodes as > 0)."""
+        B, H, Lq, Lk = self.shape
+        bits = (self.rows.unsqueeze(-1) >> torch.arange(32, device=self.rows.device, dtype=torch.int32)) & 1
+        return bits.reshape(B * H, self.rows.size(1), -1)[:, :Lq, :Lk].reshape(B, H, Lq, Lk).bool()
+
+    def dense_from_cols(self) -> torch.Tensor:
+        B, H, Lq, Lk = self.shape
+        bits = (self.cols.unsqueeze(-1) >> torch.arange(32, device=self.cols.device, dtype=torch.int32)) & 1
+        return bits.reshape(B * H, self.cols.size(1), -1)[:, :Lk, :Lq].transpose(1, 2).reshape(B, H, Lq, Lk).bool()
+
+
+_next_offset = 0
+
+
+def draw_seed_and_offset(device: torch.device, elements: int) -> Tuple[int, int]:
+    """(seed, offset) for one call: the CUDA generator's seed and a running offset that advances by the
+    number of elements a call covers, like getCounterOffset (FlashAttention_internal.cpp:46-49)."""
+    global _next_offset
+    seed = torch.cuda.default_generators[device.index if device.index is not None else torch.cuda.current_device()].initial_seed()
+    offset = _next_offset
+    _next_offset += (elements + 3) // 4
+    return seed, offset
