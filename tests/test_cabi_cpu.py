@@ -81,7 +81,9 @@ def test_workspace_query_and_validation_codes(native_lib):
     expect(lambda p: setattr(p, "head_dim", 100), _cabi.INVALID_ARG, "multiple of 8")
     expect(lambda p: setattr(p, "head_dim", 264), _cabi.INVALID_ARG, "at most 256")
     expect(lambda p: setattr(p, "head_dim", 192), _cabi.UNSUPPORTED, "up to 128")
-    expect(lambda p: setattr(p, "dropout_p", 0.1), _cabi.UNSUPPORTED, "dropout_p must be 0")
+    expect(lambda p: setattr(p, "dropout_p", 0.1), _cabi.INVALID_ARG, "needs keep_rows")
+    expect(lambda p: setattr(p, "dropout_p", 1.0), _cabi.INVALID_ARG, "inside (0, 1)")
+    expect(lambda p: setattr(p, "keep_rows", 4096), _cabi.INVALID_ARG, "must be NULL when dropout_p is 0")
     expect(lambda p: setattr(p, "dtype", 3), _cabi.UNSUPPORTED, "bf16")
     expect(lambda p: setattr(p, "max_seqlen_k", 0), _cabi.INVALID_ARG, "sequence lengths must be positive")
     expect(lambda p: setattr(p, "softmax_scale", 0.0), _cabi.INVALID_ARG, "softmax_scale")
@@ -129,8 +131,8 @@ def test_host_mirror_rejects_what_the_reference_rejects():
         ops._scaled_dot_product_flash_attention(q, q[:, :1], q[:, :1])
     with pytest.raises(RuntimeError, match="same sequence length"):
         ops._scaled_dot_product_flash_attention(q, q, q[:, :, :8])
-    with pytest.raises(RuntimeError, match="dropout"):
-        ops._scaled_dot_product_flash_attention(q, q, q, dropout_p=0.1)
+    with pytest.raises(RuntimeError, match="dropout_p must be inside"):
+        ops._scaled_dot_product_flash_attention(q, q, q, dropout_p=1.0)
     cu = torch.tensor([0, 16], dtype=torch.int64)
     p = q[0].transpose(0, 1)
     with pytest.raises(RuntimeError, match="int32"):

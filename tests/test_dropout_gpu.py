@@ -33,3 +33,93 @@ def test_keep_rate_and_stream_separation(cuda_device, native_lib):
         assert abs(agree - (0.75 ** 2 + 0.25 ** 2)) < 3e-3                  # independent patterns
     again = dropout.KeepMasks(1, 0, 0.25, B, H, L, L, cuda_device).dense()
     assert torch.equal(a, again)
+
+
+def attention_with_mask(q, k, v, keep, dropout_p, causal, scale=None):
+    """fp32 attention with a given dropout pattern: softmax first, then the kept probabilities scaled by
+    1 / (1 - p) (attention_ref, test_scaled_dot_product_attention.py:149-160). Bottom-right causal."""
+    qf, kf, vf = q.float(), k.float(), v.float()
+    sc = orc.calculate_scale(q.shape[-1], scale)
+    scores = torch.einsum("bhtd,bhsd->bhts", qf * sc, kf)
+    if causal:
+        scores = scores.masked_fill(orc.causal_mask_bottom_right(q.shape[2], k.shape[2]), float("-inf"))
+    lse = torch.logsumexp(scores, dim=-1)
+    attn = torch.softmax(scores, dim=-1)
+    dead = torch.isinf(lse) & (lse < 0)
+    attn = attn.masked_fill(dead.unsqueeze(-1), 0.0)
+    attn = attn.masked_fill(~keep, 0.0) / (1.0 - dropout_p)
+    return torch.einsum("bhts,bhsd->bhtd", attn, vf), lse.masked_fill(dead, float("inf"))
+
+
+def rand(shape, seed, dtype=torch.bfloat16):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(shape, generator=g).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,Lq,Lk,D,causal,p", [
+    (2, 4, 512, 512, 128, True, 0.22),      # the reference sweeps dropout_p 0.22 and 0.48 (test_...py:945)
+    (1, 2, 200, 333, 128, False, 0.48),
+    (1, 3, 300, 130, 64, True, 0.22),
+    (2, 2, 129, 257, 96, False, 0.1),
+])
+def test_forward_with_dropout_matches_oracle_with_the_returned_mask(cuda_device, native_lib, dtype, B, H, Lq, Lk, D, causal, p):
+    from torch_mlu_b200 import ops
+    dev = cuda_device
+    q, k, v = rand((B, H, Lq, D), 1, dtype), rand((B, H, Lk, D), 2, dtype), rand((B, H, Lk, D), 3, dtype)
+    out, lse, _, _, _, _, seed, offset, debug = ops._scaled_dot_product_flash_attention(q.to(dev), k.to(dev), v.to(dev), p, causal, True)
+    assert ops.device_status() == 0
+    assert tuple(debug.shape) == (B, H, Lq, Lk) and seed.numel() == 1 and offset.numel() == 1
+    keep = (debug > 0).cpu()
+    assert torch.equal(keep, orc.dropout_keep_mask(int(seed), int(offset), p, B, H, Lq, Lk))
+    o_ref, l_ref = attention_with_mask(q, k, v, keep, p, causal)
+    orc.assert_close_bf16(out, o_ref, "out")
+    orc.assert_close_lse(lse[..., :Lq], l_ref)        # dropout does not touch the logsumexp
+    # a second call draws another pattern
+    *_, off2, _ = ops._scaled_dot_product_flash_attention(q.to(dev), k.to(dev), v.to(dev), p, causal, False)
+    assert int(off2) != int(offset)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,Lq,Lk,D,causal,p", [
+    (2, 4, 512, 512, 128, True, 0.22),
+    (1, 2, 200, 333, 128, False, 0.48),
+    (1, 3, 300, 130, 64, True, 0.22),
+    (2, 2, 129, 257, 96, False, 0.1),
+])
+def test_backward_with_dropout_replays_the_pattern(cuda_device, native_lib, dtype, B, H, Lq, Lk, D, causal, p):
+    """Gradients against autograd through the fp32 math with the forward's mask (what the reference tests do,
+    test_scaled_dot_product_attention.py:1070-1110), held to that suite's own tolerance rule."""
+    from torch_mlu_b200 import ops
+    dev = cuda_device
+    q, k, v = rand((B, H, Lq, D), 1, dtype), rand((B, H, Lk, D), 2, dtype), rand((B, H, Lk, D), 3, dtype)
+    dout = torch.rand((B, H, Lq, D), generator=torch.Generator().manual_seed(4)).to(dtype)
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    out, lse, cq, ck, mq, mk, seed, offset, debug = ops._scaled_dot_product_flash_attention(qd, kd, vd, p, causal, True)
+    dq, dk, dv = ops._scaled_dot_product_flash_attention_backward(dout.to(dev), qd, kd, vd, out, lse, cq, ck, mq, mk, p, causal,
+                                                                  seed, offset)
+    assert ops.device_status() == 0
+    keep = (debug > 0).cpu()
+
+    def grads(compute_dtype):
+        qf, kf, vf = (t.to(compute_dtype).detach().requires_grad_(True) for t in (q, k, v))
+        sc = orc.calculate_scale(D, None)
+        scores = torch.einsum("bhtd,bhsd->bhts", qf * sc, kf)
+        if causal:
+            scores = scores.masked_fill(orc.causal_mask_bottom_right(Lq, Lk), float("-inf"))
+        attn = torch.softmax(scores, dim=-1)
+        dead = torch.isinf(torch.logsumexp(scores.float(), dim=-1))
+        attn = attn.masked_fill(dead.unsqueeze(-1), 0.0).masked_fill(~keep, 0.0) / (1.0 - p)
+        o = torch.einsum("bhts,bhsd->bhtd", attn, vf)
+        o.backward(dout.to(compute_dtype))
+        return o.detach(), qf.grad, kf.grad, vf.grad
+
+    true, lowp = grads(torch.float32), grads(dtype)
+    orc.assert_close_reference_rule(out, true[0], lowp[0], "out")
+    orc.assert_close_reference_rule(dq, true[1], lowp[1], "dq", fudge=4)
+    orc.assert_close_reference_rule(dk, true[2], lowp[2], "dk")
+    orc.assert_close_reference_rule(dv, true[3], lowp[3], "dv")
+    # and the absolute tolerances of the other parity tests where gradients are of order one
+    orc.assert_close_grad_bf16(dq, true[1], "dq")
+    orc.assert_close_grad_bf16(dk, true[2], "dk")
+    orc.assert_close_grad_bf16(dv, true[3], "dv")

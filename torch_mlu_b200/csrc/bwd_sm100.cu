@@ -90,6 +90,12 @@ struct BwdKernelParams {
   float scale, scale_log2;
   int is_causal;
   int head_dim;  // <= kD (the kernels are built for 64 and 128 columns; TMA pads loads and clips stores)
+  // dropout (kernels built with kDrop): one keep bit per (query, key) pair in both orientations, see
+  // dropout_mask.cu. P is recomputed without dropout; dV takes P o M / (1 - p), dS = P o (M o dP / (1 - p) - delta).
+  const uint32_t* keep_rows;  // [batch*heads_q][keep_lq_pad][keep_lk_pad / 32]: dQ kernel
+  const uint32_t* keep_cols;  // [batch*heads_q][keep_lk_pad][keep_lq_pad / 32]: dK/dV kernel
+  int keep_lq_pad, keep_lk_pad;
+  float keep_scale;  // 1 / (1 - dropout_p)
 #ifdef SDPA_BWD_STAMPS
   float* stamps;  // [mode 2][role 4][item 24][event 8] SM cycles since CTA start, one CTA per mode
 #endif
@@ -143,7 +149,12 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src,
                : "memory");
 }
 
-template <int kMode, int kD, bool kF16>
+// both halves of a packed 16-bit pair survive or die by two keep bits (bit 0 -> low half)
+__device__ __forceinline__ uint32_t keep_pair_mask(uint32_t two_bits) {
+  return ((two_bits & 1u) ? 0x0000ffffu : 0u) | ((two_bits & 2u) ? 0xffff0000u : 0u);
+}
+
+template <int kMode, int kD, bool kF16, bool kDrop>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -528,6 +539,16 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t sbuf = (kMode == kModeDKDV ? ((i & 1) ? t2 : t1) : ((i & 1) ? acc2 : t1)) + lane_base;
       const uint32_t dbuf = (kMode == kModeDKDV ? ((i & 1) ? t1 : t2) : t2) + lane_base;
       BWD_STAMP(half, i, 0);
+      // keep bits of this thread's 64 (row, column) pairs, in flight under the waits below
+      uint2 keep = make_uint2(0u, 0u);
+      if constexpr (kDrop) {
+        const uint32_t* words =
+            (kMode == kModeDQ)
+                ? p.keep_rows + (static_cast<size_t>(b * p.heads_q + hx) * p.keep_lq_pad + xr) * (p.keep_lk_pad >> 5)
+                : p.keep_cols + (static_cast<size_t>(b * p.heads_q + hx * p.kv_group + hi) * p.keep_lk_pad + xr) *
+                                    (p.keep_lq_pad >> 5);
+        keep = *reinterpret_cast<const uint2*>(words + ((y0 + half * 64) >> 5));
+      }
       // `ok` is made warp-uniform after every wait: the warp-level arrivals below need all 32 lanes
       ok = mbar_wait(bar + kBarSFull + (kMode == kModeDQ ? 8 * (i & 1) : 0), (kMode == kModeDQ ? (i >> 1) : i) & 1,
                      abort_flag);
@@ -591,7 +612,10 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (kMode == kModeDKDV) {
           uint32_t pw[32];
 #pragma unroll
-          for (int j2 = 0; j2 < 32; ++j2) pw[j2] = pack_16x2<kF16>(pr[2 * j2], pr[2 * j2 + 1]);
+          for (int j2 = 0; j2 < 32; ++j2) {
+            pw[j2] = pack_16x2<kF16>(pr[2 * j2], pr[2 * j2 + 1]);
+            if constexpr (kDrop) pw[j2] &= keep_pair_mask((j2 < 16 ? keep.x : keep.y) >> ((2 * j2) & 31));
+          }
           tmem_st_x16(sbuf, pw);
           tmem_st_x16(sbuf + 16, pw + 16);
           tmem_wait_st();
@@ -620,8 +644,13 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int j2 = 0; j2 < 32; ++j2) {
           const float dl0 = (kMode == kModeDKDV) ? vec_delta[2 * j2] : my_delta;
           const float dl1 = (kMode == kModeDKDV) ? vec_delta[2 * j2 + 1] : my_delta;
-          dw[j2] = pack_16x2<kF16>(pr[2 * j2] * (__uint_as_float(d[2 * j2]) - dl0),
-                               pr[2 * j2 + 1] * (__uint_as_float(d[2 * j2 + 1]) - dl1));
+          float dp0 = __uint_as_float(d[2 * j2]), dp1 = __uint_as_float(d[2 * j2 + 1]);
+          if constexpr (kDrop) {
+            const uint32_t two = (j2 < 16 ? keep.x : keep.y) >> ((2 * j2) & 31);
+            dp0 = (two & 1u) ? dp0 * p.keep_scale : 0.f;
+            dp1 = (two & 2u) ? dp1 * p.keep_scale : 0.f;
+          }
+          dw[j2] = pack_16x2<kF16>(pr[2 * j2] * (dp0 - dl0), pr[2 * j2 + 1] * (dp1 - dl1));
         }
         tmem_st_x16(sbuf + 32, dw);
         tmem_st_x16(sbuf + 48, dw + 16);
@@ -662,7 +691,7 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           dst = p.dv + ((p.cu_q != nullptr) ? static_cast<int64_t>(k_off + xr) * p.dv_row_stride
                                             : b * p.dv_batch_stride + static_cast<int64_t>(xr) * p.dv_row_stride) +
                 hx * p.dv_head_stride;
-          mul = 1.f;
+          mul = kDrop ? p.keep_scale : 1.f;
           acc = acc1;
         } else {
           dst = p.dk + ((p.cu_q != nullptr) ? static_cast<int64_t>(k_off + xr) * p.dk_row_stride
@@ -824,16 +853,20 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreParams p) 
 using TileKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
                             const CUtensorMap, const CUtensorMap, const BwdKernelParams);
 
-template <int kMode>
+template <int kMode, bool kDrop>
 TileKernel pick_tile_kernel(int head_dim, bool f16) {
-  if (head_dim <= 64) return f16 ? bwd_tile_kernel<kMode, 64, true> : bwd_tile_kernel<kMode, 64, false>;
-  return f16 ? bwd_tile_kernel<kMode, 128, true> : bwd_tile_kernel<kMode, 128, false>;
+  if (head_dim <= 64) return f16 ? bwd_tile_kernel<kMode, 64, true, kDrop> : bwd_tile_kernel<kMode, 64, false, kDrop>;
+  return f16 ? bwd_tile_kernel<kMode, 128, true, kDrop> : bwd_tile_kernel<kMode, 128, false, kDrop>;
 }
 
 int launch_tile_kernel(int mode, int head_dim, bool f16, int grid, cudaStream_t stream, const CUtensorMap& tm_q,
                        const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_do,
                        const CUtensorMap& tm_o1, const CUtensorMap& tm_o2, const BwdKernelParams& kp) {
-  TileKernel kernel = mode == kModeDKDV ? pick_tile_kernel<kModeDKDV>(head_dim, f16) : pick_tile_kernel<kModeDQ>(head_dim, f16);
+  const bool drop = kp.keep_rows != nullptr;
+  TileKernel kernel = mode == kModeDKDV ? (drop ? pick_tile_kernel<kModeDKDV, true>(head_dim, f16)
+                                                : pick_tile_kernel<kModeDKDV, false>(head_dim, f16))
+                                        : (drop ? pick_tile_kernel<kModeDQ, true>(head_dim, f16)
+                                                : pick_tile_kernel<kModeDQ, false>(head_dim, f16));
   const uint32_t smem = smem_bytes_for(mode);
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (err != cudaSuccess) {
@@ -950,6 +983,12 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   kp.lq_pad = lq_pad;
   kp.scale = p.softmax_scale;
   kp.head_dim = p.head_dim;
+  const bool drop = p.dropout_p > 0.f;
+  kp.keep_rows = drop ? p.keep_rows : nullptr;
+  kp.keep_cols = drop ? p.keep_cols : nullptr;
+  kp.keep_lq_pad = (p.max_seqlen_q + 127) / 128 * 128;
+  kp.keep_lk_pad = (p.max_seqlen_k + 127) / 128 * 128;
+  kp.keep_scale = drop ? 1.f / (1.f - p.dropout_p) : 1.f;
   kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   kp.is_causal = p.is_causal;
 #ifdef SDPA_BWD_STAMPS

@@ -88,6 +88,10 @@ struct FwdKernelParams {
   int64_t o_batch_stride, o_head_stride, o_row_stride;
   int seqlen_q, seqlen_k, total_q, heads_q, kv_group;
   int head_dim;  // <= kD: the real row length, for the paths that write rows without TMA
+  // dropout (kernels built with kDrop): one keep bit per (query, key) pair, see dropout_mask.cu
+  const uint32_t* keep_rows;  // [batch*heads_q][lq_pad][lk_words]
+  int lq_pad, lk_words;
+  float keep_scale;  // 1 / (1 - dropout_p), applied with the final 1 / l
   int num_m_blocks, num_bh, heads_per_wave, num_slots;  // work-unit order, see decode_unit()
   float scale_log2;
   int is_causal;
@@ -258,7 +262,12 @@ __device__ __forceinline__ void write_unit(uint8_t* smem, uint32_t e, const Unit
   dst[3] = make_uint4(u.n_iter, u.done, 0, 0);
 }
 
-template <int kD, bool kF16>
+// both halves of a packed 16-bit pair survive or die by two keep bits (bit 0 -> low half)
+__device__ __forceinline__ uint32_t keep_pair_mask(uint32_t two_bits) {
+  return ((two_bits & 1u) ? 0x0000ffffu : 0u) | ((two_bits & 2u) ? 0xffff0000u : 0u);
+}
+
+template <int kD, bool kF16, bool kDrop>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k,
@@ -543,10 +552,15 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       float m_run = neg_inf;
       float l_run = 0.f;
       if (row_in_tile == 0) FWD_STAMP(t, ucnt, 0);
+      const uint32_t* keep_row = nullptr;  // this row's keep bits, 4 words per key block
+      if constexpr (kDrop)
+        keep_row = p.keep_rows + (static_cast<size_t>(u.b * p.heads_q + u.h) * p.lq_pad + row) * p.lk_words;
 
       for (int j = 0; j < my_blocks; ++j) {
         const int n0 = j * kBlockN;
         const uint32_t par = (cnt + j) & 1;
+        uint4 keep = make_uint4(0u, 0u, 0u, 0u);
+        if constexpr (kDrop) keep = *reinterpret_cast<const uint4*>(keep_row + (n0 >> 5));  // in flight under the wait
         // warp-uniform, because the arrivals below are made by one lane on behalf of its warp
         ok = __all_sync(0xffffffffu, mbar_wait(bar_s, par, abort_flag));
         if (!ok) break;
@@ -617,6 +631,11 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
             const float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
             if (i & 1) lb = add2(lb, pr); else la = add2(la, pr);
             pk[i] = pack_16x2<kF16>(pr.x, pr.y);
+            if constexpr (kDrop) {
+              // the row sum above keeps every pair (softmax is normalised before dropout); only P.V loses them
+              const uint32_t word = (cc >> 1) == 0 ? keep.x : (cc >> 1) == 1 ? keep.y : (cc >> 1) == 2 ? keep.z : keep.w;
+              pk[i] &= keep_pair_mask(word >> ((cc & 1) * 16 + 2 * i));
+            }
           }
           if (cc == 4) {
             // keys 0-63 of P were stored one chunk of arithmetic ago, so this wait is short:
@@ -651,7 +670,8 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       const int u_q_off = info[0], u_h = info[1], u_b = info[2], u_len_q = info[3];
       if (row_lo < u_len_q) {
         tc_fence_after_sync();
-        const float inv_l = (l_run > 0.f) ? 1.f / l_run : 0.f;
+        float inv_l = (l_run > 0.f) ? 1.f / l_run : 0.f;
+        if constexpr (kDrop) inv_l *= p.keep_scale;
         uint32_t w[kD / 2];
 #pragma unroll
         for (int cc = 0; cc < kD / 32; ++cc) {
@@ -781,6 +801,11 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
   kp.heads_q = p.heads_q;
   kp.kv_group = p.heads_q / p.heads_kv;
   kp.head_dim = p.head_dim;
+  const bool drop = p.dropout_p > 0.f;
+  kp.keep_rows = p.keep_rows;
+  kp.lq_pad = (p.max_seqlen_q + 127) / 128 * 128;
+  kp.lk_words = (p.max_seqlen_k + 127) / 128 * 4;
+  kp.keep_scale = drop ? 1.f / (1.f - p.dropout_p) : 1.f;
   kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   kp.is_causal = p.is_causal;
 #ifdef SDPA_FWD_STAMPS
@@ -790,8 +815,12 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
   }
 #endif
 
-  auto kernel = p.head_dim <= 64 ? (f16 ? fwd_prefill_kernel<64, true> : fwd_prefill_kernel<64, false>)
-                                 : (f16 ? fwd_prefill_kernel<128, true> : fwd_prefill_kernel<128, false>);
+  auto pick = [&](auto drop_tag) {
+    constexpr bool kDrop = decltype(drop_tag)::value;
+    return p.head_dim <= 64 ? (f16 ? fwd_prefill_kernel<64, true, kDrop> : fwd_prefill_kernel<64, false, kDrop>)
+                            : (f16 ? fwd_prefill_kernel<128, true, kDrop> : fwd_prefill_kernel<128, false, kDrop>);
+  };
+  auto kernel = drop ? pick(std::true_type{}) : pick(std::false_type{});
   cudaError_t err =
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (err != cudaSuccess) {

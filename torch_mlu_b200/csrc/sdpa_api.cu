@@ -113,8 +113,26 @@ int validate_common(const sdpa_b200_params* p) {
     return SDPA_B200_UNSUPPORTED;
   }
   if (p->dropout_p != 0.f) {
-    set_error("dropout_p must be 0 (got %g)", static_cast<double>(p->dropout_p));
-    return SDPA_B200_UNSUPPORTED;
+    if (!(p->dropout_p > 0.f) || !(p->dropout_p < 1.f)) {
+      set_error("dropout_p must be 0 or inside (0, 1) (got %g)", static_cast<double>(p->dropout_p));
+      return SDPA_B200_INVALID_ARG;
+    }
+    if (p->cu_seqlens_q != nullptr || p->cu_seqlens_k != nullptr) {
+      set_error("dropout is built for dense tensors only (cu_seqlens given)");
+      return SDPA_B200_UNSUPPORTED;
+    }
+    if (p->kernel == SDPA_B200_KERNEL_DECODE) {
+      set_error("the decode kernel has no dropout");
+      return SDPA_B200_UNSUPPORTED;
+    }
+    if (p->keep_rows == nullptr || (reinterpret_cast<uintptr_t>(p->keep_rows) & 15u) != 0) {
+      set_error("dropout_p > 0 needs keep_rows from sdpa_b200_dropout_keep_mask (16-byte aligned)");
+      return SDPA_B200_INVALID_ARG;
+    }
+    if (static_cast<int64_t>(p->batch) * p->heads_q > 65535) {
+      set_error("dropout: batch * heads_q must be at most 65535");
+      return SDPA_B200_UNSUPPORTED;
+    }
   }
   if (p->batch <= 0 || p->heads_q <= 0 || p->heads_kv <= 0) {
     set_error("batch, heads_q and heads_kv must be positive (got %d, %d, %d)", p->batch, p->heads_q, p->heads_kv);
@@ -208,7 +226,7 @@ int check_device() {
 // Decode is chosen when there are too few query rows to fill a 128-row MMA tile.
 bool use_decode(const sdpa_b200_params* p) {
   if (p->kernel == SDPA_B200_KERNEL_DECODE) return true;
-  if (p->kernel == SDPA_B200_KERNEL_PREFILL) return false;
+  if (p->kernel == SDPA_B200_KERNEL_PREFILL || p->dropout_p != 0.f) return false;
   // the streaming kernel reads whole 64- or 128-element rows; other head dims take the tile kernel,
   // whose TMA loads pad the head dim with zeros
   return p->cu_seqlens_q == nullptr && p->max_seqlen_q == 1 && (p->head_dim == 64 || p->head_dim == 128);
@@ -316,6 +334,10 @@ int sdpa_b200_fwd(const sdpa_b200_params* p, void* workspace, size_t workspace_b
 int sdpa_b200_bwd(const sdpa_b200_params* p, void* workspace, size_t workspace_bytes, void* stream) {
   int st = validate_common(p);
   if (st != SDPA_B200_OK) return st;
+  if (p->dropout_p != 0.f && (p->keep_cols == nullptr || (reinterpret_cast<uintptr_t>(p->keep_cols) & 15u) != 0)) {
+    set_error("dropout_p > 0 needs keep_cols from sdpa_b200_dropout_keep_mask (16-byte aligned) in the backward");
+    return SDPA_B200_INVALID_ARG;
+  }
   const bool varlen = p->cu_seqlens_q != nullptr;
   if ((st = check_tensor("dout", p->dout, p->do_batch_stride, p->do_head_stride, p->do_row_stride, varlen,
                          p->batch, p->heads_q)) != SDPA_B200_OK)

@@ -26,7 +26,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from . import _cabi
+from . import _cabi, dropout
 
 __all__ = [
     "_scaled_dot_product_flash_attention",
@@ -161,8 +161,8 @@ def _dense_params(query, key, value, out, lse, is_causal, scale, kernel=_cabi.KE
     return p
 
 
-def _dense_forward(query, key, value, is_causal, scale, allow_gqa, kernel=_cabi.KERNEL_AUTO, num_splits=0):
-    # attention.cpp:70-100
+def _dense_forward(query, key, value, is_causal, scale, allow_gqa, kernel=_cabi.KERNEL_AUTO, num_splits=0, keep=None):
+    # attention.cpp:70-100; `keep`: dropout.KeepMasks of this call, or None
     _check(query.dim() == 4 and key.dim() == 4 and value.dim() == 4,
            "query, key and value must be 4-dimensional [batch, heads, seq_len, head_dim]")
     _check(query.size(0) == key.size(0) == value.size(0), "query, key and value must have the same batch size")
@@ -180,6 +180,9 @@ def _dense_forward(query, key, value, is_causal, scale, allow_gqa, kernel=_cabi.
     out = torch.empty((B, Lq, H, D), dtype=query.dtype, device=query.device).transpose(1, 2)
     lse = torch.empty((B, H, Lq), dtype=torch.float32, device=query.device)
     p = _dense_params(query, key, value, out, lse, is_causal, scale, kernel, num_splits)
+    if keep is not None:
+        p.dropout_p = keep.dropout_p
+        p.keep_rows, p.keep_cols = keep.rows.data_ptr(), keep.cols.data_ptr()
     _run_fwd(p, query.device)
     return out, lse
 
@@ -190,18 +193,30 @@ def _scaled_dot_product_flash_attention(query, key, value, dropout_p: float = 0.
 
     output is [B,H,Lq,D] bf16, logsumexp [B,H,Lq] fp32 (natural log, scale included).
     """
-    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
-    out, lse = _dense_forward(query, key, value, is_causal, calculate_scale(query, scale), allow_gqa=False)
-    B, _, Lq, _ = query.shape
+    _check(0.0 <= dropout_p < 1.0, "dropout_p must be inside [0, 1)")
+    _check(query.dim() == 4 and key.dim() == 4 and value.dim() == 4,
+           "query, key and value must be 4-dimensional [batch, heads, seq_len, head_dim]")
+    B, H, Lq, _ = query.shape
     Lk = key.size(2)
+    keep = None
+    seed, offset = _philox_placeholders(query)
+    debug = _empty_like_debug(query)
+    if dropout_p > 0.0:
+        # With dropout the operator returns the Philox pair that fixes the pattern (FlashAttention_internal.cpp:
+        # 190-214), as CPU int64 scalars, and on request the pattern itself (:141-146): > 0 where a pair was kept.
+        s, o = dropout.draw_seed_and_offset(query.device, B * H * Lq * Lk)
+        keep = dropout.KeepMasks(s, o, dropout_p, B, H, Lq, Lk, query.device)
+        seed, offset = torch.tensor(s, dtype=torch.int64), torch.tensor(o, dtype=torch.int64)
+        if return_debug_mask:
+            debug = keep.dense().to(query.dtype)
+    out, lse = _dense_forward(query, key, value, is_causal, calculate_scale(query, scale), allow_gqa=False, keep=keep)
     # attention.cpp:109-119; kept for callers that pass them on to the backward op
     cum_q = torch.arange(0, (B + 1) * Lq, Lq, dtype=torch.int32, device=query.device)
     cum_k = torch.arange(0, (B + 1) * Lk, Lk, dtype=torch.int32, device=query.device)
-    seed, offset = _philox_placeholders(query)
-    return out, lse, cum_q, cum_k, Lq, Lk, seed, offset, _empty_like_debug(query)
+    return out, lse, cum_q, cum_k, Lq, Lk, seed, offset, debug
 
 
-def _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, scale):
+def _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, scale, keep=None):
     _check_inputs(grad_out, query, key, value, out)
     _check(logsumexp.dtype == torch.float32 and logsumexp.is_contiguous(), "logsumexp must be contiguous fp32")
     B, H, Lq, D = query.shape
@@ -215,6 +230,9 @@ def _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, scal
     _set_strides_bhld(p, "dq", dq)
     _set_strides_bhld(p, "dk", dk)
     _set_strides_bhld(p, "dv", dv)
+    if keep is not None:
+        p.dropout_p = keep.dropout_p
+        p.keep_rows, p.keep_cols = keep.rows.data_ptr(), keep.cols.data_ptr()
     _run_bwd(p, query.device)
     return dq, dk, dv
 
@@ -222,11 +240,20 @@ def _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, scal
 def _scaled_dot_product_flash_attention_backward(grad_out, query, key, value, out, logsumexp, cum_seq_q, cum_seq_k,
                                                  max_q, max_k, dropout_p, is_causal, philox_seed, philox_offset,
                                                  *, scale: Optional[float] = None):
-    """(grad_q, grad_k, grad_v), each shaped like its input (attention.cpp:205-297)."""
-    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
+    """(grad_q, grad_k, grad_v), each shaped like its input (attention.cpp:205-297). With dropout the pattern
+    of the forward call is drawn again from ``philox_seed`` / ``philox_offset``."""
+    _check(0.0 <= dropout_p < 1.0, "dropout_p must be inside [0, 1)")
     if grad_out.stride(-1) != 1:
         grad_out = grad_out.contiguous()
-    return _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, calculate_scale(query, scale))
+    keep = None
+    if dropout_p > 0.0:
+        _check(philox_seed.numel() == 1 and philox_offset.numel() == 1,
+               "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned")
+        B, H, Lq, _ = query.shape
+        keep = dropout.KeepMasks(int(philox_seed), int(philox_offset), dropout_p, B, H, Lq, key.size(2), query.device)
+    if logsumexp.size(-1) != query.size(2):
+        logsumexp = logsumexp[..., :query.size(2)].contiguous()
+    return _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, calculate_scale(query, scale), keep=keep)
 
 
 # --------------------------------------------------------------------------------------
