@@ -63,7 +63,7 @@ extern "C" {
 enum {
   SDPA_B200_OK = 0,
   SDPA_B200_INVALID_ARG = 1,    /* null pointer, bad shape, bad stride/alignment, workspace too small */
-  SDPA_B200_UNSUPPORTED = 2,    /* valid request this build has no kernel for (dtype, head_dim > 128, dropout) */
+  SDPA_B200_UNSUPPORTED = 2,    /* valid request this build has no kernel for (dtype, head_dim > 128, varlen dropout) */
   SDPA_B200_LAUNCH_FAILED = 3,  /* CUDA reported an error while configuring or launching */
   SDPA_B200_DEVICE_TIMEOUT = 4, /* a bounded wait inside a kernel ran out (read back from workspace) */
   SDPA_B200_NO_DEVICE = 5       /* not an sm_100 device / no CUDA driver */

@@ -114,3 +114,30 @@ def test_efficient_attention_with_cu_seqlens(cuda_device, native_lib):
     want = orc.varlen_backward(flat(do)[:n], flat(q)[:n], flat(k)[:n], flat(v)[:n], cu, cu, causal=True)
     for name, g, w in zip(("dq", "dk", "dv"), (dq, dk, dv), want):
         orc.assert_close_grad_bf16(flat(g)[:n], w, name)
+
+
+def test_efficient_attention_with_dropout(cuda_device, native_lib):
+    """The reference sweeps dropout_p over the memory-efficient operator too (test_...py:1379-1402). The pattern is
+    rebuilt from the returned Philox pair with the CPU restatement of the mask rule."""
+    dev = cuda_device
+    B, H, L, D, p = 2, 2, 320, 128, 0.48
+    q, k, v = (rand((B, H, L, D), s) for s in (1, 2, 3))
+    do = torch.rand((B, H, L, D), generator=torch.Generator().manual_seed(4)).bfloat16()
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    out, lse, seed, off = ops._scaled_dot_product_efficient_attention(qd, kd, vd, None, True, p, True)
+    dq, dk, dv, _ = ops._scaled_dot_product_efficient_attention_backward(do.to(dev), qd, kd, vd, None, out, lse, seed, off, p,
+                                                                        [True, True, True, False], True)
+    assert ops.device_status() == 0
+    keep = orc.dropout_keep_mask(int(seed), int(off), p, B, H, L, L)
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    scores = torch.einsum("bhqd,bhkd->bhqk", qf, kf) / D ** 0.5
+    scores = scores.masked_fill(torch.ones(L, L, dtype=torch.bool).triu(1), float("-inf"))
+    attn = torch.softmax(scores, dim=-1).masked_fill(~keep, 0.0) / (1 - p)
+    ref = torch.einsum("bhqk,bhkd->bhqd", attn, vf)
+    ref.backward(do.float())
+    orc.assert_close_bf16(out, ref.detach(), "out")
+    orc.assert_close_grad_bf16(dq, qf.grad, "dq")
+    orc.assert_close_grad_bf16(dk, kf.grad, "dk")
+    orc.assert_close_grad_bf16(dv, vf.grad, "dv")
+    with pytest.raises(RuntimeError, match="Lq != Lk is not built"):
+        ops._scaled_dot_product_efficient_attention(qd, kd[:, :, :100], vd[:, :, :100], None, True, p, True)

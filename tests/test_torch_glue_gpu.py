@@ -91,10 +91,11 @@ def test_glue_rejects_what_the_reference_rejects(cuda_device, native_lib):
         torch.ops.b200_sdpa._scaled_dot_product_flash_attention(q, q[:, :1], q[:, :1])
     with pytest.raises(RuntimeError, match="fp16 and bf16"):
         torch.ops.b200_sdpa._scaled_dot_product_flash_attention(q.float(), q.float(), q.float())
-    with pytest.raises(RuntimeError, match="dropout"):
-        torch.ops.b200_sdpa._scaled_dot_product_flash_attention(q, q, q, 0.5)
-    with pytest.raises(RuntimeError, match="head_dim 128"):
-        torch.ops.b200_sdpa._scaled_dot_product_flash_attention(q[..., :32], q[..., :32], q[..., :32])
+    with pytest.raises(RuntimeError, match="dropout_p must be inside"):
+        torch.ops.b200_sdpa._scaled_dot_product_flash_attention(q, q, q, 1.0)
+    wide = torch.cat([q, q[..., :64]], dim=-1)
+    with pytest.raises(RuntimeError, match="up to 128"):
+        torch.ops.b200_sdpa._scaled_dot_product_flash_attention(wide, wide, wide)
 
 
 @pytest.mark.parametrize("amp_dtype", [torch.bfloat16, torch.float16])
@@ -118,3 +119,66 @@ def test_autocast_casts_fp32_inputs_like_the_reference(cuda_device, native_lib, 
     orc.assert_close_grad_bf16(qd.grad, dq, "dq")
     orc.assert_close_grad_bf16(kd.grad, dk, "dk")
     orc.assert_close_grad_bf16(vd.grad, dv, "dv")
+
+
+def _attention_with_mask(q, k, v, keep, p, causal, dtype=torch.float32):
+    qf, kf, vf = (t.to(dtype).detach().requires_grad_(True) for t in (q, k, v))
+    scores = torch.einsum("bhtd,bhsd->bhts", qf * (q.shape[-1] ** -0.5), kf)
+    if causal:
+        scores = scores.masked_fill(orc.causal_mask_bottom_right(q.shape[2], k.shape[2]), float("-inf"))
+    attn = torch.softmax(scores, dim=-1).masked_fill(~keep, 0.0) / (1.0 - p)
+    return torch.einsum("bhts,bhsd->bhtd", attn, vf), (qf, kf, vf)
+
+
+def test_dropout_through_the_registered_operator_and_autograd(cuda_device, native_lib):
+    """dropout_p > 0 with return_debug_mask, as the reference tests call it (test_...py:1018-1026): the operator
+    returns the pattern and the Philox pair; autograd's backward replays the pattern from the pair."""
+    torch_glue.load()
+    dev = cuda_device
+    p = 0.22
+    q, k, v = (rand((2, 3, 260, 128), s) for s in (1, 2, 3))
+    do = torch.rand((2, 3, 260, 128), generator=torch.Generator().manual_seed(4)).bfloat16()
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    res = torch.ops.b200_sdpa._scaled_dot_product_flash_attention(qd, kd, vd, p, True, True)
+    out, seed, offset, debug = res[0], res[6], res[7], res[8]
+    assert seed.numel() == 1 and offset.numel() == 1 and tuple(debug.shape) == (2, 3, 260, 260)
+    keep = (debug > 0).cpu()
+    assert torch.equal(keep, orc.dropout_keep_mask(int(seed), int(offset), p, 2, 3, 260, 260))
+    out.backward(do.to(dev))
+    ref, (qf, kf, vf) = _attention_with_mask(q, k, v, keep, p, True)
+    ref.backward(do.float())
+    lp, (ql, kl, vl) = _attention_with_mask(q, k, v, keep, p, True, torch.bfloat16)
+    lp.backward(do)
+    orc.assert_close_bf16(out, ref.detach(), "out")
+    orc.assert_close_reference_rule(qd.grad, qf.grad, ql.grad, "dq", fudge=4)
+    orc.assert_close_reference_rule(kd.grad, kf.grad, kl.grad, "dk")
+    orc.assert_close_reference_rule(vd.grad, vf.grad, vl.grad, "dv")
+
+
+def test_functional_sdpa_with_dropout_uses_the_cuda_generator(cuda_device, native_lib):
+    """F.scaled_dot_product_attention(dropout_p=...) on the overridden aten operators: the pattern comes from the
+    device generator's (seed, offset), which the test reads before the call to rebuild the expected result."""
+    dev = cuda_device
+    p = 0.3
+    q, k, v = (rand((1, 4, 256, 128), s) for s in (1, 2, 3))
+    do = torch.rand((1, 4, 256, 128), generator=torch.Generator().manual_seed(4)).bfloat16()
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    torch_glue.install_aten_overrides()
+    try:
+        torch.cuda.manual_seed(4242)
+        gen = torch.cuda.default_generators[dev.index or 0]
+        seed, offset = gen.initial_seed(), gen.get_offset()
+        with backends.sdp_kernel(enable_flash=True, enable_math=False, enable_mem_efficient=False):
+            out = F.scaled_dot_product_attention(qd, kd, vd, dropout_p=p, is_causal=True)
+            again = F.scaled_dot_product_attention(qd, kd, vd, dropout_p=p, is_causal=True)
+        out.backward(do.to(dev))
+    finally:
+        torch_glue.remove_aten_overrides()
+    assert not torch.equal(out, again)          # the generator moved on
+    keep = orc.dropout_keep_mask(seed, offset, p, 1, 4, 256, 256)
+    ref, (qf, kf, vf) = _attention_with_mask(q, k, v, keep, p, True)
+    ref.backward(do.float())
+    orc.assert_close_bf16(out, ref.detach(), "out")
+    orc.assert_close_grad_bf16(qd.grad, qf.grad, "dq")
+    orc.assert_close_grad_bf16(kd.grad, kf.grad, "dk")
+    orc.assert_close_grad_bf16(vd.grad, vf.grad, "dv")

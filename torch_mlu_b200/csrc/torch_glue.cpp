@@ -14,6 +14,7 @@
 #include <ATen/ATen.h>
 #include <ATen/autocast_mode.h>
 #include <ATen/cuda/CUDAContext.h>
+#include <ATen/cuda/CUDAGeneratorImpl.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 
@@ -133,9 +134,63 @@ void check_varlen(const Tensor& q, const Tensor& k, const Tensor& v, const Tenso
   check_input(v, "value");
 }
 
+// ------------------------------------------------------------------------- dropout pattern
+// One bit per (query, key) pair in both orientations, written by the library from a Philox seed / offset pair
+// (the reference draws the pattern inside its kernel from such a pair and hands the pair to the backward
+// operator, FlashAttention_internal.cpp:190-214).
+struct KeepMasks {
+  Tensor rows, cols;  // int32 [B*H, Lq_pad, Lk_pad/32] and [B*H, Lk_pad, Lq_pad/32]
+  double p = 0.0;
+};
+
+KeepMasks make_keep_masks(const Tensor& q, int64_t seqlen_k, double dropout_p, uint64_t seed, uint64_t offset) {
+  TORCH_CHECK(dropout_p > 0.0 && dropout_p < 1.0, "dropout_p must be inside [0, 1)");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t BH = q.size(0) * q.size(1), Lq = q.size(2);
+  const int64_t lq_pad = (Lq + 127) / 128 * 128, lk_pad = (seqlen_k + 127) / 128 * 128;
+  KeepMasks m;
+  m.p = dropout_p;
+  m.rows = at::empty({BH, lq_pad, lk_pad / 32}, q.options().dtype(at::kInt));
+  m.cols = at::empty({BH, lk_pad, lq_pad / 32}, q.options().dtype(at::kInt));
+  check_status(sdpa_b200_dropout_keep_mask(seed, offset, static_cast<float>(dropout_p), static_cast<int32_t>(q.size(0)),
+                                           static_cast<int32_t>(q.size(1)), static_cast<int32_t>(Lq),
+                                           static_cast<int32_t>(seqlen_k), reinterpret_cast<uint32_t*>(m.rows.data_ptr()),
+                                           reinterpret_cast<uint32_t*>(m.cols.data_ptr()),
+                                           at::cuda::getCurrentCUDAStream().stream()),
+               "sdpa_b200_dropout_keep_mask");
+  return m;
+}
+
+// (seed, offset) of the device's default generator, advanced like any other Philox consumer
+std::pair<uint64_t, uint64_t> draw_philox(const Tensor& q, int64_t elements) {
+  auto gen = at::get_generator_or_default<at::CUDAGeneratorImpl>(c10::nullopt,
+                                                                 at::cuda::detail::getDefaultCUDAGenerator(q.get_device()));
+  std::lock_guard<std::mutex> lock(gen->mutex_);
+  return gen->philox_engine_inputs(static_cast<uint64_t>((elements + 3) / 4));
+}
+
+Tensor cpu_i64(uint64_t v) { return at::scalar_tensor(at::Scalar(static_cast<int64_t>(v)), at::dtype(at::kLong)); }
+
+// > 0 where a pair was kept, in q's dtype, [B, H, Lq, Lk] (the debug mask of FlashAttention_internal.cpp:141-146)
+Tensor debug_mask_of(const KeepMasks& m, const Tensor& q, int64_t seqlen_k) {
+  Tensor bits = at::bitwise_and(at::bitwise_right_shift(m.rows.unsqueeze(-1), at::arange(32, m.rows.options())), 1);
+  return bits.reshape({m.rows.size(0), m.rows.size(1), -1})
+      .slice(1, 0, q.size(2))
+      .slice(2, 0, seqlen_k)
+      .reshape({q.size(0), q.size(1), q.size(2), seqlen_k})
+      .to(q.scalar_type());
+}
+
+void set_dropout(sdpa_b200_params& p, const KeepMasks* keep) {
+  if (keep == nullptr) return;
+  p.dropout_p = static_cast<float>(keep->p);
+  p.keep_rows = reinterpret_cast<const uint32_t*>(keep->rows.data_ptr());
+  p.keep_cols = reinterpret_cast<const uint32_t*>(keep->cols.data_ptr());
+}
+
 // ------------------------------------------------------------------------- dense [B,H,L,D]
 std::tuple<Tensor, Tensor> dense_forward(const Tensor& q, const Tensor& k, const Tensor& v, bool causal, double scale,
-                                         bool allow_gqa) {
+                                         bool allow_gqa, const KeepMasks* keep = nullptr) {
   // attention.cpp:70-100
   TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4,
               "query, key and value must be 4-dimensional [batch, heads, seq_len, head_dim]");
@@ -158,12 +213,14 @@ std::tuple<Tensor, Tensor> dense_forward(const Tensor& q, const Tensor& k, const
   Tensor lse = at::empty({B, H, L}, q.options().dtype(at::kFloat));
   sdpa_b200_params p;
   dense_params(p, q, k, v, out, lse, causal, scale);
+  set_dropout(p, keep);
   run(p, false, q);
   return {out, lse};
 }
 
 std::tuple<Tensor, Tensor, Tensor> dense_backward(const Tensor& dout_in, const Tensor& q, const Tensor& k, const Tensor& v,
-                                                  const Tensor& out, const Tensor& lse, bool causal, double scale) {
+                                                  const Tensor& out, const Tensor& lse, bool causal, double scale,
+                                                  const KeepMasks* keep = nullptr) {
   Tensor dout = dout_in.stride(-1) == 1 ? dout_in : dout_in.contiguous();
   check_input(dout, "grad_out");
   check_input(q, "query");
@@ -188,8 +245,49 @@ std::tuple<Tensor, Tensor, Tensor> dense_backward(const Tensor& dout_in, const T
   set_bhld(p.dq_batch_stride, p.dq_head_stride, p.dq_row_stride, dq);
   set_bhld(p.dk_batch_stride, p.dk_head_stride, p.dk_row_stride, dk);
   set_bhld(p.dv_batch_stride, p.dv_head_stride, p.dv_row_stride, dv);
+  set_dropout(p, keep);
   run(p, true, q);
   return {dq, dk, dv};
+}
+
+// The dense operator pair with dropout: the forward draws a Philox pair, returns it as two CPU int64 scalars
+// (and the pattern on request); the backward draws the same pattern again from them.
+struct DenseDropoutResult {
+  Tensor out, lse, seed, offset, debug;
+};
+
+DenseDropoutResult dense_forward_with_dropout(const Tensor& q, const Tensor& k, const Tensor& v, double dropout_p,
+                                              bool causal, bool return_debug_mask, double scale, bool allow_gqa) {
+  TORCH_CHECK(dropout_p >= 0.0 && dropout_p < 1.0, "dropout_p must be inside [0, 1)");
+  DenseDropoutResult r;
+  r.seed = at::empty({0}, q.options().dtype(at::kLong));
+  r.offset = at::empty({0}, q.options().dtype(at::kLong));
+  r.debug = at::empty({0}, q.options());
+  if (dropout_p == 0.0) {
+    std::tie(r.out, r.lse) = dense_forward(q, k, v, causal, scale, allow_gqa);
+    return r;
+  }
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4, "query, key and value must be 4-dimensional [batch, heads, seq_len, head_dim]");
+  auto [seed, offset] = draw_philox(q, q.size(0) * q.size(1) * q.size(2) * k.size(2));
+  KeepMasks keep = make_keep_masks(q, k.size(2), dropout_p, seed, offset);
+  std::tie(r.out, r.lse) = dense_forward(q, k, v, causal, scale, allow_gqa, &keep);
+  r.seed = cpu_i64(seed);
+  r.offset = cpu_i64(offset);
+  if (return_debug_mask) r.debug = debug_mask_of(keep, q, k.size(2));
+  return r;
+}
+
+std::tuple<Tensor, Tensor, Tensor> dense_backward_with_dropout(const Tensor& grad_out, const Tensor& q, const Tensor& k,
+                                                               const Tensor& v, const Tensor& out, const Tensor& lse,
+                                                               double dropout_p, bool causal, const Tensor& philox_seed,
+                                                               const Tensor& philox_offset, double scale) {
+  TORCH_CHECK(dropout_p >= 0.0 && dropout_p < 1.0, "dropout_p must be inside [0, 1)");
+  if (dropout_p == 0.0) return dense_backward(grad_out, q, k, v, out, lse, causal, scale);
+  TORCH_CHECK(philox_seed.numel() == 1 && philox_offset.numel() == 1,
+              "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned");
+  KeepMasks keep = make_keep_masks(q, k.size(2), dropout_p, static_cast<uint64_t>(philox_seed.item<int64_t>()),
+                                   static_cast<uint64_t>(philox_offset.item<int64_t>()));
+  return dense_backward(grad_out, q, k, v, out, lse, causal, scale, &keep);
 }
 
 // ------------------------------------------------------------------ packed [total,H,D]
@@ -235,7 +333,7 @@ std::tuple<Tensor, Tensor, Tensor> varlen_backward(const Tensor& dout_in, const 
 }
 
 void check_no_dropout(double dropout_p) {
-  TORCH_CHECK(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library");
+  TORCH_CHECK(dropout_p == 0.0, "dropout_p must be 0: dropout is built for the dense operators only");
 }
 
 Tensor empty_i64(const Tensor& like) { return at::empty({0}, like.options().dtype(at::kLong)); }
@@ -245,14 +343,13 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, int64_t, int64_t, Tensor, Tensor, Ten
     const Tensor& q, const Tensor& k, const Tensor& v, double dropout_p, bool is_causal, bool return_debug_mask,
     c10::optional<double> scale) {
   C10_LOG_API_USAGE_ONCE("torch.sdpa.flash_attention");  // attention.cpp:67
-  (void)return_debug_mask;
-  check_no_dropout(dropout_p);
-  auto [out, lse] = dense_forward(q, k, v, is_causal, scale_or_default(q, scale), /*allow_gqa=*/false);
+  auto r = dense_forward_with_dropout(q, k, v, dropout_p, is_causal, return_debug_mask, scale_or_default(q, scale),
+                                      /*allow_gqa=*/false);
   const int64_t B = q.size(0), Lq = q.size(2), Lk = k.size(2);
   auto iopt = q.options().dtype(at::kInt);
   Tensor cum_q = at::arange(0, (B + 1) * Lq, Lq, iopt);  // attention.cpp:109-119
   Tensor cum_k = at::arange(0, (B + 1) * Lk, Lk, iopt);
-  return {out, lse, cum_q, cum_k, Lq, Lk, empty_i64(q), empty_i64(q), at::empty({0}, q.options())};
+  return {r.out, r.lse, cum_q, cum_k, Lq, Lk, r.seed, r.offset, r.debug};
 }
 
 std::tuple<Tensor, Tensor, Tensor> ref_sdpa_flash_backward(const Tensor& grad_out, const Tensor& q, const Tensor& k,
@@ -261,9 +358,9 @@ std::tuple<Tensor, Tensor, Tensor> ref_sdpa_flash_backward(const Tensor& grad_ou
                                                            int64_t max_k, double dropout_p, bool is_causal,
                                                            const Tensor& philox_seed, const Tensor& philox_offset,
                                                            c10::optional<double> scale) {
-  (void)cum_q; (void)cum_k; (void)max_q; (void)max_k; (void)philox_seed; (void)philox_offset;
-  check_no_dropout(dropout_p);
-  return dense_backward(grad_out, q, k, v, out, lse, is_causal, scale_or_default(q, scale));
+  (void)cum_q; (void)cum_k; (void)max_q; (void)max_k;
+  return dense_backward_with_dropout(grad_out, q, k, v, out, lse, dropout_p, is_causal, philox_seed, philox_offset,
+                                     scale_or_default(q, scale));
 }
 
 std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> ref_flash_forward(const Tensor& q, const Tensor& k, const Tensor& v,
@@ -292,12 +389,11 @@ std::tuple<Tensor, Tensor, Tensor> ref_flash_backward(const Tensor& grad_out, co
 std::tuple<Tensor, Tensor, Tensor, Tensor, c10::SymInt, c10::SymInt, Tensor, Tensor, Tensor> aten_sdpa_flash(
     const Tensor& q, const Tensor& k, const Tensor& v, double dropout_p, bool is_causal, bool return_debug_mask,
     c10::optional<double> scale) {
-  (void)return_debug_mask;
-  check_no_dropout(dropout_p);
-  auto [out, lse] = dense_forward(q, k, v, is_causal, scale_or_default(q, scale), /*allow_gqa=*/true);
+  auto r = dense_forward_with_dropout(q, k, v, dropout_p, is_causal, return_debug_mask, scale_or_default(q, scale),
+                                      /*allow_gqa=*/true);
   Tensor none = at::empty({0}, q.options().dtype(at::kInt));
-  return {out, lse, none, none, c10::SymInt(q.size(2)), c10::SymInt(k.size(2)), empty_i64(q), empty_i64(q),
-          at::empty({0}, q.options())};
+  // the installed torch names the two slots rng_state and unused; its autograd hands both back to the backward
+  return {r.out, r.lse, none, none, c10::SymInt(q.size(2)), c10::SymInt(k.size(2)), r.seed, r.offset, r.debug};
 }
 
 std::tuple<Tensor, Tensor, Tensor> aten_sdpa_flash_backward(const Tensor& grad_out, const Tensor& q, const Tensor& k,
@@ -306,9 +402,9 @@ std::tuple<Tensor, Tensor, Tensor> aten_sdpa_flash_backward(const Tensor& grad_o
                                                             c10::SymInt max_k, double dropout_p, bool is_causal,
                                                             const Tensor& philox_seed, const Tensor& philox_offset,
                                                             c10::optional<double> scale) {
-  (void)cum_q; (void)cum_k; (void)max_q; (void)max_k; (void)philox_seed; (void)philox_offset;
-  check_no_dropout(dropout_p);
-  return dense_backward(grad_out, q, k, v, out, lse, is_causal, scale_or_default(q, scale));
+  (void)cum_q; (void)cum_k; (void)max_q; (void)max_k;
+  return dense_backward_with_dropout(grad_out, q, k, v, out, lse, dropout_p, is_causal, philox_seed, philox_offset,
+                                     scale_or_default(q, scale));
 }
 
 void check_unsupported_kwargs(const c10::optional<c10::SymInt>& wl, const c10::optional<c10::SymInt>& wr, bool causal) {

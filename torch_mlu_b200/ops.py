@@ -269,12 +269,22 @@ def _scaled_dot_product_efficient_attention(query, key, value, attn_bias, comput
     instead of the flash operator's bottom-right alignment. With Lq == Lk the two coincide; otherwise
     the top-left mask is rebuilt from what the kernels offer: keys past Lq are invisible to every row
     (Lq < Lk), and rows past Lk see every key (Lq > Lk). An additive bias is not built: it is refused.
-    ``log_sumexp`` is [B,H,Lq] fp32, or empty when ``compute_log_sumexp`` is false.
+    ``log_sumexp`` is [B,H,Lq] fp32, or empty when ``compute_log_sumexp`` is false. Dropout (Philox pair
+    returned as two CPU int64 scalars) is taken where one kernel call does the work: no causal mask, or Lq == Lk.
     """
     _check(attn_bias is None, "attn_bias is not supported: the additive-bias kernels are not built in this library")
-    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
+    _check(0.0 <= dropout_p < 1.0, "dropout_p must be inside [0, 1)")
+    _check(query.dim() == 4 and key.dim() == 4, "query, key and value must be 4-dimensional [batch, heads, seq_len, head_dim]")
     sc = calculate_scale(query, scale)
     Lq, Lk = query.size(2), key.size(2)
+    if dropout_p > 0.0:
+        _check(not is_causal or Lq == Lk, "dropout with a top-left causal mask and Lq != Lk is not built in this library")
+        s, o = dropout.draw_seed_and_offset(query.device, query.size(0) * query.size(1) * Lq * Lk)
+        keep = dropout.KeepMasks(s, o, dropout_p, query.size(0), query.size(1), Lq, Lk, query.device)
+        out, lse = _dense_forward(query, key, value, is_causal, sc, allow_gqa=False, keep=keep)
+        if not compute_log_sumexp:
+            lse = lse.new_empty((query.size(0), query.size(1), 0))
+        return out, lse, torch.tensor(s, dtype=torch.int64), torch.tensor(o, dtype=torch.int64)
     if not is_causal or Lq == Lk:
         out, lse = _dense_forward(query, key, value, is_causal, sc, allow_gqa=False)
     elif Lq < Lk:
@@ -298,12 +308,20 @@ def _scaled_dot_product_efficient_attention_backward(grad_out, query, key, value
     is an empty tensor. Needs the log_sumexp of a forward call with ``compute_log_sumexp=True``."""
     _check(attn_bias is None or attn_bias.numel() == 0,
            "attn_bias is not supported: the additive-bias kernels are not built in this library")
-    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
+    _check(0.0 <= dropout_p < 1.0, "dropout_p must be inside [0, 1)")
     _check(logsumexp.size(-1) == query.size(2), "log_sumexp is empty: run the forward with compute_log_sumexp=True")
     sc = calculate_scale(query, scale)
     if grad_out.stride(-1) != 1:
         grad_out = grad_out.contiguous()
     Lq, Lk = query.size(2), key.size(2)
+    if dropout_p > 0.0:
+        _check(not is_causal or Lq == Lk, "dropout with a top-left causal mask and Lq != Lk is not built in this library")
+        _check(philox_seed.numel() == 1 and philox_offset.numel() == 1,
+               "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned")
+        keep = dropout.KeepMasks(int(philox_seed), int(philox_offset), dropout_p, query.size(0), query.size(1), Lq, Lk,
+                                 query.device)
+        dq, dk, dv = _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, sc, keep=keep)
+        return dq, dk, dv, query.new_empty((0,))
     if not is_causal or Lq == Lk:
         dq, dk, dv = _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, sc)
     elif Lq < Lk:

@@ -172,16 +172,14 @@ def _fused_sdp_choice(query, key, value, attn_mask=None, dropout_p: float = 0.0,
     if not (backends.math_sdp_enabled() or backends.flash_sdp_enabled() or backends.mem_efficient_sdp_enabled()):
         return int(SDPBackend.ERROR)
     # priority order of sdp_utils.cpp:28-31: flash, memory efficient, math
-    if dropout_p == 0.0 and use_flash_attention(query, key, value, attn_mask, False):
+    if use_flash_attention(query, key, value, attn_mask, False):
         return int(SDPBackend.FLASH_ATTENTION)
-    if dropout_p == 0.0 and use_mem_efficient_attention(query, key, value, attn_mask, False):
+    if use_mem_efficient_attention(query, key, value, attn_mask, False):
         return int(SDPBackend.EFFICIENT_ATTENTION)
     if backends.math_sdp_enabled():
         return int(SDPBackend.MATH)
     # nothing qualifies: say why, then fail (sdp_utils.cpp:134-146)
     warnings.warn("Memory efficient kernel not used because:", UserWarning, stacklevel=2)
-    if dropout_p != 0.0:
-        warnings.warn("The fused kernels of this build do not support dropout.", UserWarning, stacklevel=2)
     use_mem_efficient_attention(query, key, value, attn_mask, True)
     warnings.warn("Flash attention kernel not used because:", UserWarning, stacklevel=2)
     use_flash_attention(query, key, value, attn_mask, True)

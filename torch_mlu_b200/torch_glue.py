@@ -26,7 +26,10 @@ _loaded = False
 
 def build(verbose: bool = False) -> str:
     """g++ the glue against the installed torch and the C-ABI library (no GPU needed)."""
-    native_build.build_native()
+    # A process that already holds the C-ABI library must not re-link it underneath itself: the glue would
+    # then load the new file as a second copy with its own state (error text, launch counter).
+    if _cabi._lib is None:
+        native_build.build_native()
     newest = max(os.path.getmtime(SRC), os.path.getmtime(os.path.join(os.path.dirname(HERE), "include", "sdpa_b200.h")))
     if os.path.exists(LIB) and os.path.getmtime(LIB) >= newest:
         return LIB
