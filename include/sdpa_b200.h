@@ -51,7 +51,7 @@
 extern "C" {
 #endif
 
-#define SDPA_B200_VERSION 102
+#define SDPA_B200_VERSION 103
 
 #if defined(__GNUC__)
 #define SDPA_B200_API __attribute__((visibility("default")))
@@ -127,6 +127,17 @@ typedef struct sdpa_b200_params {
    * lengths; both NULL when dropout_p == 0. The forward reads keep_rows; the backward reads both. */
   const uint32_t* keep_rows;
   const uint32_t* keep_cols;
+  /* Additive attention bias of the memory-efficient operators (mem_eff_fwd / mem_eff_bwd,
+   * FlashAttention_internal.cpp:485-904): out = softmax(scale * q k^T + bias) v. NULL = none. Dense tensors
+   * only; same 16-bit type as q; element strides for (batch, head, query row), 0 for a broadcast dimension;
+   * the key stride is 1. Rows start 16-byte aligned (row stride a multiple of 8, or 0) and are readable up to
+   * the next multiple of 8 keys. */
+  const void* bias;
+  int64_t bias_batch_stride, bias_head_stride, bias_row_stride;
+  /* Backward: gradient of the bias, [batch, heads_q, seqlen_q, dbias_row_stride >= seqlen_k rounded up to 8],
+   * same type, or NULL. Elements the causal mask hides are not written: clear the buffer first. */
+  void* dbias;
+  int64_t dbias_batch_stride, dbias_head_stride, dbias_row_stride;
 } sdpa_b200_params;
 
 SDPA_B200_API int sdpa_b200_version(void);

@@ -1,4 +1,4 @@
-"""The bias-free subset of the memory-efficient operators (attention.cpp:350-391, 510-600): same kernels
+"""The memory-efficient operators (attention.cpp:350-391, 510-600): same kernels
 as the flash operators, but a causal mask aligned to the TOP-LEFT corner (sdp_utils.h:32-37). torch's CPU
 scaled_dot_product_attention uses the same convention, so it is the fp32 reference here (forward and, by
 autograd, backward). Tolerances as everywhere: out / grads max-abs 2e-2, mean-abs 2e-3; lse 1e-5."""
@@ -46,7 +46,7 @@ def test_efficient_without_log_sumexp_and_with_bias(cuda_device, native_lib):
     q = rand((1, 2, 128, 128), 1).to(cuda_device)
     out, lse, _, _ = ops._scaled_dot_product_efficient_attention(q, q, q, None, False)
     assert lse.numel() == 0 and out.shape == q.shape
-    with pytest.raises(RuntimeError, match="attn_bias is not supported"):
+    with pytest.raises(RuntimeError, match="dtype and device of query"):
         ops._scaled_dot_product_efficient_attention(q, q, q, torch.zeros(1, 2, 128, 128, device=cuda_device), True)
 
 
@@ -141,3 +141,95 @@ def test_efficient_attention_with_dropout(cuda_device, native_lib):
     orc.assert_close_grad_bf16(dv, vf.grad, "dv")
     with pytest.raises(RuntimeError, match="Lq != Lk is not built"):
         ops._scaled_dot_product_efficient_attention(qd, kd[:, :, :100], vd[:, :, :100], None, True, p, True)
+
+
+def _bias_reference(q, k, v, bias, do, causal_top_left, dtype=torch.float32):
+    qf, kf, vf, bf = (t.to(dtype).detach().requires_grad_(True) for t in (q, k, v, bias))
+    scores = torch.einsum("bhqd,bhkd->bhqk", qf, kf) * (q.shape[-1] ** -0.5) + bf
+    if causal_top_left:
+        scores = scores.masked_fill(torch.ones(q.shape[2], k.shape[2], dtype=torch.bool).triu(1), float("-inf"))
+    out = torch.einsum("bhqk,bhkd->bhqd", torch.softmax(scores, dim=-1), vf)
+    out.backward(do.to(dtype))
+    return out.detach(), torch.logsumexp(scores.detach().float(), dim=-1), qf.grad, kf.grad, vf.grad, bf.grad
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("Lq,Lk,D,causal,bias_shape", [
+    (256, 256, 128, False, (2, 3, 256, 256)),    # full bias, read in place
+    (200, 333, 128, False, (1, 3, 200, 333)),    # batch broadcast, ragged key length: padded copy
+    (300, 300, 64, True, (2, 1, 300, 300)),      # head broadcast with the causal mask
+    (130, 257, 128, True, (1, 1, 1, 257)),       # one bias row for every query; top-left causal with Lq < Lk
+    (257, 130, 96, True, (2, 3, 257, 130)),      # top-left causal with Lq > Lk: two kernel calls
+])
+def test_attn_bias_forward_and_backward(cuda_device, native_lib, dtype, Lq, Lk, D, causal, bias_shape):
+    """Additive bias through the memory-efficient operators, as the reference tests exercise it (a random
+    attn_mask in the low-precision dtype next to q, k, v; test_...py:1445-1511, 1800-1901): output, log_sumexp and
+    all four gradients against autograd through the fp32 math, held to that suite's own tolerance rule, and to
+    the fixed tolerances where values are of order one."""
+    dev = cuda_device
+    B, H = 2, 3
+    g = torch.Generator().manual_seed(7)
+    q, k, v = (torch.randn(s, generator=g).to(dtype) for s in ((B, H, Lq, D), (B, H, Lk, D), (B, H, Lk, D)))
+    bias = torch.rand(bias_shape, generator=g).to(dtype)
+    do = torch.rand((B, H, Lq, D), generator=g).to(dtype)
+    qd, kd, vd, bd = q.to(dev), k.to(dev), v.to(dev), bias.to(dev)
+    out, lse, seed, off = ops._scaled_dot_product_efficient_attention(qd, kd, vd, bd, True, 0.0, causal)
+    dq, dk, dv, db = ops._scaled_dot_product_efficient_attention_backward(do.to(dev), qd, kd, vd, bd, out, lse, seed, off, 0.0,
+                                                                         [True, True, True, True], causal)
+    assert ops.device_status() == 0 and tuple(db.shape) == tuple(bias_shape)
+    true = _bias_reference(q, k, v, bias, do, causal)
+    lowp = _bias_reference(q, k, v, bias, do, causal, dtype)
+    orc.assert_close_bf16(out, true[0], "out")
+    orc.assert_close_lse(lse, true[1])
+    for name, got, i, fudge in (("dq", dq, 2, 4), ("dk", dk, 3, 2), ("dv", dv, 4, 2), ("dbias", db, 5, 4)):
+        orc.assert_close_reference_rule(got, true[i], lowp[i], name, fudge=fudge)
+    for name, got, i in (("dq", dq, 2), ("dk", dk, 3), ("dv", dv, 4)):
+        orc.assert_close_grad_bf16(got, true[i], name)
+    # without asking for it there is no bias gradient
+    *_, none = ops._scaled_dot_product_efficient_attention_backward(do.to(dev), qd, kd, vd, bd, out, lse, seed, off, 0.0,
+                                                                    [True, True, True, False], causal)
+    assert none.numel() == 0
+
+
+def test_attn_bias_of_minus_infinity_masks_keys(cuda_device, native_lib):
+    """A bias of -inf hides a key (the boolean attn_mask of F.scaled_dot_product_attention arrives that way)."""
+    dev = cuda_device
+    B, H, L, D = 1, 2, 256, 128
+    q, k, v = (rand((B, H, L, D), s) for s in (1, 2, 3))
+    bias = torch.zeros(1, 1, L, L)
+    bias[..., 100:180] = float("-inf")
+    out, lse, _, _ = ops._scaled_dot_product_efficient_attention(q.to(dev), k.to(dev), v.to(dev), bias.bfloat16().to(dev), True)
+    ref = F.scaled_dot_product_attention(q.float(), k.float(), v.float(), attn_mask=bias)
+    orc.assert_close_bf16(out, ref, "out")
+
+
+def test_efficient_attention_pair_with_bias_and_dropout_with_bias(cuda_device, native_lib):
+    dev = cuda_device
+    B, H, L, D = 1, 2, 256, 128
+    q, k, v, do = (rand((B, L, H, D), s) for s in (1, 2, 3, 4))
+    bias = torch.rand((B, H, L, L), generator=torch.Generator().manual_seed(5)).bfloat16()
+    qd, kd, vd, bd = q.to(dev), k.to(dev), v.to(dev), bias.to(dev)
+    out, lse, seed, off = ops._efficient_attention_forward(qd, kd, vd, bd, None, None, None, 0.0, 2, True)
+    dq, dk, dv, db = ops._efficient_attention_backward(do.to(dev), qd, kd, vd, bd, out.transpose(1, 2), None, None, L, L, lse, 0.0,
+                                                      seed, off, 2, True)
+    t = lambda x: x.transpose(1, 2)
+    true = _bias_reference(t(q), t(k), t(v), bias, t(do), True)
+    orc.assert_close_bf16(out, true[0], "out")
+    orc.assert_close_grad_bf16(t(dq), true[2], "dq")
+    orc.assert_close_grad_bf16(t(dk), true[3], "dk")
+    orc.assert_close_grad_bf16(t(dv), true[4], "dv")
+    orc.assert_close_grad_bf16(db, true[5], "dbias")
+    # bias together with dropout: the pattern is rebuilt from the returned Philox pair
+    p = 0.22
+    q4, k4, v4, do4 = t(q), t(k), t(v), t(do)
+    out, lse, seed, off = ops._scaled_dot_product_efficient_attention(q4.to(dev), k4.to(dev), v4.to(dev), bd, True, p, False)
+    dq, dk, dv, db = ops._scaled_dot_product_efficient_attention_backward(do4.to(dev), q4.to(dev), k4.to(dev), v4.to(dev), bd, out,
+                                                                         lse, seed, off, p, [True, True, True, True], False)
+    keep = orc.dropout_keep_mask(int(seed), int(off), p, B, H, L, L)
+    qf, kf, vf, bf = (x.float().detach().requires_grad_(True) for x in (q4, k4, v4, bias))
+    attn = torch.softmax(torch.einsum("bhqd,bhkd->bhqk", qf, kf) * D ** -0.5 + bf, dim=-1).masked_fill(~keep, 0.0) / (1 - p)
+    ref = torch.einsum("bhqk,bhkd->bhqd", attn, vf)
+    ref.backward(do4.float())
+    orc.assert_close_bf16(out, ref.detach(), "out")
+    for name, got, want in (("dq", dq, qf.grad), ("dk", dk, kf.grad), ("dv", dv, vf.grad), ("dbias", db, bf.grad)):
+        orc.assert_close_grad_bf16(got, want, name)

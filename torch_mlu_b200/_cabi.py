@@ -54,6 +54,8 @@ class SdpaParams(ctypes.Structure):
         ("softmax_scale", c_float), ("dropout_p", c_float),
         ("is_causal", c_int32), ("dtype", c_int32), ("kernel", c_int32), ("num_splits", c_int32),
         ("keep_rows", c_void_p), ("keep_cols", c_void_p),
+        ("bias", c_void_p), ("bias_batch_stride", c_int64), ("bias_head_stride", c_int64), ("bias_row_stride", c_int64),
+        ("dbias", c_void_p), ("dbias_batch_stride", c_int64), ("dbias_head_stride", c_int64), ("dbias_row_stride", c_int64),
     ]
 
 

@@ -96,6 +96,13 @@ struct BwdKernelParams {
   const uint32_t* keep_cols;  // [batch*heads_q][keep_lk_pad][keep_lq_pad / 32]: dK/dV kernel
   int keep_lq_pad, keep_lk_pad;
   float keep_scale;  // 1 / (1 - dropout_p)
+  // additive bias (kernels built with kBias): the scores are scale * Q K^T + bias; the gradient of the bias is
+  // dS itself, written by the dQ kernel (whose thread owns a query row and 64 consecutive keys of it)
+  const uint16_t* bias;
+  int64_t bias_batch_stride, bias_head_stride, bias_row_stride;
+  uint16_t* dbias;  // or null
+  int64_t dbias_batch_stride, dbias_head_stride, dbias_row_stride;
+  float inv_scale;  // 1 / softmax_scale
 #ifdef SDPA_BWD_STAMPS
   float* stamps;  // [mode 2][role 4][item 24][event 8] SM cycles since CTA start, one CTA per mode
 #endif
@@ -154,7 +161,7 @@ __device__ __forceinline__ uint32_t keep_pair_mask(uint32_t two_bits) {
   return ((two_bits & 1u) ? 0x0000ffffu : 0u) | ((two_bits & 2u) ? 0xffff0000u : 0u);
 }
 
-template <int kMode, int kD, bool kF16, bool kDrop>
+template <int kMode, int kD, bool kF16, bool kDrop, bool kBias>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -583,6 +590,43 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_ld_x32_at<32>(sbuf + 32, a);
         tmem_wait_ld();
         BWD_STAMP(half, i, 2);
+        if constexpr (kBias) {
+          // S <- S + bias / scale (then x = S c - lse2 as without bias). dQ: this thread's query row, 64
+          // consecutive keys = eight 16-byte loads; dK/dV: this thread's key in 64 consecutive query rows =
+          // 64 two-byte loads, consecutive lanes on consecutive keys.
+          const int col0 = y0 + half * 64;
+          if (kMode == kModeDQ) {
+            if (xr < len_x) {
+              const uint16_t* brow = p.bias + b * p.bias_batch_stride + hx * p.bias_head_stride +
+                                     static_cast<int64_t>(xr) * p.bias_row_stride + col0;
+#pragma unroll
+              for (int ch = 0; ch < 8; ++ch) {
+                if (col0 + ch * 8 < len_k) {
+                  const uint4 w = *reinterpret_cast<const uint4*>(brow + ch * 8);
+                  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 b2 = unpack_16x2<kF16>(ww[e]);
+                    a[ch * 8 + 2 * e] = __float_as_uint(fmaf(b2.x, p.inv_scale, __uint_as_float(a[ch * 8 + 2 * e])));
+                    a[ch * 8 + 2 * e + 1] = __float_as_uint(fmaf(b2.y, p.inv_scale, __uint_as_float(a[ch * 8 + 2 * e + 1])));
+                  }
+                }
+              }
+            }
+          } else {
+            if (xr < len_x) {
+              const uint16_t* bcol = p.bias + b * p.bias_batch_stride + (hx * p.kv_group + hi) * p.bias_head_stride + xr;
+#pragma unroll
+              for (int j = 0; j < 64; ++j) {
+                if (col0 + j < len_q) {
+                  const uint32_t raw = bcol[static_cast<int64_t>(col0 + j) * p.bias_row_stride];
+                  const float bv = unpack_16x2<kF16>(raw).x;
+                  a[j] = __float_as_uint(fmaf(bv, p.inv_scale, __uint_as_float(a[j])));
+                }
+              }
+            }
+          }
+        }
         // x = S c - lse2. In the dK/dV kernel this pass sits on the critical chain (score GEMM ->
         // exponentials -> dP read -> next score GEMM) and the exponential unit alone would bound it, so
         // kPolyOf4 of every four column pairs take their 2^x from the FMA pipe (exp2_poly3_x2). The dQ
@@ -654,6 +698,18 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         tmem_st_x16(sbuf + 32, dw);
         tmem_st_x16(sbuf + 48, dw + 16);
+        if constexpr (kBias && kMode == kModeDQ) {
+          // dbias = dS: this thread's 64 keys of its query row, already packed for the dQ GEMM
+          const int col0 = y0 + half * 64;
+          if (p.dbias != nullptr && xr < len_x) {
+            uint16_t* drow = p.dbias + b * p.dbias_batch_stride + hx * p.dbias_head_stride +
+                             static_cast<int64_t>(xr) * p.dbias_row_stride + col0;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+              if (col0 + ch * 8 < len_k)
+                *reinterpret_cast<uint4*>(drow + ch * 8) = make_uint4(dw[4 * ch], dw[4 * ch + 1], dw[4 * ch + 2], dw[4 * ch + 3]);
+          }
+        }
       }
       BWD_STAMP(half, i, 6);
       tmem_wait_st();
@@ -853,20 +909,26 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const PreParams p) 
 using TileKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
                             const CUtensorMap, const CUtensorMap, const BwdKernelParams);
 
-template <int kMode, bool kDrop>
+template <int kMode, bool kDrop, bool kBias>
 TileKernel pick_tile_kernel(int head_dim, bool f16) {
-  if (head_dim <= 64) return f16 ? bwd_tile_kernel<kMode, 64, true, kDrop> : bwd_tile_kernel<kMode, 64, false, kDrop>;
-  return f16 ? bwd_tile_kernel<kMode, 128, true, kDrop> : bwd_tile_kernel<kMode, 128, false, kDrop>;
+  if (head_dim <= 64)
+    return f16 ? bwd_tile_kernel<kMode, 64, true, kDrop, kBias> : bwd_tile_kernel<kMode, 64, false, kDrop, kBias>;
+  return f16 ? bwd_tile_kernel<kMode, 128, true, kDrop, kBias> : bwd_tile_kernel<kMode, 128, false, kDrop, kBias>;
+}
+
+template <int kMode>
+TileKernel pick_tile_kernel(bool drop, bool bias, int head_dim, bool f16) {
+  if (drop) return bias ? pick_tile_kernel<kMode, true, true>(head_dim, f16) : pick_tile_kernel<kMode, true, false>(head_dim, f16);
+  return bias ? pick_tile_kernel<kMode, false, true>(head_dim, f16) : pick_tile_kernel<kMode, false, false>(head_dim, f16);
 }
 
 int launch_tile_kernel(int mode, int head_dim, bool f16, int grid, cudaStream_t stream, const CUtensorMap& tm_q,
                        const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_do,
                        const CUtensorMap& tm_o1, const CUtensorMap& tm_o2, const BwdKernelParams& kp) {
   const bool drop = kp.keep_rows != nullptr;
-  TileKernel kernel = mode == kModeDKDV ? (drop ? pick_tile_kernel<kModeDKDV, true>(head_dim, f16)
-                                                : pick_tile_kernel<kModeDKDV, false>(head_dim, f16))
-                                        : (drop ? pick_tile_kernel<kModeDQ, true>(head_dim, f16)
-                                                : pick_tile_kernel<kModeDQ, false>(head_dim, f16));
+  const bool bias = kp.bias != nullptr;
+  TileKernel kernel = mode == kModeDKDV ? pick_tile_kernel<kModeDKDV>(drop, bias, head_dim, f16)
+                                        : pick_tile_kernel<kModeDQ>(drop, bias, head_dim, f16);
   const uint32_t smem = smem_bytes_for(mode);
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (err != cudaSuccess) {
@@ -989,6 +1051,15 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   kp.keep_lq_pad = (p.max_seqlen_q + 127) / 128 * 128;
   kp.keep_lk_pad = (p.max_seqlen_k + 127) / 128 * 128;
   kp.keep_scale = drop ? 1.f / (1.f - p.dropout_p) : 1.f;
+  kp.bias = static_cast<const uint16_t*>(p.bias);
+  kp.bias_batch_stride = p.bias_batch_stride;
+  kp.bias_head_stride = p.bias_head_stride;
+  kp.bias_row_stride = p.bias_row_stride;
+  kp.dbias = static_cast<uint16_t*>(p.dbias);
+  kp.dbias_batch_stride = p.dbias_batch_stride;
+  kp.dbias_head_stride = p.dbias_head_stride;
+  kp.dbias_row_stride = p.dbias_row_stride;
+  kp.inv_scale = 1.f / p.softmax_scale;
   kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   kp.is_causal = p.is_causal;
 #ifdef SDPA_BWD_STAMPS

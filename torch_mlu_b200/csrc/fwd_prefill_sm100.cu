@@ -92,6 +92,11 @@ struct FwdKernelParams {
   const uint32_t* keep_rows;  // [batch*heads_q][lq_pad][lk_words]
   int lq_pad, lk_words;
   float keep_scale;  // 1 / (1 - dropout_p), applied with the final 1 / l
+  // additive bias (kernels built with kBias): softmax(scale * Q K^T + bias), bias in the tensors' 16-bit type,
+  // element strides for (batch, head, query row), 0 for a broadcast dimension; the key stride is 1
+  const uint16_t* bias;
+  int64_t bias_batch_stride, bias_head_stride, bias_row_stride;
+  float inv_scale;  // 1 / softmax_scale: the bias joins the raw scores as bias / scale
   int num_m_blocks, num_bh, heads_per_wave, num_slots;  // work-unit order, see decode_unit()
   float scale_log2;
   int is_causal;
@@ -267,7 +272,7 @@ __device__ __forceinline__ uint32_t keep_pair_mask(uint32_t two_bits) {
   return ((two_bits & 1u) ? 0x0000ffffu : 0u) | ((two_bits & 2u) ? 0xffff0000u : 0u);
 }
 
-template <int kD, bool kF16, bool kDrop>
+template <int kD, bool kF16, bool kDrop, bool kBias>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
                    const __grid_constant__ CUtensorMap tm_k,
@@ -552,6 +557,11 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       float m_run = neg_inf;
       float l_run = 0.f;
       if (row_in_tile == 0) FWD_STAMP(t, ucnt, 0);
+      const uint16_t* bias_row = nullptr;  // this row's bias values, or null for a row past the sequence
+      if constexpr (kBias) {
+        if (row < u.len_q)
+          bias_row = p.bias + u.b * p.bias_batch_stride + u.h * p.bias_head_stride + static_cast<int64_t>(row) * p.bias_row_stride;
+      }
       const uint32_t* keep_row = nullptr;  // this row's keep bits, 4 words per key block
       if constexpr (kDrop)
         keep_row = p.keep_rows + (static_cast<size_t>(u.b * p.heads_q + u.h) * p.lq_pad + row) * p.lk_words;
@@ -577,6 +587,27 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
           tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < kBlockN; ++i) s[i] = __uint_as_float(r[i]);
+        }
+        if constexpr (kBias) {
+          // s <- s + bias / scale, so that everything below (maximum, s * c - m) stays as it is. Sixteen
+          // 16-byte loads per row and block, straight from global memory: shared memory has no room for a
+          // 32 KB bias tile. A chunk that starts past the last key is skipped; one that straddles it reads
+          // up to 7 elements of row padding, which the caller guarantees.
+          if (bias_row != nullptr) {
+#pragma unroll
+            for (int ch = 0; ch < kBlockN / 8; ++ch) {
+              if (n0 + ch * 8 < len_k) {
+                const uint4 w = *reinterpret_cast<const uint4*>(bias_row + n0 + ch * 8);
+                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float2 b2 = unpack_16x2<kF16>(ww[i]);
+                  s[ch * 8 + 2 * i] = fmaf(b2.x, p.inv_scale, s[ch * 8 + 2 * i]);
+                  s[ch * 8 + 2 * i + 1] = fmaf(b2.y, p.inv_scale, s[ch * 8 + 2 * i + 1]);
+                }
+              }
+            }
+          }
         }
         const bool need_mask = n0 + kBlockN > mask_from;
         if (need_mask) {
@@ -806,6 +837,11 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
   kp.lq_pad = (p.max_seqlen_q + 127) / 128 * 128;
   kp.lk_words = (p.max_seqlen_k + 127) / 128 * 4;
   kp.keep_scale = drop ? 1.f / (1.f - p.dropout_p) : 1.f;
+  kp.bias = static_cast<const uint16_t*>(p.bias);
+  kp.bias_batch_stride = p.bias_batch_stride;
+  kp.bias_head_stride = p.bias_head_stride;
+  kp.bias_row_stride = p.bias_row_stride;
+  kp.inv_scale = 1.f / p.softmax_scale;
   kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   kp.is_causal = p.is_causal;
 #ifdef SDPA_FWD_STAMPS
@@ -815,12 +851,15 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
   }
 #endif
 
-  auto pick = [&](auto drop_tag) {
+  auto pick = [&](auto drop_tag, auto bias_tag) {
     constexpr bool kDrop = decltype(drop_tag)::value;
-    return p.head_dim <= 64 ? (f16 ? fwd_prefill_kernel<64, true, kDrop> : fwd_prefill_kernel<64, false, kDrop>)
-                            : (f16 ? fwd_prefill_kernel<128, true, kDrop> : fwd_prefill_kernel<128, false, kDrop>);
+    constexpr bool kBias = decltype(bias_tag)::value;
+    return p.head_dim <= 64 ? (f16 ? fwd_prefill_kernel<64, true, kDrop, kBias> : fwd_prefill_kernel<64, false, kDrop, kBias>)
+                            : (f16 ? fwd_prefill_kernel<128, true, kDrop, kBias> : fwd_prefill_kernel<128, false, kDrop, kBias>);
   };
-  auto kernel = drop ? pick(std::true_type{}) : pick(std::false_type{});
+  const bool with_bias = p.bias != nullptr;
+  auto kernel = drop ? (with_bias ? pick(std::true_type{}, std::true_type{}) : pick(std::true_type{}, std::false_type{}))
+                     : (with_bias ? pick(std::false_type{}, std::true_type{}) : pick(std::false_type{}, std::false_type{}));
   cudaError_t err =
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (err != cudaSuccess) {

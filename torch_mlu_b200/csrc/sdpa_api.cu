@@ -169,6 +169,19 @@ int validate_common(const sdpa_b200_params* p) {
     set_error("varlen needs total_q and total_k > 0 (got %d, %d)", p->total_q, p->total_k);
     return SDPA_B200_INVALID_ARG;
   }
+  if (p->bias != nullptr) {
+    if (p->cu_seqlens_q != nullptr || p->cu_seqlens_k != nullptr || p->kernel == SDPA_B200_KERNEL_DECODE) {
+      set_error("an additive bias is built for dense tensors and the tile kernels only");
+      return SDPA_B200_UNSUPPORTED;
+    }
+    auto bad = [](int64_t s) { return s < 0 || (s % 8) != 0; };
+    if (!aligned16(p->bias) || bad(p->bias_batch_stride) || bad(p->bias_head_stride) || bad(p->bias_row_stride)) {
+      set_error("bias must be 16-byte aligned with batch / head / row strides that are 0 or multiples of 8 elements "
+                "(got %lld, %lld, %lld)",
+                (long long)p->bias_batch_stride, (long long)p->bias_head_stride, (long long)p->bias_row_stride);
+      return SDPA_B200_INVALID_ARG;
+    }
+  }
   if (p->dropout_p == 0.f && (p->keep_rows != nullptr || p->keep_cols != nullptr)) {
     set_error("keep_rows / keep_cols must be NULL when dropout_p is 0");
     return SDPA_B200_INVALID_ARG;
@@ -226,7 +239,7 @@ int check_device() {
 // Decode is chosen when there are too few query rows to fill a 128-row MMA tile.
 bool use_decode(const sdpa_b200_params* p) {
   if (p->kernel == SDPA_B200_KERNEL_DECODE) return true;
-  if (p->kernel == SDPA_B200_KERNEL_PREFILL || p->dropout_p != 0.f) return false;
+  if (p->kernel == SDPA_B200_KERNEL_PREFILL || p->dropout_p != 0.f || p->bias != nullptr) return false;
   // the streaming kernel reads whole 64- or 128-element rows; other head dims take the tile kernel,
   // whose TMA loads pad the head dim with zeros
   return p->cu_seqlens_q == nullptr && p->max_seqlen_q == 1 && (p->head_dim == 64 || p->head_dim == 128);
@@ -334,6 +347,16 @@ int sdpa_b200_fwd(const sdpa_b200_params* p, void* workspace, size_t workspace_b
 int sdpa_b200_bwd(const sdpa_b200_params* p, void* workspace, size_t workspace_bytes, void* stream) {
   int st = validate_common(p);
   if (st != SDPA_B200_OK) return st;
+  if (p->dbias != nullptr) {
+    const int64_t need = (static_cast<int64_t>(p->max_seqlen_k) + 7) / 8 * 8;
+    if (p->bias == nullptr || !aligned16(p->dbias) || p->dbias_row_stride < need || (p->dbias_row_stride % 8) != 0 ||
+        (p->dbias_head_stride % 8) != 0 || (p->dbias_batch_stride % 8) != 0 || p->dbias_head_stride <= 0 ||
+        (p->batch > 1 && p->dbias_batch_stride <= 0)) {
+      set_error("dbias needs a bias, 16-byte alignment, strides that are multiples of 8 and a row stride of at least "
+                "seqlen_k rounded up to 8");
+      return SDPA_B200_INVALID_ARG;
+    }
+  }
   if (p->dropout_p != 0.f && (p->keep_cols == nullptr || (reinterpret_cast<uintptr_t>(p->keep_cols) & 15u) != 0)) {
     set_error("dropout_p > 0 needs keep_cols from sdpa_b200_dropout_keep_mask (16-byte aligned) in the backward");
     return SDPA_B200_INVALID_ARG;

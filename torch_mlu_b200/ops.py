@@ -161,8 +161,48 @@ def _dense_params(query, key, value, out, lse, is_causal, scale, kernel=_cabi.KE
     return p
 
 
-def _dense_forward(query, key, value, is_causal, scale, allow_gqa, kernel=_cabi.KERNEL_AUTO, num_splits=0, keep=None):
-    # attention.cpp:70-100; `keep`: dropout.KeepMasks of this call, or None
+def _set_bias(p: _cabi.SdpaParams, bias, dbias=None) -> None:
+    """bias / dbias: [B, H, Lq, Lk] views prepared by _prepare_bias / _new_bias_grad (unit key stride)."""
+    if bias is None:
+        return
+    p.bias = bias.data_ptr()
+    p.bias_batch_stride, p.bias_head_stride, p.bias_row_stride = bias.stride(0), bias.stride(1), bias.stride(2)
+    if dbias is not None:
+        p.dbias = dbias.data_ptr()
+        p.dbias_batch_stride, p.dbias_head_stride, p.dbias_row_stride = dbias.stride(0), dbias.stride(1), dbias.stride(2)
+
+
+def _prepare_bias(attn_bias, query, key):
+    """The additive bias as a [B, H, Lq, Lk] view the kernels can read: broadcast dimensions keep stride 0,
+    rows start 16-byte aligned and are readable up to the next multiple of 8 keys. A bias that already has
+    that layout is used in place; any other is copied once into rows padded to a multiple of 8."""
+    B, H, Lq, _ = query.shape
+    Lk = key.size(2)
+    _check(attn_bias.dtype == query.dtype and attn_bias.device == query.device,
+           "attn_bias must have the dtype and device of query")
+    view = attn_bias.expand(B, H, Lq, Lk)
+    ok = (view.stride(3) == 1 and Lk % 8 == 0 and view.data_ptr() % 16 == 0 and
+          all(s % 8 == 0 for s in view.stride()[:3]))
+    if ok:
+        return view
+    lk8 = (Lk + 7) // 8 * 8
+    src = attn_bias.expand(*attn_bias.shape[:-1], Lk)
+    buf = torch.zeros(*src.shape[:-1], lk8, dtype=query.dtype, device=query.device)
+    buf[..., :Lk] = src
+    return buf[..., :Lk].expand(B, H, Lq, Lk)
+
+
+def _new_bias_grad(query, key):
+    """Zero-filled [B, H, Lq, Lk] gradient buffer with rows padded to a multiple of 8 (the kernels skip what the
+    causal mask hides)."""
+    B, H, Lq, _ = query.shape
+    Lk = key.size(2)
+    return torch.zeros((B, H, Lq, (Lk + 7) // 8 * 8), dtype=query.dtype, device=query.device)[..., :Lk]
+
+
+def _dense_forward(query, key, value, is_causal, scale, allow_gqa, kernel=_cabi.KERNEL_AUTO, num_splits=0, keep=None,
+                   bias=None):
+    # attention.cpp:70-100; `keep`: dropout.KeepMasks of this call, or None; `bias`: from _prepare_bias, or None
     _check(query.dim() == 4 and key.dim() == 4 and value.dim() == 4,
            "query, key and value must be 4-dimensional [batch, heads, seq_len, head_dim]")
     _check(query.size(0) == key.size(0) == value.size(0), "query, key and value must have the same batch size")
@@ -183,6 +223,7 @@ def _dense_forward(query, key, value, is_causal, scale, allow_gqa, kernel=_cabi.
     if keep is not None:
         p.dropout_p = keep.dropout_p
         p.keep_rows, p.keep_cols = keep.rows.data_ptr(), keep.cols.data_ptr()
+    _set_bias(p, bias)
     _run_fwd(p, query.device)
     return out, lse
 
@@ -216,7 +257,7 @@ def _scaled_dot_product_flash_attention(query, key, value, dropout_p: float = 0.
     return out, lse, cum_q, cum_k, Lq, Lk, seed, offset, debug
 
 
-def _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, scale, keep=None):
+def _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, scale, keep=None, bias=None, dbias=None):
     _check_inputs(grad_out, query, key, value, out)
     _check(logsumexp.dtype == torch.float32 and logsumexp.is_contiguous(), "logsumexp must be contiguous fp32")
     B, H, Lq, D = query.shape
@@ -233,6 +274,7 @@ def _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, scal
     if keep is not None:
         p.dropout_p = keep.dropout_p
         p.keep_rows, p.keep_cols = keep.rows.data_ptr(), keep.cols.data_ptr()
+    _set_bias(p, bias, dbias)
     _run_bwd(p, query.device)
     return dq, dk, dv
 
@@ -257,41 +299,44 @@ def _scaled_dot_product_flash_attention_backward(grad_out, query, key, value, ou
 
 
 # --------------------------------------------------------------------------------------
-# memory-efficient operator surface (bias-free subset)
+# memory-efficient operator surface
 # --------------------------------------------------------------------------------------
 def _scaled_dot_product_efficient_attention(query, key, value, attn_bias, compute_log_sumexp: bool,
                                             dropout_p: float = 0.0, is_causal: bool = False, *,
                                             scale: Optional[float] = None):
-    """(output, log_sumexp, philox_seed, philox_offset), attention.cpp:350-391, for ``attn_bias=None``.
+    """(output, log_sumexp, philox_seed, philox_offset), attention.cpp:350-391.
 
     The reference runs this operator on the same device kernel as the flash operator; what differs at
-    this level is the causal convention: ``CausalFromTopLeft`` (sdp_utils.h:32-37, attention.cpp:369-371)
+    this level is the additive ``attn_bias`` (anything that broadcasts to [B, H, Lq, Lk], in the dtype of
+    query) and the causal convention: ``CausalFromTopLeft`` (sdp_utils.h:32-37, attention.cpp:369-371)
     instead of the flash operator's bottom-right alignment. With Lq == Lk the two coincide; otherwise
     the top-left mask is rebuilt from what the kernels offer: keys past Lq are invisible to every row
-    (Lq < Lk), and rows past Lk see every key (Lq > Lk). An additive bias is not built: it is refused.
+    (Lq < Lk), and rows past Lk see every key (Lq > Lk).
     ``log_sumexp`` is [B,H,Lq] fp32, or empty when ``compute_log_sumexp`` is false. Dropout (Philox pair
     returned as two CPU int64 scalars) is taken where one kernel call does the work: no causal mask, or Lq == Lk.
     """
-    _check(attn_bias is None, "attn_bias is not supported: the additive-bias kernels are not built in this library")
     _check(0.0 <= dropout_p < 1.0, "dropout_p must be inside [0, 1)")
     _check(query.dim() == 4 and key.dim() == 4, "query, key and value must be 4-dimensional [batch, heads, seq_len, head_dim]")
     sc = calculate_scale(query, scale)
     Lq, Lk = query.size(2), key.size(2)
+    bias = None if attn_bias is None else _prepare_bias(attn_bias, query, key)
+    sl = (lambda t, *idx: None if t is None else t[idx])  # slices of an optional tensor
     if dropout_p > 0.0:
         _check(not is_causal or Lq == Lk, "dropout with a top-left causal mask and Lq != Lk is not built in this library")
         s, o = dropout.draw_seed_and_offset(query.device, query.size(0) * query.size(1) * Lq * Lk)
         keep = dropout.KeepMasks(s, o, dropout_p, query.size(0), query.size(1), Lq, Lk, query.device)
-        out, lse = _dense_forward(query, key, value, is_causal, sc, allow_gqa=False, keep=keep)
+        out, lse = _dense_forward(query, key, value, is_causal, sc, allow_gqa=False, keep=keep, bias=bias)
         if not compute_log_sumexp:
             lse = lse.new_empty((query.size(0), query.size(1), 0))
         return out, lse, torch.tensor(s, dtype=torch.int64), torch.tensor(o, dtype=torch.int64)
     if not is_causal or Lq == Lk:
-        out, lse = _dense_forward(query, key, value, is_causal, sc, allow_gqa=False)
+        out, lse = _dense_forward(query, key, value, is_causal, sc, allow_gqa=False, bias=bias)
     elif Lq < Lk:
-        out, lse = _dense_forward(query, key[:, :, :Lq], value[:, :, :Lq], True, sc, allow_gqa=False)
+        out, lse = _dense_forward(query, key[:, :, :Lq], value[:, :, :Lq], True, sc, allow_gqa=False,
+                                  bias=sl(bias, Ellipsis, slice(0, Lq)))
     else:
-        o1, l1 = _dense_forward(query[:, :, :Lk], key, value, True, sc, allow_gqa=False)
-        o2, l2 = _dense_forward(query[:, :, Lk:], key, value, False, sc, allow_gqa=False)
+        o1, l1 = _dense_forward(query[:, :, :Lk], key, value, True, sc, allow_gqa=False, bias=sl(bias, slice(None), slice(None), slice(0, Lk)))
+        o2, l2 = _dense_forward(query[:, :, Lk:], key, value, False, sc, allow_gqa=False, bias=sl(bias, slice(None), slice(None), slice(Lk, None)))
         out = torch.cat([o1.transpose(1, 2), o2.transpose(1, 2)], dim=1).transpose(1, 2)
         lse = torch.cat([l1, l2], dim=2)
     if not compute_log_sumexp:
@@ -304,39 +349,55 @@ def _scaled_dot_product_efficient_attention_backward(grad_out, query, key, value
                                                      philox_seed, philox_offset, dropout_p: float,
                                                      grad_input_mask, is_causal: bool = False, *,
                                                      scale: Optional[float] = None):
-    """(grad_q, grad_k, grad_v, grad_bias), attention.cpp:510-600, for a call made without bias; grad_bias
-    is an empty tensor. Needs the log_sumexp of a forward call with ``compute_log_sumexp=True``."""
-    _check(attn_bias is None or attn_bias.numel() == 0,
-           "attn_bias is not supported: the additive-bias kernels are not built in this library")
+    """(grad_q, grad_k, grad_v, grad_bias), attention.cpp:510-600. Needs the log_sumexp of a forward call with
+    ``compute_log_sumexp=True``. grad_bias has the shape of ``attn_bias`` (the [B, H, Lq, Lk] gradient the kernel
+    writes, summed over the dimensions the bias broadcasts along) when ``grad_input_mask[3]`` asks for it, else it
+    is an empty tensor."""
+    has_bias = attn_bias is not None and attn_bias.numel() > 0
     _check(0.0 <= dropout_p < 1.0, "dropout_p must be inside [0, 1)")
     _check(logsumexp.size(-1) == query.size(2), "log_sumexp is empty: run the forward with compute_log_sumexp=True")
     sc = calculate_scale(query, scale)
     if grad_out.stride(-1) != 1:
         grad_out = grad_out.contiguous()
     Lq, Lk = query.size(2), key.size(2)
+    bias = _prepare_bias(attn_bias, query, key) if has_bias else None
+    want_dbias = has_bias and len(grad_input_mask) > 3 and bool(grad_input_mask[3])
+    dbias = _new_bias_grad(query, key) if want_dbias else None
+    sl = (lambda t, *idx: None if t is None else t[idx])
+
+    def finish(dq, dk, dv):
+        if dbias is None:
+            return dq, dk, dv, query.new_empty((0,))
+        return dq, dk, dv, dbias.sum_to_size(attn_bias.shape)
+
     if dropout_p > 0.0:
         _check(not is_causal or Lq == Lk, "dropout with a top-left causal mask and Lq != Lk is not built in this library")
         _check(philox_seed.numel() == 1 and philox_offset.numel() == 1,
                "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned")
         keep = dropout.KeepMasks(int(philox_seed), int(philox_offset), dropout_p, query.size(0), query.size(1), Lq, Lk,
                                  query.device)
-        dq, dk, dv = _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, sc, keep=keep)
-        return dq, dk, dv, query.new_empty((0,))
+        return finish(*_dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, sc, keep=keep, bias=bias,
+                                       dbias=dbias))
     if not is_causal or Lq == Lk:
-        dq, dk, dv = _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, sc)
+        dq, dk, dv = _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, sc, bias=bias, dbias=dbias)
     elif Lq < Lk:
-        dq, dk_a, dv_a = _dense_backward(grad_out, query, key[:, :, :Lq], value[:, :, :Lq], out, logsumexp, True, sc)
+        cut = (Ellipsis, slice(0, Lq))
+        dq, dk_a, dv_a = _dense_backward(grad_out, query, key[:, :, :Lq], value[:, :, :Lq], out, logsumexp, True, sc,
+                                         bias=sl(bias, *cut), dbias=sl(dbias, *cut))
         dk, dv = torch.zeros_like(key), torch.zeros_like(value)
         dk[:, :, :Lq] = dk_a
         dv[:, :, :Lq] = dv_a
     else:
+        top, rest = (slice(None), slice(None), slice(0, Lk)), (slice(None), slice(None), slice(Lk, None))
         l1, l2 = logsumexp[:, :, :Lk].contiguous(), logsumexp[:, :, Lk:].contiguous()
-        dq1, dk1, dv1 = _dense_backward(grad_out[:, :, :Lk], query[:, :, :Lk], key, value, out[:, :, :Lk], l1, True, sc)
-        dq2, dk2, dv2 = _dense_backward(grad_out[:, :, Lk:], query[:, :, Lk:], key, value, out[:, :, Lk:], l2, False, sc)
+        dq1, dk1, dv1 = _dense_backward(grad_out[:, :, :Lk], query[:, :, :Lk], key, value, out[:, :, :Lk], l1, True, sc,
+                                        bias=sl(bias, *top), dbias=sl(dbias, *top))
+        dq2, dk2, dv2 = _dense_backward(grad_out[:, :, Lk:], query[:, :, Lk:], key, value, out[:, :, Lk:], l2, False, sc,
+                                        bias=sl(bias, *rest), dbias=sl(dbias, *rest))
         dq = torch.cat([dq1.transpose(1, 2), dq2.transpose(1, 2)], dim=1).transpose(1, 2)
         dk = (dk1.float() + dk2.float()).to(key.dtype)
         dv = (dv1.float() + dv2.float()).to(value.dtype)
-    return dq, dk, dv, query.new_empty((0,))
+    return finish(dq, dk, dv)
 
 
 # --------------------------------------------------------------------------------------
@@ -437,7 +498,8 @@ NO_CUSTOM_MASK, CAUSAL_FROM_TOP_LEFT, CAUSAL_FROM_BOTTOM_RIGHT = 0, 1, 2
 def _efficient_attention_forward(query, key, value, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: Optional[int],
                                  dropout_p: float, custom_mask_type: int, compute_log_sumexp: bool = False, *,
                                  scale: Optional[float] = None, causal_diagonal=None, seqlen_k=None):
-    """(output, logsumexp, philox_seed, philox_offset), attention.cpp:393-507, without bias and dropout.
+    """(output, logsumexp, philox_seed, philox_offset), attention.cpp:393-507, without dropout; ``bias``
+    ([B, H, Lq, Lk] or anything that broadcasts to it) only without cu_seqlens.
 
     query is [B, Lq, H, D], key / value [B, Lk, H, D] (sequence before heads, unlike the sdp operators).
     output comes back as the reference returns it: the [B, Lq, H, D] buffer viewed as [B, H, Lq, D]
@@ -451,8 +513,8 @@ def _efficient_attention_forward(query, key, value, bias, cu_seqlens_q, cu_seqle
     _check(key.size(1) == value.size(1), "key and value lengths differ")
     _check(query.size(2) == key.size(2) == value.size(2), "numbers of heads differ")
     _check(query.size(3) == key.size(3) == value.size(3), "head dims differ")
-    _check(bias is None, "bias is not supported: the additive-bias kernels are not built in this library")
-    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
+    _check(bias is None or cu_seqlens_q is None, "bias together with cu_seqlens is not built in this library")
+    _check(dropout_p == 0.0, "dropout_p must be 0 here: dropout is built for the scaled_dot_product operators")
     _check(causal_diagonal is None and seqlen_k is None, "causal_diagonal and seqlen_k are not supported")
     _check(custom_mask_type in (NO_CUSTOM_MASK, CAUSAL_FROM_TOP_LEFT, CAUSAL_FROM_BOTTOM_RIGHT),
            f"unknown custom_mask_type {custom_mask_type}")
@@ -464,9 +526,10 @@ def _efficient_attention_forward(query, key, value, bias, cu_seqlens_q, cu_seqle
     if cu_seqlens_q is None:
         q_t, k_t, v_t = query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2)
         if custom_mask_type == CAUSAL_FROM_TOP_LEFT:
-            out, lse, _, _ = _scaled_dot_product_efficient_attention(q_t, k_t, v_t, None, True, 0.0, True, scale=sc)
+            out, lse, _, _ = _scaled_dot_product_efficient_attention(q_t, k_t, v_t, bias, True, 0.0, True, scale=sc)
         else:
-            out, lse = _dense_forward(q_t, k_t, v_t, custom_mask_type == CAUSAL_FROM_BOTTOM_RIGHT, sc, allow_gqa=False)
+            out, lse = _dense_forward(q_t, k_t, v_t, custom_mask_type == CAUSAL_FROM_BOTTOM_RIGHT, sc, allow_gqa=False,
+                                      bias=None if bias is None else _prepare_bias(bias, q_t, k_t))
         lse = lse.permute(1, 0, 2).reshape(H, B * Lq)
     else:
         _check(cu_seqlens_q.dtype == torch.int32 and cu_seqlens_k.dtype == torch.int32, "cu_seqlens must have dtype int32")
@@ -489,10 +552,10 @@ def _efficient_attention_backward(grad_out_, query, key, value, bias, out, cu_se
                                   custom_mask_type: int, bias_requires_grad: bool, *, scale: Optional[float] = None,
                                   num_splits_key: Optional[int] = None):
     """(grad_q [B,Lq,H,D], grad_k, grad_v [B,Lk,H,D], grad_bias), attention.cpp:579-727, for a forward call
-    made without bias; grad_bias is an empty tensor. ``out`` and ``grad_out_`` are [B, Lq, H, D] (any strides
-    with unit head-dim stride); ``logsumexp`` is the [H, B*Lq] tensor of the forward."""
-    _check(bias is None, "bias is not supported: the additive-bias kernels are not built in this library")
-    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
+    ``out`` and ``grad_out_`` are [B, Lq, H, D] (any strides with unit head-dim stride); ``logsumexp`` is the
+    [H, B*Lq] tensor of the forward. grad_bias is shaped like ``bias`` when ``bias_requires_grad``, else empty."""
+    _check(bias is None or cu_seqlens_q is None, "bias together with cu_seqlens is not built in this library")
+    _check(dropout_p == 0.0, "dropout_p must be 0 here: dropout is built for the scaled_dot_product operators")
     _check(query.dim() == 4 and grad_out_.dim() == 4 and out.dim() == 4, "tensors must be [B, L, H, D]")
     _check((cu_seqlens_q is None) == (cu_seqlens_k is None), "cu_seqlens_q and cu_seqlens_k must be given together")
     B, Lq, H, D = query.shape
@@ -504,17 +567,21 @@ def _efficient_attention_backward(grad_out_, query, key, value, bias, out, cu_se
     if cu_seqlens_q is None:
         t = lambda x: x.transpose(1, 2)
         lse = logsumexp.view(H, B, Lq).permute(1, 0, 2).contiguous()
+        want_dbias = bias is not None and bool(bias_requires_grad)
         if custom_mask_type == CAUSAL_FROM_TOP_LEFT:
-            dq, dk, dv, _ = _scaled_dot_product_efficient_attention_backward(
-                t(grad_out_), t(query), t(key), t(value), None, t(out), lse, philox_seed, philox_offset, 0.0,
-                [True, True, True, False], True, scale=sc)
+            dq, dk, dv, db = _scaled_dot_product_efficient_attention_backward(
+                t(grad_out_), t(query), t(key), t(value), bias, t(out), lse, philox_seed, philox_offset, 0.0,
+                [True, True, True, want_dbias], True, scale=sc)
         else:
             go = t(grad_out_)
             if go.stride(-1) != 1:
                 go = go.contiguous()
+            b4 = None if bias is None else _prepare_bias(bias, t(query), t(key))
+            dfull = _new_bias_grad(t(query), t(key)) if want_dbias else None
             dq, dk, dv = _dense_backward(go, t(query), t(key), t(value), t(out), lse,
-                                         custom_mask_type == CAUSAL_FROM_BOTTOM_RIGHT, sc)
-        return t(dq), t(dk), t(dv), empty_bias_grad
+                                         custom_mask_type == CAUSAL_FROM_BOTTOM_RIGHT, sc, bias=b4, dbias=dfull)
+            db = dfull.sum_to_size(bias.shape) if want_dbias else empty_bias_grad
+        return t(dq), t(dk), t(dv), db
     if custom_mask_type == CAUSAL_FROM_TOP_LEFT:
         _check(cu_seqlens_q is cu_seqlens_k or torch.equal(cu_seqlens_q, cu_seqlens_k),
                "CausalFromTopLeft with cu_seqlens needs equal query and key lengths in this library")
