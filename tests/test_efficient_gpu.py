@@ -233,3 +233,29 @@ def test_efficient_attention_pair_with_bias_and_dropout_with_bias(cuda_device, n
     orc.assert_close_bf16(out, ref.detach(), "out")
     for name, got, want in (("dq", dq, qf.grad), ("dk", dk, kf.grad), ("dv", dv, vf.grad), ("dbias", db, bf.grad)):
         orc.assert_close_grad_bf16(got, want, name)
+
+
+def test_choice_routes_an_attn_mask_to_the_memory_efficient_kernels_with_autograd(cuda_device, native_lib):
+    """scaled_dot_product_attention with an attn_mask: flash refuses it, the memory-efficient backend takes it as
+    additive bias (boolean masks become 0 / -inf), and gradients flow to q, k, v and a floating-point mask."""
+    dev = cuda_device
+    B, H, L, D = 2, 2, 192, 128
+    q, k, v, do = (rand((B, H, L, D), s) for s in (1, 2, 3, 4))
+    fmask = torch.rand((B, 1, L, L), generator=torch.Generator().manual_seed(9)).bfloat16()
+    qd, kd, vd, md = (t.to(dev).requires_grad_(True) for t in (q, k, v, fmask))
+    assert sdp_choice._fused_sdp_choice(qd, kd, vd, md) == int(SDPBackend.EFFICIENT_ATTENTION)
+    out = sdp_choice.scaled_dot_product_attention(qd, kd, vd, attn_mask=md)
+    out.backward(do.to(dev))
+    qf, kf, vf, mf = (t.float().requires_grad_(True) for t in (q, k, v, fmask))
+    ref = F.scaled_dot_product_attention(qf, kf, vf, attn_mask=mf)
+    ref.backward(do.float())
+    orc.assert_close_bf16(out, ref.detach(), "out")
+    for name, got, want in (("dq", qd.grad, qf.grad), ("dk", kd.grad, kf.grad), ("dv", vd.grad, vf.grad),
+                            ("dmask", md.grad, mf.grad)):
+        assert got.shape == want.shape
+        orc.assert_close_grad_bf16(got, want, name)
+    bmask = torch.rand((L, L), generator=torch.Generator().manual_seed(10)) > 0.3
+    bmask[:, 0] = True  # no empty rows
+    out = sdp_choice.scaled_dot_product_attention(q.to(dev), k.to(dev), v.to(dev), attn_mask=bmask.to(dev))
+    ref = F.scaled_dot_product_attention(q.float(), k.float(), v.float(), attn_mask=bmask)
+    orc.assert_close_bf16(out, ref, "out with a boolean mask")

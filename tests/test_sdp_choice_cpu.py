@@ -80,12 +80,12 @@ def test_math_backend_is_the_fallback_when_enabled():
     assert torch.allclose(out, ref, atol=1e-6)
 
 
-def test_memory_efficient_backend_refuses_a_mask_with_its_own_text():
+def test_memory_efficient_backend_takes_a_mask_that_broadcasts():
     q = make((2, 2, 3, 64))
     with backends.sdp_kernel(enable_flash=False, enable_math=False, enable_mem_efficient=True):
-        with pytest.warns(UserWarning, match="built without the additive bias"):
+        with pytest.warns(UserWarning, match="does not broadcast to the attention scores"):
             with pytest.raises(RuntimeError, match="No available kernel"):
-                sdp_choice.scaled_dot_product_attention(q, q, q, torch.ones(2, 2, 3, 3, dtype=q.dtype))
+                sdp_choice.scaled_dot_product_attention(q, q, q, torch.ones(2, 2, 5, 3, dtype=q.dtype))
         with pytest.warns(UserWarning, match="Flash attention has been runtime disabled"):
             with pytest.raises(RuntimeError, match="No available kernel"):
                 sdp_choice.scaled_dot_product_attention(q, q, q)  # CPU tensors: the device check fails too

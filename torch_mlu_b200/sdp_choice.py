@@ -6,8 +6,8 @@ Same decision procedure and the same warning / error texts for the constraints t
 (sdp_utils.h:99-455): backends in priority order, each with a constraint list; if none qualifies
 and math is disabled, every constraint is re-run in debug mode (warnings) and
 ``RuntimeError("No available kernel.  Aborting execution.")`` is raised. What differs on purpose:
-both fused backends run the same kernels here (the memory-efficient one without its additive bias, so
-it refuses an attn_mask like flash does), and the MLU-occupancy heuristics of sdp_utils.h:479-524 (500-series check, split condition, valid-data
+both fused backends run the same kernels here (flash refuses an attn_mask as in the reference; the
+memory-efficient one takes it as an additive bias), and the MLU-occupancy heuristics of sdp_utils.h:479-524 (500-series check, split condition, valid-data
 ratio) are replaced by what this build needs: an sm_100 CUDA device, head_dim at most 128.
 """
 from __future__ import annotations
@@ -140,11 +140,17 @@ def _check_runtime_disabled_mem_efficient(q, k, v, mask, debug):  # sdp_utils.h:
     return True
 
 
-def _check_no_bias_for_mem_efficient(q, k, v, mask, debug):
+def _check_mask_for_mem_efficient(q, k, v, mask, debug):
+    # the bias joins the scores inside the kernel: it has to broadcast to [B, H, Lq, Lk]
     if mask is not None:
-        _warn(debug, "The memory efficient kernel of this library is built without the additive bias: "
-                     "it does not support non-null attn_mask.")
-        return False
+        try:
+            torch.broadcast_shapes(tuple(mask.shape), (q.size(0), q.size(1), q.size(2), k.size(2)))
+        except RuntimeError:
+            _warn(debug, f"attn_mask of shape {tuple(mask.shape)} does not broadcast to the attention scores.")
+            return False
+        if mask.dim() > 4:
+            _warn(debug, "attn_mask must have at most 4 dimensions.")
+            return False
     return True
 
 
@@ -152,7 +158,7 @@ _MEM_EFFICIENT_CONSTRAINTS = (
     _check_runtime_disabled_mem_efficient,
     _check_tensor_shapes,
     _check_batch_size_and_num_heads,
-    _check_no_bias_for_mem_efficient,
+    _check_mask_for_mem_efficient,
     _check_head_dim_size,
     _check_nonzero_sequence_lengths,
     _check_last_dim_stride_equals_1,
@@ -186,14 +192,52 @@ def _fused_sdp_choice(query, key, value, attn_mask=None, dropout_p: float = 0.0,
     raise RuntimeError("No available kernel.  Aborting execution.")
 
 
+class _EfficientAttention(torch.autograd.Function):
+    """Autograd for the memory-efficient operator pair of ops.py (what upstream derivatives.yaml wires for
+    _scaled_dot_product_efficient_attention): gradients for query, key, value and a floating-point bias."""
+
+    @staticmethod
+    def forward(ctx, query, key, value, bias, dropout_p, is_causal, scale):
+        from . import ops
+        out, lse, seed, offset = ops._scaled_dot_product_efficient_attention(query, key, value, bias, True, dropout_p, is_causal,
+                                                                             scale=scale)
+        ctx.save_for_backward(query, key, value, out, lse, seed, offset, *(() if bias is None else (bias,)))
+        ctx.args = (dropout_p, is_causal, scale, bias is not None)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        from . import ops
+        query, key, value, out, lse, seed, offset, *rest = ctx.saved_tensors
+        dropout_p, is_causal, scale, has_bias = ctx.args
+        bias = rest[0] if has_bias else None
+        need_bias = has_bias and ctx.needs_input_grad[3]
+        dq, dk, dv, db = ops._scaled_dot_product_efficient_attention_backward(
+            grad_out, query, key, value, bias, out, lse, seed, offset, dropout_p, [True, True, True, need_bias], is_causal,
+            scale=scale)
+        return dq, dk, dv, (db if need_bias else None), None, None, None
+
+
+def _mask_to_bias(attn_mask, query):
+    """A boolean attn_mask (True = take part) becomes 0 / -inf; a floating-point one is the bias itself."""
+    if attn_mask is None:
+        return None
+    if attn_mask.dtype == torch.bool:
+        return torch.zeros_like(attn_mask, dtype=query.dtype).masked_fill(~attn_mask, float("-inf"))
+    return attn_mask.to(query.dtype)
+
+
 def scaled_dot_product_attention(query, key, value, attn_mask=None, dropout_p: float = 0.0, is_causal: bool = False,
                                  scale: Optional[float] = None):
     """F.scaled_dot_product_attention with this package's choice function in front: the flash
-    backend runs this library's kernels (through the dispatcher glue, so autograd works), the math
-    backend is torch's composite implementation."""
+    backend runs this library's kernels (through the dispatcher glue, so autograd works), the memory
+    efficient one runs them with an attn_mask as additive bias, the math backend is torch's composite
+    implementation."""
     choice = _fused_sdp_choice(query, key, value, attn_mask, dropout_p, is_causal, scale=scale)
     if choice == int(SDPBackend.ERROR):
         raise RuntimeError("No viable backend for scaled_dot_product_attention was found.")
+    if choice == int(SDPBackend.EFFICIENT_ATTENTION) and attn_mask is not None:
+        return _EfficientAttention.apply(query, key, value, _mask_to_bias(attn_mask, query), dropout_p, is_causal, scale)
     if choice == int(SDPBackend.FLASH_ATTENTION) or (
             choice == int(SDPBackend.EFFICIENT_ATTENTION) and (not is_causal or query.size(-2) == key.size(-2))):
         # same kernels, same mask when Lq == Lk: the registered operator also carries autograd
@@ -202,12 +246,7 @@ def scaled_dot_product_attention(query, key, value, attn_mask=None, dropout_p: f
         return torch.ops.b200_sdpa._scaled_dot_product_flash_attention(query, key, value, dropout_p, is_causal, False,
                                                                        scale=scale)[0]
     if choice == int(SDPBackend.EFFICIENT_ATTENTION):
-        # top-left causal mask with Lq != Lk: forward only through the operator mirror
-        if torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value)):
-            raise RuntimeError("the memory efficient backend with is_causal and Lq != Lk has no autograd here; "
-                               "call ops._scaled_dot_product_efficient_attention[_backward] directly")
-        from . import ops
-        return ops._scaled_dot_product_efficient_attention(query, key, value, None, False, dropout_p, is_causal,
-                                                           scale=scale)[0]
+        # top-left causal mask with Lq != Lk: the operator mirror, with its own autograd
+        return _EfficientAttention.apply(query, key, value, None, dropout_p, is_causal, scale)
     return torch.ops.aten._scaled_dot_product_attention_math(query, key, value, attn_mask, dropout_p, is_causal,
                                                              scale=scale)[0]
