@@ -51,7 +51,7 @@
 extern "C" {
 #endif
 
-#define SDPA_B200_VERSION 103
+#define SDPA_B200_VERSION 104
 
 #if defined(__GNUC__)
 #define SDPA_B200_API __attribute__((visibility("default")))
@@ -193,10 +193,13 @@ SDPA_B200_API int sdpa_b200_merge_partial(float* o_acc, float* lse_acc, const vo
  *   keep_cols: uint32 [batch*heads][Lk_pad][Lq_pad/32], bit (q & 31) of word (k, q >> 5): the transpose
  * Lq_pad / Lk_pad are the lengths rounded up to a multiple of 128; `heads` is heads_q. A pair is dropped with
  * probability round(dropout_p * 256) / 256; kept probabilities are scaled by 1 / (1 - dropout_p) in the
- * attention kernels. Only the low 32 bits of `offset` enter the counter. */
+ * attention kernels. Only the low 32 bits of `offset` enter the counter. With `is_causal` (the bottom-right
+ * aligned mask of the attention calls) 128 x 128 tiles that the mask hides completely are filled with zeros
+ * instead of random bits; a call made with is_causal must be given masks made with it or without it, never the
+ * other way round. */
 SDPA_B200_API int sdpa_b200_dropout_keep_mask(uint64_t seed, uint64_t offset, float dropout_p, int32_t batch,
-                                              int32_t heads, int32_t seqlen_q, int32_t seqlen_k, uint32_t* keep_rows,
-                                              uint32_t* keep_cols, void* stream);
+                                              int32_t heads, int32_t seqlen_q, int32_t seqlen_k, int32_t is_causal,
+                                              uint32_t* keep_rows, uint32_t* keep_cols, void* stream);
 
 /* How many of this library's kernels the calling process has launched so far. */
 SDPA_B200_API uint64_t sdpa_b200_launch_count(void);

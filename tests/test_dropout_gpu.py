@@ -71,7 +71,9 @@ def test_forward_with_dropout_matches_oracle_with_the_returned_mask(cuda_device,
     assert ops.device_status() == 0
     assert tuple(debug.shape) == (B, H, Lq, Lk) and seed.numel() == 1 and offset.numel() == 1
     keep = (debug > 0).cpu()
-    assert torch.equal(keep, orc.dropout_keep_mask(int(seed), int(offset), p, B, H, Lq, Lk))
+    # (tiles the causal mask hides completely carry zeros instead of random bits)
+    visible = ~orc.causal_mask_bottom_right(Lq, Lk) if causal else torch.ones(Lq, Lk, dtype=torch.bool)
+    assert torch.equal(keep & visible, orc.dropout_keep_mask(int(seed), int(offset), p, B, H, Lq, Lk) & visible)
     o_ref, l_ref = attention_with_mask(q, k, v, keep, p, causal)
     orc.assert_close_bf16(out, o_ref, "out")
     orc.assert_close_lse(lse[..., :Lq], l_ref)        # dropout does not touch the logsumexp
@@ -123,3 +125,12 @@ def test_backward_with_dropout_replays_the_pattern(cuda_device, native_lib, dtyp
     orc.assert_close_grad_bf16(dq, true[1], "dq")
     orc.assert_close_grad_bf16(dk, true[2], "dk")
     orc.assert_close_grad_bf16(dv, true[3], "dv")
+
+
+def test_causal_masks_skip_hidden_tiles_only(cuda_device, native_lib):
+    B, H, Lq, Lk, p = 1, 2, 300, 520, 0.3
+    full = dropout.KeepMasks(9, 5, p, B, H, Lq, Lk, cuda_device).dense().cpu()
+    causal = dropout.KeepMasks(9, 5, p, B, H, Lq, Lk, cuda_device, True).dense().cpu()
+    visible = ~orc.causal_mask_bottom_right(Lq, Lk)
+    assert torch.equal(full & visible, causal & visible)
+    assert not bool((causal & ~visible)[..., :128, 384 + 128:].any())     # a tile above the diagonal: zeros

@@ -143,7 +143,8 @@ def test_dropout_through_the_registered_operator_and_autograd(cuda_device, nativ
     out, seed, offset, debug = res[0], res[6], res[7], res[8]
     assert seed.numel() == 1 and offset.numel() == 1 and tuple(debug.shape) == (2, 3, 260, 260)
     keep = (debug > 0).cpu()
-    assert torch.equal(keep, orc.dropout_keep_mask(int(seed), int(offset), p, 2, 3, 260, 260))
+    visible = ~orc.causal_mask_bottom_right(260, 260)
+    assert torch.equal(keep & visible, orc.dropout_keep_mask(int(seed), int(offset), p, 2, 3, 260, 260) & visible)
     out.backward(do.to(dev))
     ref, (qf, kf, vf) = _attention_with_mask(q, k, v, keep, p, True)
     ref.backward(do.float())

@@ -102,8 +102,8 @@ def load() -> ctypes.CDLL:
     lib.sdpa_b200_merge_partial.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                             c_int32, c_int64, c_int64, c_int64, c_void_p]
     lib.sdpa_b200_dropout_keep_mask.restype = c_int
-    lib.sdpa_b200_dropout_keep_mask.argtypes = [c_uint64, c_uint64, c_float, c_int32, c_int32, c_int32, c_int32, c_void_p,
-                                                c_void_p, c_void_p]
+    lib.sdpa_b200_dropout_keep_mask.argtypes = [c_uint64, c_uint64, c_float, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                                c_void_p, c_void_p, c_void_p]
     _lib = lib
     return lib
 

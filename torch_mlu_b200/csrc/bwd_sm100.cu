@@ -556,6 +556,27 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                     (p.keep_lq_pad >> 5);
         keep = *reinterpret_cast<const uint2*>(words + ((y0 + half * 64) >> 5));
       }
+      if constexpr (kBias) {
+        // the next item's bias values of this thread's row: into L2 now (dQ: 128 contiguous bytes of the query
+        // row; dK/dV: 64 query rows, two per lane, 64 bytes each around this warp's keys)
+        if (i + 1 < n_items && xr < len_x) {
+          const int hn = (i + 1) / tiles_per_head;
+          const int cn = (y_lo + (i + 1 - hn * tiles_per_head)) * kTile + half * 64;
+          if (kMode == kModeDQ) {
+            const uint16_t* nx = p.bias + b * p.bias_batch_stride + hx * p.bias_head_stride +
+                                 static_cast<int64_t>(xr) * p.bias_row_stride + cn;
+            if (cn < len_k) {  // only addresses inside the row
+              prefetch_l2(nx);
+              prefetch_l2(nx + min(63, len_k - 1 - cn));
+            }
+          } else {
+            const uint16_t* nx = p.bias + b * p.bias_batch_stride + (hx * p.kv_group + hn) * p.bias_head_stride + xr;
+            const int q = cn + 2 * lane;
+            if (q < len_q) prefetch_l2(nx + static_cast<int64_t>(q) * p.bias_row_stride);
+            if (q + 1 < len_q) prefetch_l2(nx + static_cast<int64_t>(q + 1) * p.bias_row_stride);
+          }
+        }
+      }
       // `ok` is made warp-uniform after every wait: the warp-level arrivals below need all 32 lanes
       ok = mbar_wait(bar + kBarSFull + (kMode == kModeDQ ? 8 * (i & 1) : 0), (kMode == kModeDQ ? (i >> 1) : i) & 1,
                      abort_flag);

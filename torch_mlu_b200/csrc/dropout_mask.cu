@@ -30,14 +30,14 @@ __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
   return c;
 }
 
-// 16 keep bits from 16 bytes: bit j set when byte j >= drop
-__device__ __forceinline__ uint32_t keep_bits16(uint4 r, uint32_t drop) {
+// 16 keep bits from 16 bytes: bit j set when byte j >= drop. `drop4` holds the threshold in all four bytes; a
+// per-byte compare gives 0xff / 0x00 per byte, and one multiply gathers bit 0 of each byte into four adjacent bits
+// (2^24 + 2^17 + 2^10 + 2^3 moves bits 0, 8, 16, 24 to 24, 25, 26, 27; the other products stay below bit 20).
+__device__ __forceinline__ uint32_t keep_bits16(uint4 r, uint32_t drop4) {
   const uint32_t w[4] = {r.x, r.y, r.z, r.w};
   uint32_t bits = 0;
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int b = 0; b < 4; ++b) bits |= (((w[i] >> (8 * b)) & 0xffu) >= drop ? 1u : 0u) << (4 * i + b);
+  for (int i = 0; i < 4; ++i) bits |= ((((__vcmpgeu4(w[i], drop4) & 0x01010101u) * 0x01020408u) >> 24) & 0xfu) << (4 * i);
   return bits;
 }
 
@@ -45,7 +45,8 @@ struct MaskParams {
   uint32_t* keep_rows;
   uint32_t* keep_cols;
   int lq_pad, lk_pad;
-  uint32_t seed_lo, seed_hi, offset, drop;
+  uint32_t seed_lo, seed_hi, offset, drop4;
+  int causal_shift;  // tiles whose first key lies past (last query of the tile + causal_shift) are zero-filled
 };
 
 // One CTA (4 warps) per 128 x 128 tile of one head; warp w owns keys [32w, 32w + 32), lane = key.
@@ -55,13 +56,17 @@ __global__ void __launch_bounds__(128) dropout_mask_kernel(const MaskParams p) {
   const uint32_t bh = blockIdx.z;
   const int q0 = blockIdx.y * 128, k0 = blockIdx.x * 128;
   const uint32_t k = k0 + warp * 32 + lane;
-  uint32_t col[4];
+  uint32_t col[4] = {0u, 0u, 0u, 0u};
+  // a tile the causal mask hides completely is never read for its bits: write zeros and skip the generator
+  const bool hidden = k0 > q0 + 127 + p.causal_shift;
+  if (!hidden) {
 #pragma unroll
-  for (int qb = 0; qb < 4; ++qb) {
-    const uint32_t g = (q0 + qb * 32) >> 4;  // first group of 16 queries
-    const uint32_t lo = keep_bits16(philox4x32_10(make_uint4(k, g, bh, p.offset), make_uint2(p.seed_lo, p.seed_hi)), p.drop);
-    const uint32_t hi = keep_bits16(philox4x32_10(make_uint4(k, g + 1, bh, p.offset), make_uint2(p.seed_lo, p.seed_hi)), p.drop);
-    col[qb] = lo | (hi << 16);
+    for (int qb = 0; qb < 4; ++qb) {
+      const uint32_t g = (q0 + qb * 32) >> 4;  // first group of 16 queries
+      const uint32_t lo = keep_bits16(philox4x32_10(make_uint4(k, g, bh, p.offset), make_uint2(p.seed_lo, p.seed_hi)), p.drop4);
+      const uint32_t hi = keep_bits16(philox4x32_10(make_uint4(k, g + 1, bh, p.offset), make_uint2(p.seed_lo, p.seed_hi)), p.drop4);
+      col[qb] = lo | (hi << 16);
+    }
   }
   // key-major words: four consecutive words (128 queries) per key
   *reinterpret_cast<uint4*>(p.keep_cols + (static_cast<size_t>(bh) * p.lk_pad + k) * (p.lq_pad >> 5) + (q0 >> 5)) =
@@ -71,10 +76,12 @@ __global__ void __launch_bounds__(128) dropout_mask_kernel(const MaskParams p) {
 #pragma unroll
   for (int qb = 0; qb < 4; ++qb) {
     uint32_t mine = 0;
+    if (!hidden) {  // uniform for the CTA
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const uint32_t w = __ballot_sync(0xffffffffu, (col[qb] >> j) & 1u);
-      if (lane == j) mine = w;
+      for (int j = 0; j < 32; ++j) {
+        const uint32_t w = __ballot_sync(0xffffffffu, (col[qb] >> j) & 1u);
+        if (lane == j) mine = w;
+      }
     }
     rows[qb * 32 + lane][warp] = mine;
   }
@@ -97,7 +104,8 @@ using namespace sdpa_b200;
 
 extern "C" SDPA_B200_API int sdpa_b200_dropout_keep_mask(uint64_t seed, uint64_t offset, float dropout_p, int32_t batch,
                                                          int32_t heads, int32_t seqlen_q, int32_t seqlen_k,
-                                                         uint32_t* keep_rows, uint32_t* keep_cols, void* stream) {
+                                                         int32_t is_causal, uint32_t* keep_rows, uint32_t* keep_cols,
+                                                         void* stream) {
   if (keep_rows == nullptr || keep_cols == nullptr || (reinterpret_cast<uintptr_t>(keep_rows) & 15u) ||
       (reinterpret_cast<uintptr_t>(keep_cols) & 15u)) {
     set_error("dropout_keep_mask: keep_rows and keep_cols must be 16-byte aligned device pointers");
@@ -120,7 +128,9 @@ extern "C" SDPA_B200_API int sdpa_b200_dropout_keep_mask(uint64_t seed, uint64_t
   m.seed_lo = static_cast<uint32_t>(seed);
   m.seed_hi = static_cast<uint32_t>(seed >> 32);
   m.offset = static_cast<uint32_t>(offset);
-  m.drop = dropout_drop_byte(dropout_p);
+  m.drop4 = dropout_drop_byte(dropout_p) * 0x01010101u;
+  // bottom-right aligned causal mask: key k is visible to query q when k <= q + seqlen_k - seqlen_q
+  m.causal_shift = is_causal ? seqlen_k - seqlen_q : (1 << 30);
   dim3 grid(m.lk_pad / 128, m.lq_pad / 128, batch * heads);
   if (grid.y > 65535) {
     set_error("dropout_keep_mask: seqlen_q too long (%d)", seqlen_q);

@@ -571,6 +571,15 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint32_t par = (cnt + j) & 1;
         uint4 keep = make_uint4(0u, 0u, 0u, 0u);
         if constexpr (kDrop) keep = *reinterpret_cast<const uint4*>(keep_row + (n0 >> 5));  // in flight under the wait
+        if constexpr (kBias) {
+          // the next block's 256 bytes of this row: into L2 now, so that the loads below find them there
+          if (bias_row != nullptr && j + 1 < my_blocks) {
+            const int last = len_k - 1;  // only addresses inside the row
+            prefetch_l2(bias_row + min(n0 + kBlockN, last));
+            prefetch_l2(bias_row + min(n0 + kBlockN + 64, last));
+            prefetch_l2(bias_row + min(n0 + 2 * kBlockN - 1, last));
+          }
+        }
         // warp-uniform, because the arrivals below are made by one lane on behalf of its warp
         ok = __all_sync(0xffffffffu, mbar_wait(bar_s, par, abort_flag));
         if (!ok) break;

@@ -106,6 +106,11 @@ __device__ __forceinline__ float2 exp2_poly3_x2(float2 x) {
                      __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23)));
 }
 
+// Ask L2 for the line holding `p` (no register, no wait): for global loads a later step will need
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 // Warpgroup-wide register re-allocation (all four warps of the warpgroup execute it).
 template <int kRegs>
 __device__ __forceinline__ void reg_increase() {

@@ -143,7 +143,7 @@ struct KeepMasks {
   double p = 0.0;
 };
 
-KeepMasks make_keep_masks(const Tensor& q, int64_t seqlen_k, double dropout_p, uint64_t seed, uint64_t offset) {
+KeepMasks make_keep_masks(const Tensor& q, int64_t seqlen_k, double dropout_p, uint64_t seed, uint64_t offset, bool causal) {
   TORCH_CHECK(dropout_p > 0.0 && dropout_p < 1.0, "dropout_p must be inside [0, 1)");
   c10::cuda::CUDAGuard guard(q.device());
   const int64_t BH = q.size(0) * q.size(1), Lq = q.size(2);
@@ -154,7 +154,8 @@ KeepMasks make_keep_masks(const Tensor& q, int64_t seqlen_k, double dropout_p, u
   m.cols = at::empty({BH, lk_pad, lq_pad / 32}, q.options().dtype(at::kInt));
   check_status(sdpa_b200_dropout_keep_mask(seed, offset, static_cast<float>(dropout_p), static_cast<int32_t>(q.size(0)),
                                            static_cast<int32_t>(q.size(1)), static_cast<int32_t>(Lq),
-                                           static_cast<int32_t>(seqlen_k), reinterpret_cast<uint32_t*>(m.rows.data_ptr()),
+                                           static_cast<int32_t>(seqlen_k), causal ? 1 : 0,
+                                           reinterpret_cast<uint32_t*>(m.rows.data_ptr()),
                                            reinterpret_cast<uint32_t*>(m.cols.data_ptr()),
                                            at::cuda::getCurrentCUDAStream().stream()),
                "sdpa_b200_dropout_keep_mask");
@@ -269,7 +270,7 @@ DenseDropoutResult dense_forward_with_dropout(const Tensor& q, const Tensor& k, 
   }
   TORCH_CHECK(q.dim() == 4 && k.dim() == 4, "query, key and value must be 4-dimensional [batch, heads, seq_len, head_dim]");
   auto [seed, offset] = draw_philox(q, q.size(0) * q.size(1) * q.size(2) * k.size(2));
-  KeepMasks keep = make_keep_masks(q, k.size(2), dropout_p, seed, offset);
+  KeepMasks keep = make_keep_masks(q, k.size(2), dropout_p, seed, offset, causal);
   std::tie(r.out, r.lse) = dense_forward(q, k, v, causal, scale, allow_gqa, &keep);
   r.seed = cpu_i64(seed);
   r.offset = cpu_i64(offset);
@@ -286,7 +287,7 @@ std::tuple<Tensor, Tensor, Tensor> dense_backward_with_dropout(const Tensor& gra
   TORCH_CHECK(philox_seed.numel() == 1 && philox_offset.numel() == 1,
               "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned");
   KeepMasks keep = make_keep_masks(q, k.size(2), dropout_p, static_cast<uint64_t>(philox_seed.item<int64_t>()),
-                                   static_cast<uint64_t>(philox_offset.item<int64_t>()));
+                                   static_cast<uint64_t>(philox_offset.item<int64_t>()), causal);
   return dense_backward(grad_out, q, k, v, out, lse, causal, scale, &keep);
 }
 

@@ -21,7 +21,7 @@ class KeepMasks:
     """keep_rows [B*H, Lq_pad, Lk_pad/32] and keep_cols [B*H, Lk_pad, Lq_pad/32] int32 words on the device."""
 
     def __init__(self, seed: int, offset: int, dropout_p: float, batch: int, heads: int, seqlen_q: int, seqlen_k: int,
-                 device: torch.device):
+                 device: torch.device, is_causal: bool = False):
         if not (0.0 < dropout_p < 1.0):
             raise ValueError(f"dropout_p must be inside (0, 1), got {dropout_p}")
         self.shape = (batch, heads, seqlen_q, seqlen_k)
@@ -34,8 +34,9 @@ class KeepMasks:
         with torch.cuda.device(device):
             stream = torch.cuda.current_stream(device).cuda_stream
             _cabi.check(lib.sdpa_b200_dropout_keep_mask(self.seed & (2 ** 64 - 1), self.offset & (2 ** 64 - 1), self.dropout_p,
-                                                        batch, heads, seqlen_q, seqlen_k, self.rows.data_ptr(),
-                                                        self.cols.data_ptr(), stream), "sdpa_b200_dropout_keep_mask")
+                                                        batch, heads, seqlen_q, seqlen_k, int(bool(is_causal)),
+                                                        self.rows.data_ptr(), self.cols.data_ptr(), stream),
+                        "sdpa_b200_dropout_keep_mask")
 
     def dense(self) -> torch.Tensor:
         """bool [B, H, Lq, Lk], True = kept (what the reference's debug mask encodes as > 0)."""

@@ -246,7 +246,7 @@ def _scaled_dot_product_flash_attention(query, key, value, dropout_p: float = 0.
         # With dropout the operator returns the Philox pair that fixes the pattern (FlashAttention_internal.cpp:
         # 190-214), as CPU int64 scalars, and on request the pattern itself (:141-146): > 0 where a pair was kept.
         s, o = dropout.draw_seed_and_offset(query.device, B * H * Lq * Lk)
-        keep = dropout.KeepMasks(s, o, dropout_p, B, H, Lq, Lk, query.device)
+        keep = dropout.KeepMasks(s, o, dropout_p, B, H, Lq, Lk, query.device, is_causal)
         seed, offset = torch.tensor(s, dtype=torch.int64), torch.tensor(o, dtype=torch.int64)
         if return_debug_mask:
             debug = keep.dense().to(query.dtype)
@@ -292,7 +292,8 @@ def _scaled_dot_product_flash_attention_backward(grad_out, query, key, value, ou
         _check(philox_seed.numel() == 1 and philox_offset.numel() == 1,
                "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned")
         B, H, Lq, _ = query.shape
-        keep = dropout.KeepMasks(int(philox_seed), int(philox_offset), dropout_p, B, H, Lq, key.size(2), query.device)
+        keep = dropout.KeepMasks(int(philox_seed), int(philox_offset), dropout_p, B, H, Lq, key.size(2), query.device,
+                                 is_causal)
     if logsumexp.size(-1) != query.size(2):
         logsumexp = logsumexp[..., :query.size(2)].contiguous()
     return _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, calculate_scale(query, scale), keep=keep)
@@ -324,7 +325,7 @@ def _scaled_dot_product_efficient_attention(query, key, value, attn_bias, comput
     if dropout_p > 0.0:
         _check(not is_causal or Lq == Lk, "dropout with a top-left causal mask and Lq != Lk is not built in this library")
         s, o = dropout.draw_seed_and_offset(query.device, query.size(0) * query.size(1) * Lq * Lk)
-        keep = dropout.KeepMasks(s, o, dropout_p, query.size(0), query.size(1), Lq, Lk, query.device)
+        keep = dropout.KeepMasks(s, o, dropout_p, query.size(0), query.size(1), Lq, Lk, query.device, is_causal)
         out, lse = _dense_forward(query, key, value, is_causal, sc, allow_gqa=False, keep=keep, bias=bias)
         if not compute_log_sumexp:
             lse = lse.new_empty((query.size(0), query.size(1), 0))
@@ -375,7 +376,7 @@ def _scaled_dot_product_efficient_attention_backward(grad_out, query, key, value
         _check(philox_seed.numel() == 1 and philox_offset.numel() == 1,
                "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned")
         keep = dropout.KeepMasks(int(philox_seed), int(philox_offset), dropout_p, query.size(0), query.size(1), Lq, Lk,
-                                 query.device)
+                                 query.device, is_causal)
         return finish(*_dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, sc, keep=keep, bias=bias,
                                        dbias=dbias))
     if not is_causal or Lq == Lk:
