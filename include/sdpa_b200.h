@@ -51,7 +51,7 @@
 extern "C" {
 #endif
 
-#define SDPA_B200_VERSION 104
+#define SDPA_B200_VERSION 106
 
 #if defined(__GNUC__)
 #define SDPA_B200_API __attribute__((visibility("default")))
@@ -138,6 +138,12 @@ typedef struct sdpa_b200_params {
    * same type, or NULL. Elements the causal mask hides are not written: clear the buffer first. */
   void* dbias;
   int64_t dbias_batch_stride, dbias_head_stride, dbias_row_stride;
+  /* Backward, optional: the same bias with keys and queries exchanged, [batch, heads_q, seqlen_k, seqlen_q]
+   * with unit query stride and the rules of `bias` for alignment and padding (strides for batch, head, key row).
+   * The dK/dV kernel, whose threads own keys, then reads 16 bytes at a time instead of two. Not needed when the
+   * bias does not depend on the query (bias_row_stride == 0). NULL = not given. */
+  const void* bias_t;
+  int64_t bias_t_batch_stride, bias_t_head_stride, bias_t_row_stride;
 } sdpa_b200_params;
 
 SDPA_B200_API int sdpa_b200_version(void);
@@ -200,6 +206,14 @@ SDPA_B200_API int sdpa_b200_merge_partial(float* o_acc, float* lse_acc, const vo
 SDPA_B200_API int sdpa_b200_dropout_keep_mask(uint64_t seed, uint64_t offset, float dropout_p, int32_t batch,
                                               int32_t heads, int32_t seqlen_q, int32_t seqlen_k, int32_t is_causal,
                                               uint32_t* keep_rows, uint32_t* keep_cols, void* stream);
+
+/* Writes sdpa_b200_params.bias_t for a bias given as in sdpa_b200_params (16-bit elements, element strides, unit
+ * key stride, row_stride != 0): out is [batch][heads][seqlen_k][out_row_stride], contiguous, out_row_stride a
+ * multiple of 8 that holds seqlen_q; the padding is zero-filled. Pass batch = 1 (heads = 1) for a bias that is
+ * broadcast along that dimension and give bias_t the stride 0 there. */
+SDPA_B200_API int sdpa_b200_transpose_bias(const void* bias, int64_t batch_stride, int64_t head_stride, int64_t row_stride,
+                                           int32_t batch, int32_t heads, int32_t seqlen_q, int32_t seqlen_k, void* out,
+                                           int64_t out_row_stride, void* stream);
 
 /* How many of this library's kernels the calling process has launched so far. */
 SDPA_B200_API uint64_t sdpa_b200_launch_count(void);

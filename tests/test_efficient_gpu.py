@@ -259,3 +259,24 @@ def test_choice_routes_an_attn_mask_to_the_memory_efficient_kernels_with_autogra
     out = sdp_choice.scaled_dot_product_attention(q.to(dev), k.to(dev), v.to(dev), attn_mask=bmask.to(dev))
     ref = F.scaled_dot_product_attention(q.float(), k.float(), v.float(), attn_mask=bmask)
     orc.assert_close_bf16(out, ref, "out with a boolean mask")
+
+
+@pytest.mark.parametrize("Lq,Lk,causal", [(256, 256, True), (200, 333, False)])
+def test_backward_with_a_transposed_bias_copy_gives_the_same_gradients(cuda_device, native_lib, Lq, Lk, causal):
+    """The optional bias_t of the C ABI (the bias with keys and queries exchanged, read 16 bytes at a time by the
+    dK/dV kernel) against the same call without it: bit-identical gradients."""
+    dev = cuda_device
+    B, H, D = 2, 2, 128
+    q, k, v, do = rand((B, H, Lq, D), 1).to(dev), rand((B, H, Lk, D), 2).to(dev), rand((B, H, Lk, D), 3).to(dev), rand((B, H, Lq, D), 4).to(dev)
+    bias = ops._prepare_bias(torch.rand((B, 1, Lq, Lk), generator=torch.Generator().manual_seed(3)).bfloat16().to(dev), q, k)
+    sc = ops.calculate_scale(q, None)
+    out, lse = ops._dense_forward(q, k, v, causal, sc, allow_gqa=False, bias=bias)
+    plain = ops._dense_backward(do, q, k, v, out, lse, causal, sc, bias=bias, bias_t=False)
+    bias_t = ops._transposed_bias(bias)
+    assert bias_t is not None and tuple(bias_t.shape) == (B, H, Lk, Lq) and bias_t.stride(1) == 0   # heads stay broadcast
+    assert torch.equal(bias_t, bias.transpose(2, 3))
+    fast = ops._dense_backward(do, q, k, v, out, lse, causal, sc, bias=bias, bias_t=bias_t)
+    assert ops.device_status() == 0
+    for a, b in zip(plain, fast):
+        assert torch.equal(a, b)
+    assert ops._transposed_bias(bias[:, :, :1].expand(B, H, Lq, Lk)) is None   # no query dependence: nothing to copy

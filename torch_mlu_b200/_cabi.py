@@ -29,6 +29,7 @@ EXPORTED_SYMBOLS = (
     "sdpa_b200_decode_static",
     "sdpa_b200_merge_partial",
     "sdpa_b200_dropout_keep_mask",
+    "sdpa_b200_transpose_bias",
     "sdpa_b200_launch_count",
 )
 STATIC_SCRATCH_BYTES = 16 << 20
@@ -56,6 +57,7 @@ class SdpaParams(ctypes.Structure):
         ("keep_rows", c_void_p), ("keep_cols", c_void_p),
         ("bias", c_void_p), ("bias_batch_stride", c_int64), ("bias_head_stride", c_int64), ("bias_row_stride", c_int64),
         ("dbias", c_void_p), ("dbias_batch_stride", c_int64), ("dbias_head_stride", c_int64), ("dbias_row_stride", c_int64),
+        ("bias_t", c_void_p), ("bias_t_batch_stride", c_int64), ("bias_t_head_stride", c_int64), ("bias_t_row_stride", c_int64),
     ]
 
 
@@ -104,6 +106,9 @@ def load() -> ctypes.CDLL:
     lib.sdpa_b200_dropout_keep_mask.restype = c_int
     lib.sdpa_b200_dropout_keep_mask.argtypes = [c_uint64, c_uint64, c_float, c_int32, c_int32, c_int32, c_int32, c_int32,
                                                 c_void_p, c_void_p, c_void_p]
+    lib.sdpa_b200_transpose_bias.restype = c_int
+    lib.sdpa_b200_transpose_bias.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p,
+                                             c_int64, c_void_p]
     _lib = lib
     return lib
 

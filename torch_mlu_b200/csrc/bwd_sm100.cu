@@ -100,6 +100,8 @@ struct BwdKernelParams {
   // dS itself, written by the dQ kernel (whose thread owns a query row and 64 consecutive keys of it)
   const uint16_t* bias;
   int64_t bias_batch_stride, bias_head_stride, bias_row_stride;
+  const uint16_t* bias_t;  // or null: the bias with keys and queries exchanged (unit query stride), for dK/dV
+  int64_t bias_t_batch_stride, bias_t_head_stride, bias_t_row_stride;
   uint16_t* dbias;  // or null
   int64_t dbias_batch_stride, dbias_head_stride, dbias_row_stride;
   float inv_scale;  // 1 / softmax_scale
@@ -570,10 +572,21 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               prefetch_l2(nx + min(63, len_k - 1 - cn));
             }
           } else {
-            const uint16_t* nx = p.bias + b * p.bias_batch_stride + (hx * p.kv_group + hn) * p.bias_head_stride + xr;
-            const int q = cn + 2 * lane;
-            if (q < len_q) prefetch_l2(nx + static_cast<int64_t>(q) * p.bias_row_stride);
-            if (q + 1 < len_q) prefetch_l2(nx + static_cast<int64_t>(q + 1) * p.bias_row_stride);
+            if (p.bias_row_stride == 0) {
+              // one value per key: nothing worth fetching ahead
+            } else if (p.bias_t != nullptr) {
+              const uint16_t* nx = p.bias_t + b * p.bias_t_batch_stride + (hx * p.kv_group + hn) * p.bias_t_head_stride +
+                                   static_cast<int64_t>(xr) * p.bias_t_row_stride + cn;
+              if (cn < len_q) {
+                prefetch_l2(nx);
+                prefetch_l2(nx + min(63, len_q - 1 - cn));
+              }
+            } else {
+              const uint16_t* nx = p.bias + b * p.bias_batch_stride + (hx * p.kv_group + hn) * p.bias_head_stride + xr;
+              const int q = cn + 2 * lane;
+              if (q < len_q) prefetch_l2(nx + static_cast<int64_t>(q) * p.bias_row_stride);
+              if (q + 1 < len_q) prefetch_l2(nx + static_cast<int64_t>(q + 1) * p.bias_row_stride);
+            }
           }
         }
       }
@@ -636,13 +649,38 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
           } else {
             if (xr < len_x) {
-              const uint16_t* bcol = p.bias + b * p.bias_batch_stride + (hx * p.kv_group + hi) * p.bias_head_stride + xr;
+              const int hq = hx * p.kv_group + hi;
+              const uint16_t* bcol = p.bias + b * p.bias_batch_stride + hq * p.bias_head_stride + xr;
+              if (p.bias_row_stride == 0) {
+                // the bias does not depend on the query (ALiBi-like): one value for this thread's key
+                const float bs = unpack_16x2<kF16>(static_cast<uint32_t>(bcol[0])).x * p.inv_scale;
 #pragma unroll
-              for (int j = 0; j < 64; ++j) {
-                if (col0 + j < len_q) {
-                  const uint32_t raw = bcol[static_cast<int64_t>(col0 + j) * p.bias_row_stride];
-                  const float bv = unpack_16x2<kF16>(raw).x;
-                  a[j] = __float_as_uint(fmaf(bv, p.inv_scale, __uint_as_float(a[j])));
+                for (int j = 0; j < 64; ++j) a[j] = __float_as_uint(__uint_as_float(a[j]) + bs);
+              } else if (p.bias_t != nullptr) {
+                // the caller's transposed copy: this key's 64 consecutive queries, eight 16-byte loads
+                const uint16_t* trow = p.bias_t + b * p.bias_t_batch_stride + hq * p.bias_t_head_stride +
+                                       static_cast<int64_t>(xr) * p.bias_t_row_stride + col0;
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch) {
+                  if (col0 + ch * 8 < len_q) {
+                    const uint4 w = *reinterpret_cast<const uint4*>(trow + ch * 8);
+                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      const float2 b2 = unpack_16x2<kF16>(ww[e]);
+                      a[ch * 8 + 2 * e] = __float_as_uint(fmaf(b2.x, p.inv_scale, __uint_as_float(a[ch * 8 + 2 * e])));
+                      a[ch * 8 + 2 * e + 1] = __float_as_uint(fmaf(b2.y, p.inv_scale, __uint_as_float(a[ch * 8 + 2 * e + 1])));
+                    }
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 64; ++j) {
+                  if (col0 + j < len_q) {
+                    const uint32_t raw = bcol[static_cast<int64_t>(col0 + j) * p.bias_row_stride];
+                    const float bv = unpack_16x2<kF16>(raw).x;
+                    a[j] = __float_as_uint(fmaf(bv, p.inv_scale, __uint_as_float(a[j])));
+                  }
                 }
               }
             }
@@ -1076,6 +1114,10 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   kp.bias_batch_stride = p.bias_batch_stride;
   kp.bias_head_stride = p.bias_head_stride;
   kp.bias_row_stride = p.bias_row_stride;
+  kp.bias_t = static_cast<const uint16_t*>(p.bias_t);
+  kp.bias_t_batch_stride = p.bias_t_batch_stride;
+  kp.bias_t_head_stride = p.bias_t_head_stride;
+  kp.bias_t_row_stride = p.bias_t_row_stride;
   kp.dbias = static_cast<uint16_t*>(p.dbias);
   kp.dbias_batch_stride = p.dbias_batch_stride;
   kp.dbias_head_stride = p.dbias_head_stride;

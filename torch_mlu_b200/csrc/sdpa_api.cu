@@ -347,6 +347,14 @@ int sdpa_b200_fwd(const sdpa_b200_params* p, void* workspace, size_t workspace_b
 int sdpa_b200_bwd(const sdpa_b200_params* p, void* workspace, size_t workspace_bytes, void* stream) {
   int st = validate_common(p);
   if (st != SDPA_B200_OK) return st;
+  if (p->bias_t != nullptr) {
+    auto bad = [](int64_t s) { return s < 0 || (s % 8) != 0; };
+    if (p->bias == nullptr || !aligned16(p->bias_t) || bad(p->bias_t_batch_stride) || bad(p->bias_t_head_stride) ||
+        bad(p->bias_t_row_stride)) {
+      set_error("bias_t needs a bias, 16-byte alignment and strides that are 0 or multiples of 8 elements");
+      return SDPA_B200_INVALID_ARG;
+    }
+  }
   if (p->dbias != nullptr) {
     const int64_t need = (static_cast<int64_t>(p->max_seqlen_k) + 7) / 8 * 8;
     if (p->bias == nullptr || !aligned16(p->dbias) || p->dbias_row_stride < need || (p->dbias_row_stride % 8) != 0 ||

@@ -161,7 +161,7 @@ def _dense_params(query, key, value, out, lse, is_causal, scale, kernel=_cabi.KE
     return p
 
 
-def _set_bias(p: _cabi.SdpaParams, bias, dbias=None) -> None:
+def _set_bias(p: _cabi.SdpaParams, bias, dbias=None, bias_t=None) -> None:
     """bias / dbias: [B, H, Lq, Lk] views prepared by _prepare_bias / _new_bias_grad (unit key stride)."""
     if bias is None:
         return
@@ -170,6 +170,26 @@ def _set_bias(p: _cabi.SdpaParams, bias, dbias=None) -> None:
     if dbias is not None:
         p.dbias = dbias.data_ptr()
         p.dbias_batch_stride, p.dbias_head_stride, p.dbias_row_stride = dbias.stride(0), dbias.stride(1), dbias.stride(2)
+    if bias_t is not None:
+        p.bias_t = bias_t.data_ptr()
+        p.bias_t_batch_stride, p.bias_t_head_stride, p.bias_t_row_stride = bias_t.stride(0), bias_t.stride(1), bias_t.stride(2)
+
+
+def _transposed_bias(bias):
+    """[B, H, Lk, Lq] view of a copy of ``bias`` (a [B, H, Lq, Lk] view from _prepare_bias) with keys and queries
+    exchanged, for the backward: the dK/dV kernel's threads own keys and read consecutive queries. Broadcast
+    batch / head dimensions stay broadcast; a bias that does not depend on the query needs no copy (None)."""
+    if bias.stride(2) == 0:
+        return None
+    B, H, Lq, Lk = bias.shape
+    nb, nh = (1 if bias.stride(0) == 0 else B), (1 if bias.stride(1) == 0 else H)
+    lq8 = (Lq + 7) // 8 * 8
+    buf = torch.empty((nb, nh, Lk, lq8), dtype=bias.dtype, device=bias.device)
+    lib = _cabi.load()
+    with torch.cuda.device(bias.device):
+        _cabi.check(lib.sdpa_b200_transpose_bias(bias.data_ptr(), bias.stride(0), bias.stride(1), bias.stride(2), nb, nh, Lq, Lk,
+                                                 buf.data_ptr(), lq8, _stream_ptr()), "sdpa_b200_transpose_bias")
+    return buf[..., :Lq].expand(B, H, Lk, Lq)
 
 
 def _prepare_bias(attn_bias, query, key):
@@ -257,7 +277,9 @@ def _scaled_dot_product_flash_attention(query, key, value, dropout_p: float = 0.
     return out, lse, cum_q, cum_k, Lq, Lk, seed, offset, debug
 
 
-def _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, scale, keep=None, bias=None, dbias=None):
+def _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, scale, keep=None, bias=None, dbias=None,
+                    bias_t=None):
+    # bias_t: a transposed copy of the bias (see _transposed_bias) kept by the caller; made here when missing
     _check_inputs(grad_out, query, key, value, out)
     _check(logsumexp.dtype == torch.float32 and logsumexp.is_contiguous(), "logsumexp must be contiguous fp32")
     B, H, Lq, D = query.shape
@@ -274,7 +296,11 @@ def _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, scal
     if keep is not None:
         p.dropout_p = keep.dropout_p
         p.keep_rows, p.keep_cols = keep.rows.data_ptr(), keep.cols.data_ptr()
-    _set_bias(p, bias, dbias)
+    if bias_t is False:
+        bias_t = None  # the caller wants the strided reads (tests compare the two paths)
+    elif bias is not None and bias_t is None:
+        bias_t = _transposed_bias(bias)  # one HBM pass; the dK/dV kernel then reads the bias 16 bytes at a time
+    _set_bias(p, bias, dbias, bias_t)
     _run_bwd(p, query.device)
     return dq, dk, dv
 
