@@ -199,7 +199,7 @@ SDPA_B200_API int sdpa_b200_merge_partial(float* o_acc, float* lse_acc, const vo
  *   keep_cols: uint32 [batch*heads][Lk_pad][Lq_pad/32], bit (q & 31) of word (k, q >> 5): the transpose
  * Lq_pad / Lk_pad are the lengths rounded up to a multiple of 128; `heads` is heads_q. A pair is dropped with
  * probability round(dropout_p * 256) / 256; kept probabilities are scaled by 1 / (1 - dropout_p) in the
- * attention kernels. Only the low 32 bits of `offset` enter the counter. With `is_causal` (the bottom-right
+ * attention kernels. With `is_causal` (the bottom-right
  * aligned mask of the attention calls) 128 x 128 tiles that the mask hides completely are filled with zeros
  * instead of random bits; a call made with is_causal must be given masks made with it or without it, never the
  * other way round. */

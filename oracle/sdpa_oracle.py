@@ -291,7 +291,7 @@ def philox4x32_10(counter, key):
 
 def dropout_keep_mask(seed: int, offset: int, dropout_p: float, batch: int, heads: int, seqlen_q: int, seqlen_k: int):
     """bool [batch, heads, seqlen_q, seqlen_k], True = kept: the rule of the library's mask kernel restated.
-    counter = (key, query // 16, batch*heads_index, offset & 0xffffffff), key = (seed low, seed high); element
+    counter = (key, query // 16, batch*heads_index, offset & 0xffffffff), key = (seed low, seed high ^ offset high); element
     (q, k) is kept when byte (q % 16) of the 16 output bytes is >= round(dropout_p * 256)."""
     import numpy as np
     drop = min(255, max(0, int(dropout_p * 256.0 + 0.5)))
@@ -299,7 +299,7 @@ def dropout_keep_mask(seed: int, offset: int, dropout_p: float, batch: int, head
     bh, g, k = np.meshgrid(np.arange(batch * heads, dtype=np.uint32), np.arange(groups, dtype=np.uint32),
                            np.arange(seqlen_k, dtype=np.uint32), indexing="ij")
     counter = np.stack([k, g, bh, np.full_like(k, offset & 0xFFFFFFFF)], axis=-1)
-    out = philox4x32_10(counter, (seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF))   # [BH, G, Lk, 4]
+    out = philox4x32_10(counter, (seed & 0xFFFFFFFF, ((seed >> 32) ^ (offset >> 32)) & 0xFFFFFFFF))   # [BH, G, Lk, 4]
     by = out.view(np.uint8).reshape(batch * heads, groups, seqlen_k, 16)            # little-endian bytes
     keep = by >= drop                                                               # [BH, G, Lk, 16]
     keep = keep.transpose(0, 1, 3, 2).reshape(batch * heads, groups * 16, seqlen_k)[:, :seqlen_q]

@@ -12,8 +12,9 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("B,H,Lq,Lk,p", [(2, 3, 200, 300, 0.22), (1, 2, 129, 1, 0.48), (1, 1, 16, 513, 0.1)])
 def test_keep_masks_match_the_cpu_philox(cuda_device, native_lib, B, H, Lq, Lk, p):
-    m = dropout.KeepMasks(0x1234567890ABCDEF, 77, p, B, H, Lq, Lk, cuda_device)
-    want = orc.dropout_keep_mask(0x1234567890ABCDEF, 77, p, B, H, Lq, Lk)
+    m = dropout.KeepMasks(0x1234567890ABCDEF, (5 << 32) + 77, p, B, H, Lq, Lk, cuda_device)
+    want = orc.dropout_keep_mask(0x1234567890ABCDEF, (5 << 32) + 77, p, B, H, Lq, Lk)
+    assert not torch.equal(want, orc.dropout_keep_mask(0x1234567890ABCDEF, 77, p, B, H, Lq, Lk))
     assert torch.equal(m.dense().cpu(), want)
     assert torch.equal(m.dense_from_cols().cpu(), want)   # the transposed copy holds the same pattern
 
@@ -134,3 +135,15 @@ def test_causal_masks_skip_hidden_tiles_only(cuda_device, native_lib):
     visible = ~orc.causal_mask_bottom_right(Lq, Lk)
     assert torch.equal(full & visible, causal & visible)
     assert not bool((causal & ~visible)[..., :128, 384 + 128:].any())     # a tile above the diagonal: zeros
+
+
+def test_manual_seed_repeats_the_pattern(cuda_device, native_lib):
+    from torch_mlu_b200 import ops
+    q = rand((1, 2, 256, 128), 1).to(cuda_device)
+    torch.cuda.manual_seed(77)
+    a = ops._scaled_dot_product_flash_attention(q, q, q, 0.3, True, False)
+    b = ops._scaled_dot_product_flash_attention(q, q, q, 0.3, True, False)
+    torch.cuda.manual_seed(77)
+    c = ops._scaled_dot_product_flash_attention(q, q, q, 0.3, True, False)
+    assert int(a[7]) != int(b[7]) and not torch.equal(a[0], b[0])
+    assert int(a[6]) == int(c[6]) and int(a[7]) == int(c[7]) and torch.equal(a[0], c[0])

@@ -11,8 +11,8 @@
 // never read outside the array.
 //
 // Random stream: Philox4x32-10 (Salmon et al., SC'11). One call yields 16 bytes = the keep decisions of
-// 16 consecutive queries for one key: counter = (key, query / 16, batch*heads + head, offset), key =
-// the 64-bit seed. Element (q, k) is kept when byte (q & 15) of the output >= round(p * 256).
+// 16 consecutive queries for one key: counter = (key, query / 16, batch*heads + head, low half of the
+// offset), key = (low half of the seed, high half of the seed xor high half of the offset). Element (q, k) is kept when byte (q & 15) of the output >= round(p * 256).
 #include "kernels.h"
 
 namespace sdpa_b200 {
@@ -126,7 +126,7 @@ extern "C" SDPA_B200_API int sdpa_b200_dropout_keep_mask(uint64_t seed, uint64_t
   m.lq_pad = (seqlen_q + 127) / 128 * 128;
   m.lk_pad = (seqlen_k + 127) / 128 * 128;
   m.seed_lo = static_cast<uint32_t>(seed);
-  m.seed_hi = static_cast<uint32_t>(seed >> 32);
+  m.seed_hi = static_cast<uint32_t>(seed >> 32) ^ static_cast<uint32_t>(offset >> 32);  // all 64 offset bits count
   m.offset = static_cast<uint32_t>(offset);
   m.drop4 = dropout_drop_byte(dropout_p) * 0x01010101u;
   // bottom-right aligned causal mask: key k is visible to query q when k <= q + seqlen_k - seqlen_q

@@ -50,14 +50,11 @@ class KeepMasks:
         return bits.reshape(B * H, self.cols.size(1), -1)[:, :Lk, :Lq].transpose(1, 2).reshape(B, H, Lq, Lk).bool()
 
 
-_next_offset = 0
-
-
 def draw_seed_and_offset(device: torch.device, elements: int) -> Tuple[int, int]:
-    """(seed, offset) for one call: the CUDA generator's seed and a running offset that advances by the
-    number of elements a call covers, like getCounterOffset (FlashAttention_internal.cpp:46-49)."""
-    global _next_offset
-    seed = torch.cuda.default_generators[device.index if device.index is not None else torch.cuda.current_device()].initial_seed()
-    offset = _next_offset
-    _next_offset += (elements + 3) // 4
+    """(seed, offset) for one call from the device's default generator, which moves on by the number of Philox
+    calls the elements stand for (what getCounterOffset does, FlashAttention_internal.cpp:46-49): the same
+    stream every other torch consumer draws from, so torch.cuda.manual_seed makes a run repeatable."""
+    gen = torch.cuda.default_generators[device.index if device.index is not None else torch.cuda.current_device()]
+    seed, offset = gen.initial_seed(), gen.get_offset()
+    gen.set_offset(offset + ((elements + 3) // 4 + 3) // 4 * 4)  # the generator keeps offsets in multiples of 4
     return seed, offset
