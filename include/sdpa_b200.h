@@ -51,7 +51,7 @@
 extern "C" {
 #endif
 
-#define SDPA_B200_VERSION 106
+#define SDPA_B200_VERSION 107
 
 #if defined(__GNUC__)
 #define SDPA_B200_API __attribute__((visibility("default")))
@@ -63,7 +63,7 @@ extern "C" {
 enum {
   SDPA_B200_OK = 0,
   SDPA_B200_INVALID_ARG = 1,    /* null pointer, bad shape, bad stride/alignment, workspace too small */
-  SDPA_B200_UNSUPPORTED = 2,    /* valid request this build has no kernel for (dtype, head_dim > 128, varlen dropout) */
+  SDPA_B200_UNSUPPORTED = 2,    /* valid request this build has no kernel for (dtype, head_dim > 128, varlen bias) */
   SDPA_B200_LAUNCH_FAILED = 3,  /* CUDA reported an error while configuring or launching */
   SDPA_B200_DEVICE_TIMEOUT = 4, /* a bounded wait inside a kernel ran out (read back from workspace) */
   SDPA_B200_NO_DEVICE = 5       /* not an sm_100 device / no CUDA driver */
@@ -118,13 +118,14 @@ typedef struct sdpa_b200_params {
   int64_t dv_batch_stride, dv_head_stride, dv_row_stride;
 
   float softmax_scale; /* > 0; the reference default is 1/sqrt(head_dim), sdp_utils.h:40-47 */
-  float dropout_p;     /* 0, or inside (0, 1) together with keep_rows / keep_cols (dense tensors only) */
+  float dropout_p;     /* 0, or inside (0, 1) together with keep_rows / keep_cols */
   int32_t is_causal;
   int32_t dtype;      /* SDPA_B200_BF16 or SDPA_B200_F16 */
   int32_t kernel;     /* SDPA_B200_KERNEL_* (forward only) */
   int32_t num_splits; /* decode: 0 = choose; otherwise the number of KV splits */
-  /* Dropout keep-masks written by sdpa_b200_dropout_keep_mask() for the same batch, heads_q and sequence
-   * lengths; both NULL when dropout_p == 0. The forward reads keep_rows; the backward reads both. */
+  /* Dropout keep-masks written by sdpa_b200_dropout_keep_mask() (dense) or ..._varlen() (packed) for the same
+   * batch, heads_q and sequence lengths; both NULL when dropout_p == 0. The forward reads keep_rows; the
+   * backward reads both. */
   const uint32_t* keep_rows;
   const uint32_t* keep_cols;
   /* Additive attention bias of the memory-efficient operators (mem_eff_fwd / mem_eff_bwd,
@@ -206,6 +207,18 @@ SDPA_B200_API int sdpa_b200_merge_partial(float* o_acc, float* lse_acc, const vo
 SDPA_B200_API int sdpa_b200_dropout_keep_mask(uint64_t seed, uint64_t offset, float dropout_p, int32_t batch,
                                               int32_t heads, int32_t seqlen_q, int32_t seqlen_k, int32_t is_causal,
                                               uint32_t* keep_rows, uint32_t* keep_cols, void* stream);
+
+/* The same pattern for packed (varlen) tensors: sequence b of the batch gets the bits batch index b would get
+ * in the dense form, addressed by packed token index:
+ *   keep_rows: uint32 [heads][total_q + 128][Lk_pad/32], row = packed query index, bit = key position inside
+ *              the query's sequence;   keep_cols: uint32 [heads][total_k + 128][Lq_pad/32], the transpose.
+ * Lq_pad / Lk_pad are max_seqlen_q / max_seqlen_k rounded up to 128. Both arrays must arrive zero-filled: only
+ * words an attention kernel reads are written. */
+SDPA_B200_API int sdpa_b200_dropout_keep_mask_varlen(uint64_t seed, uint64_t offset, float dropout_p, int32_t batch,
+                                                     int32_t heads, const int32_t* cu_seqlens_q,
+                                                     const int32_t* cu_seqlens_k, int32_t total_q, int32_t total_k,
+                                                     int32_t max_seqlen_q, int32_t max_seqlen_k, int32_t is_causal,
+                                                     uint32_t* keep_rows, uint32_t* keep_cols, void* stream);
 
 /* Writes sdpa_b200_params.bias_t for a bias given as in sdpa_b200_params (16-bit elements, element strides, unit
  * key stride, row_stride != 0): out is [batch][heads][seqlen_k][out_row_stride], contiguous, out_row_stride a

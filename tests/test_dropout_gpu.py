@@ -147,3 +147,56 @@ def test_manual_seed_repeats_the_pattern(cuda_device, native_lib):
     c = ops._scaled_dot_product_flash_attention(q, q, q, 0.3, True, False)
     assert int(a[7]) != int(b[7]) and not torch.equal(a[0], b[0])
     assert int(a[6]) == int(c[6]) and int(a[7]) == int(c[7]) and torch.equal(a[0], c[0])
+
+
+@pytest.mark.parametrize("lens_q,lens_k,Hq,Hkv,causal,p", [
+    ([100, 300, 257], [100, 300, 257], 4, 2, True, 0.22),
+    ([512, 64, 130], [200, 333, 130], 2, 2, False, 0.48),
+    ([1, 129, 255], [70, 129, 400], 4, 1, True, 0.1),
+])
+def test_packed_varlen_forward_and_backward_with_dropout(cuda_device, native_lib, lens_q, lens_k, Hq, Hkv, causal, p):
+    """_flash_attention_forward / _backward with dropout_p > 0 (the path the reference's dense wrapper runs on,
+    FlashAttention_internal.cpp:57-267): every sequence against fp32 math with the returned pattern, whose bits are
+    those of the dense operator for the same batch index."""
+    from torch_mlu_b200 import ops
+    dev = cuda_device
+    D = 128
+    cu_q, cu_k = [0], [0]
+    for a, b in zip(lens_q, lens_k):
+        cu_q.append(cu_q[-1] + a)
+        cu_k.append(cu_k[-1] + b)
+    q, k, v = rand((cu_q[-1], Hq, D), 1), rand((cu_k[-1], Hkv, D), 2), rand((cu_k[-1], Hkv, D), 3)
+    dout = torch.rand((cu_q[-1], Hq, D), generator=torch.Generator().manual_seed(4)).bfloat16()
+    cq, ck = (torch.tensor(c, dtype=torch.int32, device=dev) for c in (cu_q, cu_k))
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    out, lse, seed, offset, debug = ops._flash_attention_forward(qd, kd, vd, cq, ck, max(lens_q), max(lens_k), p, causal, True)
+    dq, dk, dv = ops._flash_attention_backward(dout.to(dev), qd, kd, vd, out, lse, cq, ck, max(lens_q), max(lens_k), p, causal,
+                                               seed, offset)
+    assert ops.device_status() == 0
+    B = len(lens_q)
+    assert tuple(debug.shape) == (B, Hq, max(lens_q), max(lens_k))
+    g = Hq // Hkv
+    for b in range(B):
+        lq, lk = lens_q[b], lens_k[b]
+        sq, sk = slice(cu_q[b], cu_q[b + 1]), slice(cu_k[b], cu_k[b + 1])
+        keep = (debug[b, :, :lq, :lk] > 0).cpu().unsqueeze(0)
+        visible = ~orc.causal_mask_bottom_right(lq, lk) if causal else torch.ones(lq, lk, dtype=torch.bool)
+        want_bits = orc.dropout_keep_mask(int(seed), int(offset), p, B, Hq, lq, lk)[b:b + 1]
+        assert torch.equal(keep & visible, want_bits & visible), f"sequence {b}"
+        one = lambda x, sl: x[sl].transpose(0, 1).unsqueeze(0)
+
+        def run(dtype):
+            qf, kf, vf = (one(t, s).to(dtype).detach().requires_grad_(True) for t, s in ((q, sq), (k, sk), (v, sk)))
+            scores = torch.einsum("bhtd,bhsd->bhts", qf * D ** -0.5, kf.repeat_interleave(g, dim=1))
+            if causal:
+                scores = scores.masked_fill(~visible, float("-inf"))
+            dead = torch.isinf(torch.logsumexp(scores.float(), dim=-1))
+            attn = torch.softmax(scores, dim=-1).masked_fill(dead.unsqueeze(-1), 0.0).masked_fill(~keep, 0.0) / (1 - p)
+            o = torch.einsum("bhts,bhsd->bhtd", attn, vf.repeat_interleave(g, dim=1))
+            o.backward(one(dout, sq).to(dtype))
+            return o.detach(), qf.grad, kf.grad, vf.grad
+
+        true, lowp = run(torch.float32), run(torch.bfloat16)
+        orc.assert_close_bf16(one(out, sq), true[0], f"out[{b}]")
+        for name, got, i, fudge in (("dq", one(dq, sq), 1, 4), ("dk", one(dk, sk), 2, 2), ("dv", one(dv, sk), 3, 2)):
+            orc.assert_close_reference_rule(got, true[i], lowp[i], f"{name}[{b}]", fudge=fudge)

@@ -183,3 +183,30 @@ def test_functional_sdpa_with_dropout_uses_the_cuda_generator(cuda_device, nativ
     orc.assert_close_grad_bf16(qd.grad, qf.grad, "dq")
     orc.assert_close_grad_bf16(kd.grad, kf.grad, "dk")
     orc.assert_close_grad_bf16(vd.grad, vf.grad, "dv")
+
+
+def test_packed_operator_with_dropout_and_autograd(cuda_device, native_lib):
+    """b200_sdpa::_flash_attention_forward with dropout_p > 0: the Philox pair comes back, autograd's backward
+    replays the pattern, and everything matches fp32 math with the pattern rebuilt on the CPU."""
+    torch_glue.load()
+    dev = cuda_device
+    p, H, D = 0.22, 2, 128
+    lens = [130, 257]
+    cu = [0, 130, 387]
+    q, k, v = (rand((387, H, D), s) for s in (1, 2, 3))
+    do = torch.rand((387, H, D), generator=torch.Generator().manual_seed(4)).bfloat16()
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    out, lse, seed, offset, _ = torch.ops.b200_sdpa._flash_attention_forward(qd, kd, vd, cu_t, cu_t, 257, 257, p, True, False)
+    assert seed.numel() == 1 and offset.numel() == 1
+    out.backward(do.to(dev))
+    for b, L in enumerate(lens):
+        sl = slice(cu[b], cu[b + 1])
+        one = lambda x: x[sl].transpose(0, 1).unsqueeze(0)
+        keep = orc.dropout_keep_mask(int(seed), int(offset), p, len(lens), H, L, L)[b:b + 1]
+        ref, (qf, kf, vf) = _attention_with_mask(one(q), one(k), one(v), keep, p, True)
+        ref.backward(one(do).float())
+        orc.assert_close_bf16(one(out), ref.detach(), f"out[{b}]")
+        orc.assert_close_grad_bf16(one(qd.grad), qf.grad, f"dq[{b}]")
+        orc.assert_close_grad_bf16(one(kd.grad), kf.grad, f"dk[{b}]")
+        orc.assert_close_grad_bf16(one(vd.grad), vf.grad, f"dv[{b}]")

@@ -29,6 +29,7 @@ EXPORTED_SYMBOLS = (
     "sdpa_b200_decode_static",
     "sdpa_b200_merge_partial",
     "sdpa_b200_dropout_keep_mask",
+    "sdpa_b200_dropout_keep_mask_varlen",
     "sdpa_b200_transpose_bias",
     "sdpa_b200_launch_count",
 )
@@ -106,6 +107,9 @@ def load() -> ctypes.CDLL:
     lib.sdpa_b200_dropout_keep_mask.restype = c_int
     lib.sdpa_b200_dropout_keep_mask.argtypes = [c_uint64, c_uint64, c_float, c_int32, c_int32, c_int32, c_int32, c_int32,
                                                 c_void_p, c_void_p, c_void_p]
+    lib.sdpa_b200_dropout_keep_mask_varlen.restype = c_int
+    lib.sdpa_b200_dropout_keep_mask_varlen.argtypes = [c_uint64, c_uint64, c_float, c_int32, c_int32, c_void_p, c_void_p, c_int32,
+                                                       c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p]
     lib.sdpa_b200_transpose_bias.restype = c_int
     lib.sdpa_b200_transpose_bias.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p,
                                              c_int64, c_void_p]

@@ -94,7 +94,8 @@ struct BwdKernelParams {
   // dropout_mask.cu. P is recomputed without dropout; dV takes P o M / (1 - p), dS = P o (M o dP / (1 - p) - delta).
   const uint32_t* keep_rows;  // [batch*heads_q][keep_lq_pad][keep_lk_pad / 32]: dQ kernel
   const uint32_t* keep_cols;  // [batch*heads_q][keep_lk_pad][keep_lq_pad / 32]: dK/dV kernel
-  int keep_lq_pad, keep_lk_pad;
+  int keep_lq_pad, keep_lk_pad;  // longest sequences rounded up to 128: the bits per row
+  int keep_q_rows, keep_k_rows;  // rows per leading index: the same for dense tensors, total tokens + 128 when packed
   float keep_scale;  // 1 / (1 - dropout_p)
   // additive bias (kernels built with kBias): the scores are scale * Q K^T + bias; the gradient of the bias is
   // dS itself, written by the dQ kernel (whose thread owns a query row and 64 consecutive keys of it)
@@ -553,8 +554,12 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if constexpr (kDrop) {
         const uint32_t* words =
             (kMode == kModeDQ)
-                ? p.keep_rows + (static_cast<size_t>(b * p.heads_q + hx) * p.keep_lq_pad + xr) * (p.keep_lk_pad >> 5)
-                : p.keep_cols + (static_cast<size_t>(b * p.heads_q + hx * p.kv_group + hi) * p.keep_lk_pad + xr) *
+                ? p.keep_rows + (p.cu_q != nullptr ? static_cast<size_t>(hx) * p.keep_q_rows + q_off + xr
+                                                   : static_cast<size_t>(b * p.heads_q + hx) * p.keep_q_rows + xr) *
+                                    (p.keep_lk_pad >> 5)
+                : p.keep_cols + (p.cu_q != nullptr
+                                     ? static_cast<size_t>(hx * p.kv_group + hi) * p.keep_k_rows + k_off + xr
+                                     : static_cast<size_t>(b * p.heads_q + hx * p.kv_group + hi) * p.keep_k_rows + xr) *
                                     (p.keep_lq_pad >> 5);
         keep = *reinterpret_cast<const uint2*>(words + ((y0 + half * 64) >> 5));
       }
@@ -1109,6 +1114,8 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   kp.keep_cols = drop ? p.keep_cols : nullptr;
   kp.keep_lq_pad = (p.max_seqlen_q + 127) / 128 * 128;
   kp.keep_lk_pad = (p.max_seqlen_k + 127) / 128 * 128;
+  kp.keep_q_rows = p.cu_seqlens_q != nullptr ? p.total_q + 128 : kp.keep_lq_pad;
+  kp.keep_k_rows = p.cu_seqlens_q != nullptr ? p.total_k + 128 : kp.keep_lk_pad;
   kp.keep_scale = drop ? 1.f / (1.f - p.dropout_p) : 1.f;
   kp.bias = static_cast<const uint16_t*>(p.bias);
   kp.bias_batch_stride = p.bias_batch_stride;

@@ -47,6 +47,10 @@ struct MaskParams {
   int lq_pad, lk_pad;
   uint32_t seed_lo, seed_hi, offset, drop4;
   int causal_shift;  // tiles whose first key lies past (last query of the tile + causal_shift) are zero-filled
+  // packed (varlen) form: rows are packed token indices, bits are positions inside the token's sequence
+  const int32_t* cu_q;
+  const int32_t* cu_k;
+  int heads, total_q_pad, total_k_pad, is_causal;
 };
 
 // One CTA (4 warps) per 128 x 128 tile of one head; warp w owns keys [32w, 32w + 32), lane = key.
@@ -91,6 +95,49 @@ __global__ void __launch_bounds__(128) dropout_mask_kernel(const MaskParams p) {
       make_uint4(rows[threadIdx.x][0], rows[threadIdx.x][1], rows[threadIdx.x][2], rows[threadIdx.x][3]);
 }
 
+// Packed form: one CTA per 128 x 128 tile of one (sequence, head) in the sequence's own coordinates, so that the
+// pattern of a sequence is the dense pattern of the same batch index. keep_rows [heads][total_q_pad][lk_pad/32],
+// keep_cols [heads][total_k_pad][lq_pad/32] with lq_pad / lk_pad from the longest sequences. Only words that an
+// attention kernel can read are written (the arrays arrive zero-filled): rows of real tokens, tiles the causal
+// mask does not hide completely.
+__global__ void __launch_bounds__(128) dropout_mask_varlen_kernel(const MaskParams p) {
+  __shared__ uint32_t rows[128][4];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int z = blockIdx.z, b = z / p.heads, h = z - b * p.heads;
+  const int q_off = p.cu_q[b], len_q = p.cu_q[b + 1] - q_off;
+  const int k_off = p.cu_k[b], len_k = p.cu_k[b + 1] - k_off;
+  const int q0 = blockIdx.y * 128, k0 = blockIdx.x * 128;
+  if (q0 >= len_q || k0 >= len_k) return;
+  if (p.is_causal && k0 > q0 + 127 + (len_k - len_q)) return;
+  const uint32_t k = k0 + warp * 32 + lane;
+  uint32_t col[4];
+#pragma unroll
+  for (int qb = 0; qb < 4; ++qb) {
+    const uint32_t g = (q0 + qb * 32) >> 4;
+    const uint32_t lo = keep_bits16(philox4x32_10(make_uint4(k, g, z, p.offset), make_uint2(p.seed_lo, p.seed_hi)), p.drop4);
+    const uint32_t hi = keep_bits16(philox4x32_10(make_uint4(k, g + 1, z, p.offset), make_uint2(p.seed_lo, p.seed_hi)), p.drop4);
+    col[qb] = lo | (hi << 16);
+  }
+  if (static_cast<int>(k) < len_k)
+    *reinterpret_cast<uint4*>(p.keep_cols + (static_cast<size_t>(h) * p.total_k_pad + k_off + k) * (p.lq_pad >> 5) + (q0 >> 5)) =
+        make_uint4(col[0], col[1], col[2], col[3]);
+#pragma unroll
+  for (int qb = 0; qb < 4; ++qb) {
+    uint32_t mine = 0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const uint32_t w = __ballot_sync(0xffffffffu, (col[qb] >> j) & 1u);
+      if (lane == j) mine = w;
+    }
+    rows[qb * 32 + lane][warp] = mine;
+  }
+  __syncthreads();
+  const int q = q0 + threadIdx.x;
+  if (q < len_q)
+    *reinterpret_cast<uint4*>(p.keep_rows + (static_cast<size_t>(h) * p.total_q_pad + q_off + q) * (p.lk_pad >> 5) + (k0 >> 5)) =
+        make_uint4(rows[threadIdx.x][0], rows[threadIdx.x][1], rows[threadIdx.x][2], rows[threadIdx.x][3]);
+}
+
 }  // namespace
 
 uint32_t dropout_drop_byte(float dropout_p) {
@@ -120,7 +167,7 @@ extern "C" SDPA_B200_API int sdpa_b200_dropout_keep_mask(uint64_t seed, uint64_t
     set_error("dropout_keep_mask: dropout_p must be inside (0, 1) (got %g)", static_cast<double>(dropout_p));
     return SDPA_B200_INVALID_ARG;
   }
-  MaskParams m;
+  MaskParams m = {};
   m.keep_rows = keep_rows;
   m.keep_cols = keep_cols;
   m.lq_pad = (seqlen_q + 127) / 128 * 128;
@@ -140,6 +187,56 @@ extern "C" SDPA_B200_API int sdpa_b200_dropout_keep_mask(uint64_t seed, uint64_t
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("dropout_keep_mask: launch failed: %s", cudaGetErrorString(err));
+    return SDPA_B200_LAUNCH_FAILED;
+  }
+  count_launch();
+  return SDPA_B200_OK;
+}
+
+extern "C" SDPA_B200_API int sdpa_b200_dropout_keep_mask_varlen(uint64_t seed, uint64_t offset, float dropout_p, int32_t batch,
+                                                                int32_t heads, const int32_t* cu_seqlens_q,
+                                                                const int32_t* cu_seqlens_k, int32_t total_q, int32_t total_k,
+                                                                int32_t max_seqlen_q, int32_t max_seqlen_k, int32_t is_causal,
+                                                                uint32_t* keep_rows, uint32_t* keep_cols, void* stream) {
+  if (keep_rows == nullptr || keep_cols == nullptr || cu_seqlens_q == nullptr || cu_seqlens_k == nullptr ||
+      (reinterpret_cast<uintptr_t>(keep_rows) & 15u) || (reinterpret_cast<uintptr_t>(keep_cols) & 15u)) {
+    set_error("dropout_keep_mask_varlen: NULL pointer, or keep_rows / keep_cols not 16-byte aligned");
+    return SDPA_B200_INVALID_ARG;
+  }
+  if (batch <= 0 || heads <= 0 || total_q <= 0 || total_k <= 0 || max_seqlen_q <= 0 || max_seqlen_k <= 0 ||
+      static_cast<int64_t>(batch) * heads > 65535) {
+    set_error("dropout_keep_mask_varlen: sizes must be positive and batch*heads at most 65535");
+    return SDPA_B200_INVALID_ARG;
+  }
+  if (!(dropout_p > 0.f) || !(dropout_p < 1.f)) {
+    set_error("dropout_keep_mask_varlen: dropout_p must be inside (0, 1) (got %g)", static_cast<double>(dropout_p));
+    return SDPA_B200_INVALID_ARG;
+  }
+  MaskParams m = {};
+  m.keep_rows = keep_rows;
+  m.keep_cols = keep_cols;
+  m.lq_pad = (max_seqlen_q + 127) / 128 * 128;
+  m.lk_pad = (max_seqlen_k + 127) / 128 * 128;
+  m.seed_lo = static_cast<uint32_t>(seed);
+  m.seed_hi = static_cast<uint32_t>(seed >> 32) ^ static_cast<uint32_t>(offset >> 32);
+  m.offset = static_cast<uint32_t>(offset);
+  m.drop4 = dropout_drop_byte(dropout_p) * 0x01010101u;
+  m.causal_shift = 0;
+  m.cu_q = cu_seqlens_q;
+  m.cu_k = cu_seqlens_k;
+  m.heads = heads;
+  m.total_q_pad = total_q + 128;
+  m.total_k_pad = total_k + 128;
+  m.is_causal = is_causal;
+  dim3 grid(m.lk_pad / 128, m.lq_pad / 128, batch * heads);
+  if (grid.y > 65535) {
+    set_error("dropout_keep_mask_varlen: max_seqlen_q too long (%d)", max_seqlen_q);
+    return SDPA_B200_INVALID_ARG;
+  }
+  dropout_mask_varlen_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(m);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("dropout_keep_mask_varlen: launch failed: %s", cudaGetErrorString(err));
     return SDPA_B200_LAUNCH_FAILED;
   }
   count_launch();

@@ -89,8 +89,8 @@ struct FwdKernelParams {
   int seqlen_q, seqlen_k, total_q, heads_q, kv_group;
   int head_dim;  // <= kD: the real row length, for the paths that write rows without TMA
   // dropout (kernels built with kDrop): one keep bit per (query, key) pair, see dropout_mask.cu
-  const uint32_t* keep_rows;  // [batch*heads_q][lq_pad][lk_words]
-  int lq_pad, lk_words;
+  const uint32_t* keep_rows;  // dense [batch*heads_q][lq_pad][lk_words]; packed [heads_q][total_q + 128][lk_words]
+  int lq_pad, lk_words;       // lq_pad: rows per leading index (dense: padded seqlen_q; packed: total_q + 128)
   float keep_scale;  // 1 / (1 - dropout_p), applied with the final 1 / l
   // additive bias (kernels built with kBias): softmax(scale * Q K^T + bias), bias in the tensors' 16-bit type,
   // element strides for (batch, head, query row), 0 for a broadcast dimension; the key stride is 1
@@ -564,7 +564,8 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       const uint32_t* keep_row = nullptr;  // this row's keep bits, 4 words per key block
       if constexpr (kDrop)
-        keep_row = p.keep_rows + (static_cast<size_t>(u.b * p.heads_q + u.h) * p.lq_pad + row) * p.lk_words;
+        keep_row = p.keep_rows + (p.cu_q != nullptr ? static_cast<size_t>(u.h) * p.lq_pad + u.q_off + row
+                                                    : static_cast<size_t>(u.b * p.heads_q + u.h) * p.lq_pad + row) * p.lk_words;
 
       for (int j = 0; j < my_blocks; ++j) {
         const int n0 = j * kBlockN;
@@ -843,7 +844,7 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
   kp.head_dim = p.head_dim;
   const bool drop = p.dropout_p > 0.f;
   kp.keep_rows = p.keep_rows;
-  kp.lq_pad = (p.max_seqlen_q + 127) / 128 * 128;
+  kp.lq_pad = varlen ? p.total_q + 128 : (p.max_seqlen_q + 127) / 128 * 128;
   kp.lk_words = (p.max_seqlen_k + 127) / 128 * 4;
   kp.keep_scale = drop ? 1.f / (1.f - p.dropout_p) : 1.f;
   kp.bias = static_cast<const uint16_t*>(p.bias);

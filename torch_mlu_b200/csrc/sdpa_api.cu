@@ -117,10 +117,6 @@ int validate_common(const sdpa_b200_params* p) {
       set_error("dropout_p must be 0 or inside (0, 1) (got %g)", static_cast<double>(p->dropout_p));
       return SDPA_B200_INVALID_ARG;
     }
-    if (p->cu_seqlens_q != nullptr || p->cu_seqlens_k != nullptr) {
-      set_error("dropout is built for dense tensors only (cu_seqlens given)");
-      return SDPA_B200_UNSUPPORTED;
-    }
     if (p->kernel == SDPA_B200_KERNEL_DECODE) {
       set_error("the decode kernel has no dropout");
       return SDPA_B200_UNSUPPORTED;

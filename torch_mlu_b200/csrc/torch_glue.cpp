@@ -292,14 +292,36 @@ std::tuple<Tensor, Tensor, Tensor> dense_backward_with_dropout(const Tensor& gra
 }
 
 // ------------------------------------------------------------------ packed [total,H,D]
+// packed form of the pattern: rows by packed token index, see sdpa_b200_dropout_keep_mask_varlen
+KeepMasks make_keep_masks_varlen(const Tensor& q, const Tensor& k, const Tensor& cu_q, const Tensor& cu_k, int64_t max_q,
+                                 int64_t max_k, double dropout_p, uint64_t seed, uint64_t offset, bool causal) {
+  TORCH_CHECK(dropout_p > 0.0 && dropout_p < 1.0, "dropout_p must be inside [0, 1)");
+  c10::cuda::CUDAGuard guard(q.device());
+  KeepMasks m;
+  m.p = dropout_p;
+  const int64_t H = q.size(1);
+  m.rows = at::zeros({H, q.size(0) + 128, (max_k + 127) / 128 * 4}, q.options().dtype(at::kInt));
+  m.cols = at::zeros({H, k.size(0) + 128, (max_q + 127) / 128 * 4}, q.options().dtype(at::kInt));
+  check_status(sdpa_b200_dropout_keep_mask_varlen(
+                   seed, offset, static_cast<float>(dropout_p), static_cast<int32_t>(cu_q.numel() - 1), static_cast<int32_t>(H),
+                   cu_q.data_ptr<int32_t>(), cu_k.data_ptr<int32_t>(), static_cast<int32_t>(q.size(0)),
+                   static_cast<int32_t>(k.size(0)), static_cast<int32_t>(max_q), static_cast<int32_t>(max_k), causal ? 1 : 0,
+                   reinterpret_cast<uint32_t*>(m.rows.data_ptr()), reinterpret_cast<uint32_t*>(m.cols.data_ptr()),
+                   at::cuda::getCurrentCUDAStream().stream()),
+               "sdpa_b200_dropout_keep_mask_varlen");
+  return m;
+}
+
 std::tuple<Tensor, Tensor> varlen_forward(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& cu_q,
-                                          const Tensor& cu_k, int64_t max_q, int64_t max_k, bool causal, double scale) {
+                                          const Tensor& cu_k, int64_t max_q, int64_t max_k, bool causal, double scale,
+                                          const KeepMasks* keep = nullptr) {
   check_varlen(q, k, v, cu_q, cu_k);
   c10::cuda::CUDAGuard guard(q.device());
   Tensor out = at::empty(q.sizes(), q.options());
   Tensor lse = at::empty({q.size(1), q.size(0)}, q.options().dtype(at::kFloat));  // FlashAttention_internal.cpp:129
   sdpa_b200_params p;
   varlen_params(p, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, causal, scale);
+  set_dropout(p, keep);
   run(p, false, q);
   return {out, lse};
 }
@@ -307,7 +329,7 @@ std::tuple<Tensor, Tensor> varlen_forward(const Tensor& q, const Tensor& k, cons
 std::tuple<Tensor, Tensor, Tensor> varlen_backward(const Tensor& dout_in, const Tensor& q, const Tensor& k, const Tensor& v,
                                                    const Tensor& out, const Tensor& lse, const Tensor& cu_q,
                                                    const Tensor& cu_k, int64_t max_q, int64_t max_k, bool causal,
-                                                   double scale) {
+                                                   double scale, const KeepMasks* keep = nullptr) {
   check_varlen(q, k, v, cu_q, cu_k);
   Tensor dout = dout_in.stride(-1) == 1 ? dout_in : dout_in.contiguous();
   check_input(dout, "grad_out");
@@ -329,15 +351,52 @@ std::tuple<Tensor, Tensor, Tensor> varlen_backward(const Tensor& dout_in, const 
   set_thd(p.dq_batch_stride, p.dq_head_stride, p.dq_row_stride, dq);
   set_thd(p.dk_batch_stride, p.dk_head_stride, p.dk_row_stride, dk);
   set_thd(p.dv_batch_stride, p.dv_head_stride, p.dv_row_stride, dv);
+  set_dropout(p, keep);
   run(p, true, q);
   return {dq, dk, dv};
 }
 
-void check_no_dropout(double dropout_p) {
-  TORCH_CHECK(dropout_p == 0.0, "dropout_p must be 0: dropout is built for the dense operators only");
+// The packed operator pair with dropout (the debug mask is left to the Python mirror: it needs cu_seqlens on the host).
+struct VarlenDropoutResult {
+  Tensor out, lse, seed, offset;
+};
+
+VarlenDropoutResult varlen_forward_with_dropout(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& cu_q,
+                                                const Tensor& cu_k, int64_t max_q, int64_t max_k, double dropout_p, bool causal,
+                                                double scale) {
+  TORCH_CHECK(dropout_p >= 0.0 && dropout_p < 1.0, "dropout_p must be inside [0, 1)");
+  VarlenDropoutResult r;
+  r.seed = at::empty({0}, q.options().dtype(at::kLong));
+  r.offset = at::empty({0}, q.options().dtype(at::kLong));
+  if (dropout_p == 0.0) {
+    std::tie(r.out, r.lse) = varlen_forward(q, k, v, cu_q, cu_k, max_q, max_k, causal, scale);
+    return r;
+  }
+  check_varlen(q, k, v, cu_q, cu_k);
+  auto [seed, offset] = draw_philox(q, (cu_q.numel() - 1) * q.size(1) * max_q * max_k);
+  KeepMasks keep = make_keep_masks_varlen(q, k, cu_q, cu_k, max_q, max_k, dropout_p, seed, offset, causal);
+  std::tie(r.out, r.lse) = varlen_forward(q, k, v, cu_q, cu_k, max_q, max_k, causal, scale, &keep);
+  r.seed = cpu_i64(seed);
+  r.offset = cpu_i64(offset);
+  return r;
 }
 
-Tensor empty_i64(const Tensor& like) { return at::empty({0}, like.options().dtype(at::kLong)); }
+std::tuple<Tensor, Tensor, Tensor> varlen_backward_with_dropout(const Tensor& grad_out, const Tensor& q, const Tensor& k,
+                                                                const Tensor& v, const Tensor& out, const Tensor& lse,
+                                                                const Tensor& cu_q, const Tensor& cu_k, int64_t max_q,
+                                                                int64_t max_k, double dropout_p, bool causal,
+                                                                const Tensor& philox_seed, const Tensor& philox_offset,
+                                                                double scale) {
+  TORCH_CHECK(dropout_p >= 0.0 && dropout_p < 1.0, "dropout_p must be inside [0, 1)");
+  if (dropout_p == 0.0) return varlen_backward(grad_out, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, causal, scale);
+  TORCH_CHECK(philox_seed.numel() == 1 && philox_offset.numel() == 1,
+              "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned");
+  check_varlen(q, k, v, cu_q, cu_k);
+  KeepMasks keep = make_keep_masks_varlen(q, k, cu_q, cu_k, max_q, max_k, dropout_p,
+                                          static_cast<uint64_t>(philox_seed.item<int64_t>()),
+                                          static_cast<uint64_t>(philox_offset.item<int64_t>()), causal);
+  return varlen_backward(grad_out, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, causal, scale, &keep);
+}
 
 // ------------------------------------------------ operators with the reference's schemas
 std::tuple<Tensor, Tensor, Tensor, Tensor, int64_t, int64_t, Tensor, Tensor, Tensor> ref_sdpa_flash(
@@ -369,10 +428,10 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> ref_flash_forward(const Tenso
                                                                      int64_t max_q, int64_t max_k, double dropout_p,
                                                                      bool is_causal, bool return_debug_mask,
                                                                      c10::optional<double> scale) {
-  (void)return_debug_mask;
-  check_no_dropout(dropout_p);
-  auto [out, lse] = varlen_forward(q, k, v, cum_q, cum_k, max_q, max_k, is_causal, scale_or_default(q, scale));
-  return {out, lse, empty_i64(q), empty_i64(q), at::empty({0}, q.options())};
+  TORCH_CHECK(!(return_debug_mask && dropout_p > 0.0),
+              "return_debug_mask with packed tensors is served by torch_mlu_b200.ops._flash_attention_forward");
+  auto r = varlen_forward_with_dropout(q, k, v, cum_q, cum_k, max_q, max_k, dropout_p, is_causal, scale_or_default(q, scale));
+  return {r.out, r.lse, r.seed, r.offset, at::empty({0}, q.options())};
 }
 
 std::tuple<Tensor, Tensor, Tensor> ref_flash_backward(const Tensor& grad_out, const Tensor& q, const Tensor& k,
@@ -381,9 +440,8 @@ std::tuple<Tensor, Tensor, Tensor> ref_flash_backward(const Tensor& grad_out, co
                                                       int64_t max_k, double dropout_p, bool is_causal,
                                                       const Tensor& philox_seed, const Tensor& philox_offset,
                                                       c10::optional<double> scale) {
-  (void)philox_seed; (void)philox_offset;
-  check_no_dropout(dropout_p);
-  return varlen_backward(grad_out, q, k, v, out, lse, cum_q, cum_k, max_q, max_k, is_causal, scale_or_default(q, scale));
+  return varlen_backward_with_dropout(grad_out, q, k, v, out, lse, cum_q, cum_k, max_q, max_k, dropout_p, is_causal,
+                                      philox_seed, philox_offset, scale_or_default(q, scale));
 }
 
 // ------------------------------------ CUDA-key kernels for the installed torch's aten schemas
@@ -420,24 +478,22 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> aten_flash_forward(
     c10::SymInt max_q, c10::SymInt max_k, double dropout_p, bool is_causal, bool return_debug_mask,
     c10::optional<double> scale, c10::optional<c10::SymInt> window_size_left, c10::optional<c10::SymInt> window_size_right,
     const c10::optional<Tensor>& seqused_k, const c10::optional<Tensor>& alibi_slopes) {
-  (void)return_debug_mask;
-  check_no_dropout(dropout_p);
   check_unsupported_kwargs(window_size_left, window_size_right, is_causal);
   TORCH_CHECK(!seqused_k.has_value() || !seqused_k->defined(), "seqused_k is not built in this library");
   TORCH_CHECK(!alibi_slopes.has_value() || !alibi_slopes->defined(), "alibi_slopes is not built in this library");
   const double sc = scale_or_default(q, scale);
-  Tensor out, lse;
   if (cum_q.has_value() && cum_q->defined()) {
     TORCH_CHECK(cum_k.has_value() && cum_k->defined(), "cum_seq_q and cum_seq_k must be given together");
-    std::tie(out, lse) = varlen_forward(q, k, v, *cum_q, *cum_k, max_q.expect_int(), max_k.expect_int(), is_causal, sc);
-  } else {
-    // dense form of the installed torch: [batch, seq, heads, head_dim]
-    TORCH_CHECK(q.dim() == 4, "dense _flash_attention_forward expects [batch, seq_len, heads, head_dim]");
-    auto [o, l] = dense_forward(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal, sc, /*allow_gqa=*/true);
-    out = o.transpose(1, 2);
-    lse = l;
+    TORCH_CHECK(!(return_debug_mask && dropout_p > 0.0),
+                "return_debug_mask with packed tensors is served by torch_mlu_b200.ops._flash_attention_forward");
+    auto r = varlen_forward_with_dropout(q, k, v, *cum_q, *cum_k, max_q.expect_int(), max_k.expect_int(), dropout_p, is_causal, sc);
+    return {r.out, r.lse, r.seed, r.offset, at::empty({0}, q.options())};
   }
-  return {out, lse, empty_i64(q), empty_i64(q), at::empty({0}, q.options())};
+  // dense form of the installed torch: [batch, seq, heads, head_dim]
+  TORCH_CHECK(q.dim() == 4, "dense _flash_attention_forward expects [batch, seq_len, heads, head_dim]");
+  auto r = dense_forward_with_dropout(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), dropout_p, is_causal,
+                                      return_debug_mask, sc, /*allow_gqa=*/true);
+  return {r.out.transpose(1, 2), r.lse, r.seed, r.offset, r.debug};
 }
 
 std::tuple<Tensor, Tensor, Tensor> aten_flash_backward(
@@ -445,15 +501,15 @@ std::tuple<Tensor, Tensor, Tensor> aten_flash_backward(
     const Tensor& cum_q, const Tensor& cum_k, c10::SymInt max_q, c10::SymInt max_k, double dropout_p, bool is_causal,
     const Tensor& rng_state, const Tensor& unused, c10::optional<double> scale, c10::optional<c10::SymInt> window_size_left,
     c10::optional<c10::SymInt> window_size_right) {
-  (void)rng_state; (void)unused;
-  check_no_dropout(dropout_p);
   check_unsupported_kwargs(window_size_left, window_size_right, is_causal);
   const double sc = scale_or_default(q, scale);
   if (cum_q.defined() && cum_q.numel() > 0) {
-    return varlen_backward(grad_out, q, k, v, out, lse, cum_q, cum_k, max_q.expect_int(), max_k.expect_int(), is_causal, sc);
+    return varlen_backward_with_dropout(grad_out, q, k, v, out, lse, cum_q, cum_k, max_q.expect_int(), max_k.expect_int(),
+                                        dropout_p, is_causal, rng_state, unused, sc);
   }
-  auto [dq, dk, dv] = dense_backward(grad_out.transpose(1, 2), q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
-                                     out.transpose(1, 2), lse, is_causal, sc);
+  auto [dq, dk, dv] = dense_backward_with_dropout(grad_out.transpose(1, 2), q.transpose(1, 2), k.transpose(1, 2),
+                                                  v.transpose(1, 2), out.transpose(1, 2), lse, dropout_p, is_causal, rng_state,
+                                                  unused, sc);
   return {dq.transpose(1, 2), dk.transpose(1, 2), dv.transpose(1, 2)};
 }
 

@@ -50,6 +50,43 @@ class KeepMasks:
         return bits.reshape(B * H, self.cols.size(1), -1)[:, :Lk, :Lq].transpose(1, 2).reshape(B, H, Lq, Lk).bool()
 
 
+class KeepMasksVarlen:
+    """The packed form: keep_rows [H, total_q + 128, Lk_pad/32] and keep_cols [H, total_k + 128, Lq_pad/32], rows
+    addressed by packed token index, bits by the position inside the token's sequence. Sequence b gets the bits
+    batch index b would get in the dense form."""
+
+    def __init__(self, seed: int, offset: int, dropout_p: float, heads: int, cu_q: torch.Tensor, cu_k: torch.Tensor,
+                 total_q: int, total_k: int, max_q: int, max_k: int, is_causal: bool = False):
+        if not (0.0 < dropout_p < 1.0):
+            raise ValueError(f"dropout_p must be inside (0, 1), got {dropout_p}")
+        device = cu_q.device
+        self.dropout_p = float(dropout_p)
+        self.seed, self.offset = int(seed), int(offset)
+        self.heads, self.max_q, self.max_k = heads, max_q, max_k
+        self.cu_q, self.cu_k = cu_q, cu_k
+        self.rows = torch.zeros((heads, total_q + 128, padded(max_k) // 32), dtype=torch.int32, device=device)
+        self.cols = torch.zeros((heads, total_k + 128, padded(max_q) // 32), dtype=torch.int32, device=device)
+        lib = _cabi.load()
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream(device).cuda_stream
+            _cabi.check(lib.sdpa_b200_dropout_keep_mask_varlen(
+                self.seed & (2 ** 64 - 1), self.offset & (2 ** 64 - 1), self.dropout_p, cu_q.numel() - 1, heads,
+                cu_q.data_ptr(), cu_k.data_ptr(), total_q, total_k, max_q, max_k, int(bool(is_causal)), self.rows.data_ptr(),
+                self.cols.data_ptr(), stream), "sdpa_b200_dropout_keep_mask_varlen")
+
+    def dense(self) -> torch.Tensor:
+        """bool [B, H, max_q, max_k], True = kept, False outside a sequence (reads cu_seqlens back to the host)."""
+        cu_q, cu_k = self.cu_q.tolist(), self.cu_k.tolist()
+        out = torch.zeros((len(cu_q) - 1, self.heads, self.max_q, self.max_k), dtype=torch.bool, device=self.rows.device)
+        shifts = torch.arange(32, device=self.rows.device, dtype=torch.int32)
+        for b in range(len(cu_q) - 1):
+            lq, lk = cu_q[b + 1] - cu_q[b], cu_k[b + 1] - cu_k[b]
+            words = self.rows[:, cu_q[b]:cu_q[b + 1]]
+            bits = ((words.unsqueeze(-1) >> shifts) & 1).reshape(self.heads, lq, -1)[:, :, :lk]
+            out[b, :, :lq, :lk] = bits.bool()
+        return out
+
+
 def draw_seed_and_offset(device: torch.device, elements: int) -> Tuple[int, int]:
     """(seed, offset) for one call from the device's default generator, which moves on by the number of Philox
     calls the elements stand for (what getCounterOffset does, FlashAttention_internal.cpp:46-49): the same

@@ -476,15 +476,26 @@ def _flash_attention_forward(query, key, value, cum_seq_q, cum_seq_k, max_q: int
     as [Hq, B, max_q] (:261-265), which only exists for equal-length batches; ragged batches
     keep the packed layout here.
     """
-    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
+    _check(0.0 <= dropout_p < 1.0, "dropout_p must be inside [0, 1)")
     _check_varlen(query, key, value, cum_seq_q, cum_seq_k)
     out = torch.empty_like(query, memory_format=torch.contiguous_format)
     lse = torch.empty((query.size(1), query.size(0)), dtype=torch.float32, device=query.device)
     p = _varlen_params(query, key, value, out, lse, cum_seq_q, cum_seq_k, max_q, max_k, is_causal,
                        calculate_scale(query, scale))
-    _run_fwd(p, query.device)
     seed, offset = _philox_placeholders(query)
-    return out, lse, seed, offset, _empty_like_debug(query)
+    debug = _empty_like_debug(query)
+    if dropout_p > 0.0:
+        # the Philox pair as two CPU int64 scalars; on request the pattern as [B, Hq, max_q, max_k], > 0 = kept
+        s, o = dropout.draw_seed_and_offset(query.device, (cum_seq_q.numel() - 1) * query.size(1) * int(max_q) * int(max_k))
+        keep = dropout.KeepMasksVarlen(s, o, dropout_p, query.size(1), cum_seq_q, cum_seq_k, query.size(0), key.size(0),
+                                       int(max_q), int(max_k), is_causal)
+        p.dropout_p = keep.dropout_p
+        p.keep_rows, p.keep_cols = keep.rows.data_ptr(), keep.cols.data_ptr()
+        seed, offset = torch.tensor(s, dtype=torch.int64), torch.tensor(o, dtype=torch.int64)
+        if return_debug_mask:
+            debug = keep.dense().to(query.dtype)
+    _run_fwd(p, query.device)
+    return out, lse, seed, offset, debug
 
 
 def _flash_attention_backward(grad_out, query, key, value, out, logsumexp, cum_seq_q, cum_seq_k, max_q: int,
@@ -493,7 +504,7 @@ def _flash_attention_backward(grad_out, query, key, value, out, logsumexp, cum_s
     """(dq, dk, dv) for packed varlen tensors. dk/dv have Hkv heads: the GQA group is reduced
     inside the kernel (the reference's shape check at FlashAttention_internal.cpp:363-364
     cannot pass for Hq != Hkv; here it can)."""
-    _check(dropout_p == 0.0, "dropout_p must be 0: dropout is not built in this library")
+    _check(0.0 <= dropout_p < 1.0, "dropout_p must be inside [0, 1)")
     _check_varlen(query, key, value, cum_seq_q, cum_seq_k)
     if grad_out.stride(-1) != 1:
         grad_out = grad_out.contiguous()
@@ -511,6 +522,13 @@ def _flash_attention_backward(grad_out, query, key, value, out, logsumexp, cum_s
     _set_strides_thd(p, "dq", dq)
     _set_strides_thd(p, "dk", dk)
     _set_strides_thd(p, "dv", dv)
+    if dropout_p > 0.0:
+        _check(philox_seed.numel() == 1 and philox_offset.numel() == 1,
+               "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned")
+        keep = dropout.KeepMasksVarlen(int(philox_seed), int(philox_offset), dropout_p, query.size(1), cum_seq_q, cum_seq_k,
+                                       query.size(0), key.size(0), int(max_q), int(max_k), is_causal)
+        p.dropout_p = keep.dropout_p
+        p.keep_rows, p.keep_cols = keep.rows.data_ptr(), keep.cols.data_ptr()
     _run_bwd(p, query.device)
     return dq, dk, dv
 
