@@ -12,7 +12,8 @@
 //
 // Random stream: Philox4x32-10 (Salmon et al., SC'11). One call yields 16 bytes = the keep decisions of
 // 16 consecutive queries for one key: counter = (key, query / 16, batch*heads + head, low half of the
-// offset), key = (low half of the seed, high half of the seed xor high half of the offset). Element (q, k) is kept when byte (q & 15) of the output >= round(p * 256).
+// offset), key = (low half of the seed, high half of the seed xor high half of the offset). Element (q, k) is
+// kept when byte (q & 15) of the output >= round(p * 256).
 #include "kernels.h"
 
 namespace sdpa_b200 {
