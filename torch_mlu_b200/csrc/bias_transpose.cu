@@ -16,7 +16,9 @@ struct TransposeParams {
 };
 
 __global__ void __launch_bounds__(256) bias_transpose_kernel(const TransposeParams p) {
-  __shared__ uint16_t tile[64][72];  // [key][query], rows padded against bank conflicts
+  // [key][query]; 33 words per row: the transposing 2-byte writes of a warp (rows 8 apart) fall on 4 banks instead of
+  // one, the 4-byte reads of the second phase on 32 different banks
+  __shared__ uint16_t tile[64][66];
   const int t = threadIdx.x;
   const int q0 = blockIdx.y * 64, k0 = blockIdx.x * 64;
   const int z = blockIdx.z, b = z / p.heads, h = z - b * p.heads;

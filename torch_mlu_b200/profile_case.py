@@ -3,6 +3,9 @@
     python -m torch_mlu_b200.profile_case prefill --batch 2 --heads 32 --seqlen 4096 --launches 3
     python -m torch_mlu_b200.profile_case decode  --batch 8 --seqlen-k 32768 --launches 3
     python -m torch_mlu_b200.profile_case backward --batch 2 --heads 16 --seqlen 2048 --launches 3
+    python -m torch_mlu_b200.profile_case helpers  --batch 4 --heads 16 --seqlen 2048 --launches 2
+
+``helpers`` launches the two HBM-bound side kernels: the dropout keep-mask kernel and the bias transpose.
 
 Inputs are device-generated N(0,1) bf16; sizes default to a few hundred MB so that a
 multi-pass profiler capture stays short while the working set still exceeds L2.
@@ -13,12 +16,12 @@ import argparse
 
 import torch
 
-from . import ops
+from . import dropout, ops
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["prefill", "decode", "backward"])
+    ap.add_argument("kernel", choices=["prefill", "decode", "backward", "helpers"])
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--heads-kv", type=int, default=0)
@@ -31,7 +34,12 @@ def main() -> None:
     g = torch.Generator(device=dev).manual_seed(0)
     rn = lambda *s: torch.randn(*s, generator=g, device=dev).to(torch.bfloat16)
     hkv = a.heads_kv or a.heads
-    if a.kernel == "decode":
+    if a.kernel == "helpers":
+        bias = rn(a.batch, a.heads, a.seqlen, a.seqlen)
+        for i in range(a.launches):
+            dropout.KeepMasks(1, i, 0.1, a.batch, a.heads, a.seqlen, a.seqlen, dev, not a.non_causal)
+            ops._transposed_bias(bias)
+    elif a.kernel == "decode":
         hkv = a.heads_kv or 8
         q, k, v = rn(a.batch, a.heads, 1, 128), rn(a.batch, hkv, a.seqlen_k, 128), rn(a.batch, hkv, a.seqlen_k, 128)
         for _ in range(a.launches):
