@@ -581,6 +581,18 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
             prefetch_l2(bias_row + min(n0 + 2 * kBlockN - 1, last));
           }
         }
+        // This block's bias values, packed as they come (64 registers): loaded before the wait for the scores,
+        // whose 128 registers are not live yet, so the load latency passes under the tile's MMAs. A chunk that
+        // starts past the last key is skipped; one that straddles it reads up to 7 elements of row padding,
+        // which the caller guarantees. (Shared memory has no room for a 32 KB bias tile.)
+        uint4 bw[kBias ? kBlockN / 8 : 1];
+        if constexpr (kBias) {
+#pragma unroll
+          for (int ch = 0; ch < kBlockN / 8; ++ch) {
+            bw[ch] = make_uint4(0u, 0u, 0u, 0u);
+            if (bias_row != nullptr && n0 + ch * 8 < len_k) bw[ch] = *reinterpret_cast<const uint4*>(bias_row + n0 + ch * 8);
+          }
+        }
         // warp-uniform, because the arrivals below are made by one lane on behalf of its warp
         ok = __all_sync(0xffffffffu, mbar_wait(bar_s, par, abort_flag));
         if (!ok) break;
@@ -599,23 +611,16 @@ fwd_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
           for (int i = 0; i < kBlockN; ++i) s[i] = __uint_as_float(r[i]);
         }
         if constexpr (kBias) {
-          // s <- s + bias / scale, so that everything below (maximum, s * c - m) stays as it is. Sixteen
-          // 16-byte loads per row and block, straight from global memory: shared memory has no room for a
-          // 32 KB bias tile. A chunk that starts past the last key is skipped; one that straddles it reads
-          // up to 7 elements of row padding, which the caller guarantees.
-          if (bias_row != nullptr) {
+          // s <- s + bias / scale, so that everything below (maximum, s * c - m) stays as it is (a skipped chunk
+          // holds zeros; its keys are masked further down)
 #pragma unroll
-            for (int ch = 0; ch < kBlockN / 8; ++ch) {
-              if (n0 + ch * 8 < len_k) {
-                const uint4 w = *reinterpret_cast<const uint4*>(bias_row + n0 + ch * 8);
-                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+          for (int ch = 0; ch < kBlockN / 8; ++ch) {
+            const uint32_t ww[4] = {bw[ch].x, bw[ch].y, bw[ch].z, bw[ch].w};
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const float2 b2 = unpack_16x2<kF16>(ww[i]);
-                  s[ch * 8 + 2 * i] = fmaf(b2.x, p.inv_scale, s[ch * 8 + 2 * i]);
-                  s[ch * 8 + 2 * i + 1] = fmaf(b2.y, p.inv_scale, s[ch * 8 + 2 * i + 1]);
-                }
-              }
+            for (int i = 0; i < 4; ++i) {
+              const float2 b2 = unpack_16x2<kF16>(ww[i]);
+              s[ch * 8 + 2 * i] = fmaf(b2.x, p.inv_scale, s[ch * 8 + 2 * i]);
+              s[ch * 8 + 2 * i + 1] = fmaf(b2.y, p.inv_scale, s[ch * 8 + 2 * i + 1]);
             }
           }
         }
