@@ -595,6 +595,32 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
       }
+      // This item's bias values where they are contiguous for this thread (dQ: its query row; dK/dV: its key's row
+      // of the transposed copy): eight 16-byte loads issued before the waits, so their latency passes under the
+      // score GEMM. A chunk that starts past the end is skipped (zeros); one that straddles it reads row padding.
+      uint4 bw[kBias ? 8 : 1];
+      bool bias_in_regs = false;
+      if constexpr (kBias) {
+        const int col0 = y0 + half * 64;
+        const uint16_t* vrow = nullptr;
+        int vlen = 0;
+        if (kMode == kModeDQ) {
+          vrow = p.bias + b * p.bias_batch_stride + hx * p.bias_head_stride + static_cast<int64_t>(xr) * p.bias_row_stride;
+          vlen = len_k;
+        } else if (p.bias_row_stride != 0 && p.bias_t != nullptr) {
+          vrow = p.bias_t + b * p.bias_t_batch_stride + (hx * p.kv_group + hi) * p.bias_t_head_stride +
+                 static_cast<int64_t>(xr) * p.bias_t_row_stride;
+          vlen = len_q;
+        }
+        bias_in_regs = vrow != nullptr;
+        if (bias_in_regs) {
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            bw[ch] = make_uint4(0u, 0u, 0u, 0u);
+            if (xr < len_x && col0 + ch * 8 < vlen) bw[ch] = *reinterpret_cast<const uint4*>(vrow + col0 + ch * 8);
+          }
+        }
+      }
       // `ok` is made warp-uniform after every wait: the warp-level arrivals below need all 32 lanes
       ok = mbar_wait(bar + kBarSFull + (kMode == kModeDQ ? 8 * (i & 1) : 0), (kMode == kModeDQ ? (i >> 1) : i) & 1,
                      abort_flag);
@@ -630,62 +656,35 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_wait_ld();
         BWD_STAMP(half, i, 2);
         if constexpr (kBias) {
-          // S <- S + bias / scale (then x = S c - lse2 as without bias). dQ: this thread's query row, 64
-          // consecutive keys = eight 16-byte loads; dK/dV: this thread's key in 64 consecutive query rows =
-          // 64 two-byte loads, consecutive lanes on consecutive keys.
+          // S <- S + bias / scale (then x = S c - lse2 as without bias)
           const int col0 = y0 + half * 64;
-          if (kMode == kModeDQ) {
-            if (xr < len_x) {
-              const uint16_t* brow = p.bias + b * p.bias_batch_stride + hx * p.bias_head_stride +
-                                     static_cast<int64_t>(xr) * p.bias_row_stride + col0;
+          if (bias_in_regs) {
 #pragma unroll
-              for (int ch = 0; ch < 8; ++ch) {
-                if (col0 + ch * 8 < len_k) {
-                  const uint4 w = *reinterpret_cast<const uint4*>(brow + ch * 8);
-                  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+            for (int ch = 0; ch < 8; ++ch) {
+              const uint32_t ww[4] = {bw[ch].x, bw[ch].y, bw[ch].z, bw[ch].w};
 #pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    const float2 b2 = unpack_16x2<kF16>(ww[e]);
-                    a[ch * 8 + 2 * e] = __float_as_uint(fmaf(b2.x, p.inv_scale, __uint_as_float(a[ch * 8 + 2 * e])));
-                    a[ch * 8 + 2 * e + 1] = __float_as_uint(fmaf(b2.y, p.inv_scale, __uint_as_float(a[ch * 8 + 2 * e + 1])));
-                  }
-                }
+              for (int e = 0; e < 4; ++e) {
+                const float2 b2 = unpack_16x2<kF16>(ww[e]);
+                a[ch * 8 + 2 * e] = __float_as_uint(fmaf(b2.x, p.inv_scale, __uint_as_float(a[ch * 8 + 2 * e])));
+                a[ch * 8 + 2 * e + 1] = __float_as_uint(fmaf(b2.y, p.inv_scale, __uint_as_float(a[ch * 8 + 2 * e + 1])));
               }
             }
-          } else {
-            if (xr < len_x) {
-              const int hq = hx * p.kv_group + hi;
-              const uint16_t* bcol = p.bias + b * p.bias_batch_stride + hq * p.bias_head_stride + xr;
-              if (p.bias_row_stride == 0) {
-                // the bias does not depend on the query (ALiBi-like): one value for this thread's key
-                const float bs = unpack_16x2<kF16>(static_cast<uint32_t>(bcol[0])).x * p.inv_scale;
+          } else if (kMode == kModeDKDV && xr < len_x) {
+            const uint16_t* bcol = p.bias + b * p.bias_batch_stride + (hx * p.kv_group + hi) * p.bias_head_stride + xr;
+            if (p.bias_row_stride == 0) {
+              // the bias does not depend on the query (ALiBi-like): one value for this thread's key
+              const float bs = unpack_16x2<kF16>(static_cast<uint32_t>(bcol[0])).x * p.inv_scale;
 #pragma unroll
-                for (int j = 0; j < 64; ++j) a[j] = __float_as_uint(__uint_as_float(a[j]) + bs);
-              } else if (p.bias_t != nullptr) {
-                // the caller's transposed copy: this key's 64 consecutive queries, eight 16-byte loads
-                const uint16_t* trow = p.bias_t + b * p.bias_t_batch_stride + hq * p.bias_t_head_stride +
-                                       static_cast<int64_t>(xr) * p.bias_t_row_stride + col0;
+              for (int j = 0; j < 64; ++j) a[j] = __float_as_uint(__uint_as_float(a[j]) + bs);
+            } else {
+              // no transposed copy: this key in 64 consecutive query rows, 64 two-byte loads (consecutive lanes on
+              // consecutive keys)
 #pragma unroll
-                for (int ch = 0; ch < 8; ++ch) {
-                  if (col0 + ch * 8 < len_q) {
-                    const uint4 w = *reinterpret_cast<const uint4*>(trow + ch * 8);
-                    const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                      const float2 b2 = unpack_16x2<kF16>(ww[e]);
-                      a[ch * 8 + 2 * e] = __float_as_uint(fmaf(b2.x, p.inv_scale, __uint_as_float(a[ch * 8 + 2 * e])));
-                      a[ch * 8 + 2 * e + 1] = __float_as_uint(fmaf(b2.y, p.inv_scale, __uint_as_float(a[ch * 8 + 2 * e + 1])));
-                    }
-                  }
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 64; ++j) {
-                  if (col0 + j < len_q) {
-                    const uint32_t raw = bcol[static_cast<int64_t>(col0 + j) * p.bias_row_stride];
-                    const float bv = unpack_16x2<kF16>(raw).x;
-                    a[j] = __float_as_uint(fmaf(bv, p.inv_scale, __uint_as_float(a[j])));
-                  }
+              for (int j = 0; j < 64; ++j) {
+                if (col0 + j < len_q) {
+                  const uint32_t raw = bcol[static_cast<int64_t>(col0 + j) * p.bias_row_stride];
+                  const float bv = unpack_16x2<kF16>(raw).x;
+                  a[j] = __float_as_uint(fmaf(bv, p.inv_scale, __uint_as_float(a[j])));
                 }
               }
             }
