@@ -210,6 +210,18 @@ def secondary_measurements(dev, steps):
         except Exception as e:  # backward kernel absent or failing: say so, do not hide it
             entry["bwd_error"] = str(e)[:200]
         out["fwd_bwd"] = entry
+        # the same step with dropout through the operator pair: each call also makes its keep-masks
+        try:
+            fo = lambda: ops._scaled_dot_product_flash_attention(q, k, v, 0.1, True, False)
+            r = fo()
+            bo = lambda: ops._scaled_dot_product_flash_attention_backward(do, q, k, v, r[0], r[1], r[2], r[3], r[4], r[5], 0.1,
+                                                                         True, r[6], r[7])
+            ms_fd, ms_bd = timed_loop(fo, n, 3, sync) / n, timed_loop(bo, n, 3, sync) / n
+            out["fwd_bwd_dropout"] = {"workload": "the same with dropout_p=0.1 (mask kernel included in both)", "fwd_ms": ms_fd,
+                                      "bwd_ms": ms_bd, "fwd_bwd_tflops": 3.5 * fwd_flops / (ms_fd + ms_bd) / 1e9}
+            del r
+        except Exception as e:
+            out["fwd_bwd_dropout"] = {"error": str(e)[:200]}
         del q, k, v, do, o, lse
     except Exception as e:
         out["fwd_bwd"] = {"error": str(e)[:200]}
