@@ -13,6 +13,11 @@
  *                            <- cnnlGetFlashAttention{Forward,Backward}WorkspaceSize_v2
  *                               .../internal/FlashAttention_internal.cpp:215-230, 437-447
  *   sdpa_b200_status_string  <- TORCH_CNNL_CHECK's status-to-text, torch_mlu/csrc/aten/utils/exceptions.h:77-83
+ *   sdpa_b200_dropout_keep_mask[_varlen]
+ *                            <- the Philox state the reference hands to its kernel (cnnlRandGenerator / seed, offset,
+ *                               .../internal/FlashAttention_internal.cpp:190-214): here the pattern itself, as bits
+ *   bias / dbias fields      <- the attn_bias and grad_bias descriptors of mem_eff_fwd / mem_eff_bwd
+ *                               (.../internal/FlashAttention_internal.cpp:485-904)
  *
  * Conventions
  *   - Plain C: pointers, sizes, one POD struct. No C++ or torch types cross this boundary.

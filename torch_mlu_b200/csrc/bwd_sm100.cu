@@ -5,7 +5,9 @@
 // given dO, Q, K, V, O and the saved logsumexp, recompute P = exp(scale*QK^T - lse) and
 //   dV = P^T dO,  dP = dO V^T,  dS = P o (dP - delta),  dQ = scale dS K,  dK = scale dS^T Q
 // with delta = rowsum(dO o O). GQA: dK/dV of one KV head sum over its query heads inside one
-// CTA, so nothing is accumulated with atomics and results are bit-reproducible.
+// CTA, so nothing is accumulated with atomics and results are bit-reproducible. With dropout (kDrop
+// instances) dV takes P o M / (1 - p) and dS = P o (M o dP / (1 - p) - delta); with an additive bias (kBias
+// instances) the scores are scale*QK^T + bias and the dQ kernel also writes dS as the bias gradient.
 //
 // Three launches:
 //   1. bwd_preprocess_kernel: delta and the log2-domain logsumexp into a padded

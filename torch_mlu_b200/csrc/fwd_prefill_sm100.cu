@@ -5,7 +5,10 @@
 //   O = softmax(scale * Q K^T + causal mask) V,  LSE = logsumexp(scale * Q K^T)
 // for bf16 or f16 Q/K/V with head_dim <= 128 (a multiple of 8), dense or packed-varlen, GQA by head
 // broadcast. The kernel is built for 64 and 128 columns; other head dims run in the next larger one:
-// TMA loads fill the missing columns with zeros and TMA stores clip them.
+// TMA loads fill the missing columns with zeros and TMA stores clip them. Two optional extras are separate
+// template instances, so that the plain kernel pays nothing for them: dropout (kDrop: keep bits per (query,
+// key) pair from dropout_mask.cu) and the additive bias of the memory-efficient operators (kBias:
+// softmax(scale * Q K^T + bias), mem_eff_fwd, FlashAttention_internal.cpp:485-690).
 //
 // A work unit is 256 query rows of one (batch, head): two 128-row Q tiles. One persistent CTA per SM
 // walks the unit list; its barriers, TMEM and K/V ring live across units, so the next unit's loads
