@@ -42,6 +42,21 @@ __device__ __forceinline__ uint32_t keep_bits16(uint4 r, uint32_t drop4) {
   return bits;
 }
 
+// Transposes a 32 x 32 bit block held one word per lane: afterwards bit c of lane r is what bit r of lane c was.
+// Five butterfly stages (block sizes 16 ... 1): each lane keeps the half of its word that stays and takes the other
+// half from the lane `j` away.
+__device__ __forceinline__ uint32_t transpose_bits_32x32(uint32_t x, int lane) {
+  constexpr uint32_t kMask[5] = {0x0000ffffu, 0x00ff00ffu, 0x0f0f0f0fu, 0x33333333u, 0x55555555u};
+#pragma unroll
+  for (int s = 0; s < 5; ++s) {
+    const int j = 16 >> s;
+    const uint32_t m = kMask[s];
+    const uint32_t y = __shfl_xor_sync(0xffffffffu, x, j);
+    x = (lane & j) ? (((y >> j) & m) | (x & ~m)) : ((x & m) | ((y << j) & ~m));
+  }
+  return x;
+}
+
 struct MaskParams {
   uint32_t* keep_rows;
   uint32_t* keep_cols;
@@ -76,19 +91,11 @@ __global__ void __launch_bounds__(128) dropout_mask_kernel(const MaskParams p) {
   // key-major words: four consecutive words (128 queries) per key
   *reinterpret_cast<uint4*>(p.keep_cols + (static_cast<size_t>(bh) * p.lk_pad + k) * (p.lq_pad >> 5) + (q0 >> 5)) =
       make_uint4(col[0], col[1], col[2], col[3]);
-  // query-major words: transpose 32 x 32 bit blocks with ballots, gather the four key blocks of the
+  // query-major words: transpose the 32 x 32 bit blocks across the warp, gather the four key blocks of the
   // tile in shared memory, then one 16-byte store per query row
 #pragma unroll
   for (int qb = 0; qb < 4; ++qb) {
-    uint32_t mine = 0;
-    if (!hidden) {  // uniform for the CTA
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const uint32_t w = __ballot_sync(0xffffffffu, (col[qb] >> j) & 1u);
-        if (lane == j) mine = w;
-      }
-    }
-    rows[qb * 32 + lane][warp] = mine;
+    rows[qb * 32 + lane][warp] = hidden ? 0u : transpose_bits_32x32(col[qb], lane);  // `hidden` is uniform for the CTA
   }
   __syncthreads();
   const int q = q0 + threadIdx.x;
@@ -124,13 +131,7 @@ __global__ void __launch_bounds__(128) dropout_mask_varlen_kernel(const MaskPara
         make_uint4(col[0], col[1], col[2], col[3]);
 #pragma unroll
   for (int qb = 0; qb < 4; ++qb) {
-    uint32_t mine = 0;
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const uint32_t w = __ballot_sync(0xffffffffu, (col[qb] >> j) & 1u);
-      if (lane == j) mine = w;
-    }
-    rows[qb * 32 + lane][warp] = mine;
+    rows[qb * 32 + lane][warp] = transpose_bits_32x32(col[qb], lane);
   }
   __syncthreads();
   const int q = q0 + threadIdx.x;
