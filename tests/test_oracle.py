@@ -122,3 +122,30 @@ def test_reference_tolerance_rule_floors_and_fudge():
     orc.assert_close_reference_rule(torch.tensor([1.0, 2.0, 5.0]), true, lowp, "x", fudge=4)
     with pytest.raises(AssertionError):
         orc.assert_close_reference_rule(torch.tensor([1.0, 2.0, 9.0]), true, lowp, "x")
+
+
+def test_philox4x32_10_known_answers():
+    """The dropout pattern's generator against the published known-answer vectors of Philox4x32-10 (the three
+    philox4x32 10-round lines of the Random123 distribution's kat_vectors: zero, all-ones and pi-digit inputs)."""
+    import numpy as np
+    cases = [
+        ((0, 0, 0, 0), (0, 0), (0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8)),
+        ((0xFFFFFFFF,) * 4, (0xFFFFFFFF, 0xFFFFFFFF), (0x408F276D, 0x41C83B0E, 0xA20BC7C6, 0x6D5451FD)),
+        ((0x243F6A88, 0x85A308D3, 0x13198A2E, 0x03707344), (0xA4093822, 0x299F31D0),
+         (0xD16CFE09, 0x94FDCCEB, 0x5001E420, 0x24126EA1)),
+    ]
+    for counter, key, want in cases:
+        got = orc.philox4x32_10(np.array([counter], dtype=np.uint32), key)[0]
+        assert tuple(int(x) for x in got) == want
+
+
+def test_dropout_keep_mask_rule():
+    """Keep rate, dependence on seed / offset / head, and the byte rule: with p = 0.5 an element is kept exactly
+    when its byte is >= 128."""
+    a = orc.dropout_keep_mask(7, 0, 0.25, 2, 3, 200, 300)
+    assert a.shape == (2, 3, 200, 300) and abs(float(a.float().mean()) - 0.75) < 5e-3
+    assert not torch.equal(a, orc.dropout_keep_mask(7, 1, 0.25, 2, 3, 200, 300))
+    assert not torch.equal(a, orc.dropout_keep_mask(8, 0, 0.25, 2, 3, 200, 300))
+    assert not torch.equal(a[0, 0], a[0, 1]) and not torch.equal(a[0, 0], a[1, 0])
+    # a longer sequence extends the pattern, it does not change it
+    assert torch.equal(a[..., :100, :150], orc.dropout_keep_mask(7, 0, 0.25, 2, 3, 100, 150))
