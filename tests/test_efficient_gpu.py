@@ -139,8 +139,45 @@ def test_efficient_attention_with_dropout(cuda_device, native_lib):
     orc.assert_close_grad_bf16(dq, qf.grad, "dq")
     orc.assert_close_grad_bf16(dk, kf.grad, "dk")
     orc.assert_close_grad_bf16(dv, vf.grad, "dv")
-    with pytest.raises(RuntimeError, match="Lq != Lk is not built"):
-        ops._scaled_dot_product_efficient_attention(qd, kd[:, :, :100], vd[:, :, :100], None, True, p, True)
+
+
+@pytest.mark.parametrize("Lq,Lk", [(200, 456), (456, 200)])
+def test_efficient_attention_with_dropout_and_unequal_lengths(cuda_device, native_lib, Lq, Lk):
+    """Top-left causal mask with Lq != Lk and dropout: the operator is made of one or two kernel calls, each with
+    its own pattern from the one Philox pair (the second call, rows past Lk, on the stream with bit 62 of the
+    offset set)."""
+    dev = cuda_device
+    B, H, D, p = 1, 2, 128, 0.22
+    q, k, v = rand((B, H, Lq, D), 1), rand((B, H, Lk, D), 2), rand((B, H, Lk, D), 3)
+    do = torch.rand((B, H, Lq, D), generator=torch.Generator().manual_seed(4)).bfloat16()
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    out, lse, seed, off = ops._scaled_dot_product_efficient_attention(qd, kd, vd, None, True, p, True)
+    dq, dk, dv, _ = ops._scaled_dot_product_efficient_attention_backward(do.to(dev), qd, kd, vd, None, out, lse, seed, off, p,
+                                                                        [True, True, True, False], True)
+    assert ops.device_status() == 0
+    s0, o0 = int(seed), int(off)
+    keep = torch.zeros(B, H, Lq, Lk, dtype=torch.bool)
+    if Lq < Lk:
+        keep[..., :Lq] = orc.dropout_keep_mask(s0, o0, p, B, H, Lq, Lq)       # keys past Lq are hidden anyway
+    else:
+        keep[:, :, :Lk] = orc.dropout_keep_mask(s0, o0, p, B, H, Lk, Lk)
+        keep[:, :, Lk:] = orc.dropout_keep_mask(s0, o0 ^ (1 << 62), p, B, H, Lq - Lk, Lk)
+
+    def run(dtype):
+        qf, kf, vf = (t.to(dtype).requires_grad_(True) for t in (q, k, v))
+        scores = torch.einsum("bhqd,bhkd->bhqk", qf, kf) / D ** 0.5
+        scores = scores.masked_fill(torch.ones(Lq, Lk, dtype=torch.bool).triu(1), float("-inf"))
+        attn = torch.softmax(scores, dim=-1).masked_fill(~keep, 0.0) / (1 - p)
+        ref = torch.einsum("bhqk,bhkd->bhqd", attn, vf)
+        ref.backward(do.to(dtype))
+        return ref.detach(), qf.grad, kf.grad, vf.grad
+
+    # gradients by the reference suite's own rule (test_...py:1077-1110): dV sums hundreds of queries per key here
+    true, lowp = run(torch.float32), run(torch.bfloat16)
+    orc.assert_close_bf16(out, true[0], "out")
+    orc.assert_close_reference_rule(dq, true[1], lowp[1], "dq", fudge=4)
+    orc.assert_close_reference_rule(dk, true[2], lowp[2], "dk")
+    orc.assert_close_reference_rule(dv, true[3], lowp[3], "dv")
 
 
 def _bias_reference(q, k, v, bias, do, causal_top_left, dtype=torch.float32):

@@ -339,8 +339,8 @@ def _scaled_dot_product_efficient_attention(query, key, value, attn_bias, comput
     instead of the flash operator's bottom-right alignment. With Lq == Lk the two coincide; otherwise
     the top-left mask is rebuilt from what the kernels offer: keys past Lq are invisible to every row
     (Lq < Lk), and rows past Lk see every key (Lq > Lk).
-    ``log_sumexp`` is [B,H,Lq] fp32, or empty when ``compute_log_sumexp`` is false. Dropout (Philox pair
-    returned as two CPU int64 scalars) is taken where one kernel call does the work: no causal mask, or Lq == Lk.
+    ``log_sumexp`` is [B,H,Lq] fp32, or empty when ``compute_log_sumexp`` is false. With dropout the Philox pair
+    comes back as two CPU int64 scalars.
     """
     _check(0.0 <= dropout_p < 1.0, "dropout_p must be inside [0, 1)")
     _check(query.dim() == 4 and key.dim() == 4, "query, key and value must be 4-dimensional [batch, heads, seq_len, head_dim]")
@@ -348,28 +348,35 @@ def _scaled_dot_product_efficient_attention(query, key, value, attn_bias, comput
     Lq, Lk = query.size(2), key.size(2)
     bias = None if attn_bias is None else _prepare_bias(attn_bias, query, key)
     sl = (lambda t, *idx: None if t is None else t[idx])  # slices of an optional tensor
+    seed, offset = _philox_placeholders(query)
+    keep_for = lambda lq, lk, causal, part: None
     if dropout_p > 0.0:
-        _check(not is_causal or Lq == Lk, "dropout with a top-left causal mask and Lq != Lk is not built in this library")
-        s, o = dropout.draw_seed_and_offset(query.device, query.size(0) * query.size(1) * Lq * Lk)
-        keep = dropout.KeepMasks(s, o, dropout_p, query.size(0), query.size(1), Lq, Lk, query.device, is_causal)
-        out, lse = _dense_forward(query, key, value, is_causal, sc, allow_gqa=False, keep=keep, bias=bias)
-        if not compute_log_sumexp:
-            lse = lse.new_empty((query.size(0), query.size(1), 0))
-        return out, lse, torch.tensor(s, dtype=torch.int64), torch.tensor(o, dtype=torch.int64)
+        s0, o0 = dropout.draw_seed_and_offset(query.device, query.size(0) * query.size(1) * Lq * Lk)
+        seed, offset = torch.tensor(s0, dtype=torch.int64), torch.tensor(o0, dtype=torch.int64)
+        keep_for = _keep_factory(s0, o0, dropout_p, query)
     if not is_causal or Lq == Lk:
-        out, lse = _dense_forward(query, key, value, is_causal, sc, allow_gqa=False, bias=bias)
+        out, lse = _dense_forward(query, key, value, is_causal, sc, allow_gqa=False, bias=bias, keep=keep_for(Lq, Lk, is_causal, 0))
     elif Lq < Lk:
         out, lse = _dense_forward(query, key[:, :, :Lq], value[:, :, :Lq], True, sc, allow_gqa=False,
-                                  bias=sl(bias, Ellipsis, slice(0, Lq)))
+                                  bias=sl(bias, Ellipsis, slice(0, Lq)), keep=keep_for(Lq, Lq, True, 0))
     else:
-        o1, l1 = _dense_forward(query[:, :, :Lk], key, value, True, sc, allow_gqa=False, bias=sl(bias, slice(None), slice(None), slice(0, Lk)))
-        o2, l2 = _dense_forward(query[:, :, Lk:], key, value, False, sc, allow_gqa=False, bias=sl(bias, slice(None), slice(None), slice(Lk, None)))
+        o1, l1 = _dense_forward(query[:, :, :Lk], key, value, True, sc, allow_gqa=False,
+                                bias=sl(bias, slice(None), slice(None), slice(0, Lk)), keep=keep_for(Lk, Lk, True, 0))
+        o2, l2 = _dense_forward(query[:, :, Lk:], key, value, False, sc, allow_gqa=False,
+                                bias=sl(bias, slice(None), slice(None), slice(Lk, None)), keep=keep_for(Lq - Lk, Lk, False, 1))
         out = torch.cat([o1.transpose(1, 2), o2.transpose(1, 2)], dim=1).transpose(1, 2)
         lse = torch.cat([l1, l2], dim=2)
     if not compute_log_sumexp:
         lse = lse.new_empty((query.size(0), query.size(1), 0))
-    seed, offset = _philox_placeholders(query)
     return out, lse, seed, offset
+
+
+def _keep_factory(seed: int, offset: int, dropout_p: float, query):
+    """Keep-masks for the kernel calls one memory-efficient operator call is made of: the same Philox pair, the
+    second call (rows past Lk of a top-left causal mask) on a stream of its own (bit 62 of the offset)."""
+    B, H = query.size(0), query.size(1)
+    return lambda lq, lk, causal, part: dropout.KeepMasks(seed, offset ^ (part << 62), dropout_p, B, H, lq, lk, query.device,
+                                                          causal)
 
 
 def _scaled_dot_product_efficient_attention_backward(grad_out, query, key, value, attn_bias, out, logsumexp,
@@ -397,20 +404,18 @@ def _scaled_dot_product_efficient_attention_backward(grad_out, query, key, value
             return dq, dk, dv, query.new_empty((0,))
         return dq, dk, dv, dbias.sum_to_size(attn_bias.shape)
 
+    keep_for = lambda lq, lk, causal, part: None
     if dropout_p > 0.0:
-        _check(not is_causal or Lq == Lk, "dropout with a top-left causal mask and Lq != Lk is not built in this library")
         _check(philox_seed.numel() == 1 and philox_offset.numel() == 1,
                "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned")
-        keep = dropout.KeepMasks(int(philox_seed), int(philox_offset), dropout_p, query.size(0), query.size(1), Lq, Lk,
-                                 query.device, is_causal)
-        return finish(*_dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, sc, keep=keep, bias=bias,
-                                       dbias=dbias))
+        keep_for = _keep_factory(int(philox_seed), int(philox_offset), dropout_p, query)
     if not is_causal or Lq == Lk:
-        dq, dk, dv = _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, sc, bias=bias, dbias=dbias)
+        dq, dk, dv = _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, sc, bias=bias, dbias=dbias,
+                                     keep=keep_for(Lq, Lk, is_causal, 0))
     elif Lq < Lk:
         cut = (Ellipsis, slice(0, Lq))
         dq, dk_a, dv_a = _dense_backward(grad_out, query, key[:, :, :Lq], value[:, :, :Lq], out, logsumexp, True, sc,
-                                         bias=sl(bias, *cut), dbias=sl(dbias, *cut))
+                                         bias=sl(bias, *cut), dbias=sl(dbias, *cut), keep=keep_for(Lq, Lq, True, 0))
         dk, dv = torch.zeros_like(key), torch.zeros_like(value)
         dk[:, :, :Lq] = dk_a
         dv[:, :, :Lq] = dv_a
@@ -418,9 +423,9 @@ def _scaled_dot_product_efficient_attention_backward(grad_out, query, key, value
         top, rest = (slice(None), slice(None), slice(0, Lk)), (slice(None), slice(None), slice(Lk, None))
         l1, l2 = logsumexp[:, :, :Lk].contiguous(), logsumexp[:, :, Lk:].contiguous()
         dq1, dk1, dv1 = _dense_backward(grad_out[:, :, :Lk], query[:, :, :Lk], key, value, out[:, :, :Lk], l1, True, sc,
-                                        bias=sl(bias, *top), dbias=sl(dbias, *top))
+                                        bias=sl(bias, *top), dbias=sl(dbias, *top), keep=keep_for(Lk, Lk, True, 0))
         dq2, dk2, dv2 = _dense_backward(grad_out[:, :, Lk:], query[:, :, Lk:], key, value, out[:, :, Lk:], l2, False, sc,
-                                        bias=sl(bias, *rest), dbias=sl(dbias, *rest))
+                                        bias=sl(bias, *rest), dbias=sl(dbias, *rest), keep=keep_for(Lq - Lk, Lk, False, 1))
         dq = torch.cat([dq1.transpose(1, 2), dq2.transpose(1, 2)], dim=1).transpose(1, 2)
         dk = (dk1.float() + dk2.float()).to(key.dtype)
         dv = (dv1.float() + dv2.float()).to(value.dtype)
