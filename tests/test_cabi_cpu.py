@@ -139,3 +139,22 @@ def test_host_mirror_rejects_what_the_reference_rejects():
         ops._flash_attention_forward(p, p, p, cu, cu, 16, 16, 0.0, False, False)
     assert ops.calculate_scale(q, None) == pytest.approx(128 ** -0.5)
     assert ops.calculate_scale(q, 0.5) == 0.5
+
+
+def test_helper_entry_points_check_their_arguments_before_touching_a_device(native_lib):
+    """sdpa_b200_dropout_keep_mask[_varlen] and sdpa_b200_transpose_bias refuse bad arguments with INVALID_ARG
+    and a message; none of these checks needs a GPU."""
+    lib = native_lib
+    err = lambda: lib.sdpa_b200_last_error().decode()
+    assert lib.sdpa_b200_dropout_keep_mask(1, 0, 0.1, 1, 1, 128, 128, 0, None, None, None) == _cabi.INVALID_ARG
+    assert "16-byte aligned" in err()
+    assert lib.sdpa_b200_dropout_keep_mask(1, 0, 0.1, 1, 1, 128, 128, 0, 4096, 8192 + 8, None) == _cabi.INVALID_ARG
+    assert lib.sdpa_b200_dropout_keep_mask(1, 0, 1.5, 1, 1, 128, 128, 0, 4096, 8192, None) == _cabi.INVALID_ARG
+    assert "inside (0, 1)" in err()
+    assert lib.sdpa_b200_dropout_keep_mask(1, 0, 0.1, 70000, 1, 128, 128, 0, 4096, 8192, None) == _cabi.INVALID_ARG
+    assert "65535" in err()
+    assert lib.sdpa_b200_dropout_keep_mask_varlen(1, 0, 0.1, 2, 1, None, None, 10, 10, 8, 8, 0, 4096, 8192, None) == _cabi.INVALID_ARG
+    assert lib.sdpa_b200_transpose_bias(4096, 0, 0, 0, 1, 1, 64, 64, 8192, 64, None) == _cabi.INVALID_ARG
+    assert "non-zero row stride" in err()
+    assert lib.sdpa_b200_transpose_bias(4096, 0, 0, 64, 1, 1, 64, 64, 8192, 60, None) == _cabi.INVALID_ARG
+    assert "out_row_stride" in err()
