@@ -45,11 +45,14 @@ def causal_mask_bottom_right(seqlen_q: int, seqlen_k: int) -> torch.Tensor:
 
 
 def attention_math(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = False,
-                   scale: Optional[float] = None, dtype: torch.dtype = torch.float32
+                   scale: Optional[float] = None, dtype: torch.dtype = torch.float32,
+                   keep: Optional[torch.Tensor] = None, dropout_p: float = 0.0
                    ) -> Tuple[torch.Tensor, torch.Tensor]:
     """q [B,Hq,Lq,D], k/v [B,Hkv,Lk,D] -> (out [B,Hq,Lq,D], lse [B,Hq,Lq]) in ``dtype``.
 
-    Fully masked rows give out = 0 (attention_ref, :143-147) and lse = +inf.
+    Fully masked rows give out = 0 (attention_ref, :143-147) and lse = +inf. ``keep`` (bool [B,Hq,Lq,Lk],
+    True = kept) with ``dropout_p`` applies dropout after the softmax: dropped probabilities become 0 and the
+    rest is scaled by 1 / (1 - dropout_p) (attention_ref, :153-158); the logsumexp is not affected.
     """
     q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
     g = q.shape[1] // k.shape[1]
@@ -67,18 +70,20 @@ def attention_math(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal:
     if dead.any():
         attn = attn.masked_fill(dead.unsqueeze(-1), 0.0)
         lse = lse.masked_fill(dead, float("inf"))
+    if keep is not None:
+        attn = attn.masked_fill(~keep, 0.0) / (1.0 - dropout_p)
     out = torch.einsum("bhts,bhsd->bhtd", attn, v)
     return out, lse
 
 
-def attention_math_backward(q, k, v, dout, *, causal=False, scale=None, dtype=torch.float32):
+def attention_math_backward(q, k, v, dout, *, causal=False, scale=None, dtype=torch.float32, keep=None, dropout_p=0.0):
     """Gradients of ``attention_math`` by autograd (what the reference tests do with
     out.backward, test_scaled_dot_product_attention.py:1018-1075). dk/dv come back with Hkv
     heads (the group is summed)."""
     q = q.to(dtype).detach().requires_grad_(True)
     k = k.to(dtype).detach().requires_grad_(True)
     v = v.to(dtype).detach().requires_grad_(True)
-    out, _ = attention_math(q, k, v, causal=causal, scale=scale, dtype=dtype)
+    out, _ = attention_math(q, k, v, causal=causal, scale=scale, dtype=dtype, keep=keep, dropout_p=dropout_p)
     out.backward(dout.to(dtype))
     return q.grad, k.grad, v.grad
 

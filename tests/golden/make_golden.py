@@ -39,6 +39,16 @@ CASES = [
 ]
 
 
+# Dropout: the reference's device kernel draws the pattern itself, so its tests feed the pattern the operator
+# returns back into attention_ref (:1048-1068). Here the pattern comes from this repository's own rule
+# (oracle.sdpa_oracle.dropout_keep_mask, a fixed seed / offset pair) and attention_ref is executed with it.
+# name, B, Hq, Hkv, Lq, Lk, D, causal, dropout_p, seed, offset
+DROPOUT_CASES = [
+    ("causal_square_p22", 1, 2, 2, 128, 128, 128, True, 0.22, 20240607, 12),
+    ("noncausal_gqa_p48", 2, 4, 2, 96, 160, 64, False, 0.48, 99, (3 << 32) + 5),
+]
+
+
 def load_reference_functions(ref_root: str):
     path = os.path.join(ref_root, REL)
     tree = ast.parse(open(path).read(), filename=path)
@@ -90,6 +100,29 @@ def main() -> None:
             lse_derived=lse.numpy(), causal=np.array(causal), scale=np.array(-1.0 if scale is None else scale),
         )
         print(name, "out", tuple(out.shape), "finite", bool(torch.isfinite(out).all()))
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from oracle.sdpa_oracle import dropout_keep_mask
+    for idx, (name, B, Hq, Hkv, Lq, Lk, D, causal, p, seed, offset) in enumerate(DROPOUT_CASES):
+        g = torch.Generator().manual_seed(4321 + idx)
+        q = torch.randn(B, Hq, Lq, D, generator=g).bfloat16()
+        k = torch.randn(B, Hkv, Lk, D, generator=g).bfloat16()
+        v = torch.randn(B, Hkv, Lk, D, generator=g).bfloat16()
+        dout = torch.randn(B, Hq, Lq, D, generator=g).bfloat16()
+        keep = dropout_keep_mask(seed, offset, p, B, Hq, Lq, Lk)
+        qf = q.float().transpose(1, 2).detach().requires_grad_(True)
+        kf = k.float().transpose(1, 2).detach().requires_grad_(True)
+        vf = v.float().transpose(1, 2).detach().requires_grad_(True)
+        out, _ = attention_ref(qf, kf, vf, dropout_p=p, dropout_mask=keep, causal=causal, upcast=True)
+        out.backward(dout.float())
+        np.savez_compressed(
+            os.path.join(HERE, f"dropout_ref_{name}.npz"),
+            q=bf16_bits(q), k=bf16_bits(k), v=bf16_bits(v), dout=bf16_bits(dout), keep=np.packbits(keep.numpy()),
+            keep_shape=np.array(keep.shape), out=out.detach().numpy().astype(np.float32),
+            dq=qf.grad.transpose(1, 2).contiguous().numpy(), dk=kf.grad.transpose(1, 2).contiguous().numpy(),
+            dv=vf.grad.transpose(1, 2).contiguous().numpy(), causal=np.array(causal), dropout_p=np.array(p),
+            seed=np.array(seed, dtype=np.int64), offset=np.array(offset, dtype=np.int64),
+        )
+        print("dropout", name, "kept", float(keep.float().mean()), "finite", bool(torch.isfinite(out).all()))
 
 
 if __name__ == "__main__":

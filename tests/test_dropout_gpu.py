@@ -200,3 +200,26 @@ def test_packed_varlen_forward_and_backward_with_dropout(cuda_device, native_lib
         orc.assert_close_bf16(one(out, sq), true[0], f"out[{b}]")
         for name, got, i, fudge in (("dq", one(dq, sq), 1, 4), ("dk", one(dk, sk), 2, 2), ("dv", one(dv, sk), 3, 2)):
             orc.assert_close_reference_rule(got, true[i], lowp[i], f"{name}[{b}]", fudge=fudge)
+
+
+from test_oracle import DROPOUT_GOLDEN, load_dropout_golden  # noqa: E402
+
+
+@pytest.mark.parametrize("path", DROPOUT_GOLDEN, ids=lambda p: p.split("dropout_ref_")[-1][:-4])
+def test_kernels_with_dropout_match_reference_golden(cuda_device, native_lib, path):
+    """Forward and backward with the golden file's Philox pair against what the reference's attention_ref gave
+    for the same pattern (GQA included: the kernels reduce dK/dV over the group)."""
+    from torch_mlu_b200 import ops
+    dev = cuda_device
+    g = load_dropout_golden(path)
+    B, H, Lq, Lk = g["keep"].shape
+    q, k, v, do = (g[n].to(dev) for n in ("q", "k", "v", "dout"))
+    keep = dropout.KeepMasks(g["seed"], g["offset"], g["p"], B, H, Lq, Lk, dev, g["causal"])
+    sc = ops.calculate_scale(q, None)
+    out, lse = ops._dense_forward(q, k, v, g["causal"], sc, allow_gqa=True, kernel=1, keep=keep)
+    dq, dk, dv = ops._dense_backward(do, q, k, v, out, lse, g["causal"], sc, keep=keep)
+    assert ops.device_status() == 0
+    orc.assert_close_bf16(out, g["out"], "out")
+    orc.assert_close_grad_bf16(dq, g["dq"], "dq")
+    orc.assert_close_grad_bf16(dk, g["dk"], "dk")
+    orc.assert_close_grad_bf16(dv, g["dv"], "dv")

@@ -149,3 +149,31 @@ def test_dropout_keep_mask_rule():
     assert not torch.equal(a[0, 0], a[0, 1]) and not torch.equal(a[0, 0], a[1, 0])
     # a longer sequence extends the pattern, it does not change it
     assert torch.equal(a[..., :100, :150], orc.dropout_keep_mask(7, 0, 0.25, 2, 3, 100, 150))
+
+
+DROPOUT_GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "dropout_ref_*.npz")))
+
+
+def load_dropout_golden(path):
+    z = np.load(path)
+    bits = lambda a: torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)
+    shape = tuple(int(x) for x in z["keep_shape"])
+    keep = torch.from_numpy(np.unpackbits(z["keep"])[:int(np.prod(shape))].astype(bool)).reshape(shape)
+    return dict(q=bits(z["q"]), k=bits(z["k"]), v=bits(z["v"]), dout=bits(z["dout"]), keep=keep,
+                out=torch.from_numpy(z["out"]), dq=torch.from_numpy(z["dq"]), dk=torch.from_numpy(z["dk"]),
+                dv=torch.from_numpy(z["dv"]), causal=bool(z["causal"]), p=float(z["dropout_p"]), seed=int(z["seed"]),
+                offset=int(z["offset"]))
+
+
+@pytest.mark.parametrize("path", DROPOUT_GOLDEN, ids=[os.path.basename(p)[12:-4] for p in DROPOUT_GOLDEN])
+def test_oracle_with_dropout_matches_reference_golden(path):
+    """attention_math with a keep-mask against the reference's attention_ref executed with the same mask
+    (tests/golden/make_golden.py); the stored mask is what the pattern rule gives for the stored seed / offset."""
+    g = load_dropout_golden(path)
+    B, H, Lq, Lk = g["keep"].shape
+    assert torch.equal(g["keep"], orc.dropout_keep_mask(g["seed"], g["offset"], g["p"], B, H, Lq, Lk))
+    kw = dict(causal=g["causal"], keep=g["keep"], dropout_p=g["p"])
+    out, _ = orc.attention_math(g["q"], g["k"], g["v"], **kw)
+    assert orc.error_stats(out, g["out"])[0] < 2e-5
+    for name, got in zip(("dq", "dk", "dv"), orc.attention_math_backward(g["q"], g["k"], g["v"], g["dout"], **kw)):
+        assert orc.error_stats(got, g[name])[0] < 1e-4, name
