@@ -181,6 +181,9 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* smem = smem_raw + (base - raw_addr);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // The dQ kernel follows in the stream and depends on nothing written here: once every dK/dV CTA has begun (this
+  // signal), its CTAs may take over SMs as they free up, instead of waiting for the last dK/dV CTA to finish.
+  if (kMode == kModeDKDV && threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   constexpr int kStages = stages_for(kMode);
   constexpr uint32_t kSmemVec = smem_vec_off(kMode);
   constexpr uint32_t kSmemBar = smem_bar_off(kMode);
@@ -987,9 +990,14 @@ TileKernel pick_tile_kernel(bool drop, bool bias, int head_dim, bool f16) {
   return bias ? pick_tile_kernel<kMode, false, true>(head_dim, f16) : pick_tile_kernel<kMode, false, false>(head_dim, f16);
 }
 
+// `overlap_previous`: launch with programmatic stream serialization, so that this grid's CTAs may start as soon as
+// every CTA of the kernel before it in the stream has begun (see the launch_dependents signal at the top of the
+// dK/dV kernel) and an SM has room. Used for the dQ kernel, which needs nothing the dK/dV kernel writes: its CTAs
+// fill the SMs the last, partly empty wave of dK/dV CTAs leaves idle.
 int launch_tile_kernel(int mode, int head_dim, bool f16, int grid, cudaStream_t stream, const CUtensorMap& tm_q,
                        const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_do,
-                       const CUtensorMap& tm_o1, const CUtensorMap& tm_o2, const BwdKernelParams& kp) {
+                       const CUtensorMap& tm_o1, const CUtensorMap& tm_o2, const BwdKernelParams& kp,
+                       bool overlap_previous = false) {
   const bool drop = kp.keep_rows != nullptr;
   const bool bias = kp.bias != nullptr;
   TileKernel kernel = mode == kModeDKDV ? pick_tile_kernel<kModeDKDV>(drop, bias, head_dim, f16)
@@ -1000,8 +1008,18 @@ int launch_tile_kernel(int mode, int head_dim, bool f16, int grid, cudaStream_t 
     set_error("backward: cudaFuncSetAttribute(%u bytes smem): %s", smem, cudaGetErrorString(err));
     return SDPA_B200_LAUNCH_FAILED;
   }
-  kernel<<<dim3(grid), kThreads, smem, stream>>>(tm_q, tm_k, tm_v, tm_do, tm_o1, tm_o2, kp);
-  err = cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap_previous ? 1 : 0;
+  err = cudaLaunchKernelEx(&cfg, kernel, tm_q, tm_k, tm_v, tm_do, tm_o1, tm_o2, kp);
+  if (err == cudaSuccess) err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("backward %s: launch failed: %s", mode == kModeDKDV ? "dK/dV" : "dQ", cudaGetErrorString(err));
     return SDPA_B200_LAUNCH_FAILED;
@@ -1159,7 +1177,8 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
     return st;
   kp.num_row_blocks = (p.max_seqlen_q + kTile - 1) / kTile;
   const int grid_dq = set_order(p.heads_q, p.max_seqlen_k, 1);
-  return launch_tile_kernel(kModeDQ, p.head_dim, f16, grid_dq, stream, tm_q, tm_k, tm_v, tm_do, tm_dq, tm_dq, kp);
+  return launch_tile_kernel(kModeDQ, p.head_dim, f16, grid_dq, stream, tm_q, tm_k, tm_v, tm_do, tm_dq, tm_dq, kp,
+                            /*overlap_previous=*/true);
 }
 
 }  // namespace sdpa_b200
