@@ -107,6 +107,53 @@ def test_decode_workspace_grows_with_splits(native_lib):
     assert n1 == 256 and n16 >= 256 + 2 * 8 * 16 * 129 * 4
 
 
+def test_decode_static_refuses_what_it_has_no_kernel_for_before_touching_a_device(native_lib):
+    """sdpa_b200_decode_static launches the 64- and 128-column split-KV kernels only: any other head dim, dropout,
+    a bias, packed tensors, more than one query row and partials beyond the built-in array are turned away by
+    status code. All of these answers come before the device check, so they are the same with and without a GPU."""
+    lib = native_lib
+
+    def decode_params():
+        p = _valid_params()
+        p.max_seqlen_q, p.max_seqlen_k, p.kernel = 1, 4096, _cabi.KERNEL_DECODE
+        return p
+
+    def expect(mutate, status, needle):
+        p = decode_params()
+        mutate(p)
+        st = lib.sdpa_b200_decode_static(ctypes.byref(p), None)
+        assert st == status, (st, lib.sdpa_b200_last_error())
+        assert needle in lib.sdpa_b200_last_error().decode(), lib.sdpa_b200_last_error()
+
+    expect(lambda p: setattr(p, "head_dim", 96), _cabi.UNSUPPORTED, "head_dim 64 and 128 only")
+    expect(lambda p: setattr(p, "head_dim", 32), _cabi.UNSUPPORTED, "head_dim 64 and 128 only")
+    expect(lambda p: setattr(p, "bias", 4096), _cabi.UNSUPPORTED, "bias")
+
+    def dropout_auto(p):
+        p.kernel, p.dropout_p, p.keep_rows = _cabi.KERNEL_AUTO, 0.1, 4096
+    expect(dropout_auto, _cabi.UNSUPPORTED, "no dropout")
+    expect(lambda p: setattr(p, "dropout_p", 0.1), _cabi.UNSUPPORTED, "no dropout")
+
+    def bias_auto(p):
+        p.kernel, p.bias = _cabi.KERNEL_AUTO, 4096
+    expect(bias_auto, _cabi.UNSUPPORTED, "bias")
+    expect(lambda p: setattr(p, "kernel", _cabi.KERNEL_PREFILL), _cabi.UNSUPPORTED, "decode kernel only")
+    expect(lambda p: setattr(p, "max_seqlen_q", 4), _cabi.UNSUPPORTED, "seqlen_q == 1")
+
+    def packed(p):
+        p.cu_seqlens_q = p.cu_seqlens_k = 4096
+        p.total_q, p.total_k = 2, 8192
+    expect(packed, _cabi.UNSUPPORTED, "dense tensors only")
+
+    def too_large(p):
+        p.batch, p.heads_q, p.num_splits = 64, 32, 64
+    expect(too_large, _cabi.INVALID_ARG, "more than the")
+    # the ordinary forward entry point gives the same answer for the head dim
+    p = decode_params()
+    p.head_dim = 96
+    assert lib.sdpa_b200_fwd(ctypes.byref(p), 4096, 1 << 24, None) == _cabi.UNSUPPORTED
+
+
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU answer")
 def test_compute_calls_refuse_without_a_gpu(native_lib):
     """No CPU fallback: with valid arguments but no device the call reports NO_DEVICE."""

@@ -29,7 +29,7 @@ def decode_params(q, k, v, out, lse, num_splits):
 def run_static(lib, q, k, v, num_splits):
     """The new entry point: caller-owned out/lse, no workspace argument at all."""
     B, Hq = q.shape[0], q.shape[1]
-    out = torch.full((B, Hq, 1, 128), float("nan"), dtype=torch.bfloat16, device=q.device)
+    out = torch.full((B, Hq, 1, q.shape[-1]), float("nan"), dtype=torch.bfloat16, device=q.device)
     lse = torch.full((B, Hq, 1), float("nan"), dtype=torch.float32, device=q.device)
     p = decode_params(q, k, v, out, lse, num_splits)
     st = lib.sdpa_b200_decode_static(ctypes.byref(p), torch.cuda.current_stream().cuda_stream)
@@ -41,11 +41,13 @@ def test_static_scratch_decode_matches_workspace_decode_twice(cuda_device, nativ
     dev = cuda_device
     lib = native_lib
     # two different problems back to back: the second starts from the first one's leftovers
-    cases = [((4, 32, 8, 6000), 8, 1), ((2, 8, 2, 1500), 5, 2), ((4, 32, 8, 6000), 8, 3)]
-    for (B, Hq, Hkv, Lk), splits, seed in cases:
-        q = rand((B, Hq, 1, 128), seed).to(dev)
-        k = rand((B, Hkv, Lk, 128), seed + 10).to(dev)
-        v = rand((B, Hkv, Lk, 128), seed + 20).to(dev)
+    # (the head_dim 64 case runs the other kernel instance, whose partial slots are half as wide)
+    cases = [((4, 32, 8, 6000), 128, 8, 1), ((2, 8, 2, 1500), 128, 5, 2), ((3, 16, 4, 3000), 64, 6, 4),
+             ((4, 32, 8, 6000), 128, 8, 3)]
+    for (B, Hq, Hkv, Lk), D, splits, seed in cases:
+        q = rand((B, Hq, 1, D), seed).to(dev)
+        k = rand((B, Hkv, Lk, D), seed + 10).to(dev)
+        v = rand((B, Hkv, Lk, D), seed + 20).to(dev)
         before = torch.cuda.memory_allocated(dev)
         out_s, lse_s = run_static(lib, q, k, v, splits)
         # only the two output tensors this test created were allocated around the call
@@ -78,3 +80,10 @@ def test_static_scratch_decode_refuses_oversized_requests(cuda_device, native_li
     q4 = rand((1, 8, 4, 128), 2).to(dev)
     p = decode_params(q4, k[:1], k[:1], out, lse, 1)
     assert lib.sdpa_b200_decode_static(ctypes.byref(p), None) == _cabi.UNSUPPORTED
+    # a head dim the streaming kernels are not built for is refused, not run in the 128-column instance
+    q96, k96 = rand((2, 8, 1, 96), 3).to(dev), rand((2, 2, 512, 96), 4).to(dev)
+    out96 = torch.full((2, 8, 1, 96), float("nan"), dtype=torch.bfloat16, device=dev)
+    p = decode_params(q96, k96, k96, out96, lse, 2)
+    assert lib.sdpa_b200_decode_static(ctypes.byref(p), None) == _cabi.UNSUPPORTED
+    torch.cuda.synchronize()
+    assert torch.isnan(out96).all()

@@ -408,28 +408,19 @@ size_t decode_workspace_bytes(const sdpa_b200_params& p, int* num_splits_out) {
   return rows * sizeof(float) * (p.head_dim + 1) + 256;
 }
 
-int launch_fwd_decode(const sdpa_b200_params& p, void* workspace, size_t workspace_bytes,
-                      cudaStream_t stream) {
-  if (p.max_seqlen_q != 1) {
-    set_error("decode kernel needs seqlen_q == 1 (got %d)", p.max_seqlen_q);
-    return SDPA_B200_UNSUPPORTED;
-  }
-  int splits = 1;
-  const size_t need = decode_workspace_bytes(p, &splits);
-  if (workspace_bytes < kWorkspaceHeaderBytes + need) {
-    set_error("decode workspace too small: %zu < %zu", workspace_bytes, kWorkspaceHeaderBytes + need);
-    return SDPA_B200_INVALID_ARG;
-  }
+namespace {
+
+// Kernel arguments for one decode call; the split partials go to part_o / part_lse
+// (rows = batch * heads_q * splits slots of head_dim and of one float).
+DecodeParams fill_decode_params(const sdpa_b200_params& p, int splits, float* part_o, float* part_lse) {
   DecodeParams d;
   d.q = static_cast<const uint16_t*>(p.q);
   d.k = static_cast<const uint16_t*>(p.k);
   d.v = static_cast<const uint16_t*>(p.v);
   d.out = static_cast<uint16_t*>(p.out);
   d.lse = p.lse;
-  const size_t rows = static_cast<size_t>(p.batch) * p.heads_q * splits;
-  float* ws = reinterpret_cast<float*>(static_cast<char*>(workspace) + kWorkspaceHeaderBytes);
-  d.part_o = ws;
-  d.part_lse = ws + rows * p.head_dim;
+  d.part_o = part_o;
+  d.part_lse = part_lse;
   d.q_batch_stride = p.q_batch_stride;
   d.q_head_stride = p.q_head_stride;
   d.k_batch_stride = p.k_batch_stride;
@@ -451,26 +442,73 @@ int launch_fwd_decode(const sdpa_b200_params& p, void* workspace, size_t workspa
   d.keys_per_split = ((kps + 63) / 64) * 64;  // whole 4-warp steps
   d.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   d.f16 = p.dtype == SDPA_B200_F16;
+  return d;
+}
 
-  dim3 grid(splits, p.heads_kv * d.chunks, p.batch);
+// The split kernel and, with more than one split, the merge kernel.
+int launch_decode_pair(const DecodeParams& d, int batch, const char* who, cudaStream_t stream) {
+  dim3 grid(d.num_splits, d.heads_kv * d.chunks, batch);
   launch_decode_kernel(d, grid, stream);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {
-    set_error("decode: launch failed: %s", cudaGetErrorString(err));
+    set_error("%s: launch failed: %s", who, cudaGetErrorString(err));
     return SDPA_B200_LAUNCH_FAILED;
   }
   count_launch();
-  if (splits > 1) {
-    const int nrows = p.batch * p.heads_q;
+  if (d.num_splits > 1) {
+    const int nrows = batch * d.heads_q;
     decode_combine_kernel<<<(nrows + 3) / 4, 128, 0, stream>>>(d, nrows);
     err = cudaGetLastError();
     if (err != cudaSuccess) {
-      set_error("decode combine: launch failed: %s", cudaGetErrorString(err));
+      set_error("%s merge: launch failed: %s", who, cudaGetErrorString(err));
       return SDPA_B200_LAUNCH_FAILED;
     }
     count_launch();
   }
   return SDPA_B200_OK;
+}
+
+}  // namespace
+
+// What the streaming kernels cannot do; shared by every entry point that launches them.
+int check_decode_request(const sdpa_b200_params& p) {
+  if (p.cu_seqlens_q != nullptr || p.cu_seqlens_k != nullptr) {
+    set_error("the decode kernel takes dense tensors only");
+    return SDPA_B200_UNSUPPORTED;
+  }
+  if (p.max_seqlen_q != 1) {
+    set_error("decode kernel needs seqlen_q == 1 (got %d)", p.max_seqlen_q);
+    return SDPA_B200_UNSUPPORTED;
+  }
+  if (p.head_dim != 64 && p.head_dim != 128) {
+    set_error("the decode kernel is built for head_dim 64 and 128 only (got %d)", p.head_dim);
+    return SDPA_B200_UNSUPPORTED;
+  }
+  if (p.dropout_p != 0.f || p.keep_rows != nullptr || p.keep_cols != nullptr) {
+    set_error("the decode kernel has no dropout");
+    return SDPA_B200_UNSUPPORTED;
+  }
+  if (p.bias != nullptr) {
+    set_error("the decode kernel takes no additive bias");
+    return SDPA_B200_UNSUPPORTED;
+  }
+  return SDPA_B200_OK;
+}
+
+int launch_fwd_decode(const sdpa_b200_params& p, void* workspace, size_t workspace_bytes,
+                      cudaStream_t stream) {
+  int st = check_decode_request(p);
+  if (st != SDPA_B200_OK) return st;
+  int splits = 1;
+  const size_t need = decode_workspace_bytes(p, &splits);
+  if (workspace_bytes < kWorkspaceHeaderBytes + need) {
+    set_error("decode workspace too small: %zu < %zu", workspace_bytes, kWorkspaceHeaderBytes + need);
+    return SDPA_B200_INVALID_ARG;
+  }
+  const size_t rows = static_cast<size_t>(p.batch) * p.heads_q * splits;
+  float* ws = reinterpret_cast<float*>(static_cast<char*>(workspace) + kWorkspaceHeaderBytes);
+  const DecodeParams d = fill_decode_params(p, splits, ws, ws + rows * p.head_dim);
+  return launch_decode_pair(d, p.batch, "decode", stream);
 }
 
 }  // namespace sdpa_b200
@@ -533,12 +571,15 @@ int static_scratch_address(void** out) {
 
 extern "C" SDPA_B200_API int sdpa_b200_decode_static(const sdpa_b200_params* p, void* stream) {
   using namespace sdpa_b200;
-  int st = validate_forward_call(p);
+  // argument checks first, the device last: a refused request never needs a GPU
+  int st = validate_forward_args(p);
   if (st != SDPA_B200_OK) return st;
-  if (p->cu_seqlens_q != nullptr || p->max_seqlen_q != 1) {
-    set_error("decode_static takes dense tensors with seqlen_q == 1 (got %d)", p->max_seqlen_q);
+  if (p->kernel == SDPA_B200_KERNEL_PREFILL) {
+    set_error("decode_static runs the split-KV decode kernel only (kernel must be AUTO or DECODE)");
     return SDPA_B200_UNSUPPORTED;
   }
+  st = check_decode_request(*p);
+  if (st != SDPA_B200_OK) return st;
   const int splits = choose_splits(*p);
   const size_t rows = static_cast<size_t>(p->batch) * p->heads_q * splits;
   const size_t need = rows * sizeof(float) * (p->head_dim + 1);
@@ -548,59 +589,12 @@ extern "C" SDPA_B200_API int sdpa_b200_decode_static(const sdpa_b200_params* p, 
               p->batch, p->heads_q, splits, need, static_cast<unsigned>(SDPA_B200_STATIC_SCRATCH_BYTES));
     return SDPA_B200_INVALID_ARG;
   }
+  st = check_device();
+  if (st != SDPA_B200_OK) return st;
   void* scratch = nullptr;
   st = static_scratch_address(&scratch);
   if (st != SDPA_B200_OK) return st;
-
-  DecodeParams d;
-  d.q = static_cast<const uint16_t*>(p->q);
-  d.k = static_cast<const uint16_t*>(p->k);
-  d.v = static_cast<const uint16_t*>(p->v);
-  d.out = static_cast<uint16_t*>(p->out);
-  d.lse = p->lse;
-  d.part_o = static_cast<float*>(scratch);
-  d.part_lse = d.part_o + rows * p->head_dim;
-  d.q_batch_stride = p->q_batch_stride;
-  d.q_head_stride = p->q_head_stride;
-  d.k_batch_stride = p->k_batch_stride;
-  d.k_head_stride = p->k_head_stride;
-  d.k_row_stride = p->k_row_stride;
-  d.v_batch_stride = p->v_batch_stride;
-  d.v_head_stride = p->v_head_stride;
-  d.v_row_stride = p->v_row_stride;
-  d.o_batch_stride = p->o_batch_stride;
-  d.o_head_stride = p->o_head_stride;
-  d.heads_q = p->heads_q;
-  d.heads_kv = p->heads_kv;
-  d.group = p->heads_q / p->heads_kv;
-  d.chunks = (d.group + 15) / 16;
-  d.len_k = p->max_seqlen_k;
-  d.num_splits = splits;
-  d.head_dim = p->head_dim;
-  const int kps = (p->max_seqlen_k + splits - 1) / splits;
-  d.keys_per_split = ((kps + 63) / 64) * 64;
-  d.scale_log2 = p->softmax_scale * 1.4426950408889634f;
-  d.f16 = p->dtype == SDPA_B200_F16;
-
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  dim3 grid(splits, p->heads_kv * d.chunks, p->batch);
-  launch_decode_kernel(d, grid, s);
-  cudaError_t err = cudaGetLastError();
-  if (err != cudaSuccess) {
-    set_error("decode_static: launch failed: %s", cudaGetErrorString(err));
-    return SDPA_B200_LAUNCH_FAILED;
-  }
-  count_launch();
-  if (splits > 1) {
-    const int nrows = p->batch * p->heads_q;
-    decode_combine_kernel<<<(nrows + 3) / 4, 128, 0, s>>>(d, nrows);
-    err = cudaGetLastError();
-    if (err != cudaSuccess) {
-      set_error("decode_static merge: launch failed: %s", cudaGetErrorString(err));
-      return SDPA_B200_LAUNCH_FAILED;
-    }
-    count_launch();
-  }
-  return SDPA_B200_OK;
+  float* part_o = static_cast<float*>(scratch);
+  const DecodeParams d = fill_decode_params(*p, splits, part_o, part_o + rows * p->head_dim);
+  return launch_decode_pair(d, p->batch, "decode_static", static_cast<cudaStream_t>(stream));
 }
-

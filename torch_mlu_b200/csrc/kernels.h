@@ -34,9 +34,14 @@ size_t decode_workspace_bytes(const sdpa_b200_params& p, int* num_splits_out);
 int launch_fwd_decode(const sdpa_b200_params& p, void* workspace, size_t workspace_bytes,
                       cudaStream_t stream);
 
-// Argument and device checks of the forward entry point, for entry points defined outside
-// sdpa_api.cu. Returns an SDPA_B200_* status and sets the error text.
-int validate_forward_call(const sdpa_b200_params* p);
+// Argument checks of the forward entry point (no device is touched) and the device check, for entry
+// points defined outside sdpa_api.cu. Each returns an SDPA_B200_* status and sets the error text.
+int validate_forward_args(const sdpa_b200_params* p);
+int check_device();
+
+// Refuses what the split-KV decode kernels have no code for (packed tensors, seqlen_q != 1, head dims other
+// than 64 and 128, dropout, bias). Touches no device.
+int check_decode_request(const sdpa_b200_params& p);
 
 // round(dropout_p * 256), the byte threshold of the dropout keep-masks (dropout_mask.cu)
 uint32_t dropout_drop_byte(float dropout_p);

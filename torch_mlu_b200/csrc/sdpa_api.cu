@@ -214,24 +214,6 @@ int validate_workspace(void* workspace, size_t have, size_t need) {
   return SDPA_B200_OK;
 }
 
-int check_device() {
-  static int cached_dev = -1;
-  static int cached_status = SDPA_B200_NO_DEVICE;
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess) {
-    (void)cudaGetLastError();
-    set_error("no CUDA device is available; this library has no CPU path");
-    return SDPA_B200_NO_DEVICE;
-  }
-  if (dev == cached_dev) return cached_status;
-  int major = 0;
-  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-  cached_dev = dev;
-  cached_status = (major == 10) ? SDPA_B200_OK : SDPA_B200_NO_DEVICE;
-  if (cached_status != SDPA_B200_OK) set_error("device %d has compute capability %d.x; sm_100 is required", dev, major);
-  return cached_status;
-}
-
 // Decode is chosen when there are too few query rows to fill a 128-row MMA tile.
 bool use_decode(const sdpa_b200_params* p) {
   if (p->kernel == SDPA_B200_KERNEL_DECODE) return true;
@@ -257,10 +239,36 @@ int sm_count() {
   return cached[dev];
 }
 
-int validate_forward_call(const sdpa_b200_params* p) {
-  int st = validate_common(p);
-  if (st != SDPA_B200_OK) return st;
-  return check_device();
+int validate_forward_args(const sdpa_b200_params* p) { return validate_common(p); }
+
+// The compute capability is looked up once per device; the table is shared by all host threads.
+int check_device() {
+  static std::mutex mu;
+  static int8_t major_of[64] = {0};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    (void)cudaGetLastError();
+    set_error("no CUDA device is available; this library has no CPU path");
+    return SDPA_B200_NO_DEVICE;
+  }
+  int major = 0;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (major_of[dev] == 0) {
+      int m = 0;
+      if (cudaDeviceGetAttribute(&m, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        m = -1;
+      }
+      major_of[dev] = static_cast<int8_t>(m);
+    }
+    major = major_of[dev];
+  }
+  if (major != 10) {
+    set_error("device %d has compute capability %d.x; sm_100 is required", dev, major);
+    return SDPA_B200_NO_DEVICE;
+  }
+  return SDPA_B200_OK;
 }
 
 }  // namespace sdpa_b200
@@ -314,6 +322,7 @@ int sdpa_b200_bwd_workspace_bytes(const sdpa_b200_params* p, size_t* bytes) {
 int sdpa_b200_fwd(const sdpa_b200_params* p, void* workspace, size_t workspace_bytes, void* stream) {
   int st = validate_common(p);
   if (st != SDPA_B200_OK) return st;
+  if (use_decode(p) && (st = check_decode_request(*p)) != SDPA_B200_OK) return st;
   size_t need = 0;
   st = sdpa_b200_fwd_workspace_bytes(p, &need);
   if (st != SDPA_B200_OK) return st;
@@ -326,17 +335,7 @@ int sdpa_b200_fwd(const sdpa_b200_params* p, void* workspace, size_t workspace_b
     set_error("clearing the workspace header failed: %s", cudaGetErrorString(cudaGetLastError()));
     return SDPA_B200_LAUNCH_FAILED;
   }
-  if (use_decode(p)) {
-    if (p->cu_seqlens_q != nullptr) {
-      set_error("the decode kernel takes dense tensors only");
-      return SDPA_B200_UNSUPPORTED;
-    }
-    if (p->head_dim != 64 && p->head_dim != 128) {
-      set_error("the decode kernel is built for head_dim 64 and 128 only (got %d)", p->head_dim);
-      return SDPA_B200_UNSUPPORTED;
-    }
-    return launch_fwd_decode(*p, workspace, workspace_bytes, s);
-  }
+  if (use_decode(p)) return launch_fwd_decode(*p, workspace, workspace_bytes, s);
   return launch_fwd_prefill(*p, workspace, s);
 }
 
