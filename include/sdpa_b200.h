@@ -56,7 +56,7 @@
 extern "C" {
 #endif
 
-#define SDPA_B200_VERSION 107
+#define SDPA_B200_VERSION 108
 
 #if defined(__GNUC__)
 #define SDPA_B200_API __attribute__((visibility("default")))
@@ -68,7 +68,7 @@ extern "C" {
 enum {
   SDPA_B200_OK = 0,
   SDPA_B200_INVALID_ARG = 1,    /* null pointer, bad shape, bad stride/alignment, workspace too small */
-  SDPA_B200_UNSUPPORTED = 2,    /* valid request this build has no kernel for (dtype, head_dim > 128, varlen bias) */
+  SDPA_B200_UNSUPPORTED = 2,    /* valid request this build has no kernel for (dtype, head_dim > 128, decode with bias) */
   SDPA_B200_LAUNCH_FAILED = 3,  /* CUDA reported an error while configuring or launching */
   SDPA_B200_DEVICE_TIMEOUT = 4, /* a bounded wait inside a kernel ran out (read back from workspace) */
   SDPA_B200_NO_DEVICE = 5       /* not an sm_100 device / no CUDA driver */
@@ -134,10 +134,12 @@ typedef struct sdpa_b200_params {
   const uint32_t* keep_rows;
   const uint32_t* keep_cols;
   /* Additive attention bias of the memory-efficient operators (mem_eff_fwd / mem_eff_bwd,
-   * FlashAttention_internal.cpp:485-904): out = softmax(scale * q k^T + bias) v. NULL = none. Dense tensors
-   * only; same 16-bit type as q; element strides for (batch, head, query row), 0 for a broadcast dimension;
-   * the key stride is 1. Rows start 16-byte aligned (row stride a multiple of 8, or 0) and are readable up to
-   * the next multiple of 8 keys. */
+   * FlashAttention_internal.cpp:485-904): out = softmax(scale * q k^T + bias) v. NULL = none. Same 16-bit
+   * type as q; element strides for (batch, head, query row), 0 for a broadcast dimension; the key stride is 1.
+   * Rows start 16-byte aligned (row stride a multiple of 8, or 0) and are readable up to the next multiple of
+   * 8 keys. With packed (varlen) q / k / v the bias stays a [batch, heads_q, max_seqlen_q, max_seqlen_k] tensor:
+   * sequence b reads bias[b, h, i, j] for its query i and key j counted from the start of the sequence. The
+   * same holds for dbias and bias_t. */
   const void* bias;
   int64_t bias_batch_stride, bias_head_stride, bias_row_stride;
   /* Backward: gradient of the bias, [batch, heads_q, seqlen_q, dbias_row_stride >= seqlen_k rounded up to 8],
@@ -150,6 +152,18 @@ typedef struct sdpa_b200_params {
    * bias does not depend on the query (bias_row_stride == 0). NULL = not given. */
   const void* bias_t;
   int64_t bias_t_batch_stride, bias_t_head_stride, bias_t_row_stride;
+  /* Backward: 0 = the fused kernel, which forms every tile's scores once and adds its dQ contributions into an
+   * fp32 workspace with floating-point reductions whose order varies between launches (dK and dV are still summed
+   * in a fixed order); non-zero = separate dK/dV and dQ kernels with fixed summation order throughout, so that the
+   * same call gives the same bits every time, at about 1.4x the time. A call with a bias always takes the second
+   * path. Ignored by the forward. */
+  int32_t deterministic;
+  int32_t reserved_;
+  /* Optional device word (4-byte aligned) that collects kernel status across calls: a kernel whose bounded wait
+   * runs out stores SDPA_B200_DEVICE_TIMEOUT there. The library never clears it, so one word can watch a whole
+   * stream of calls whose workspaces come and go; read it with sdpa_b200_read_device_status and clear it
+   * yourself. NULL = the first word of the call's workspace, cleared at the start of each call. */
+  uint32_t* device_status;
 } sdpa_b200_params;
 
 SDPA_B200_API int sdpa_b200_version(void);
@@ -168,9 +182,16 @@ SDPA_B200_API int sdpa_b200_fwd(const sdpa_b200_params* p, void* workspace, size
 /* dq, dk, dv <- backward(dout, q, k, v, out, lse). */
 SDPA_B200_API int sdpa_b200_bwd(const sdpa_b200_params* p, void* workspace, size_t workspace_bytes, void* stream);
 
-/* Synchronises `stream`, reads the status word a kernel may have left in `workspace` and
- * returns it in *device_status (SDPA_B200_OK or SDPA_B200_DEVICE_TIMEOUT). */
+/* Synchronises `stream`, reads the status word a kernel may have left in `workspace` (or in the word given as
+ * sdpa_b200_params.device_status) and returns it in *device_status (SDPA_B200_OK or SDPA_B200_DEVICE_TIMEOUT). */
 SDPA_B200_API int sdpa_b200_read_device_status(const void* workspace, void* stream, int* device_status);
+
+/* Self-test of the time-out path every kernel of this library shares: launches one warp that waits, for at most
+ * `budget_us` microseconds, on a shared-memory barrier nobody will ever arrive on - no copy or MMA is in flight -
+ * then gives up exactly as the attention kernels do: it stores SDPA_B200_DEVICE_TIMEOUT into *device_status and
+ * returns normally, leaving the context usable. No counterpart in the reference, whose vendor kernels report
+ * nothing back from the device. */
+SDPA_B200_API int sdpa_b200_selftest_wait_timeout(uint32_t* device_status, uint32_t budget_us, void* stream);
 
 /* Split-KV decode (dense tensors, seqlen_q == 1) for callers that cannot allocate device memory
  * where they call it - inside an allocator or memory-pool callback, or after the process has

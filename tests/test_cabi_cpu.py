@@ -26,7 +26,7 @@ def test_header_symbols_are_exported(native_lib):
     assert set(names) == set(_cabi.EXPORTED_SYMBOLS), names
     for n in names:
         assert hasattr(native_lib, n), f"{n} declared in the header but not exported"
-    assert native_lib.sdpa_b200_version() == 107
+    assert native_lib.sdpa_b200_version() == 108
     assert native_lib.sdpa_b200_status_string(1) == b"invalid argument"
 
 

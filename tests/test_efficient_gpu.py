@@ -51,8 +51,14 @@ def test_efficient_without_log_sumexp_and_with_bias(cuda_device, native_lib):
 
 
 def test_choice_prefers_flash_then_memory_efficient(cuda_device, native_lib):
+    # short queries, head_dim 64: the default order (sdp_utils.cpp:8-50) tries flash first
+    q64 = rand((1, 2, 64, 64), 1).to(cuda_device)
+    assert sdp_choice._fused_sdp_choice(q64, q64, q64) == int(SDPBackend.FLASH_ATTENTION)
     q = rand((1, 2, 256, 128), 1).to(cuda_device)
-    assert sdp_choice._fused_sdp_choice(q, q, q) == int(SDPBackend.FLASH_ATTENTION)
+    # inference with head_dim 128 puts the memory-efficient operator first; with it disabled, flash
+    assert sdp_choice._fused_sdp_choice(q, q, q) == int(SDPBackend.EFFICIENT_ATTENTION)
+    with backends.sdp_kernel(enable_flash=True, enable_math=True, enable_mem_efficient=False):
+        assert sdp_choice._fused_sdp_choice(q, q, q) == int(SDPBackend.FLASH_ATTENTION)
     with backends.sdp_kernel(enable_flash=False, enable_math=True, enable_mem_efficient=True):
         assert sdp_choice._fused_sdp_choice(q, q, q) == int(SDPBackend.EFFICIENT_ATTENTION)
         out = sdp_choice.scaled_dot_product_attention(q, q, q, is_causal=True)

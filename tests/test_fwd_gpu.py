@@ -160,9 +160,9 @@ def test_varlen_different_q_and_k_lengths(cuda_device, native_lib):
     orc.assert_close_lse(lse, l_ref)
 
 
-def test_untouched_guard_bands_and_determinism(cuda_device, native_lib):
-    """Outputs land only where they belong (NaN-poisoned neighbours stay NaN) and two runs
-    give identical bits."""
+def test_forward_is_deterministic_and_packed_neighbours_do_not_mix(cuda_device, native_lib):
+    """Two runs give identical bits, and two packed sequences that share a 128-row tile get their own results
+    (writes outside an output are checked in test_guard_bands_gpu.py)."""
     dev = cuda_device
     B, H, L, D = 1, 2, 200, 128
     q, k, v = rand((B, H, L, D), 1).to(dev), rand((B, H, L, D), 2).to(dev), rand((B, H, L, D), 3).to(dev)
@@ -203,8 +203,8 @@ def test_config2_shape_on_sampled_heads_and_causality_property(cuda_device, nati
 
 
 def test_config4_varlen_gqa_scaled_down(cuda_device, native_lib):
-    """BASELINE config 4 drawn with the documented recipe at 1/4 of the lengths (the oracle
-    finishes in seconds): ragged cu_seqlens, Hq 32 / Hkv 8, causal."""
+    """BASELINE config 4 drawn with the documented recipe at 1/4 of the lengths, every element against the
+    oracle (the full-size run is in test_full_size_gpu.py): ragged cu_seqlens, Hq 32 / Hkv 8, causal."""
     dev = cuda_device
     c = workloads.config4_varlen_gqa(num_seqs=8, lo=128, hi=1024)
     cu = c.cu_seqlens.tolist()

@@ -89,3 +89,21 @@ def test_memory_efficient_backend_takes_a_mask_that_broadcasts():
         with pytest.warns(UserWarning, match="Flash attention has been runtime disabled"):
             with pytest.raises(RuntimeError, match="No available kernel"):
                 sdp_choice.scaled_dot_product_attention(q, q, q)  # CPU tensors: the device check fails too
+
+
+def test_priority_order_follows_the_reference_heuristics():
+    """sdp_utils.cpp:8-50, on tensor metadata only."""
+    F, E, M = SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION, SDPBackend.MATH
+    z = lambda *s: torch.zeros(*s, dtype=torch.bfloat16)
+    order = sdp_choice.priority_order
+    assert order(z(1, 2, 64, 64), z(1, 2, 64, 64), z(1, 2, 64, 64)) == (F, E, M)        # few threads, short queries
+    assert order(z(1, 2, 256, 64), z(1, 2, 256, 64), z(1, 2, 256, 64)) == (E, F, M)     # few threads, long queries
+    assert order(z(8, 16, 256, 64), z(8, 16, 256, 64), z(8, 16, 256, 64)) == (F, E, M)  # 128 (batch, head) units
+    assert order(z(8, 16, 256, 128), z(8, 16, 256, 128), z(8, 16, 256, 128)) == (E, F, M)  # head_dim 128, inference
+    q = z(8, 16, 2048, 128).requires_grad_(True)
+    assert order(q, q, q) == (F, E, M)              # training: 6 * 128 <= 2048
+    q = z(8, 16, 512, 128).requires_grad_(True)
+    assert order(q, q, q) == (E, F, M)              # training: 6 * 128 > 512
+    with torch.no_grad():
+        assert order(q, q, q) == (E, F, M)          # grad mode off: the inference rule (head_dim 128)
+    assert order(z(2, 64, 64), z(2, 64, 64), z(2, 64, 64)) == (F, E, M)  # not 4-dimensional

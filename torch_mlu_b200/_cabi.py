@@ -26,6 +26,7 @@ EXPORTED_SYMBOLS = (
     "sdpa_b200_fwd",
     "sdpa_b200_bwd",
     "sdpa_b200_read_device_status",
+    "sdpa_b200_selftest_wait_timeout",
     "sdpa_b200_decode_static",
     "sdpa_b200_merge_partial",
     "sdpa_b200_dropout_keep_mask",
@@ -59,6 +60,8 @@ class SdpaParams(ctypes.Structure):
         ("bias", c_void_p), ("bias_batch_stride", c_int64), ("bias_head_stride", c_int64), ("bias_row_stride", c_int64),
         ("dbias", c_void_p), ("dbias_batch_stride", c_int64), ("dbias_head_stride", c_int64), ("dbias_row_stride", c_int64),
         ("bias_t", c_void_p), ("bias_t_batch_stride", c_int64), ("bias_t_head_stride", c_int64), ("bias_t_row_stride", c_int64),
+        ("deterministic", c_int32), ("reserved_", c_int32),
+        ("device_status", c_void_p),
     ]
 
 
@@ -99,6 +102,8 @@ def load() -> ctypes.CDLL:
         fn.argtypes = [POINTER(SdpaParams), c_void_p, c_size_t, c_void_p]
     lib.sdpa_b200_read_device_status.restype = c_int
     lib.sdpa_b200_read_device_status.argtypes = [c_void_p, c_void_p, POINTER(c_int)]
+    lib.sdpa_b200_selftest_wait_timeout.restype = c_int
+    lib.sdpa_b200_selftest_wait_timeout.argtypes = [c_void_p, ctypes.c_uint32, c_void_p]
     lib.sdpa_b200_decode_static.restype = c_int
     lib.sdpa_b200_decode_static.argtypes = [POINTER(SdpaParams), c_void_p]
     lib.sdpa_b200_merge_partial.restype = c_int

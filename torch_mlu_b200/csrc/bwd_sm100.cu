@@ -161,6 +161,12 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src,
                : "memory");
 }
 
+// A grid launched with programmatic stream serialization may start before the grid in front of it has finished. This
+// wait returns once that grid has completed and its stores are visible; a CTA that executes it before it exits keeps its
+// own grid from completing first, so whatever follows in the stream is ordered behind BOTH grids, as it would be without
+// the overlap. (A no-op for a grid launched the ordinary way.)
+__device__ __forceinline__ void wait_for_previous_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // both halves of a packed 16-bit pair survive or die by two keep bits (bit 0 -> low half)
 __device__ __forceinline__ uint32_t keep_pair_mask(uint32_t two_bits) {
   return ((two_bits & 1u) ? 0x0000ffffu : 0u) | ((two_bits & 2u) ? 0xffff0000u : 0u);
@@ -200,7 +206,10 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int size = min(p.heads_per_wave, p.num_bh - grp * p.heads_per_wave);
     const int rank = w / size;
     const int bh = grp * p.heads_per_wave + (w - rank * size);
-    if (rank >= p.num_row_blocks) return;  // padding slots of a short last group
+    if (rank >= p.num_row_blocks) {  // padding slots of a short last group
+      if (kMode == kModeDQ) wait_for_previous_grid();
+      return;
+    }
     xb = (kMode == kModeDKDV) ? rank : p.num_row_blocks - 1 - rank;
     b = bh / p.heads_x;
     hx = bh - b * p.heads_x;
@@ -216,7 +225,10 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int causal_off = len_k - len_q;
   const int len_x = (kMode == kModeDKDV) ? len_k : len_q;
   const int x0 = xb * kTile;
-  if (x0 >= len_x) return;
+  if (x0 >= len_x) {
+    if (kMode == kModeDQ) wait_for_previous_grid();
+    return;
+  }
 
   // streamed tile range [y_lo, y_hi) (in tiles of 128) per head, and heads per CTA
   int y_lo = 0, y_hi = 0;
@@ -890,6 +902,8 @@ bwd_tile_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   if (warp == 0) BWD_STAMP(0, 23, 2);
   if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, SDPA_B200_DEVICE_TIMEOUT);
+  // the dQ grid overlaps the tail of the dK/dV grid: it must not be the first of the two to complete
+  if (kMode == kModeDQ && threadIdx.x == 0) wait_for_previous_grid();
 }
 
 // delta[row] = sum_d dO[row,d] * O[row,d]; lse2[row] = lse[row] * log2(e);
@@ -1110,7 +1124,7 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   kp.dv = static_cast<uint16_t*>(p.dv);
   kp.cu_q = p.cu_seqlens_q;
   kp.cu_k = p.cu_seqlens_k;
-  kp.status = static_cast<uint32_t*>(workspace);
+  kp.status = p.device_status != nullptr ? p.device_status : static_cast<uint32_t*>(workspace);
   kp.dq_batch_stride = p.dq_batch_stride;
   kp.dq_head_stride = p.dq_head_stride;
   kp.dq_row_stride = p.dq_row_stride;

@@ -839,8 +839,8 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
   kp.lse = p.lse;
   kp.cu_q = p.cu_seqlens_q;
   kp.cu_k = p.cu_seqlens_k;
-  kp.status = static_cast<uint32_t*>(workspace);
-  kp.unit_counter = kp.status + 1;  // workspace header word 1, cleared with the header
+  kp.status = p.device_status != nullptr ? p.device_status : static_cast<uint32_t*>(workspace);
+  kp.unit_counter = static_cast<uint32_t*>(workspace) + 1;  // workspace header word 1, cleared with the header
   kp.o_batch_stride = p.o_batch_stride;
   kp.o_head_stride = p.o_head_stride;
   kp.o_row_stride = p.o_row_stride;

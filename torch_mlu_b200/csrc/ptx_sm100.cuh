@@ -197,8 +197,8 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // rest of the CTA stops waiting too. Returns false on abort or after `budget_ns`.
 constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s; a healthy kernel waits microseconds
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile uint32_t* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_budget(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                 uint64_t budget_ns) {
   if (mbar_test(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t spin = 1;; ++spin) {
@@ -207,12 +207,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
       if (*abort_flag != 0) return false;
       uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitBudgetNs) {
+      else if (now - t0 > budget_ns) {
         *abort_flag = 1;
         return false;
       }
     }
   }
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          volatile uint32_t* abort_flag) {
+  return mbar_wait_budget(bar, parity, abort_flag, kWaitBudgetNs);
 }
 
 // After a time-out the CTA must not return while copies it started or MMAs it issued are still in

@@ -10,6 +10,7 @@
 #include <mutex>
 
 #include "kernels.h"
+#include "ptx_sm100.cuh"
 
 namespace sdpa_b200 {
 
@@ -166,8 +167,8 @@ int validate_common(const sdpa_b200_params* p) {
     return SDPA_B200_INVALID_ARG;
   }
   if (p->bias != nullptr) {
-    if (p->cu_seqlens_q != nullptr || p->cu_seqlens_k != nullptr || p->kernel == SDPA_B200_KERNEL_DECODE) {
-      set_error("an additive bias is built for dense tensors and the tile kernels only");
+    if (p->kernel == SDPA_B200_KERNEL_DECODE) {
+      set_error("an additive bias is built for the tile kernels only");
       return SDPA_B200_UNSUPPORTED;
     }
     auto bad = [](int64_t s) { return s < 0 || (s % 8) != 0; };
@@ -177,6 +178,10 @@ int validate_common(const sdpa_b200_params* p) {
                 (long long)p->bias_batch_stride, (long long)p->bias_head_stride, (long long)p->bias_row_stride);
       return SDPA_B200_INVALID_ARG;
     }
+  }
+  if ((reinterpret_cast<uintptr_t>(p->device_status) & 3u) != 0) {
+    set_error("device_status must be 4-byte aligned");
+    return SDPA_B200_INVALID_ARG;
   }
   if (p->dropout_p == 0.f && (p->keep_rows != nullptr || p->keep_cols != nullptr)) {
     set_error("keep_rows / keep_cols must be NULL when dropout_p is 0");
@@ -273,9 +278,51 @@ int check_device() {
 
 }  // namespace sdpa_b200
 
+namespace sdpa_b200 {
+namespace {
+// One warp, one barrier that nothing arrives on: the wait runs out after `budget_ns`, lane 0 records the status the
+// way the attention kernels do, and the kernel returns.
+__global__ void selftest_wait_timeout_kernel(uint32_t* status, uint64_t budget_ns) {
+  __shared__ uint64_t barrier;
+  __shared__ uint32_t abort_word;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&barrier), 1);
+    abort_word = 0;
+    fence_mbar_init();
+  }
+  __syncwarp();
+  const bool ok = mbar_wait_budget(smem_u32(&barrier), 0, &abort_word, budget_ns);
+  __syncwarp();
+  if (threadIdx.x == 0 && (!ok || abort_word != 0)) atomicExch(status, static_cast<uint32_t>(SDPA_B200_DEVICE_TIMEOUT));
+}
+}  // namespace
+}  // namespace sdpa_b200
+
 using namespace sdpa_b200;
 
 extern "C" {
+
+int sdpa_b200_selftest_wait_timeout(uint32_t* device_status, uint32_t budget_us, void* stream) {
+  if (device_status == nullptr || (reinterpret_cast<uintptr_t>(device_status) & 3u) != 0) {
+    set_error("device_status must be a 4-byte aligned device pointer");
+    return SDPA_B200_INVALID_ARG;
+  }
+  if (budget_us == 0 || budget_us > 1000000u) {
+    set_error("budget_us must be between 1 and 1000000 (got %u)", budget_us);
+    return SDPA_B200_INVALID_ARG;
+  }
+  int st = check_device();
+  if (st != SDPA_B200_OK) return st;
+  selftest_wait_timeout_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(device_status,
+                                                                                static_cast<uint64_t>(budget_us) * 1000ull);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("selftest: launch failed: %s", cudaGetErrorString(err));
+    return SDPA_B200_LAUNCH_FAILED;
+  }
+  count_launch();
+  return SDPA_B200_OK;
+}
 
 int sdpa_b200_version(void) { return SDPA_B200_VERSION; }
 

@@ -20,6 +20,7 @@
 
 #include <cmath>
 #include <memory>
+#include <mutex>
 #include <tuple>
 
 #include "../../include/sdpa_b200.h"
@@ -108,7 +109,35 @@ void varlen_params(sdpa_b200_params& p, const Tensor& q, const Tensor& k, const 
   set_thd(p.o_batch_stride, p.o_head_stride, p.o_row_stride, out);
 }
 
-void run(const sdpa_b200_params& p, bool backward, const Tensor& like) {
+// One int32 per device that every call made through this glue hands to the kernels (sdpa_b200_params.device_status):
+// a kernel whose bounded wait runs out leaves SDPA_B200_DEVICE_TIMEOUT in it, and it stays there, whatever happens
+// to the per-call workspaces, until b200_sdpa::_device_status reads and clears it.
+Tensor& status_word(int device) {
+  static std::mutex mu;
+  static Tensor words[64];
+  TORCH_CHECK(device >= 0 && device < 64, "device index out of range");
+  std::lock_guard<std::mutex> lock(mu);
+  if (!words[device].defined())
+    words[device] = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+  return words[device];
+}
+
+int64_t device_status(int64_t device) {
+  if (device < 0) device = at::cuda::current_device();
+  c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+  Tensor& word = status_word(static_cast<int>(device));
+  int st = 0;
+  check_status(sdpa_b200_read_device_status(word.data_ptr(), at::cuda::getCurrentCUDAStream(device).stream(), &st),
+               "sdpa_b200_read_device_status");
+  if (st != 0) word.zero_();
+  return st;
+}
+
+void run(const sdpa_b200_params& params, bool backward, const Tensor& like) {
+  sdpa_b200_params p = params;
+  p.device_status = reinterpret_cast<uint32_t*>(status_word(like.get_device()).data_ptr());
+  // torch.use_deterministic_algorithms(True) selects the backward with a fixed summation order
+  p.deterministic = at::globalContext().deterministicAlgorithms() ? 1 : 0;
   size_t bytes = 0;
   check_status(backward ? sdpa_b200_bwd_workspace_bytes(&p, &bytes) : sdpa_b200_fwd_workspace_bytes(&p, &bytes),
                "sdpa_b200 workspace query");
@@ -160,6 +189,74 @@ KeepMasks make_keep_masks(const Tensor& q, int64_t seqlen_k, double dropout_p, u
                                            at::cuda::getCurrentCUDAStream().stream()),
                "sdpa_b200_dropout_keep_mask");
   return m;
+}
+
+// The masks of the most recent forward call per device stay here, so that the backward operator that is handed the same
+// Philox pair (and shapes) takes them instead of drawing the whole pattern again; any other pair is drawn afresh.
+struct KeepKey {
+  int device = -1;
+  uint64_t seed = 0, offset = 0;
+  double p = 0.0;
+  int64_t a = 0, b = 0, c = 0, d = 0;  // dense: batch, heads, Lq, Lk; packed: heads, total_q, total_k, max_q * 2^32 + max_k
+  bool causal = false, packed = false;
+  const void* cu_q = nullptr;
+  bool operator==(const KeepKey& o) const {
+    return device == o.device && seed == o.seed && offset == o.offset && p == o.p && a == o.a && b == o.b && c == o.c &&
+           d == o.d && causal == o.causal && packed == o.packed && cu_q == o.cu_q;
+  }
+};
+
+struct KeepCache {
+  std::mutex mu;
+  KeepKey key[64];
+  KeepMasks masks[64];
+  void put(const KeepKey& k, const KeepMasks& m) {
+    if (k.device < 0 || k.device >= 64) return;
+    std::lock_guard<std::mutex> lock(mu);
+    key[k.device] = k;
+    masks[k.device] = m;
+  }
+  bool take(const KeepKey& k, KeepMasks* m) {
+    if (k.device < 0 || k.device >= 64) return false;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!(key[k.device] == k) || !masks[k.device].rows.defined()) return false;
+    *m = masks[k.device];
+    key[k.device] = KeepKey();  // one forward, one backward: drop the reference so the memory can go back
+    masks[k.device] = KeepMasks();
+    return true;
+  }
+};
+KeepCache g_keep_cache;
+
+KeepKey dense_keep_key(const Tensor& q, int64_t seqlen_k, double p, uint64_t seed, uint64_t offset, bool causal) {
+  KeepKey k;
+  k.device = q.get_device();
+  k.seed = seed;
+  k.offset = offset;
+  k.p = p;
+  k.a = q.size(0);
+  k.b = q.size(1);
+  k.c = q.size(2);
+  k.d = seqlen_k;
+  k.causal = causal;
+  return k;
+}
+
+KeepKey packed_keep_key(const Tensor& q, const Tensor& k_, const Tensor& cu_q, int64_t max_q, int64_t max_k, double p,
+                        uint64_t seed, uint64_t offset, bool causal) {
+  KeepKey k;
+  k.device = q.get_device();
+  k.seed = seed;
+  k.offset = offset;
+  k.p = p;
+  k.a = q.size(1);
+  k.b = q.size(0);
+  k.c = k_.size(0);
+  k.d = (max_q << 32) + max_k;
+  k.causal = causal;
+  k.packed = true;
+  k.cu_q = cu_q.data_ptr();
+  return k;
 }
 
 // (seed, offset) of the device's default generator, advanced like any other Philox consumer
@@ -272,6 +369,7 @@ DenseDropoutResult dense_forward_with_dropout(const Tensor& q, const Tensor& k, 
   auto [seed, offset] = draw_philox(q, q.size(0) * q.size(1) * q.size(2) * k.size(2));
   KeepMasks keep = make_keep_masks(q, k.size(2), dropout_p, seed, offset, causal);
   std::tie(r.out, r.lse) = dense_forward(q, k, v, causal, scale, allow_gqa, &keep);
+  g_keep_cache.put(dense_keep_key(q, k.size(2), dropout_p, seed, offset, causal), keep);
   r.seed = cpu_i64(seed);
   r.offset = cpu_i64(offset);
   if (return_debug_mask) r.debug = debug_mask_of(keep, q, k.size(2));
@@ -286,8 +384,11 @@ std::tuple<Tensor, Tensor, Tensor> dense_backward_with_dropout(const Tensor& gra
   if (dropout_p == 0.0) return dense_backward(grad_out, q, k, v, out, lse, causal, scale);
   TORCH_CHECK(philox_seed.numel() == 1 && philox_offset.numel() == 1,
               "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned");
-  KeepMasks keep = make_keep_masks(q, k.size(2), dropout_p, static_cast<uint64_t>(philox_seed.item<int64_t>()),
-                                   static_cast<uint64_t>(philox_offset.item<int64_t>()), causal);
+  const uint64_t seed = static_cast<uint64_t>(philox_seed.item<int64_t>());
+  const uint64_t offset = static_cast<uint64_t>(philox_offset.item<int64_t>());
+  KeepMasks keep;
+  if (!g_keep_cache.take(dense_keep_key(q, k.size(2), dropout_p, seed, offset, causal), &keep))
+    keep = make_keep_masks(q, k.size(2), dropout_p, seed, offset, causal);
   return dense_backward(grad_out, q, k, v, out, lse, causal, scale, &keep);
 }
 
@@ -356,18 +457,40 @@ std::tuple<Tensor, Tensor, Tensor> varlen_backward(const Tensor& dout_in, const 
   return {dq, dk, dv};
 }
 
-// The packed operator pair with dropout (the debug mask is left to the Python mirror: it needs cu_seqlens on the host).
+// The debug mask of a packed call: [B, Hq, max_q, max_k] in q's dtype, > 0 where a pair was kept and 0 outside a
+// sequence (attention.cpp:178-196 normalises the vendor kernel's mask to the same form). Reads cu_seqlens back
+// to the host: a debugging aid, not a hot path.
+Tensor debug_mask_of_varlen(const KeepMasks& m, const Tensor& q, const Tensor& cu_q, const Tensor& cu_k, int64_t max_q,
+                            int64_t max_k) {
+  Tensor hq = cu_q.cpu(), hk = cu_k.cpu();
+  const int32_t* cq = hq.data_ptr<int32_t>();
+  const int32_t* ck = hk.data_ptr<int32_t>();
+  const int64_t B = cu_q.numel() - 1, H = q.size(1);
+  Tensor out = at::zeros({B, H, max_q, max_k}, q.options());
+  Tensor shifts = at::arange(32, m.rows.options());
+  for (int64_t b = 0; b < B; ++b) {
+    const int64_t lq = cq[b + 1] - cq[b], lk = ck[b + 1] - ck[b];
+    if (lq <= 0 || lk <= 0) continue;
+    Tensor words = m.rows.slice(1, cq[b], cq[b + 1]);  // [H, lq, words]
+    Tensor bits = at::bitwise_and(at::bitwise_right_shift(words.unsqueeze(-1), shifts), 1).reshape({H, lq, -1}).slice(2, 0, lk);
+    out.select(0, b).slice(1, 0, lq).slice(2, 0, lk).copy_(bits);
+  }
+  return out;
+}
+
+// The packed operator pair with dropout.
 struct VarlenDropoutResult {
-  Tensor out, lse, seed, offset;
+  Tensor out, lse, seed, offset, debug;
 };
 
 VarlenDropoutResult varlen_forward_with_dropout(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& cu_q,
                                                 const Tensor& cu_k, int64_t max_q, int64_t max_k, double dropout_p, bool causal,
-                                                double scale) {
+                                                double scale, bool return_debug_mask = false) {
   TORCH_CHECK(dropout_p >= 0.0 && dropout_p < 1.0, "dropout_p must be inside [0, 1)");
   VarlenDropoutResult r;
   r.seed = at::empty({0}, q.options().dtype(at::kLong));
   r.offset = at::empty({0}, q.options().dtype(at::kLong));
+  r.debug = at::empty({0}, q.options());
   if (dropout_p == 0.0) {
     std::tie(r.out, r.lse) = varlen_forward(q, k, v, cu_q, cu_k, max_q, max_k, causal, scale);
     return r;
@@ -376,6 +499,8 @@ VarlenDropoutResult varlen_forward_with_dropout(const Tensor& q, const Tensor& k
   auto [seed, offset] = draw_philox(q, (cu_q.numel() - 1) * q.size(1) * max_q * max_k);
   KeepMasks keep = make_keep_masks_varlen(q, k, cu_q, cu_k, max_q, max_k, dropout_p, seed, offset, causal);
   std::tie(r.out, r.lse) = varlen_forward(q, k, v, cu_q, cu_k, max_q, max_k, causal, scale, &keep);
+  g_keep_cache.put(packed_keep_key(q, k, cu_q, max_q, max_k, dropout_p, seed, offset, causal), keep);
+  if (return_debug_mask) r.debug = debug_mask_of_varlen(keep, q, cu_q, cu_k, max_q, max_k);
   r.seed = cpu_i64(seed);
   r.offset = cpu_i64(offset);
   return r;
@@ -392,9 +517,11 @@ std::tuple<Tensor, Tensor, Tensor> varlen_backward_with_dropout(const Tensor& gr
   TORCH_CHECK(philox_seed.numel() == 1 && philox_offset.numel() == 1,
               "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned");
   check_varlen(q, k, v, cu_q, cu_k);
-  KeepMasks keep = make_keep_masks_varlen(q, k, cu_q, cu_k, max_q, max_k, dropout_p,
-                                          static_cast<uint64_t>(philox_seed.item<int64_t>()),
-                                          static_cast<uint64_t>(philox_offset.item<int64_t>()), causal);
+  const uint64_t seed = static_cast<uint64_t>(philox_seed.item<int64_t>());
+  const uint64_t offset = static_cast<uint64_t>(philox_offset.item<int64_t>());
+  KeepMasks keep;
+  if (!g_keep_cache.take(packed_keep_key(q, k, cu_q, max_q, max_k, dropout_p, seed, offset, causal), &keep))
+    keep = make_keep_masks_varlen(q, k, cu_q, cu_k, max_q, max_k, dropout_p, seed, offset, causal);
   return varlen_backward(grad_out, q, k, v, out, lse, cu_q, cu_k, max_q, max_k, causal, scale, &keep);
 }
 
@@ -409,7 +536,12 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, int64_t, int64_t, Tensor, Tensor, Ten
   auto iopt = q.options().dtype(at::kInt);
   Tensor cum_q = at::arange(0, (B + 1) * Lq, Lq, iopt);  // attention.cpp:109-119
   Tensor cum_k = at::arange(0, (B + 1) * Lk, Lk, iopt);
-  return {r.out, r.lse, cum_q, cum_k, Lq, Lk, r.seed, r.offset, r.debug};
+  // the reference hands back the logsumexp with its last dimension rounded up to 16 (FlashAttention_internal.cpp:261-265);
+  // the padding holds zeros here and the backward operator cuts it off again (:374-375)
+  Tensor lse = r.lse;
+  const int64_t lq16 = (Lq + 15) / 16 * 16;
+  if (lq16 != Lq) lse = at::constant_pad_nd(lse, {0, lq16 - Lq}, 0);
+  return {r.out, lse, cum_q, cum_k, Lq, Lk, r.seed, r.offset, r.debug};
 }
 
 std::tuple<Tensor, Tensor, Tensor> ref_sdpa_flash_backward(const Tensor& grad_out, const Tensor& q, const Tensor& k,
@@ -419,7 +551,9 @@ std::tuple<Tensor, Tensor, Tensor> ref_sdpa_flash_backward(const Tensor& grad_ou
                                                            const Tensor& philox_seed, const Tensor& philox_offset,
                                                            c10::optional<double> scale) {
   (void)cum_q; (void)cum_k; (void)max_q; (void)max_k;
-  return dense_backward_with_dropout(grad_out, q, k, v, out, lse, dropout_p, is_causal, philox_seed, philox_offset,
+  Tensor lse_q = lse;
+  if (lse.dim() == 3 && lse.size(2) != q.size(2)) lse_q = lse.slice(2, 0, q.size(2)).contiguous();
+  return dense_backward_with_dropout(grad_out, q, k, v, out, lse_q, dropout_p, is_causal, philox_seed, philox_offset,
                                      scale_or_default(q, scale));
 }
 
@@ -428,10 +562,9 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> ref_flash_forward(const Tenso
                                                                      int64_t max_q, int64_t max_k, double dropout_p,
                                                                      bool is_causal, bool return_debug_mask,
                                                                      c10::optional<double> scale) {
-  TORCH_CHECK(!(return_debug_mask && dropout_p > 0.0),
-              "return_debug_mask with packed tensors is served by torch_mlu_b200.ops._flash_attention_forward");
-  auto r = varlen_forward_with_dropout(q, k, v, cum_q, cum_k, max_q, max_k, dropout_p, is_causal, scale_or_default(q, scale));
-  return {r.out, r.lse, r.seed, r.offset, at::empty({0}, q.options())};
+  auto r = varlen_forward_with_dropout(q, k, v, cum_q, cum_k, max_q, max_k, dropout_p, is_causal, scale_or_default(q, scale),
+                                       return_debug_mask);
+  return {r.out, r.lse, r.seed, r.offset, r.debug};
 }
 
 std::tuple<Tensor, Tensor, Tensor> ref_flash_backward(const Tensor& grad_out, const Tensor& q, const Tensor& k,
@@ -484,10 +617,9 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> aten_flash_forward(
   const double sc = scale_or_default(q, scale);
   if (cum_q.has_value() && cum_q->defined()) {
     TORCH_CHECK(cum_k.has_value() && cum_k->defined(), "cum_seq_q and cum_seq_k must be given together");
-    TORCH_CHECK(!(return_debug_mask && dropout_p > 0.0),
-                "return_debug_mask with packed tensors is served by torch_mlu_b200.ops._flash_attention_forward");
-    auto r = varlen_forward_with_dropout(q, k, v, *cum_q, *cum_k, max_q.expect_int(), max_k.expect_int(), dropout_p, is_causal, sc);
-    return {r.out, r.lse, r.seed, r.offset, at::empty({0}, q.options())};
+    auto r = varlen_forward_with_dropout(q, k, v, *cum_q, *cum_k, max_q.expect_int(), max_k.expect_int(), dropout_p, is_causal, sc,
+                                         return_debug_mask);
+    return {r.out, r.lse, r.seed, r.offset, r.debug};
   }
   // dense form of the installed torch: [batch, seq, heads, head_dim]
   TORCH_CHECK(q.dim() == 4, "dense _flash_attention_forward expects [batch, seq_len, heads, head_dim]");
@@ -576,6 +708,8 @@ TORCH_LIBRARY(b200_sdpa, m) {
   m.def("_install_aten_overrides() -> ()", install_aten_overrides);
   m.def("_remove_aten_overrides() -> ()", remove_aten_overrides);
   m.def("_launch_count() -> int", launch_count);
+  // status word of `device` (-1 = current): 0, or 4 when a kernel gave up a bounded wait since the last read; clears it
+  m.def("_device_status(int device=-1) -> int", device_status);
 }
 
 TORCH_LIBRARY_IMPL(b200_sdpa, AutocastCUDA, m) {

@@ -87,6 +87,56 @@ class KeepMasksVarlen:
         return out
 
 
+class _LastForward:
+    """The keep-masks of the most recent forward call per device. A backward operator that is handed the same Philox
+    pair for the same shapes takes them from here instead of drawing the whole pattern a second time (it is the
+    same pattern by construction); anything else is drawn afresh. One entry per device: one forward, one backward."""
+
+    _slots: dict = {}
+
+    @classmethod
+    def put(cls, device: torch.device, key: tuple, masks) -> None:
+        cls._slots[device.index] = (key, masks)
+
+    @classmethod
+    def take(cls, device: torch.device, key: tuple):
+        slot = cls._slots.get(device.index)
+        if slot is None or slot[0] != key:
+            return None
+        del cls._slots[device.index]
+        return slot[1]
+
+
+def dense_masks(seed: int, offset: int, dropout_p: float, batch: int, heads: int, seqlen_q: int, seqlen_k: int,
+                device: torch.device, is_causal: bool, *, forward: bool) -> KeepMasks:
+    """KeepMasks for one dense operator call: a forward call draws them and leaves them for its backward, a backward
+    call takes what its forward left or draws them again from the pair."""
+    key = ("dense", int(seed), int(offset), float(dropout_p), batch, heads, seqlen_q, seqlen_k, bool(is_causal))
+    if not forward:
+        hit = _LastForward.take(device, key)
+        if hit is not None:
+            return hit
+    masks = KeepMasks(seed, offset, dropout_p, batch, heads, seqlen_q, seqlen_k, device, is_causal)
+    if forward:
+        _LastForward.put(device, key, masks)
+    return masks
+
+
+def packed_masks(seed: int, offset: int, dropout_p: float, heads: int, cu_q: torch.Tensor, cu_k: torch.Tensor, total_q: int,
+                 total_k: int, max_q: int, max_k: int, is_causal: bool, *, forward: bool) -> KeepMasksVarlen:
+    """The same for packed (varlen) calls; the offsets tensors are part of the key by identity of their memory."""
+    key = ("packed", int(seed), int(offset), float(dropout_p), heads, cu_q.data_ptr(), cu_k.data_ptr(), total_q, total_k, max_q,
+           max_k, bool(is_causal))
+    if not forward:
+        hit = _LastForward.take(cu_q.device, key)
+        if hit is not None:
+            return hit
+    masks = KeepMasksVarlen(seed, offset, dropout_p, heads, cu_q, cu_k, total_q, total_k, max_q, max_k, is_causal)
+    if forward:
+        _LastForward.put(cu_q.device, key, masks)
+    return masks
+
+
 def draw_seed_and_offset(device: torch.device, elements: int) -> Tuple[int, int]:
     """(seed, offset) for one call from the device's default generator, which moves on by the number of Philox
     calls the elements stand for (what getCounterOffset does, FlashAttention_internal.cpp:46-49): the same

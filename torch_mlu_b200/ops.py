@@ -62,8 +62,8 @@ def _check_inputs(*tensors: torch.Tensor) -> None:
         _check(t.stride(-1) == 1, "Input tensor must have contiguous last dimension")
 
 
-def _stream_ptr() -> int:
-    return torch.cuda.current_stream().cuda_stream
+def _stream_ptr(device: Optional[torch.device] = None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
 
 
 def _set_strides_bhld(p: _cabi.SdpaParams, prefix: str, t: torch.Tensor) -> None:
@@ -81,9 +81,11 @@ def _set_strides_thd(p: _cabi.SdpaParams, prefix: str, t: torch.Tensor) -> None:
 
 
 class _Workspace:
-    """Per-device cache of one growing workspace buffer (torch owns the memory)."""
+    """Per-device cache of one growing workspace buffer per stream, and of the device's status word (torch owns
+    the memory)."""
 
     _bufs: dict = {}
+    _status: dict = {}
 
     @classmethod
     def get(cls, device: torch.device, nbytes: int) -> torch.Tensor:
@@ -94,6 +96,16 @@ class _Workspace:
             cls._bufs[key] = buf
         return buf
 
+    @classmethod
+    def status_word(cls, device: torch.device) -> torch.Tensor:
+        """One int32 per device that every call made through this module hands to the kernels: a kernel whose
+        bounded wait runs out leaves DEVICE_TIMEOUT in it, and it stays there until device_status() reads it."""
+        word = cls._status.get(device.index)
+        if word is None:
+            word = torch.zeros(1, dtype=torch.int32, device=device)
+            cls._status[device.index] = word
+        return word
+
 
 def workspace_for(params: _cabi.SdpaParams, backward: bool, device: torch.device) -> torch.Tensor:
     lib = _cabi.load()
@@ -103,29 +115,47 @@ def workspace_for(params: _cabi.SdpaParams, backward: bool, device: torch.device
     return _Workspace.get(device, need.value)
 
 
-def _run_fwd(p: _cabi.SdpaParams, device: torch.device) -> None:
+def _run(p: _cabi.SdpaParams, device: torch.device, backward: bool) -> None:
+    # the library works on the current device and the stream it is given: make both the tensors' own
     lib = _cabi.load()
-    ws = workspace_for(p, False, device)
-    _cabi.check(lib.sdpa_b200_fwd(ctypes.byref(p), ws.data_ptr(), ws.numel(), _stream_ptr()),
-                "sdpa_b200_fwd")
+    with torch.cuda.device(device):
+        p.device_status = _Workspace.status_word(device).data_ptr()
+        ws = workspace_for(p, backward, device)
+        fn = lib.sdpa_b200_bwd if backward else lib.sdpa_b200_fwd
+        _cabi.check(fn(ctypes.byref(p), ws.data_ptr(), ws.numel(), _stream_ptr(device)),
+                    "sdpa_b200_bwd" if backward else "sdpa_b200_fwd")
+
+
+def _run_fwd(p: _cabi.SdpaParams, device: torch.device) -> None:
+    _run(p, device, False)
 
 
 def _run_bwd(p: _cabi.SdpaParams, device: torch.device) -> None:
-    lib = _cabi.load()
-    ws = workspace_for(p, True, device)
-    _cabi.check(lib.sdpa_b200_bwd(ctypes.byref(p), ws.data_ptr(), ws.numel(), _stream_ptr()),
-                "sdpa_b200_bwd")
+    _run(p, device, True)
 
 
 def device_status(device: Optional[torch.device] = None) -> int:
-    """Synchronise the current stream and return the status word the last call's kernels
-    left in the workspace (0, or DEVICE_TIMEOUT when a bounded in-kernel wait ran out)."""
+    """Synchronise the device's current stream and return what the kernels launched through this module since
+    the last call of this function left in the device's status word: 0, or DEVICE_TIMEOUT when a bounded in-kernel
+    wait ran out. The word is cleared on the way out."""
     device = device or torch.device("cuda", torch.cuda.current_device())
-    ws = _Workspace.get(device, 256)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    word = _Workspace.status_word(device)
     out = ctypes.c_int(0)
-    _cabi.check(_cabi.load().sdpa_b200_read_device_status(ws.data_ptr(), _stream_ptr(), ctypes.byref(out)),
-                "read_device_status")
+    with torch.cuda.device(device):
+        _cabi.check(_cabi.load().sdpa_b200_read_device_status(word.data_ptr(), _stream_ptr(device), ctypes.byref(out)),
+                    "read_device_status")
+        if out.value != 0:
+            word.zero_()
     return out.value
+
+
+def check_device_status(device: Optional[torch.device] = None) -> None:
+    """Raise when a kernel reported a time-out since the last check."""
+    st = device_status(device)
+    if st != 0:
+        raise _cabi.SdpaError(st, "a kernel of this library gave up a bounded wait (DEVICE_TIMEOUT): its outputs are invalid")
 
 
 def _empty_like_debug(q: torch.Tensor) -> torch.Tensor:
@@ -188,7 +218,7 @@ def _transposed_bias(bias):
     lib = _cabi.load()
     with torch.cuda.device(bias.device):
         _cabi.check(lib.sdpa_b200_transpose_bias(bias.data_ptr(), bias.stride(0), bias.stride(1), bias.stride(2), nb, nh, Lq, Lk,
-                                                 buf.data_ptr(), lq8, _stream_ptr()), "sdpa_b200_transpose_bias")
+                                                 buf.data_ptr(), lq8, _stream_ptr(bias.device)), "sdpa_b200_transpose_bias")
     return buf[..., :Lq].expand(B, H, Lk, Lq)
 
 
@@ -252,7 +282,8 @@ def _scaled_dot_product_flash_attention(query, key, value, dropout_p: float = 0.
                                         return_debug_mask: bool = False, *, scale: Optional[float] = None):
     """(output, logsumexp, cum_seq_q, cum_seq_k, max_q, max_k, philox_seed, philox_offset, debug_attn_mask).
 
-    output is [B,H,Lq,D] bf16, logsumexp [B,H,Lq] fp32 (natural log, scale included).
+    output is [B,H,Lq,D] bf16, logsumexp [B,H,ceil16(Lq)] fp32 (natural log, scale included; columns from Lq on
+    are padding).
     """
     _check(0.0 <= dropout_p < 1.0, "dropout_p must be inside [0, 1)")
     _check(query.dim() == 4 and key.dim() == 4 and value.dim() == 4,
@@ -266,20 +297,30 @@ def _scaled_dot_product_flash_attention(query, key, value, dropout_p: float = 0.
         # With dropout the operator returns the Philox pair that fixes the pattern (FlashAttention_internal.cpp:
         # 190-214), as CPU int64 scalars, and on request the pattern itself (:141-146): > 0 where a pair was kept.
         s, o = dropout.draw_seed_and_offset(query.device, B * H * Lq * Lk)
-        keep = dropout.KeepMasks(s, o, dropout_p, B, H, Lq, Lk, query.device, is_causal)
+        keep = dropout.dense_masks(s, o, dropout_p, B, H, Lq, Lk, query.device, is_causal, forward=True)
         seed, offset = torch.tensor(s, dtype=torch.int64), torch.tensor(o, dtype=torch.int64)
         if return_debug_mask:
             debug = keep.dense().to(query.dtype)
     out, lse = _dense_forward(query, key, value, is_causal, calculate_scale(query, scale), allow_gqa=False, keep=keep)
+    if Lq % 16 != 0:
+        # the reference hands the logsumexp back with its last dimension rounded up to 16
+        # (FlashAttention_internal.cpp:261-265); the padding holds zeros and the backward operator cuts it off (:374-375)
+        lse = torch.nn.functional.pad(lse, (0, (Lq + 15) // 16 * 16 - Lq))
     # attention.cpp:109-119; kept for callers that pass them on to the backward op
     cum_q = torch.arange(0, (B + 1) * Lq, Lq, dtype=torch.int32, device=query.device)
     cum_k = torch.arange(0, (B + 1) * Lk, Lk, dtype=torch.int32, device=query.device)
     return out, lse, cum_q, cum_k, Lq, Lk, seed, offset, debug
 
 
+def _deterministic(flag: Optional[bool]) -> int:
+    """The backward's `deterministic` switch: an explicit choice, else torch's global setting."""
+    return int(torch.are_deterministic_algorithms_enabled() if flag is None else bool(flag))
+
+
 def _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, scale, keep=None, bias=None, dbias=None,
-                    bias_t=None):
+                    bias_t=None, deterministic: Optional[bool] = None):
     # bias_t: a transposed copy of the bias (see _transposed_bias) kept by the caller; made here when missing
+    # deterministic: True = the kernels with a fixed summation order; None = torch.are_deterministic_algorithms_enabled()
     _check_inputs(grad_out, query, key, value, out)
     _check(logsumexp.dtype == torch.float32 and logsumexp.is_contiguous(), "logsumexp must be contiguous fp32")
     B, H, Lq, D = query.shape
@@ -301,6 +342,7 @@ def _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, scal
     elif bias is not None and bias_t is None:
         bias_t = _transposed_bias(bias)  # one HBM pass; the dK/dV kernel then reads the bias 16 bytes at a time
     _set_bias(p, bias, dbias, bias_t)
+    p.deterministic = _deterministic(deterministic)
     _run_bwd(p, query.device)
     return dq, dk, dv
 
@@ -318,8 +360,8 @@ def _scaled_dot_product_flash_attention_backward(grad_out, query, key, value, ou
         _check(philox_seed.numel() == 1 and philox_offset.numel() == 1,
                "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned")
         B, H, Lq, _ = query.shape
-        keep = dropout.KeepMasks(int(philox_seed), int(philox_offset), dropout_p, B, H, Lq, key.size(2), query.device,
-                                 is_causal)
+        keep = dropout.dense_masks(int(philox_seed), int(philox_offset), dropout_p, B, H, Lq, key.size(2), query.device,
+                                   is_causal, forward=False)
     if logsumexp.size(-1) != query.size(2):
         logsumexp = logsumexp[..., :query.size(2)].contiguous()
     return _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, calculate_scale(query, scale), keep=keep)
@@ -353,7 +395,7 @@ def _scaled_dot_product_efficient_attention(query, key, value, attn_bias, comput
     if dropout_p > 0.0:
         s0, o0 = dropout.draw_seed_and_offset(query.device, query.size(0) * query.size(1) * Lq * Lk)
         seed, offset = torch.tensor(s0, dtype=torch.int64), torch.tensor(o0, dtype=torch.int64)
-        keep_for = _keep_factory(s0, o0, dropout_p, query)
+        keep_for = _keep_factory(s0, o0, dropout_p, query, True)
     if not is_causal or Lq == Lk:
         out, lse = _dense_forward(query, key, value, is_causal, sc, allow_gqa=False, bias=bias, keep=keep_for(Lq, Lk, is_causal, 0))
     elif Lq < Lk:
@@ -371,12 +413,18 @@ def _scaled_dot_product_efficient_attention(query, key, value, attn_bias, comput
     return out, lse, seed, offset
 
 
-def _keep_factory(seed: int, offset: int, dropout_p: float, query):
+def _keep_factory(seed: int, offset: int, dropout_p: float, query, forward: bool):
     """Keep-masks for the kernel calls one memory-efficient operator call is made of: the same Philox pair, the
     second call (rows past Lk of a top-left causal mask) on a stream of its own (bit 62 of the offset)."""
     B, H = query.size(0), query.size(1)
-    return lambda lq, lk, causal, part: dropout.KeepMasks(seed, offset ^ (part << 62), dropout_p, B, H, lq, lk, query.device,
-                                                          causal)
+    return lambda lq, lk, causal, part: dropout.dense_masks(seed, offset ^ (part << 62), dropout_p, B, H, lq, lk, query.device,
+                                                            causal, forward=forward)
+
+
+def _philox_ints(philox_seed, philox_offset) -> Tuple[int, int]:
+    _check(philox_seed.numel() == 1 and philox_offset.numel() == 1,
+           "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned")
+    return int(philox_seed), int(philox_offset)
 
 
 def _scaled_dot_product_efficient_attention_backward(grad_out, query, key, value, attn_bias, out, logsumexp,
@@ -408,7 +456,7 @@ def _scaled_dot_product_efficient_attention_backward(grad_out, query, key, value
     if dropout_p > 0.0:
         _check(philox_seed.numel() == 1 and philox_offset.numel() == 1,
                "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned")
-        keep_for = _keep_factory(int(philox_seed), int(philox_offset), dropout_p, query)
+        keep_for = _keep_factory(int(philox_seed), int(philox_offset), dropout_p, query, False)
     if not is_causal or Lq == Lk:
         dq, dk, dv = _dense_backward(grad_out, query, key, value, out, logsumexp, is_causal, sc, bias=bias, dbias=dbias,
                                      keep=keep_for(Lq, Lk, is_causal, 0))
@@ -472,6 +520,48 @@ def _check_varlen(query, key, value, cu_q, cu_k):
     _check_inputs(query, key, value)
 
 
+def _varlen_forward(query, key, value, cu_q, cu_k, max_q, max_k, is_causal, scale, keep=None, bias=None):
+    """Packed forward: (out [total_q, Hq, D], lse [Hq, total_q]). `keep`: dropout.KeepMasksVarlen or None; `bias`: a
+    [B, Hq, max_q, max_k] view from _prepare_bias or None (sequence b reads bias[b] by positions inside the sequence)."""
+    _check_varlen(query, key, value, cu_q, cu_k)
+    out = torch.empty_like(query, memory_format=torch.contiguous_format)
+    lse = torch.empty((query.size(1), query.size(0)), dtype=torch.float32, device=query.device)
+    p = _varlen_params(query, key, value, out, lse, cu_q, cu_k, max_q, max_k, is_causal, scale)
+    if keep is not None:
+        p.dropout_p = keep.dropout_p
+        p.keep_rows, p.keep_cols = keep.rows.data_ptr(), keep.cols.data_ptr()
+    _set_bias(p, bias)
+    _run_fwd(p, query.device)
+    return out, lse
+
+
+def _varlen_backward(grad_out, query, key, value, out, logsumexp, cu_q, cu_k, max_q, max_k, is_causal, scale, keep=None,
+                     bias=None, dbias=None, deterministic: Optional[bool] = None):
+    _check_varlen(query, key, value, cu_q, cu_k)
+    if grad_out.stride(-1) != 1:
+        grad_out = grad_out.contiguous()
+    _check_inputs(grad_out, out)
+    _check(logsumexp.dtype == torch.float32 and logsumexp.is_contiguous()
+           and tuple(logsumexp.shape) == (query.size(1), query.size(0)),
+           "logsumexp must be contiguous fp32 [heads_q, total_q]")
+    dq = torch.empty_like(query, memory_format=torch.contiguous_format)
+    dk = torch.empty_like(key, memory_format=torch.contiguous_format)
+    dv = torch.empty_like(value, memory_format=torch.contiguous_format)
+    p = _varlen_params(query, key, value, out, logsumexp, cu_q, cu_k, max_q, max_k, is_causal, scale)
+    p.dout, p.dq, p.dk, p.dv = grad_out.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    _set_strides_thd(p, "do", grad_out)
+    _set_strides_thd(p, "dq", dq)
+    _set_strides_thd(p, "dk", dk)
+    _set_strides_thd(p, "dv", dv)
+    if keep is not None:
+        p.dropout_p = keep.dropout_p
+        p.keep_rows, p.keep_cols = keep.rows.data_ptr(), keep.cols.data_ptr()
+    _set_bias(p, bias, dbias, None if bias is None else _transposed_bias(bias))
+    p.deterministic = _deterministic(deterministic)
+    _run_bwd(p, query.device)
+    return dq, dk, dv
+
+
 def _flash_attention_forward(query, key, value, cum_seq_q, cum_seq_k, max_q: int, max_k: int, dropout_p: float,
                              is_causal: bool, return_debug_mask: bool, *, scale: Optional[float] = None):
     """(output, softmax_logsumexp, philox_seed, philox_offset, debug_attn_mask).
@@ -483,23 +573,19 @@ def _flash_attention_forward(query, key, value, cum_seq_q, cum_seq_k, max_q: int
     """
     _check(0.0 <= dropout_p < 1.0, "dropout_p must be inside [0, 1)")
     _check_varlen(query, key, value, cum_seq_q, cum_seq_k)
-    out = torch.empty_like(query, memory_format=torch.contiguous_format)
-    lse = torch.empty((query.size(1), query.size(0)), dtype=torch.float32, device=query.device)
-    p = _varlen_params(query, key, value, out, lse, cum_seq_q, cum_seq_k, max_q, max_k, is_causal,
-                       calculate_scale(query, scale))
     seed, offset = _philox_placeholders(query)
     debug = _empty_like_debug(query)
+    keep = None
     if dropout_p > 0.0:
         # the Philox pair as two CPU int64 scalars; on request the pattern as [B, Hq, max_q, max_k], > 0 = kept
         s, o = dropout.draw_seed_and_offset(query.device, (cum_seq_q.numel() - 1) * query.size(1) * int(max_q) * int(max_k))
-        keep = dropout.KeepMasksVarlen(s, o, dropout_p, query.size(1), cum_seq_q, cum_seq_k, query.size(0), key.size(0),
-                                       int(max_q), int(max_k), is_causal)
-        p.dropout_p = keep.dropout_p
-        p.keep_rows, p.keep_cols = keep.rows.data_ptr(), keep.cols.data_ptr()
+        keep = dropout.packed_masks(s, o, dropout_p, query.size(1), cum_seq_q, cum_seq_k, query.size(0), key.size(0),
+                                    int(max_q), int(max_k), is_causal, forward=True)
         seed, offset = torch.tensor(s, dtype=torch.int64), torch.tensor(o, dtype=torch.int64)
         if return_debug_mask:
             debug = keep.dense().to(query.dtype)
-    _run_fwd(p, query.device)
+    out, lse = _varlen_forward(query, key, value, cum_seq_q, cum_seq_k, max_q, max_k, is_causal, calculate_scale(query, scale),
+                               keep=keep)
     return out, lse, seed, offset, debug
 
 
@@ -511,35 +597,17 @@ def _flash_attention_backward(grad_out, query, key, value, out, logsumexp, cum_s
     cannot pass for Hq != Hkv; here it can)."""
     _check(0.0 <= dropout_p < 1.0, "dropout_p must be inside [0, 1)")
     _check_varlen(query, key, value, cum_seq_q, cum_seq_k)
-    if grad_out.stride(-1) != 1:
-        grad_out = grad_out.contiguous()
-    _check_inputs(grad_out, out)
-    _check(logsumexp.dtype == torch.float32 and logsumexp.is_contiguous()
-           and tuple(logsumexp.shape) == (query.size(1), query.size(0)),
-           "logsumexp must be contiguous fp32 [heads_q, total_q]")
-    dq = torch.empty_like(query, memory_format=torch.contiguous_format)
-    dk = torch.empty_like(key, memory_format=torch.contiguous_format)
-    dv = torch.empty_like(value, memory_format=torch.contiguous_format)
-    p = _varlen_params(query, key, value, out, logsumexp, cum_seq_q, cum_seq_k, max_q, max_k, is_causal,
-                       calculate_scale(query, scale))
-    p.dout, p.dq, p.dk, p.dv = grad_out.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
-    _set_strides_thd(p, "do", grad_out)
-    _set_strides_thd(p, "dq", dq)
-    _set_strides_thd(p, "dk", dk)
-    _set_strides_thd(p, "dv", dv)
+    keep = None
     if dropout_p > 0.0:
-        _check(philox_seed.numel() == 1 and philox_offset.numel() == 1,
-               "dropout_p > 0 needs the philox_seed and philox_offset the forward operator returned")
-        keep = dropout.KeepMasksVarlen(int(philox_seed), int(philox_offset), dropout_p, query.size(1), cum_seq_q, cum_seq_k,
-                                       query.size(0), key.size(0), int(max_q), int(max_k), is_causal)
-        p.dropout_p = keep.dropout_p
-        p.keep_rows, p.keep_cols = keep.rows.data_ptr(), keep.cols.data_ptr()
-    _run_bwd(p, query.device)
-    return dq, dk, dv
+        s, o = _philox_ints(philox_seed, philox_offset)
+        keep = dropout.packed_masks(s, o, dropout_p, query.size(1), cum_seq_q, cum_seq_k, query.size(0), key.size(0),
+                                    int(max_q), int(max_k), is_causal, forward=False)
+    return _varlen_backward(grad_out, query, key, value, out, logsumexp, cum_seq_q, cum_seq_k, max_q, max_k, is_causal,
+                            calculate_scale(query, scale), keep=keep)
 
 
 # --------------------------------------------------------------------------------------
-# decode (seqlen_q == 1, GQA allowed) - no reference counterpart
+# memory-efficient operators on [B, L, H, D] tensors
 # --------------------------------------------------------------------------------------
 # sdp::CustomMaskType (sdp_utils.h:32-37)
 NO_CUSTOM_MASK, CAUSAL_FROM_TOP_LEFT, CAUSAL_FROM_BOTTOM_RIGHT = 0, 1, 2
@@ -548,23 +616,23 @@ NO_CUSTOM_MASK, CAUSAL_FROM_TOP_LEFT, CAUSAL_FROM_BOTTOM_RIGHT = 0, 1, 2
 def _efficient_attention_forward(query, key, value, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q: Optional[int],
                                  dropout_p: float, custom_mask_type: int, compute_log_sumexp: bool = False, *,
                                  scale: Optional[float] = None, causal_diagonal=None, seqlen_k=None):
-    """(output, logsumexp, philox_seed, philox_offset), attention.cpp:393-507, without dropout; ``bias``
-    ([B, H, Lq, Lk] or anything that broadcasts to it) only without cu_seqlens.
+    """(output, logsumexp, philox_seed, philox_offset), attention.cpp:393-507.
 
     query is [B, Lq, H, D], key / value [B, Lk, H, D] (sequence before heads, unlike the sdp operators).
     output comes back as the reference returns it: the [B, Lq, H, D] buffer viewed as [B, H, Lq, D]
     (:503-506). logsumexp is [H, B*Lq] fp32 (mem_eff_fwd, FlashAttention_internal.cpp:603), empty unless
-    asked for. With cu_seqlens (int32 [B+1], offsets into the flattened B*L token axis, :435-470) the packed
-    kernels run; their causal mask is bottom-right aligned, so ``CausalFromTopLeft`` is taken there only
-    when both offset tensors are equal (the two alignments then coincide).
+    asked for. ``bias`` is [B, H, Lq, Lk] or anything that broadcasts to it; with dropout the Philox pair comes
+    back as two CPU int64 scalars. With cu_seqlens (int32 [B+1], offsets into the flattened B*L token axis,
+    :435-470) the packed kernels run: sequence b reads bias[b] by positions counted from its own start, and the
+    causal mask is bottom-right aligned, so ``CausalFromTopLeft`` is taken there only when both offset tensors are
+    equal (the two alignments then coincide).
     """
     _check(query.dim() == 4 and key.dim() == 4 and value.dim() == 4, "query, key and value must be [B, L, H, D]")
     _check(query.size(0) == key.size(0) == value.size(0), "batch sizes differ")
     _check(key.size(1) == value.size(1), "key and value lengths differ")
     _check(query.size(2) == key.size(2) == value.size(2), "numbers of heads differ")
     _check(query.size(3) == key.size(3) == value.size(3), "head dims differ")
-    _check(bias is None or cu_seqlens_q is None, "bias together with cu_seqlens is not built in this library")
-    _check(dropout_p == 0.0, "dropout_p must be 0 here: dropout is built for the scaled_dot_product operators")
+    _check(0.0 <= dropout_p < 1.0, "dropout_p must be inside [0, 1)")
     _check(causal_diagonal is None and seqlen_k is None, "causal_diagonal and seqlen_k are not supported")
     _check(custom_mask_type in (NO_CUSTOM_MASK, CAUSAL_FROM_TOP_LEFT, CAUSAL_FROM_BOTTOM_RIGHT),
            f"unknown custom_mask_type {custom_mask_type}")
@@ -573,24 +641,37 @@ def _efficient_attention_forward(query, key, value, bias, cu_seqlens_q, cu_seqle
     Lk = key.size(1)
     sc = calculate_scale(query, scale)
     seed, offset = _philox_placeholders(query)
+    q_t, k_t, v_t = query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2)
     if cu_seqlens_q is None:
-        q_t, k_t, v_t = query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2)
         if custom_mask_type == CAUSAL_FROM_TOP_LEFT:
-            out, lse, _, _ = _scaled_dot_product_efficient_attention(q_t, k_t, v_t, bias, True, 0.0, True, scale=sc)
+            out, lse, seed, offset = _scaled_dot_product_efficient_attention(q_t, k_t, v_t, bias, True, dropout_p, True, scale=sc)
         else:
-            out, lse = _dense_forward(q_t, k_t, v_t, custom_mask_type == CAUSAL_FROM_BOTTOM_RIGHT, sc, allow_gqa=False,
+            causal = custom_mask_type == CAUSAL_FROM_BOTTOM_RIGHT
+            keep = None
+            if dropout_p > 0.0:
+                s, o = dropout.draw_seed_and_offset(query.device, B * H * Lq * Lk)
+                seed, offset = torch.tensor(s, dtype=torch.int64), torch.tensor(o, dtype=torch.int64)
+                keep = dropout.dense_masks(s, o, dropout_p, B, H, Lq, Lk, query.device, causal, forward=True)
+            out, lse = _dense_forward(q_t, k_t, v_t, causal, sc, allow_gqa=False, keep=keep,
                                       bias=None if bias is None else _prepare_bias(bias, q_t, k_t))
         lse = lse.permute(1, 0, 2).reshape(H, B * Lq)
     else:
         _check(cu_seqlens_q.dtype == torch.int32 and cu_seqlens_k.dtype == torch.int32, "cu_seqlens must have dtype int32")
         _check(cu_seqlens_q.numel() == B + 1 and cu_seqlens_k.numel() == B + 1, "cu_seqlens must have batch + 1 entries")
+        causal = custom_mask_type != NO_CUSTOM_MASK
         if custom_mask_type == CAUSAL_FROM_TOP_LEFT:
             _check(cu_seqlens_q is cu_seqlens_k or torch.equal(cu_seqlens_q, cu_seqlens_k),
                    "CausalFromTopLeft with cu_seqlens needs equal query and key lengths in this library")
         max_q = Lq if max_seqlen_q is None else int(max_seqlen_q)
-        out, lse, _, _, _ = _flash_attention_forward(
-            query.reshape(B * Lq, H, D), key.reshape(B * Lk, H, D), value.reshape(B * Lk, H, D), cu_seqlens_q.contiguous(),
-            cu_seqlens_k.contiguous(), max_q, Lk, 0.0, custom_mask_type != NO_CUSTOM_MASK, False, scale=sc)
+        cu_q, cu_k = cu_seqlens_q.contiguous(), cu_seqlens_k.contiguous()
+        keep = None
+        if dropout_p > 0.0:
+            s, o = dropout.draw_seed_and_offset(query.device, B * H * max_q * Lk)
+            seed, offset = torch.tensor(s, dtype=torch.int64), torch.tensor(o, dtype=torch.int64)
+            keep = dropout.packed_masks(s, o, dropout_p, H, cu_q, cu_k, B * Lq, B * Lk, max_q, Lk, causal, forward=True)
+        out, lse = _varlen_forward(query.reshape(B * Lq, H, D), key.reshape(B * Lk, H, D), value.reshape(B * Lk, H, D), cu_q,
+                                   cu_k, max_q, Lk, causal, sc, keep=keep,
+                                   bias=None if bias is None else _prepare_bias(bias, q_t, k_t))
         out = out.view(B, Lq, H, D).transpose(1, 2)
     if not compute_log_sumexp:
         lse = lse.new_empty((0,))
@@ -603,9 +684,9 @@ def _efficient_attention_backward(grad_out_, query, key, value, bias, out, cu_se
                                   num_splits_key: Optional[int] = None):
     """(grad_q [B,Lq,H,D], grad_k, grad_v [B,Lk,H,D], grad_bias), attention.cpp:579-727, for a forward call
     ``out`` and ``grad_out_`` are [B, Lq, H, D] (any strides with unit head-dim stride); ``logsumexp`` is the
-    [H, B*Lq] tensor of the forward. grad_bias is shaped like ``bias`` when ``bias_requires_grad``, else empty."""
-    _check(bias is None or cu_seqlens_q is None, "bias together with cu_seqlens is not built in this library")
-    _check(dropout_p == 0.0, "dropout_p must be 0 here: dropout is built for the scaled_dot_product operators")
+    [H, B*Lq] tensor of the forward. grad_bias is shaped like ``bias`` when ``bias_requires_grad``, else empty.
+    With ``dropout_p`` the pattern of the forward call is drawn again from ``philox_seed`` / ``philox_offset``."""
+    _check(0.0 <= dropout_p < 1.0, "dropout_p must be inside [0, 1)")
     _check(query.dim() == 4 and grad_out_.dim() == 4 and out.dim() == 4, "tensors must be [B, L, H, D]")
     _check((cu_seqlens_q is None) == (cu_seqlens_k is None), "cu_seqlens_q and cu_seqlens_k must be given together")
     B, Lq, H, D = query.shape
@@ -614,32 +695,46 @@ def _efficient_attention_backward(grad_out_, query, key, value, bias, out, cu_se
                                                   "compute_log_sumexp=True")
     sc = calculate_scale(query, scale)
     empty_bias_grad = query.new_empty((0,))
+    t = lambda x: x.transpose(1, 2)
+    want_dbias = bias is not None and bool(bias_requires_grad)
     if cu_seqlens_q is None:
-        t = lambda x: x.transpose(1, 2)
         lse = logsumexp.view(H, B, Lq).permute(1, 0, 2).contiguous()
-        want_dbias = bias is not None and bool(bias_requires_grad)
         if custom_mask_type == CAUSAL_FROM_TOP_LEFT:
             dq, dk, dv, db = _scaled_dot_product_efficient_attention_backward(
-                t(grad_out_), t(query), t(key), t(value), bias, t(out), lse, philox_seed, philox_offset, 0.0,
+                t(grad_out_), t(query), t(key), t(value), bias, t(out), lse, philox_seed, philox_offset, dropout_p,
                 [True, True, True, want_dbias], True, scale=sc)
         else:
+            causal = custom_mask_type == CAUSAL_FROM_BOTTOM_RIGHT
             go = t(grad_out_)
             if go.stride(-1) != 1:
                 go = go.contiguous()
             b4 = None if bias is None else _prepare_bias(bias, t(query), t(key))
             dfull = _new_bias_grad(t(query), t(key)) if want_dbias else None
-            dq, dk, dv = _dense_backward(go, t(query), t(key), t(value), t(out), lse,
-                                         custom_mask_type == CAUSAL_FROM_BOTTOM_RIGHT, sc, bias=b4, dbias=dfull)
+            keep = None
+            if dropout_p > 0.0:
+                s, o = _philox_ints(philox_seed, philox_offset)
+                keep = dropout.dense_masks(s, o, dropout_p, B, H, Lq, Lk, query.device, causal, forward=False)
+            dq, dk, dv = _dense_backward(go, t(query), t(key), t(value), t(out), lse, causal, sc, bias=b4, dbias=dfull,
+                                         keep=keep)
             db = dfull.sum_to_size(bias.shape) if want_dbias else empty_bias_grad
         return t(dq), t(dk), t(dv), db
+    causal = custom_mask_type != NO_CUSTOM_MASK
     if custom_mask_type == CAUSAL_FROM_TOP_LEFT:
         _check(cu_seqlens_q is cu_seqlens_k or torch.equal(cu_seqlens_q, cu_seqlens_k),
                "CausalFromTopLeft with cu_seqlens needs equal query and key lengths in this library")
-    dq, dk, dv = _flash_attention_backward(
-        grad_out_.reshape(B * Lq, H, D), query.reshape(B * Lq, H, D), key.reshape(B * Lk, H, D), value.reshape(B * Lk, H, D),
-        out.reshape(B * Lq, H, D), logsumexp.contiguous(), cu_seqlens_q.contiguous(), cu_seqlens_k.contiguous(),
-        int(max_seqlen_q), int(max_seqlen_k), 0.0, custom_mask_type != NO_CUSTOM_MASK, philox_seed, philox_offset, scale=sc)
-    return dq.view(B, Lq, H, D), dk.view(B, Lk, H, D), dv.view(B, Lk, H, D), empty_bias_grad
+    cu_q, cu_k = cu_seqlens_q.contiguous(), cu_seqlens_k.contiguous()
+    keep = None
+    if dropout_p > 0.0:
+        s, o = _philox_ints(philox_seed, philox_offset)
+        keep = dropout.packed_masks(s, o, dropout_p, H, cu_q, cu_k, B * Lq, B * Lk, int(max_seqlen_q), int(max_seqlen_k), causal,
+                                    forward=False)
+    b4 = None if bias is None else _prepare_bias(bias, t(query), t(key))
+    dfull = _new_bias_grad(t(query), t(key)) if want_dbias else None
+    dq, dk, dv = _varlen_backward(grad_out_.reshape(B * Lq, H, D), query.reshape(B * Lq, H, D), key.reshape(B * Lk, H, D),
+                                  value.reshape(B * Lk, H, D), out.reshape(B * Lq, H, D), logsumexp.contiguous(), cu_q, cu_k,
+                                  int(max_seqlen_q), int(max_seqlen_k), causal, sc, keep=keep, bias=b4, dbias=dfull)
+    db = dfull.sum_to_size(bias.shape) if want_dbias else empty_bias_grad
+    return dq.view(B, Lq, H, D), dk.view(B, Lk, H, D), dv.view(B, Lk, H, D), db
 
 
 def decode_attention(query, key_cache, value_cache, *, scale: Optional[float] = None, num_splits: int = 0):

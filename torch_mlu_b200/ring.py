@@ -30,10 +30,11 @@ def merge_partial(o_acc: torch.Tensor, lse_acc: torch.Tensor, o_part: torch.Tens
     assert o_part.dtype in (torch.bfloat16, torch.float16) and o_part.stride(-1) == 1
     B, H, L, D = o_acc.shape
     lib = _cabi.load()
-    st = lib.sdpa_b200_merge_partial(o_acc.data_ptr(), lse_acc.data_ptr(), o_part.data_ptr(), lse_part.data_ptr(), B, H, L, D,
-                                     _cabi.DTYPE_F16 if o_part.dtype == torch.float16 else _cabi.DTYPE_BF16,
-                                     o_part.stride(0), o_part.stride(1), o_part.stride(2),
-                                     torch.cuda.current_stream().cuda_stream)
+    with torch.cuda.device(o_acc.device):  # the library launches on the current device
+        st = lib.sdpa_b200_merge_partial(o_acc.data_ptr(), lse_acc.data_ptr(), o_part.data_ptr(), lse_part.data_ptr(), B, H, L, D,
+                                         _cabi.DTYPE_F16 if o_part.dtype == torch.float16 else _cabi.DTYPE_BF16,
+                                         o_part.stride(0), o_part.stride(1), o_part.stride(2),
+                                         torch.cuda.current_stream(o_acc.device).cuda_stream)
     _cabi.check(st, "sdpa_b200_merge_partial")
 
 
@@ -67,19 +68,21 @@ def zigzag_take(x: torch.Tensor, rank: int, world: int, dim: int = 2) -> torch.T
 
 def ring_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal: bool, scale: Optional[float] = None,
                  group=None, attention_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None,
-                 layout: str = "contiguous") -> Tuple[torch.Tensor, torch.Tensor]:
+                 layout: str = "contiguous", exchange: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
     """q [B,Hq,Ls,D], k/v [B,Hkv,Ls,D]: this rank's slice of the sequence.
     ``layout="contiguous"``: rank r owns rows [r*Ls, (r+1)*Ls). ``layout="zigzag"`` (causal only): rank r owns
     chunks r and 2*world-1-r of 2*world equal chunks (``zigzag_take``), which balances the causal work: every
     rank computes half a block per hop instead of rank 0 idling and the last rank doing all of them.
     Returns (out [B,Hq,Ls,D] in q's dtype, lse [B,Hq,Ls] fp32) for the local queries over the
     whole sequence. ``attention_fn(q, k, v, is_causal=, scale=) -> (out, lse)`` and ``merge_fn``
-    default to this library's kernels."""
+    default to this library's kernels. ``exchange=False`` runs the same kernels hop by hop on the local slice
+    without sending anything: a timing aid that shows what the kernels cost without the transfers (its
+    result is not attention over the whole sequence)."""
     if layout == "zigzag":
         if not is_causal:
             layout = "contiguous"  # without a mask every slice order is balanced and equivalent
         else:
-            return _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn)
+            return _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn, exchange)
     elif layout != "contiguous":
         raise ValueError(f"unknown layout {layout!r}")
     if attention_fn is None:
@@ -97,7 +100,7 @@ def ring_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal
     for step in range(world):
         src = (rank - step) % world  # owner of the slice now visiting
         reqs = []
-        if step + 1 < world:
+        if step + 1 < world and exchange:
             k_next, v_next = torch.empty_like(k_cur), torch.empty_like(v_cur)
             ops_list = [dist.P2POp(dist.isend, k_cur, send_to, group), dist.P2POp(dist.isend, v_cur, send_to, group),
                         dist.P2POp(dist.irecv, k_next, recv_from, group), dist.P2POp(dist.irecv, v_next, recv_from, group)]
@@ -107,13 +110,13 @@ def ring_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal
             merge_fn(o_acc, lse_acc, o_part, lse_part.contiguous())
         for r in reqs:
             r.wait()
-        if step + 1 < world:
+        if step + 1 < world and exchange:
             k_cur, v_cur = k_next, v_next
     lse = torch.where(torch.isneginf(lse_acc), torch.full_like(lse_acc, float("inf")), lse_acc)
     return o_acc.to(q.dtype), lse
 
 
-def _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn):
+def _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn, exchange=True):
     """Causal ring prefill over zig-zag slices. Local rows are [chunk r | chunk 2W-1-r]; a visiting slice from
     rank s is [chunk s | chunk 2W-1-s]. Which parts meet:
       s == r : plain causal attention over the local slice (its two chunks are in sequence order);
@@ -138,7 +141,7 @@ def _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn):
     for step in range(world):
         src = (rank - step) % world
         reqs = []
-        if step + 1 < world:
+        if step + 1 < world and exchange:
             k_next, v_next = torch.empty_like(k_cur), torch.empty_like(v_cur)
             ops_list = [dist.P2POp(dist.isend, k_cur, send_to, group), dist.P2POp(dist.isend, v_cur, send_to, group),
                         dist.P2POp(dist.irecv, k_next, recv_from, group), dist.P2POp(dist.irecv, v_next, recv_from, group)]
@@ -157,7 +160,7 @@ def _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn):
             merge_fn(acc[half], lse[half], o_part[:, :, rows], l_part[:, :, rows].contiguous())
         for r in reqs:
             r.wait()
-        if step + 1 < world:
+        if step + 1 < world and exchange:
             k_cur, v_cur = k_next, v_next
     o_acc, lse_acc = torch.cat(acc, dim=2), torch.cat(lse, dim=2)
     lse_out = torch.where(torch.isneginf(lse_acc), torch.full_like(lse_acc, float("inf")), lse_acc)

@@ -172,18 +172,47 @@ def use_mem_efficient_attention(query, key, value, attn_mask=None, debug: bool =
     return all(c(query, key, value, attn_mask, debug) for c in _MEM_EFFICIENT_CONSTRAINTS)
 
 
+def priority_order(query, key, value):
+    """The order in which the backends are tried (sdp_utils.cpp:8-50): flash, memory efficient, math - except that the
+    memory-efficient operator goes first for nested inputs, for inference with head_dim 128 or with few (batch x head)
+    units and long queries, and for training when 6 * batch * heads exceeds the query length. Here both fused
+    operators run the same kernels, so the order only decides which operator (and which causal alignment for
+    Lq != Lk) a call lands on - as it does in the reference."""
+    default_order = (SDPBackend.FLASH_ATTENTION, SDPBackend.EFFICIENT_ATTENTION, SDPBackend.MATH)
+    efficient_first = (SDPBackend.EFFICIENT_ATTENTION, SDPBackend.FLASH_ATTENTION, SDPBackend.MATH)
+    if query.is_nested or key.is_nested or value.is_nested:
+        return efficient_first
+    if query.dim() != 4:
+        return default_order
+    batch_size, num_heads, query_lengths, head_dim = query.shape
+    if batch_size > 0:
+        threads_flash = batch_size * num_heads
+        threads_cutlass = threads_flash * (query_lengths // 64)
+        more_threads_cutlass = (threads_cutlass // 2) >= threads_flash
+        small_threads_flash = threads_flash < 60
+        large_head_dim = max(head_dim, key.size(3) if key.dim() == 4 else head_dim) == 128
+        requires_grad = torch.is_grad_enabled() and (query.requires_grad or key.requires_grad or value.requires_grad)
+        if requires_grad:
+            if 6 * threads_flash > query_lengths:
+                return efficient_first
+        elif (small_threads_flash and more_threads_cutlass) or large_head_dim:
+            return efficient_first
+    return default_order
+
+
 def _fused_sdp_choice(query, key, value, attn_mask=None, dropout_p: float = 0.0, is_causal: bool = False,
                       *, scale: Optional[float] = None) -> int:
-    """Returns the SDPBackend value (int) the call would use, or raises like the reference."""
+    """Returns the SDPBackend value (int) the call would use, or raises like the reference (select_sdp_backend,
+    sdp_utils.cpp:97-147)."""
     if not (backends.math_sdp_enabled() or backends.flash_sdp_enabled() or backends.mem_efficient_sdp_enabled()):
         return int(SDPBackend.ERROR)
-    # priority order of sdp_utils.cpp:28-31: flash, memory efficient, math
-    if use_flash_attention(query, key, value, attn_mask, False):
-        return int(SDPBackend.FLASH_ATTENTION)
-    if use_mem_efficient_attention(query, key, value, attn_mask, False):
-        return int(SDPBackend.EFFICIENT_ATTENTION)
-    if backends.math_sdp_enabled():
-        return int(SDPBackend.MATH)
+    for backend in priority_order(query, key, value):
+        if backend == SDPBackend.FLASH_ATTENTION and use_flash_attention(query, key, value, attn_mask, False):
+            return int(SDPBackend.FLASH_ATTENTION)
+        if backend == SDPBackend.EFFICIENT_ATTENTION and use_mem_efficient_attention(query, key, value, attn_mask, False):
+            return int(SDPBackend.EFFICIENT_ATTENTION)
+        if backend == SDPBackend.MATH and backends.math_sdp_enabled():
+            return int(SDPBackend.MATH)
     # nothing qualifies: say why, then fail (sdp_utils.cpp:134-146)
     warnings.warn("Memory efficient kernel not used because:", UserWarning, stacklevel=2)
     use_mem_efficient_attention(query, key, value, attn_mask, True)

@@ -60,9 +60,9 @@ def config1_cpu_reference(batch=2, heads=8, seqlen=256, head_dim=64) -> DenseCas
     return DenseCase("c1_cpu_reference_fp32", q, k, v, None, False, 1.0 / math.sqrt(head_dim))
 
 
-def config2_causal_prefill(batch=4, heads=32, seqlen=4096, head_dim=128) -> DenseCase:
-    """bf16 causal prefill forward, seed 1."""
-    g = torch.Generator().manual_seed(1)
+def config2_causal_prefill(batch=4, heads=32, seqlen=4096, head_dim=128, seed=1) -> DenseCase:
+    """bf16 causal prefill forward, seed 1 (other seeds: further batch slices of a multi-GPU job, drawn the same way)."""
+    g = torch.Generator().manual_seed(seed)
     q = _randn(g, (batch, heads, seqlen, head_dim), torch.bfloat16)
     k = _randn(g, (batch, heads, seqlen, head_dim), torch.bfloat16)
     v = _randn(g, (batch, heads, seqlen, head_dim), torch.bfloat16)
