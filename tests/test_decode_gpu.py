@@ -62,7 +62,7 @@ def test_decode_auto_dispatch_and_strided_cache(cuda_device, native_lib):
     res = ops._scaled_dot_product_flash_attention(qq.to(dev), kk.to(dev), kk.to(dev))
     o_ref, l_ref = orc.cpu_sdpa_forward(qq, kk, kk)
     orc.assert_close_bf16(res[0], o_ref, "out")
-    orc.assert_close_lse(res[1], l_ref)
+    orc.assert_close_lse(res[1][..., :1], l_ref)  # the operator pads the logsumexp to 16 rows
 
 
 def test_decode_split_count_does_not_change_the_answer_much(cuda_device, native_lib):

@@ -82,8 +82,7 @@ def test_efficient_attention_with_cu_seqlens_and_bias(cuda_device, native_lib, w
     dev = cuda_device
     B, L, H, D = 3, 256, 2, 128
     p = 0.25 if with_dropout else 0.0
-    q, k, v = (rand((B, L, H, D), s) for s in (1, 2, 3))
-    do = torch.rand((B, L, H, D), generator=torch.Generator().manual_seed(4)).bfloat16()
+    q, k, v, do = (rand((B, L, H, D), s) for s in (1, 2, 3, 4))
     bias = rand((B, H, L, L), 5)
     lens = [200, 256, 77]
     cu = [0, 200, 456, 533]

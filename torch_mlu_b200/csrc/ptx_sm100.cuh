@@ -360,6 +360,17 @@ __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[
       : "memory");
 }
 
+// 64 columns into r[0..63] with two loads (the caller waits once)
+__device__ __forceinline__ void tmem_ld_x64(uint32_t taddr, uint32_t (&r)[64]) {
+  tmem_ld_x32_at<0>(taddr, r);
+  tmem_ld_x32_at<32>(taddr + 32, r);
+}
+
+// fp32 reduce-add of four consecutive floats in global memory (16-byte aligned), no return value
+__device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t* r) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -440,6 +451,22 @@ __device__ __forceinline__ void umma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint3
       "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
       "}\n"
       ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kDescHiSw128), "r"(kIdesc), "r"(kAccumulate ? 1u : 0u)
+      : "memory");
+}
+
+// the same with the accumulate flag as a run-time value
+template <uint32_t kIdesc>
+__device__ __forceinline__ void umma_ss_lo_acc(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(kDescHiSw128), "r"(kIdesc), "r"(accumulate)
       : "memory");
 }
 
