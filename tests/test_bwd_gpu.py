@@ -21,10 +21,11 @@ def rand(shape, seed):
     return torch.randn(shape, generator=g).bfloat16()
 
 
-def run_fwd_bwd(dev, q, k, v, dout, causal, scale=None):
+def run_fwd_bwd(dev, q, k, v, dout, causal, scale=None, deterministic=None):
     qd, kd, vd, dd = q.to(dev), k.to(dev), v.to(dev), dout.to(dev)
     out, lse = ops.gqa_prefill(qd, kd, vd, is_causal=causal, scale=scale)
-    dq, dk, dv = ops._dense_backward(dd, qd, kd, vd, out, lse, causal, ops.calculate_scale(qd, scale))
+    dq, dk, dv = ops._dense_backward(dd, qd, kd, vd, out, lse, causal, ops.calculate_scale(qd, scale),
+                                     deterministic=deterministic)
     assert ops.device_status() == 0
     return out, lse, dq, dk, dv
 
@@ -119,10 +120,25 @@ def test_backward_varlen(cuda_device, native_lib, lens, Hq, Hkv, causal):
 
 
 def test_backward_is_deterministic(cuda_device, native_lib):
+    """With `deterministic` every gradient comes back with the same bits on every call (the dK/dV and dQ kernels sum
+    in a fixed order). The fused kernel keeps that promise for dK and dV; its dQ sums are formed by floating-point
+    reductions in global memory and repeat only to fp32 rounding."""
     q, k, v, dout = (rand((1, 4, 640, 128), s) for s in (1, 2, 3, 4))
-    a = run_fwd_bwd(cuda_device, q, k[:, :2], v[:, :2], dout, True)
-    b = run_fwd_bwd(cuda_device, q, k[:, :2], v[:, :2], dout, True)
+    a = run_fwd_bwd(cuda_device, q, k[:, :2], v[:, :2], dout, True, deterministic=True)
+    b = run_fwd_bwd(cuda_device, q, k[:, :2], v[:, :2], dout, True, deterministic=True)
     for x, y in zip(a, b):
+        assert torch.equal(x, y)
+    c = run_fwd_bwd(cuda_device, q, k[:, :2], v[:, :2], dout, True, deterministic=False)
+    d = run_fwd_bwd(cuda_device, q, k[:, :2], v[:, :2], dout, True, deterministic=False)
+    assert torch.equal(c[3], d[3]) and torch.equal(c[4], d[4])
+    assert orc.error_stats(c[2], d[2])[0] <= 2e-2 and orc.error_stats(c[2], a[2])[0] <= 2e-2
+    # torch's global switch selects the same path
+    torch.use_deterministic_algorithms(True)
+    try:
+        e = run_fwd_bwd(cuda_device, q, k[:, :2], v[:, :2], dout, True)
+    finally:
+        torch.use_deterministic_algorithms(False)
+    for x, y in zip(a, e):
         assert torch.equal(x, y)
 
 
@@ -134,17 +150,24 @@ def test_config3_sampled_heads_and_linearity(cuda_device, native_lib):
     c = workloads.config3_causal_fwd_bwd()
     qd, kd, vd, dd = c.q.to(dev), c.k.to(dev), c.v.to(dev), c.dout.to(dev)
     out, lse = ops.gqa_prefill(qd, kd, vd, is_causal=True, scale=c.softmax_scale)
-    dq, dk, dv = ops._dense_backward(dd, qd, kd, vd, out, lse, True, c.softmax_scale)
-    assert ops.device_status() == 0
+    wants = {}
     for b, h in ((0, 0), (5, 9), (7, 15)):
         sl = (slice(b, b + 1), slice(h, h + 1))
         o_ref, l_ref = orc.cpu_sdpa_forward(c.q[sl], c.k[sl], c.v[sl], causal=True, scale=c.softmax_scale)
-        want = orc.cpu_sdpa_backward(c.dout[sl], c.q[sl], c.k[sl], c.v[sl], o_ref, l_ref, causal=True, scale=c.softmax_scale)
-        check_grads((dq[sl], dk[sl], dv[sl]), want)
-    dq2, dk2, dv2 = ops._dense_backward(dd * 2, qd, kd, vd, out, lse, True, c.softmax_scale)
-    assert torch.equal(dq2, dq * 2) and torch.equal(dk2, dk * 2) and torch.equal(dv2, dv * 2)
-    for t in (dq, dk, dv):
-        assert torch.isfinite(t.float()).all()
+        wants[sl] = orc.cpu_sdpa_backward(c.dout[sl], c.q[sl], c.k[sl], c.v[sl], o_ref, l_ref, causal=True, scale=c.softmax_scale)
+    for deterministic in (False, True):  # the fused kernel, then the dK/dV + dQ pair
+        dq, dk, dv = ops._dense_backward(dd, qd, kd, vd, out, lse, True, c.softmax_scale, deterministic=deterministic)
+        assert ops.device_status() == 0
+        for sl, want in wants.items():
+            check_grads((dq[sl], dk[sl], dv[sl]), want)
+        dq2, dk2, dv2 = ops._dense_backward(dd * 2, qd, kd, vd, out, lse, True, c.softmax_scale, deterministic=deterministic)
+        assert torch.equal(dk2, dk * 2) and torch.equal(dv2, dv * 2)
+        if deterministic:
+            assert torch.equal(dq2, dq * 2)
+        else:  # the order of the fused kernel's dQ reductions varies: equal up to fp32 rounding of the sums
+            assert orc.error_stats(dq2, dq.float() * 2)[0] <= 2e-2
+        for t in (dq, dk, dv):
+            assert torch.isfinite(t.float()).all()
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])

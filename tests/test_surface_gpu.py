@@ -107,7 +107,10 @@ def test_efficient_attention_with_cu_seqlens_and_bias(cuda_device, native_lib, w
         orc.assert_close_grad_bf16(flat(dq)[sl].transpose(0, 1).unsqueeze(0), dq_r, f"dq[{b}]")
         orc.assert_close_grad_bf16(flat(dk)[sl].transpose(0, 1).unsqueeze(0), dk_r, f"dk[{b}]")
         orc.assert_close_grad_bf16(flat(dv)[sl].transpose(0, 1).unsqueeze(0), dv_r, f"dv[{b}]")
-        orc.assert_close_grad_bf16(db[b:b + 1, :, :n, :n], ds_r, f"dbias[{b}]")
+        # the bias gradient is dS itself, element by element: P (dP - delta) with delta = rowsum(dO o O) taken from the
+        # 16-bit O. In the first rows of a sequence P is close to 1 and the rounding of O (2^-9 per element, 128
+        # elements) shows undiminished, so the absolute bound is 5e-2 here (dq, dk, dv average it out)
+        orc.assert_close_grad_bf16(db[b:b + 1, :, :n, :n], ds_r, f"dbias[{b}]", max_abs=5e-2)
         assert float(db[b, :, n:, :].abs().max() if n < L else 0.0) == 0.0
         assert float(db[b, :, :, n:].abs().max() if n < L else 0.0) == 0.0
 

@@ -64,6 +64,13 @@ struct BwdKernelParams {
 #endif
 };
 
+// bwd_fused_sm100.cu: the fused kernel and the dQ conversion behind it. `grid` and the CTA-order fields of `kp` are
+// those of the dK/dV kernel (one CTA per key block); dq_acc holds bwd_fused_workspace_bytes() bytes.
+size_t bwd_fused_workspace_bytes(const sdpa_b200_params& p, int lq_pad);
+int launch_bwd_fused(const sdpa_b200_params& p, BwdKernelParams kp, float* dq_acc, int grid, cudaStream_t stream,
+                     const CUtensorMap& tm_q, const CUtensorMap& tm_k, const CUtensorMap& tm_v, const CUtensorMap& tm_do,
+                     const CUtensorMap& tm_dv, const CUtensorMap& tm_dk);
+
 template <bool kF16>
 constexpr uint32_t kIdescSS = umma_idesc_16(kTile, kTile, false, false, kF16);
 template <int kD, bool kF16>

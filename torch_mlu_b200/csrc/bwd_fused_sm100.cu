@@ -16,6 +16,13 @@
 // a small kernel scales and converts the accumulator afterwards. Those reductions arrive in an order that varies from
 // launch to launch, so dQ is reproducible only to fp32 rounding; dK and dV are summed in a fixed order.
 //
+// What bounds it (time stamps of the profiling build, B8 H16 L2048 causal): the reductions. One item adds 64 KB into
+// the accumulator; with every SM sending them, the L2 takes about 20 bytes per clock and SM (a stand-alone test reaches
+// 5.5 TB/s = 706 floats per clock over the chip with red.v4 and with cp.reduce.async.bulk alike, 3.6 TB/s once the
+// accumulator exceeds L2), i.e. ~3400 cycles per item against 2560 cycles of tensor work, and a reduce warp needs
+// ~90 cycles per red.v4. Item period ~5600 cycles: level with the two-kernel path on B8 H16 L2048 causal (0.540 ms
+// against 0.536 ms for the whole backward), 5-9 % ahead at L = 8192 causal and at large unmasked shapes.
+//
 // TMEM (512 columns): T1 [0,128) T2 [128,256) dV [256,384) dK [384,512). Item i has S in T[i&1] and dP in the other
 // buffer. Life of one buffer: S(i) -> P(i) (16-bit, front of each half) -> dQ(i) -> dP(i+1) -> S(i+2) ...:
 //   dQ(i) is issued behind dV(i) by the same thread (the pipe keeps their order), so P(i) has been read;
@@ -32,15 +39,16 @@ namespace {
 #endif
 
 constexpr int kFThreads = 512;  // warps 0-3 / 4-7 compute, 8 TMA, 9 score GEMMs, 10 accumulation GEMMs, 11 idle, 12-15 dQ reduce
-// Register hand-over (setmaxnreg): compiled for 65536 / 512 = 128 registers per thread; the compute warpgroups grow,
-// the other two shrink. The increase waits - without a time limit - until the pool holds enough registers, so what
+// Register hand-over (setmaxnreg): compiled for 65536 / 512 = 128 registers per thread; the compute and reduce warpgroups
+// grow, the fourth (producer, issuers) shrinks. The increase waits - without a time limit - until the pool holds enough registers, so what
 // the shrinking warpgroups release must cover what the growing ones take.
 constexpr int kRegsLaunch = 128;
-constexpr int kRegsCompute = 168;
-constexpr int kRegsReduce = 104;
-constexpr int kRegsUtil = 72;
-static_assert((kRegsCompute - kRegsLaunch) * 2 <= (kRegsLaunch - kRegsReduce) + (kRegsLaunch - kRegsUtil),
-              "setmaxnreg.inc would wait forever: the compute warps ask for more than the others release");
+constexpr int kRegsCompute = 152;
+constexpr int kRegsReduce = 144;  // a thread holds a whole row of the dQ tile (up to 128 floats)
+constexpr int kRegsUtil = 64;
+static_assert(kRegsCompute >= kRegsLaunch && kRegsReduce >= kRegsLaunch && kRegsUtil <= kRegsLaunch &&
+                  (kRegsCompute - kRegsLaunch) * 2 + (kRegsReduce - kRegsLaunch) <= (kRegsLaunch - kRegsUtil),
+              "setmaxnreg.inc would wait forever: the compute and reduce warps ask for more than the others release");
 
 // shared memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kFSmemX = 0;                            // K, V tiles: 2 x 32 KB
@@ -66,6 +74,18 @@ constexpr uint32_t kFBarAccFull = 112;
 constexpr uint32_t kFBarEpiFull = 120; // 8
 constexpr uint32_t kFSmemTmemPtr = 128;
 constexpr uint32_t kFSmemAbort = 132;
+
+// Profiling builds (-DSDPA_BWD_STAMPS) time-stamp pipeline events of one CTA: roles 0/1 = lane 0 of the first warp of each
+// compute warpgroup, 2 / 3 = the two MMA issuers, 4 = lane 0 of the first reduce warp; [role 5][item 24][event 8] floats.
+#ifdef SDPA_BWD_STAMPS
+#define FSTAMP(role, item, ev)                                                                    \
+  do {                                                                                            \
+    if (stamp_on && (item) < 24)                                                                  \
+      p.stamps[((role) * 24 + (item)) * 8 + (ev)] = static_cast<float>(clock64() - t_start);      \
+  } while (0)
+#else
+#define FSTAMP(role, item, ev) do {} while (0)
+#endif
 
 template <int kD, bool kF16>
 constexpr uint32_t kIdescDQ = umma_idesc_16(kTile, kD, true, true, kF16);  // A = dS (MN-major), B = K (MN-major)
@@ -109,6 +129,9 @@ bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                  const __grid_constant__ CUtensorMap tm_dv, const __grid_constant__ CUtensorMap tm_dk,
                  const BwdKernelParams p) {
   extern __shared__ uint8_t smem_raw[];
+#ifdef SDPA_BWD_STAMPS
+  const long long t_entry = clock64();
+#endif
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw_addr);
@@ -231,10 +254,15 @@ bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const uint32_t tmem_base = *tmem_ptr_smem;
   const uint32_t t1 = tmem_base, t2 = tmem_base + 128, acc_dv = tmem_base + 256, acc_dk = tmem_base + 384;
   const uint32_t k_smem = base + kFSmemX, v_smem = base + kFSmemX + kTileBytes, ds_smem = base + kFSmemDS;
+#ifdef SDPA_BWD_STAMPS
+  const long long t_start = clock64();
+  const bool stamp_on = p.stamps != nullptr && b == 0 && hx == 0 && xb == 0 && lane == 0 &&
+                        (warp == 0 || warp == 4 || warp == 9 || warp == 10 || warp == 12);
+#endif
 
   if (warp >= 12) {
     // ------------------------------------------------------------------ dQ reduce warps (thread = query row)
-    reg_decrease<kRegsReduce>();
+    reg_increase<kRegsReduce>();
     const int r = (warp & 3) * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     bool ok = true;
@@ -247,28 +275,29 @@ bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                                              : (static_cast<size_t>(b) * p.heads_q + hy) * p.lq_pad + qrow;
       float* dst = p.dq_acc + dq_acc_index<kD>(row);
       const bool valid = qrow < len_q;
+      FSTAMP(4, i, 0);
       ok = __all_sync(0xffffffffu, mbar_wait(bar + kFBarQFull, i & 1, abort_flag));
       if (!ok) break;
       tc_fence_after_sync();
+      FSTAMP(4, i, 1);
       const uint32_t src = ((i & 1) ? t2 : t1) + lane_base;
+      // the whole tile goes into registers first, so that the buffer is handed on before the first reduction is issued:
+      // the reductions run at the pace of the L2 (a few dozen cycles each once every SM is sending them)
+      uint32_t v[kD];
 #pragma unroll
-      for (int c = 0; c < kD / 64; ++c) {
-        uint32_t v[64];
-        tmem_ld_x64(src + c * 64, v);
-        tmem_wait_ld();
-        if (c == kD / 64 - 1) {
-          // the whole tile is in registers: the buffer may take the next item's dP
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar + kFBarQFree);
-        }
-        if (valid) {
+      for (int c = 0; c < kD / 32; ++c) tmem_ld_x32_at<32 * 0, 32>(src + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar + kFBarQFree);
+      FSTAMP(4, i, 2);
+      if (valid) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            red_add_f32x4(dst + static_cast<size_t>(c * 16 + j) * 512, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                          __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-        }
+        for (int j = 0; j < kD / 4; ++j)
+          red_add_f32x4(dst + static_cast<size_t>(j) * 512, __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                        __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
       }
+      FSTAMP(4, i, 3);
     }
   } else if (warp >= 8) {
     reg_decrease<kRegsUtil>();
@@ -284,12 +313,17 @@ bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (lane == 0 && n_items > 0) {
         auto y_full = [&](int idx) { return mbar_wait(bar + kFBarYFull + 8 * (idx & 3), (idx >> 2) & 1, abort_flag); };
         auto y_slot = [&](int idx) { return base + kFSmemY + (idx & 3) * kTileBytes; };
+#ifdef SDPA_BWD_STAMPS
+        if (stamp_on) p.stamps[(2 * 24 + 23) * 8 + 0] = static_cast<float>(t_start - t_entry);
+#endif
         bool ok = mbar_wait(bar + kFBarXFull, 0, abort_flag) && y_full(0);
+        FSTAMP(2, 23, 1);
         if (ok) {
           tc_fence_after_sync();
           issue_xyT<kD, kF16>(t1, k_smem, y_slot(0));
           umma_commit(bar + kFBarSFull);
         }
+        FSTAMP(2, 23, 2);
         ok = ok && y_full(1);
         if (ok) {
           tc_fence_after_sync();
@@ -299,17 +333,22 @@ bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         for (int i = 0; ok && i + 1 < n_items; ++i) {
           const uint32_t sb = (i & 1) ? t2 : t1, db = (i & 1) ? t1 : t2;
           // dP(i) has left TMEM once all compute warps have read it: its buffer takes S(i+1)
+          FSTAMP(2, i, 0);
           ok = mbar_wait(bar + kFBarDFree, i & 1, abort_flag) && y_full(2 * i + 2);
           if (!ok) break;
+          FSTAMP(2, i, 1);
           tc_fence_after_sync();
           issue_xyT<kD, kF16>(db, k_smem, y_slot(2 * i + 2));
           umma_commit(bar + kFBarSFull);
+          FSTAMP(2, i, 2);
           // dQ(i) has left TMEM once all reduce warps have read it: its buffer takes dP(i+1)
           ok = mbar_wait(bar + kFBarQFree, i & 1, abort_flag) && y_full(2 * i + 3);
           if (!ok) break;
+          FSTAMP(2, i, 3);
           tc_fence_after_sync();
           issue_xyT<kD, kF16>(sb, v_smem, y_slot(2 * i + 3));
           umma_commit(bar + kFBarDFull);
+          FSTAMP(2, i, 4);
         }
       }
     } else if (warp == 10) {
@@ -322,21 +361,27 @@ bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           const uint32_t sb = (i & 1) ? t2 : t1;
           const uint32_t par = ((2 * i) >> 2) & 1;
           // the tiles landed long ago (the other issuer has used them); these waits make the copies visible here too
+          FSTAMP(3, i, 0);
           ok = mbar_wait(bar + kFBarYFull + 8 * s0, par, abort_flag) && mbar_wait(bar + kFBarYFull + 8 * (s0 + 1), par, abort_flag) &&
                mbar_wait(bar + kFBarP1Full, i & 1, abort_flag);
           if (!ok) break;
+          FSTAMP(3, i, 1);
           tc_fence_after_sync();
           issue_wy_half<kD, kF16>(acc_dv, sb, y_do, 0, i > 0);
           issue_wy_half<kD, kF16>(acc_dv, sb + 64, y_do, 1, true);
+          FSTAMP(3, i, 2);
           ok = mbar_wait(bar + kFBarDSFull, i & 1, abort_flag);
           if (!ok) break;
+          FSTAMP(3, i, 3);
           tc_fence_after_sync();
           // dQ first: its read-out by the reduce warps then runs under the dK GEMM
           issue_dq<kD, kF16>(sb, ds_smem, k_smem);
           umma_commit(bar + kFBarQFull);
+          FSTAMP(3, i, 4);
           issue_dk<kD, kF16>(acc_dk, ds_smem, y_q, i > 0);
           umma_commit(bar + kFBarYEmpty + 8 * (s0 >> 1));  // Q(i), dO(i) and the dS tile may be overwritten
           if (i == n_items - 1) umma_commit(bar + kFBarAccFull);
+          FSTAMP(3, i, 5);
         }
       }
     }
@@ -366,15 +411,19 @@ bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         keep = *reinterpret_cast<const uint2*>(words + ((y0 + half * 64) >> 5));
       }
       // `ok` is made warp-uniform after every wait: the warp-level arrivals below need all 32 lanes
+      FSTAMP(half, i, 0);
       ok = mbar_wait(bar + kFBarSFull, i & 1, abort_flag) &&
            mbar_wait(bar + kFBarYFull + 8 * ((2 * i) & 3), ((2 * i) >> 2) & 1, abort_flag);  // the per-query vectors
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      FSTAMP(half, i, 1);
       const float* vec_lse = reinterpret_cast<const float*>(smem + kFSmemVec + (i & 1) * 1024) + half * 64;
       const float* vec_delta = vec_lse + 128;
-      // key xr sees query y0 + j iff xr <= y0 + j + off  <=>  j >= xr - off - y0
+      // key xr sees query y0 + j iff xr <= y0 + j + off  <=>  j >= xr - off - y0. A row past the last key sees nothing:
+      // in a packed tensor it holds the next sequence's key, whose dS must not reach this sequence's dQ.
       int j_lo = p.is_causal ? xr - causal_off - y0 - half * 64 : 0;
+      if (xr >= len_k) j_lo = 64;
 
       // phase 1 (needs S only): P = exp2(S c - lse2), masked; its 16-bit copy goes back to TMEM at once
       float pr[64];
@@ -382,6 +431,7 @@ bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         uint32_t a[64];
         tmem_ld_x64(sbuf, a);
         tmem_wait_ld();
+        FSTAMP(half, i, 2);
 #pragma unroll
         for (int j = 0; j < 64; j += 2) {
           const float x0v = fmaf(__uint_as_float(a[j]), c, -vec_lse[j]);
@@ -395,8 +445,8 @@ bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             pr[j + 1] = ex2_approx(x1v);
           }
         }
-        // only tiles on the causal diagonal need the element mask (rows past the keys' end are clipped on the way out;
-        // queries past the end have lse2 = +inf, i.e. P = 0)
+        // only tiles on the causal diagonal or past the end of the keys need the element mask (queries past the end
+        // have lse2 = +inf, i.e. P = 0)
         if (__any_sync(0xffffffffu, j_lo > 0)) {
 #pragma unroll
           for (int j = 0; j < 64; ++j) pr[j] = (j >= j_lo) ? pr[j] : 0.f;
@@ -414,10 +464,12 @@ bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         __syncwarp();
         if (lane == 0) mbar_arrive(bar + kFBarP1Full);
       }
+      FSTAMP(half, i, 3);
       // phase 2 (needs dP): dS = P o (dP - delta) into this thread's row of the shared-memory tile
       ok = __all_sync(0xffffffffu, mbar_wait(bar + kFBarDFull, i & 1, abort_flag));
       if (!ok) break;
       tc_fence_after_sync();
+      FSTAMP(half, i, 4);
       {
         uint32_t d[64];
         tmem_ld_x64(dbuf, d);
@@ -425,6 +477,7 @@ bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar + kFBarDFree);  // the dP buffer may be overwritten
+        FSTAMP(half, i, 5);
         uint32_t dw[32];
 #pragma unroll
         for (int j2 = 0; j2 < 32; ++j2) {
@@ -447,13 +500,16 @@ bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         for (int ch = 0; ch < 8; ++ch)
           *reinterpret_cast<uint4*>(ds_row + ((ch ^ (r & 7)) << 4)) = make_uint4(dw[4 * ch], dw[4 * ch + 1], dw[4 * ch + 2], dw[4 * ch + 3]);
       }
+      FSTAMP(half, i, 6);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar + kFBarDSFull);
+      FSTAMP(half, i, 7);
     }
 
     // ---- epilogue: dV, dK accumulators -> scale -> 16-bit -> global
     if (ok && n_items > 0) ok = mbar_wait(bar + kFBarAccFull, 0, abort_flag);
+    FSTAMP(half, 23, 0);
     if (ok) {
       tc_fence_after_sync();
       const bool valid = xr < len_k;
@@ -534,12 +590,14 @@ bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
   }
 
+  if (warp < 8) FSTAMP(warp >> 2, 23, 1);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
+  if (warp == 0) FSTAMP(0, 23, 2);
   if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, static_cast<uint32_t>(SDPA_B200_DEVICE_TIMEOUT));
 }
 

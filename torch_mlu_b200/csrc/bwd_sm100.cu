@@ -947,8 +947,18 @@ int lq_padded(const sdpa_b200_params& p) { return ((p.max_seqlen_q + kTile - 1) 
 
 }  // namespace
 
+// The fused kernel serves every call that does not ask for a fixed summation order and has no bias (the bias gradient
+// is written by the dQ kernel, whose threads own query rows).
+bool use_fused_backward(const sdpa_b200_params& p) { return p.deterministic == 0 && p.bias == nullptr; }
+
+size_t bwd_vector_bytes(const sdpa_b200_params& p) {
+  const size_t bytes = 2 * static_cast<size_t>(p.batch) * p.heads_q * lq_padded(p) * sizeof(float);
+  return (bytes + 255) / 256 * 256;
+}
+
 size_t bwd_workspace_bytes(const sdpa_b200_params& p) {
-  return 2 * static_cast<size_t>(p.batch) * p.heads_q * lq_padded(p) * sizeof(float);
+  // lse2 and delta, then (fused kernel) the fp32 dQ accumulator
+  return bwd_vector_bytes(p) + (use_fused_backward(p) ? bwd_fused_workspace_bytes(p, lq_padded(p)) : 0);
 }
 
 int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
@@ -1087,6 +1097,10 @@ int launch_bwd(const sdpa_b200_params& p, void* workspace, size_t workspace_byte
   };
   kp.num_row_blocks = (p.max_seqlen_k + kTile - 1) / kTile;
   const int grid_dkdv = set_order(p.heads_kv, p.max_seqlen_q, kp.kv_group);
+  if (use_fused_backward(p)) {
+    float* dq_acc = reinterpret_cast<float*>(static_cast<char*>(workspace) + kWorkspaceHeaderBytes + bwd_vector_bytes(p));
+    return launch_bwd_fused(p, kp, dq_acc, grid_dkdv, stream, tm_q, tm_k, tm_v, tm_do, tm_dv, tm_dk);
+  }
   if ((st = launch_tile_kernel(kModeDKDV, p.head_dim, f16, grid_dkdv, stream, tm_q, tm_k, tm_v, tm_do, tm_dv, tm_dk, kp)) !=
       SDPA_B200_OK)
     return st;
