@@ -158,7 +158,10 @@ typedef struct sdpa_b200_params {
    * same call gives the same bits every time, at about 1.4x the time. A call with a bias always takes the second
    * path. Ignored by the forward. */
   int32_t deterministic;
-  int32_t reserved_;
+  /* Forward (tile kernel): number of SMs the persistent kernel leaves free, for a kernel that is to run beside it on
+   * another stream - a collective that reassembles the previous step's outputs, say. 0 = one CTA on every SM, which
+   * keeps any other kernel out until the CTAs leave. At least one SM is always used. */
+  int32_t sm_margin;
   /* Optional device word (4-byte aligned) that collects kernel status across calls: a kernel whose bounded wait
    * runs out stores SDPA_B200_DEVICE_TIMEOUT there. The library never clears it, so one word can watch a whole
    * stream of calls whose workspaces come and go; read it with sdpa_b200_read_device_status and clear it

@@ -231,6 +231,18 @@ def assert_close_grad_bf16(got, want, name: str, max_abs: float = BF16_MAX_ABS, 
     return float(d.max()), float(d.mean())
 
 
+def grad_error_report(got, want, max_abs: float = BF16_MAX_ABS) -> dict:
+    """How a gradient meets assert_close_grad_bf16's bound: the largest error among elements with |want| <= 2 (where
+    the absolute bound alone applies), and how many elements lie beyond `max_abs` and pass on the relative arm."""
+    g = got.detach().float().cpu()
+    w = want.detach().float().cpu()
+    d = (g - w).abs()
+    small = w.abs() <= 2.0
+    return {"max_abs_where_want_le_2": float(d[small].max()) if small.any() else 0.0,
+            "elements": d.numel(), "beyond_abs_bound": int((d > max_abs).sum()),
+            "largest_want": float(w.abs().max()), "max_abs": float(d.max()), "mean_abs": float(d.mean())}
+
+
 def assert_close_lse(got, want, name: str = "lse", max_abs: float = LSE_MAX_ABS):
     g = got.detach().float().cpu()
     w = want.detach().float().cpu()

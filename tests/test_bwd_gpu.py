@@ -160,6 +160,13 @@ def test_config3_sampled_heads_and_linearity(cuda_device, native_lib):
         assert ops.device_status() == 0
         for sl, want in wants.items():
             check_grads((dq[sl], dk[sl], dv[sl]), want)
+            # how the bound was met: where |want| <= 2 the plain 2e-2 must hold; the relative arm is for the few larger
+            # values bf16 cannot hold to 2e-2 (at most one element in a thousand may need it)
+            for name, g, w in zip(("dq", "dk", "dv"), (dq[sl], dk[sl], dv[sl]), want):
+                rep = orc.grad_error_report(g, w)
+                print(f"config 3 {name}{tuple((x.start for x in sl))} deterministic={deterministic}: {rep}")
+                assert rep["max_abs_where_want_le_2"] <= 2e-2, (name, rep)
+                assert rep["beyond_abs_bound"] <= rep["elements"] // 1000, (name, rep)
         dq2, dk2, dv2 = ops._dense_backward(dd * 2, qd, kd, vd, out, lse, True, c.softmax_scale, deterministic=deterministic)
         assert torch.equal(dk2, dk * 2) and torch.equal(dv2, dv * 2)
         if deterministic:

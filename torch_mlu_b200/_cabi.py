@@ -60,7 +60,7 @@ class SdpaParams(ctypes.Structure):
         ("bias", c_void_p), ("bias_batch_stride", c_int64), ("bias_head_stride", c_int64), ("bias_row_stride", c_int64),
         ("dbias", c_void_p), ("dbias_batch_stride", c_int64), ("dbias_head_stride", c_int64), ("dbias_row_stride", c_int64),
         ("bias_t", c_void_p), ("bias_t_batch_stride", c_int64), ("bias_t_head_stride", c_int64), ("bias_t_row_stride", c_int64),
-        ("deterministic", c_int32), ("reserved_", c_int32),
+        ("deterministic", c_int32), ("sm_margin", c_int32),
         ("device_status", c_void_p),
     ]
 

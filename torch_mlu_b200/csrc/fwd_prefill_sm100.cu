@@ -901,8 +901,9 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
     set_error("prefill: cannot read the SM count of the current device");
     return SDPA_B200_NO_DEVICE;
   }
-  // one persistent CTA per SM (shared memory and TMEM allow no second one)
-  dim3 grid(kp.num_slots < sms ? kp.num_slots : sms, 1, 1);
+  // one persistent CTA per SM (shared memory and TMEM allow no second one), less the SMs the caller wants left free
+  const int usable = sms - p.sm_margin > 1 ? sms - p.sm_margin : 1;
+  dim3 grid(kp.num_slots < usable ? kp.num_slots : usable, 1, 1);
   kernel<<<grid, kNumThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, kp);
   err = cudaGetLastError();
   if (err != cudaSuccess) {

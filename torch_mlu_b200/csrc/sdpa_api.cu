@@ -179,6 +179,10 @@ int validate_common(const sdpa_b200_params* p) {
       return SDPA_B200_INVALID_ARG;
     }
   }
+  if (p->sm_margin < 0) {
+    set_error("sm_margin must not be negative (got %d)", p->sm_margin);
+    return SDPA_B200_INVALID_ARG;
+  }
   if ((reinterpret_cast<uintptr_t>(p->device_status) & 3u) != 0) {
     set_error("device_status must be 4-byte aligned");
     return SDPA_B200_INVALID_ARG;

@@ -251,7 +251,7 @@ def _new_bias_grad(query, key):
 
 
 def _dense_forward(query, key, value, is_causal, scale, allow_gqa, kernel=_cabi.KERNEL_AUTO, num_splits=0, keep=None,
-                   bias=None):
+                   bias=None, sm_margin=0):
     # attention.cpp:70-100; `keep`: dropout.KeepMasks of this call, or None; `bias`: from _prepare_bias, or None
     _check(query.dim() == 4 and key.dim() == 4 and value.dim() == 4,
            "query, key and value must be 4-dimensional [batch, heads, seq_len, head_dim]")
@@ -274,6 +274,7 @@ def _dense_forward(query, key, value, is_causal, scale, allow_gqa, kernel=_cabi.
         p.dropout_p = keep.dropout_p
         p.keep_rows, p.keep_cols = keep.rows.data_ptr(), keep.cols.data_ptr()
     _set_bias(p, bias)
+    p.sm_margin = int(sm_margin)
     _run_fwd(p, query.device)
     return out, lse
 
@@ -747,8 +748,9 @@ def decode_attention(query, key_cache, value_cache, *, scale: Optional[float] = 
     return out, lse
 
 
-def gqa_prefill(query, key, value, *, is_causal: bool = False, scale: Optional[float] = None):
+def gqa_prefill(query, key, value, *, is_causal: bool = False, scale: Optional[float] = None, sm_margin: int = 0):
     """Dense [B,Hq,L,D] x [B,Hkv,L,D] prefill with head broadcast (the dense reference op
-    refuses Hq != Hkv, attention.cpp:82-83; the kernel underneath does not)."""
+    refuses Hq != Hkv, attention.cpp:82-83; the kernel underneath does not). ``sm_margin`` SMs are left free
+    for a kernel that runs beside this one on another stream (a collective, for example)."""
     return _dense_forward(query, key, value, is_causal, calculate_scale(query, scale), allow_gqa=True,
-                          kernel=_cabi.KERNEL_PREFILL)
+                          kernel=_cabi.KERNEL_PREFILL, sm_margin=sm_margin)
