@@ -301,17 +301,29 @@ def measure_fwd_bwd(job: Job, n: int):
 
 
 def measure_dropout(job: Job, n: int):
+    """Config 3 with dropout through the operator pair, forward and backward alternating as in training: the forward
+    draws the keep-masks (one extra kernel) and leaves them for its backward."""
     from torch_mlu_b200 import ops
     rn = device_randn(job.dev, 2)
     q, k, v, do = (rn(8, 16, 2048, 128) for _ in range(4))
     fwd_flops = 4.0 * 8 * 16 * 2048 * 2048 * 128 / 2
     fo = lambda: ops._scaled_dot_product_flash_attention(q, k, v, 0.1, True, False)
-    r = fo()
-    bo = lambda: ops._scaled_dot_product_flash_attention_backward(do, q, k, v, r[0], r[1], r[2], r[3], r[4], r[5], 0.1, True,
-                                                                 r[6], r[7])
-    ms_f, ms_b = job.timed(fo, n, 3), job.timed(bo, n, 3)
-    return {"workload": "config 3 with dropout_p=0.1 through the operator pair (keep-mask kernel included)", "fwd_ms": ms_f,
-            "bwd_ms": ms_b, "fwd_bwd_tflops": 3.5 * fwd_flops / (ms_f + ms_b) / 1e9}
+
+    def pair():
+        r = fo()
+        return ops._scaled_dot_product_flash_attention_backward(do, q, k, v, r[0], r[1], r[2], r[3], r[4], r[5], 0.1, True,
+                                                                r[6], r[7])
+
+    ms_f = job.timed(fo, n, 3)
+    ms_pair = job.timed(pair, n, 3)
+    torch.use_deterministic_algorithms(True)
+    try:
+        ms_pair_det = job.timed(pair, n, 3)
+    finally:
+        torch.use_deterministic_algorithms(False)
+    return {"workload": "config 3 with dropout_p=0.1 through the operator pair, forward then backward (keep-mask kernel included)",
+            "fwd_ms": ms_f, "fwd_bwd_ms": ms_pair, "fwd_bwd_tflops": 3.5 * fwd_flops / ms_pair / 1e9,
+            "fwd_bwd_deterministic_ms": ms_pair_det, "fwd_bwd_deterministic_tflops": 3.5 * fwd_flops / ms_pair_det / 1e9}
 
 
 def measure_varlen(job: Job, n: int):
