@@ -18,7 +18,7 @@ OBJ_DIR = os.path.join(HERE, "build")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 SOURCES = ["sdpa_api.cu", "fwd_prefill_sm100.cu", "decode_splitkv.cu", "bwd_sm100.cu", "bwd_fused_sm100.cu", "merge_partials.cu",
-           "dropout_mask.cu", "bias_transpose.cu"]
+           "dropout_mask.cu", "bias_transpose.cu", "d256_sm100.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

@@ -26,6 +26,9 @@ int make_tensor_map_16(bool f16, CUtensorMap* map, const void* base, int head_di
 // Prefill forward (TMA + tcgen05), a persistent kernel with one CTA per SM.
 int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t stream);
 
+// Forward for head dims above 128 (up to 256): one CTA per 128 query rows, Q in tensor memory (d256_sm100.cu).
+int launch_fwd_d256(const sdpa_b200_params& p, void* workspace, cudaStream_t stream);
+
 // Number of SMs of the current device (cached per device), <= 0 on error.
 int sm_count();
 

@@ -144,8 +144,8 @@ int validate_common(const sdpa_b200_params* p) {
     set_error("head_dim must be a multiple of 8 and at most 256 (got %d)", p->head_dim);
     return SDPA_B200_INVALID_ARG;
   }
-  if (p->head_dim > 128) {
-    set_error("this build has kernels for head_dim up to 128 only (got %d)", p->head_dim);
+  if (p->head_dim > 128 && (p->dropout_p != 0.f || p->bias != nullptr || p->kernel == SDPA_B200_KERNEL_DECODE)) {
+    set_error("head dims above 128 (got %d) run in the tile kernels without dropout and without a bias", p->head_dim);
     return SDPA_B200_UNSUPPORTED;
   }
   if (!(p->softmax_scale > 0.f) || !(p->softmax_scale < 3.0e38f)) {
@@ -387,12 +387,17 @@ int sdpa_b200_fwd(const sdpa_b200_params* p, void* workspace, size_t workspace_b
     return SDPA_B200_LAUNCH_FAILED;
   }
   if (use_decode(p)) return launch_fwd_decode(*p, workspace, workspace_bytes, s);
+  if (p->head_dim > 128) return launch_fwd_d256(*p, workspace, s);
   return launch_fwd_prefill(*p, workspace, s);
 }
 
 int sdpa_b200_bwd(const sdpa_b200_params* p, void* workspace, size_t workspace_bytes, void* stream) {
   int st = validate_common(p);
   if (st != SDPA_B200_OK) return st;
+  if (p->head_dim > 128) {
+    set_error("the backward is built for head dims up to 128 (got %d)", p->head_dim);
+    return SDPA_B200_UNSUPPORTED;
+  }
   if (p->bias_t != nullptr) {
     auto bad = [](int64_t s) { return s < 0 || (s % 8) != 0; };
     if (p->bias == nullptr || !aligned16(p->bias_t) || bad(p->bias_t_batch_stride) || bad(p->bias_t_head_stride) ||
