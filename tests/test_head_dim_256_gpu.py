@@ -71,3 +71,56 @@ def test_forward_packed_head_dims_above_128(cuda_device, native_lib, lens, Hq, H
     o_ref, l_ref = orc.varlen_forward(q, k, v, cu, cu, causal=causal)
     orc.assert_close_bf16(out, o_ref, "out")
     orc.assert_close_lse(lse, l_ref)
+
+
+def check_grads(got, want):
+    for name, g, w in zip(("dq", "dk", "dv"), got, want):
+        assert g.shape == w.shape, name
+        orc.assert_close_grad_bf16(g, w, name)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Lq,Lk,D,causal", [
+    (4, 2, 2, 512, 512, 256, True),      # the reference's backward shapes (test_...py:728-935)
+    (4, 2, 2, 512, 512, 256, False),
+    (1, 2, 2, 1024, 512, 256, True),     # leading rows see no key: their dq is 0
+    (1, 2, 2, 512, 1024, 256, True),
+    (1, 1, 1, 64, 128, 256, False),
+    (1, 1, 1, 1, 1, 256, True),
+    (2, 4, 2, 333, 777, 256, True),      # ragged lengths, GQA: dk / dv summed over two query heads
+    (1, 8, 1, 200, 130, 192, False),     # MQA, padded head_dim
+    (2, 2, 2, 257, 255, 136, True),
+    (1, 2, 2, 130, 2100, 160, False),
+])
+def test_backward_head_dims_above_128(cuda_device, native_lib, B, Hq, Hkv, Lq, Lk, D, causal):
+    dev = cuda_device
+    q, k, v, dout = rand((B, Hq, Lq, D), 1), rand((B, Hkv, Lk, D), 2), rand((B, Hkv, Lk, D), 3), rand((B, Hq, Lq, D), 4)
+    qd, kd, vd, dd = q.to(dev), k.to(dev), v.to(dev), dout.to(dev)
+    out, lse = ops.gqa_prefill(qd, kd, vd, is_causal=causal)
+    dq, dk, dv = ops._dense_backward(dd, qd, kd, vd, out, lse, causal, D ** -0.5)
+    assert ops.device_status() == 0
+    o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=causal)
+    check_grads((dq, dk, dv), orc.cpu_sdpa_backward(dout, q, k, v, o_ref, l_ref, causal=causal))
+    # fixed summation order everywhere: the same call gives the same bits
+    dq2, dk2, dv2 = ops._dense_backward(dd, qd, kd, vd, out, lse, causal, D ** -0.5)
+    assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
+
+
+@pytest.mark.parametrize("lens,Hq,Hkv,D,causal", [
+    ([100, 300, 257, 128], 4, 2, 256, True),
+    ([1, 2, 255, 64, 65], 2, 2, 256, False),
+    ([640, 130], 4, 1, 192, True),
+])
+def test_backward_packed_head_dims_above_128(cuda_device, native_lib, lens, Hq, Hkv, D, causal):
+    dev = cuda_device
+    total = sum(lens)
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    q, k, v, dout = rand((total, Hq, D), 1), rand((total, Hkv, D), 2), rand((total, Hkv, D), 3), rand((total, Hq, D), 4)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+    qd, kd, vd = q.to(dev), k.to(dev), v.to(dev)
+    out, lse, seed, off, _ = ops._flash_attention_forward(qd, kd, vd, cu_t, cu_t, max(lens), max(lens), 0.0, causal, False)
+    dq, dk, dv = ops._flash_attention_backward(dout.to(dev), qd, kd, vd, out, lse, cu_t, cu_t, max(lens), max(lens), 0.0, causal,
+                                               seed, off)
+    assert ops.device_status() == 0
+    check_grads((dq, dk, dv), orc.varlen_backward(dout, q, k, v, cu, cu, causal=causal))

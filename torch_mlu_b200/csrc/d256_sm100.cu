@@ -408,6 +408,517 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
   if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, static_cast<uint32_t>(SDPA_B200_DEVICE_TIMEOUT));
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Backward. Three kernels from one template, all with 128 stationary rows in tensor memory and 64-row streamed blocks:
+//   kDV: CTA = 128 keys. X1 = K (TMEM). Streams (Q, dO) blocks of 64 queries of every query head of the KV head.
+//        S^T = K Q^T; P^T = exp2(S^T c - lse2[q]); dV += P^T dO.                                TMEM: K | S0 S1 | dV
+//   kDK: CTA = 128 keys. X1 = K (TMEM), X2 = V (shared memory, 64 KB). Streams (Q, dO).
+//        S^T = K Q^T, dP^T = V dO^T; dS^T = P^T o (dP^T - delta[q]); dK += dS^T Q.               TMEM: K | TA TB | dK
+//   kDQ: CTA = 128 queries. X1 = Q (TMEM), X2 = dO (shared memory). Streams (K, V) blocks of 64 keys.
+//        S = Q K^T, dP = dO V^T; dS = P o (dP - delta[row]); dQ += dS K.                          TMEM: Q | TA TB | dQ
+// A 128 x 256 fp32 accumulator is half the tensor memory, so every kernel owns exactly one; dK and dV therefore come from
+// two kernels that both form S (9 GEMM-equivalents per tile pair against the 5 of the algorithm). The score GEMM with X2
+// reads both operands from shared memory (N = 64: 48 cycles per MMA instead of 32).
+// Score buffers rotate as in the 128-column kernels: S(i) in T[i&1], dP(i) in the other one; the 16-bit dS goes over the
+// front of S(i); S(i+1) takes dP(i)'s buffer once the compute warps have read it, dP(i+1) follows the accumulation of
+// item i in the issuer's own order.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kDV = 0, kDK = 1, kDQ = 2;
+
+__host__ __device__ constexpr int ring_slots_for(int mode) { return mode == kDV ? 6 : (mode == kDK ? 4 : 5); }
+__host__ __device__ constexpr uint32_t ring_base_for(int mode) { return mode == kDV ? 0u : 2u * kSlotBytes; }  // behind X2
+// per ring slot: lse2[64], delta[64] of the streamed queries (kDV, kDK). Those two kernels use six of the seven 32 KB
+// slots (kDV: ring of 6; kDK: V + ring of 4), so the vectors live at the start of the seventh.
+constexpr uint32_t kSmemVecs = 6 * kSlotBytes;
+constexpr uint32_t kSmemBytesBwd256 = kSmemBytesD256;
+static_assert(ring_base_for(kDQ) + ring_slots_for(kDQ) * kSlotBytes <= kSmemBars && 6 * 512 <= kSlotBytes,
+              "shared memory map does not fit");
+
+// barrier offsets of the backward kernels (bytes from kSmemBars); kBFull / kBEmpty / kBAReady / kBStage as above
+constexpr uint32_t kBX2Full = kBAReady + 8;
+constexpr uint32_t kBTFull = kBX2Full + 8;     // 2: the score GEMM into T[b] has finished
+constexpr uint32_t kBDFree = kBTFull + 16;     // 4 warps: dP has been read out of TMEM
+constexpr uint32_t kBWFull = kBDFree + 8;      // 4 warps: the 16-bit P / dS is in TMEM
+constexpr uint32_t kBAccFull = kBWFull + 8;
+constexpr uint32_t kBStageB = kBAccFull + 8;   // 4 warps
+constexpr uint32_t kTmemPtrB = kBStageB + 8;
+constexpr uint32_t kAbortWordB = kTmemPtrB + 4;
+static_assert(kAbortWordB + 4 <= 512, "barrier block too small");
+
+struct Bwd256Params {
+  const uint16_t* x1;        // rows kept in tensor memory: K (kDV, kDK) or Q (kDQ)
+  uint16_t* out;             // dV, dK or dQ
+  const float* lse2;         // padded [batch, heads_q, lq_pad]
+  const float* delta;
+  const int32_t* cu_q;
+  const int32_t* cu_k;
+  uint32_t* status;
+  int64_t x1_batch_stride, x1_head_stride, x1_row_stride;
+  int64_t o_batch_stride, o_head_stride, o_row_stride;
+  int seqlen_q, seqlen_k, heads_q, heads_kv, kv_group, head_dim, lq_pad;
+  int num_row_blocks, num_bh, heads_x, heads_per_wave;
+  float scale, scale_log2;
+  int is_causal;
+};
+
+template <bool kF16>
+constexpr uint32_t kIdescS64SS = umma_idesc_16(kRowsA, kRowsB, false, false, kF16);
+
+// T (128 x 64) = X2 (shared memory, 128 rows x 256 as four boxes of 64 columns) * Y^T, Y = one streamed block, both K-major
+template <bool kF16>
+__device__ __forceinline__ void issue_scores_ss(uint32_t t, uint32_t x2_smem, uint32_t slot) {
+#pragma unroll
+  for (int ks = 0; ks < kWide / 16; ++ks) {
+    const uint32_t a_lo = umma_desc_lo_kmajor(x2_smem + (ks >> 2) * (kRowsA * 128) + (ks & 3) * 32);
+    const uint32_t b_lo = umma_desc_lo_kmajor(slot + (ks >> 2) * kBoxBytes + (ks & 3) * 32);
+    umma_ss_lo_acc<kIdescS64SS<kF16>>(t, a_lo, b_lo, ks > 0 ? 1u : 0u);
+  }
+}
+
+template <int kMode, bool kF16>
+__global__ void __launch_bounds__(192, 1)
+bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant__ CUtensorMap tm_y1,
+                const __grid_constant__ CUtensorMap tm_y2, const __grid_constant__ CUtensorMap tm_out,
+                const Bwd256Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr int kRing = ring_slots_for(kMode);
+  constexpr uint32_t kRingBase = ring_base_for(kMode);
+  constexpr bool kKeys = kMode != kDQ;  // the stationary rows are keys
+
+  // CTA order as in the forward: groups of heads whose streamed tensors fit L2, heaviest row blocks first
+  // (key block 0 sees every query; the last query block sees every key)
+  int b, hx, xb;
+  {
+    const int per_group = p.heads_per_wave * p.num_row_blocks;
+    const int grp = blockIdx.x / per_group;
+    const int w = blockIdx.x - grp * per_group;
+    const int size = min(p.heads_per_wave, p.num_bh - grp * p.heads_per_wave);
+    const int rank = w / size;
+    const int bh = grp * p.heads_per_wave + (w - rank * size);
+    if (rank >= p.num_row_blocks) return;
+    xb = kKeys ? rank : p.num_row_blocks - 1 - rank;
+    b = bh / p.heads_x;
+    hx = bh - b * p.heads_x;
+  }
+  int q_off = 0, k_off = 0, len_q = p.seqlen_q, len_k = p.seqlen_k, bcoord = b;
+  if (p.cu_q != nullptr) {
+    q_off = p.cu_q[b];
+    len_q = p.cu_q[b + 1] - q_off;
+    k_off = p.cu_k[b];
+    len_k = p.cu_k[b + 1] - k_off;
+    bcoord = 0;
+  }
+  const int causal_off = len_k - len_q;
+  const int len_x = kKeys ? len_k : len_q;
+  const int x0 = xb * kRowsA;
+  if (x0 >= len_x) return;
+  const int x_off = kKeys ? k_off : q_off;
+  const int y_off = kKeys ? q_off : k_off;
+
+  // streamed 64-row blocks [y_lo, y_hi) per head, and heads per CTA
+  int y_lo = 0, y_hi;
+  if (kKeys) {
+    y_hi = (len_q + kRowsB - 1) / kRowsB;
+    if (p.is_causal) {
+      y_lo = max(0, (x0 - causal_off) / kRowsB);  // first query block with a row >= x0 - off
+      if (x0 - causal_off > len_q - 1) y_lo = y_hi;
+    }
+  } else {
+    int vis_end = len_k;
+    if (p.is_causal) vis_end = min(len_k, x0 + kRowsA + causal_off);
+    y_hi = vis_end > 0 ? (vis_end + kRowsB - 1) / kRowsB : 0;
+  }
+  const int blocks_per_head = max(0, y_hi - y_lo);
+  const int heads_here = kKeys ? p.kv_group : 1;
+  const int n_items = blocks_per_head * heads_here;
+  const int hkv = kKeys ? hx : hx / p.kv_group;
+
+  const uint32_t bar = base + kSmemBars;
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kSmemBars + kAbortWordB);
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + kSmemBars + kTmemPtrB);
+
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tm_y1);
+    tma_prefetch_desc(&tm_y2);
+    for (int s = 0; s < kRing; ++s) {
+      mbar_init(bar + kBFull + 8 * s, 1);
+      mbar_init(bar + kBEmpty + 8 * s, 1);
+    }
+    mbar_init(bar + kBAReady, 4);
+    mbar_init(bar + kBX2Full, 1);
+    mbar_init(bar + kBTFull, 1);
+    mbar_init(bar + kBTFull + 8, 1);
+    mbar_init(bar + kBDFree, 4);
+    mbar_init(bar + kBWFull, 4);
+    mbar_init(bar + kBAccFull, 1);
+    mbar_init(bar + kBStageB, 4);
+    *abort_flag = 0;
+    fence_mbar_init();
+    if (kMode != kDV && n_items > 0) {
+      // X2: 128 rows x 256 columns as four boxes of 128 rows x 64 columns at the start of shared memory
+      mbar_arrive_expect_tx(bar + kBX2Full, 4 * kRowsA * 128);
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        tma_load_4d(base + c * (kRowsA * 128), &tm_x2, bar + kBX2Full, c * 64, x_off + x0, kKeys ? hkv : hx, bcoord);
+    }
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(base + kSmemBars + kTmemPtrB, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  const uint32_t t_x1 = tmem_base, t_a = tmem_base + 128, t_b = tmem_base + 192, t_acc = tmem_base + 256;
+  // ring tile t: Y1(t/2) if even, Y2(t/2) if odd; item i = (head index i / blocks_per_head, block y_lo + i % blocks_per_head)
+  auto slot_index = [&](int t) { return t % kRing; };
+  auto slot_addr = [&](int t) { return base + kRingBase + (t % kRing) * kSlotBytes; };
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int t = 0; t < 2 * n_items; ++t) {
+        const int i = t >> 1;
+        const int s = slot_index(t);
+        if (!mbar_wait(bar + kBEmpty + 8 * s, ((static_cast<uint32_t>(t / kRing)) & 1u) ^ 1u, abort_flag)) break;
+        const int hi = i / blocks_per_head;
+        const int yb = y_lo + (i - hi * blocks_per_head);
+        const int hy = kKeys ? hx * p.kv_group + hi : hkv;  // streamed head: a query head of the group, or the KV head
+        const uint32_t full = bar + kBFull + 8 * s;
+        const uint32_t dst = slot_addr(t);
+        const int row = y_off + yb * kRowsB;
+        const bool first = (t & 1) == 0;
+        if (kKeys && first) {
+          mbar_arrive_expect_tx(full, kSlotBytes + 512);
+          const size_t vec = (static_cast<size_t>(b) * p.heads_q + hy) * p.lq_pad + static_cast<size_t>(yb) * kRowsB;
+          const uint32_t vdst = base + kSmemVecs + s * 512;
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(vdst),
+                       "l"(p.lse2 + vec), "r"(256), "r"(full) : "memory");
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(vdst + 256),
+                       "l"(p.delta + vec), "r"(256), "r"(full) : "memory");
+        } else {
+          mbar_arrive_expect_tx(full, kSlotBytes);
+        }
+        const CUtensorMap* tm = first ? &tm_y1 : &tm_y2;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tma_load_4d(dst + c * kBoxBytes, tm, full, c * 64, row, hy, bcoord);
+      }
+      drain_after_abort(abort_flag);
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_items > 0) {
+      auto wait_full = [&](int t) { return mbar_wait(bar + kBFull + 8 * slot_index(t), (t / kRing) & 1, abort_flag); };
+      auto release = [&](int t) { umma_commit(bar + kBEmpty + 8 * slot_index(t)); };
+      auto t_buf = [&](int k) { return (k & 1) ? t_b : t_a; };
+      bool ok = mbar_wait(bar + kBAReady, 0, abort_flag);
+      if (kMode != kDV) ok = ok && mbar_wait(bar + kBX2Full, 0, abort_flag);
+      if (kMode == kDV) {
+        // S(i) in T[i&1]; P over its front; dV += P^T dO. S(i+1) goes out ahead, S(i+2) behind the accumulation of item i.
+        auto issue_s = [&](int i) {
+          tc_fence_after_sync();
+          issue_scores<kF16>(t_buf(i), t_x1, slot_addr(2 * i));
+          umma_commit(bar + kBTFull + 8 * (i & 1));
+        };
+        ok = ok && wait_full(0);
+        if (ok) issue_s(0);
+        if (ok && n_items > 1) {
+          ok = wait_full(2);
+          if (ok) issue_s(1);
+        }
+        for (int i = 0; ok && i < n_items; ++i) {
+          ok = mbar_wait(bar + kBWFull, i & 1, abort_flag) && wait_full(2 * i + 1);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_accumulate256<kF16>(t_acc, t_buf(i), slot_addr(2 * i + 1), i > 0);
+          // the Q block goes with it: its slot also carries the per-query vectors the compute warps have just used
+          release(2 * i);
+          release(2 * i + 1);
+          if (i == n_items - 1) umma_commit(bar + kBAccFull);
+          if (i + 2 < n_items) {
+            ok = wait_full(2 * i + 4);
+            if (!ok) break;
+            issue_s(i + 2);
+          }
+        }
+      } else {
+        // S(i) in T[i&1], dP(i) in T[(i&1)^1]
+        ok = ok && wait_full(0);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_scores<kF16>(t_buf(0), t_x1, slot_addr(0));
+          umma_commit(bar + kBTFull);
+        }
+        ok = ok && wait_full(1);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_scores_ss<kF16>(t_buf(1), base, slot_addr(1));
+          umma_commit(bar + kBTFull + 8);
+          release(1);  // the Y2 block is read by this GEMM only
+        }
+        for (int i = 0; ok && i < n_items; ++i) {
+          const bool more = i + 1 < n_items;
+          // dP(i) has left TMEM once the compute warps have read it: its buffer takes S(i+1)
+          ok = mbar_wait(bar + kBDFree, i & 1, abort_flag);
+          if (!ok) break;
+          if (more) {
+            ok = wait_full(2 * i + 2);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_scores<kF16>(t_buf(i + 1), t_x1, slot_addr(2 * i + 2));
+            umma_commit(bar + kBTFull + 8 * ((i + 1) & 1));
+          }
+          ok = mbar_wait(bar + kBWFull, i & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_accumulate256<kF16>(t_acc, t_buf(i), slot_addr(2 * i), i > 0);  // += dS Y1
+          release(2 * i);
+          if (!more) {
+            umma_commit(bar + kBAccFull);
+          } else {
+            ok = wait_full(2 * i + 3);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_scores_ss<kF16>(t_buf(i), base, slot_addr(2 * i + 3));  // dP(i+1) over S(i) / dS(i), behind the accumulation
+            umma_commit(bar + kBTFull + 8 * (i & 1));
+            release(2 * i + 3);
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ compute warps (thread = stationary row)
+    const int r = warp * 32 + lane;
+    const int xr = x0 + r;
+    const bool valid = xr < len_x;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    {
+      const uint16_t* xrow = nullptr;
+      if (valid)
+        xrow = p.x1 + ((p.cu_q != nullptr) ? static_cast<int64_t>(x_off + xr) * p.x1_row_stride
+                                           : b * p.x1_batch_stride + static_cast<int64_t>(xr) * p.x1_row_stride) +
+               (kKeys ? hkv : hx) * p.x1_head_stride;
+      row_to_tmem(t_x1 + lane_base, xrow, p.head_dim);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar + kBAReady);
+    }
+    const float c = p.scale_log2;
+    float my_lse2 = INFINITY, my_delta = 0.f;  // kDQ: this row's own values
+    if (kMode == kDQ && valid) {
+      const size_t vec = (static_cast<size_t>(b) * p.heads_q + hx) * p.lq_pad + xr;
+      my_lse2 = p.lse2[vec];
+      my_delta = p.delta[vec];
+    }
+    bool ok = true;
+    // phase counters of the two score barriers (a buffer receives S and dP alternately)
+    uint32_t seen[2] = {0u, 0u};
+    for (int i = 0; i < n_items; ++i) {
+      const int hi = i / blocks_per_head;
+      const int y0 = (y_lo + (i - hi * blocks_per_head)) * kRowsB;
+      const int sb = i & 1;                              // buffer of S(i)
+      const int db = (kMode == kDV) ? sb : (sb ^ 1);     // buffer of dP(i)
+      const uint32_t t_s = ((sb) ? t_b : t_a) + lane_base;
+      const uint32_t t_d = ((db) ? t_b : t_a) + lane_base;
+      ok = mbar_wait(bar + kBTFull + 8 * sb, seen[sb] & 1u, abort_flag);
+      ++seen[sb];
+      if (kKeys) ok = ok && mbar_wait(bar + kBFull + 8 * slot_index(2 * i), ((2 * i) / kRing) & 1, abort_flag);  // the vectors
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const float* vec_lse = reinterpret_cast<const float*>(smem + kSmemVecs + slot_index(2 * i) * 512);
+      const float* vec_delta = vec_lse + 64;
+      // visibility of element (row xr, column y0 + j)
+      //   keys as rows : key xr, query y0+j : visible iff j >= xr - off - y0 (and the key exists)
+      //   queries      : query xr, key y0+j : visible iff y0 + j <= xr + off and y0 + j < len_k
+      int j_lo = 0, j_hi = kRowsB;
+      if (kKeys) {
+        if (p.is_causal) j_lo = xr - causal_off - y0;
+        if (!valid) j_lo = kRowsB;  // a row past the last key holds zeros (or, packed, the next sequence's key)
+      } else {
+        j_hi = len_k - y0;
+        if (p.is_causal) j_hi = min(j_hi, xr + causal_off + 1 - y0);
+      }
+      float pr[kRowsB];
+      {
+        uint32_t a[kRowsB];
+        tmem_ld_x64(t_s, a);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < kRowsB; ++j) {
+          const float l2 = kKeys ? vec_lse[j] : my_lse2;
+          pr[j] = ex2_approx(fmaf(__uint_as_float(a[j]), c, -l2));
+        }
+        if (__any_sync(0xffffffffu, j_lo > 0 || j_hi < kRowsB)) {
+#pragma unroll
+          for (int j = 0; j < kRowsB; ++j) pr[j] = (j >= j_lo && j < j_hi) ? pr[j] : 0.f;
+        }
+      }
+      uint32_t w[kRowsB / 2];
+      if (kMode == kDV) {
+#pragma unroll
+        for (int j2 = 0; j2 < kRowsB / 2; ++j2) w[j2] = pack_16x2<kF16>(pr[2 * j2], pr[2 * j2 + 1]);
+      } else {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar + kBTFull + 8 * db, seen[db] & 1u, abort_flag));
+        ++seen[db];
+        if (!ok) break;
+        tc_fence_after_sync();
+        uint32_t d[kRowsB];
+        tmem_ld_x64(t_d, d);
+        tmem_wait_ld();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar + kBDFree);  // the dP buffer may be overwritten
+#pragma unroll
+        for (int j2 = 0; j2 < kRowsB / 2; ++j2) {
+          const float dl0 = kKeys ? vec_delta[2 * j2] : my_delta;
+          const float dl1 = kKeys ? vec_delta[2 * j2 + 1] : my_delta;
+          w[j2] = pack_16x2<kF16>(pr[2 * j2] * (__uint_as_float(d[2 * j2]) - dl0),
+                                  pr[2 * j2 + 1] * (__uint_as_float(d[2 * j2 + 1]) - dl1));
+        }
+      }
+      tmem_st_x32(t_s, w);  // over the front of S(i): 32 columns = 64 streamed rows
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar + kBWFull);
+    }
+
+    // ---- epilogue: accumulator -> scale -> 16 bit -> global
+    if (ok && n_items > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar + kBAccFull, 0, abort_flag));
+    if (ok) {
+      tc_fence_after_sync();
+      const float mul = (kMode == kDV) ? 1.f : p.scale;
+      const bool use_tma = (p.cu_q == nullptr) || (x0 + kRowsA <= len_x);
+      uint16_t* orow = p.out + ((p.cu_q != nullptr) ? static_cast<int64_t>(x_off + xr) * p.o_row_stride
+                                                    : b * p.o_batch_stride + static_cast<int64_t>(xr) * p.o_row_stride) +
+                       hx * p.o_head_stride;
+#pragma unroll
+      for (int cc = 0; cc < kWide / 32; ++cc) {
+        uint32_t o[32];
+        if (n_items > 0) {
+          tmem_ld_x32(t_acc + lane_base + cc * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = 0u;
+        }
+        uint4 wv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          wv[j].x = pack_16x2<kF16>(__uint_as_float(o[8 * j]) * mul, __uint_as_float(o[8 * j + 1]) * mul);
+          wv[j].y = pack_16x2<kF16>(__uint_as_float(o[8 * j + 2]) * mul, __uint_as_float(o[8 * j + 3]) * mul);
+          wv[j].z = pack_16x2<kF16>(__uint_as_float(o[8 * j + 4]) * mul, __uint_as_float(o[8 * j + 5]) * mul);
+          wv[j].w = pack_16x2<kF16>(__uint_as_float(o[8 * j + 6]) * mul, __uint_as_float(o[8 * j + 7]) * mul);
+        }
+        const int col = cc * 32;
+        if (use_tma) {
+          // staged behind X2 (the ring is idle by now): four boxes of 128 rows x 64 columns
+          uint8_t* srow = smem + kRingBase + (col >> 6) * (kRowsA * 128) + r * 128;
+          const int chunk0 = (col & 63) >> 3;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(srow + (((chunk0 + j) ^ (r & 7)) << 4)) = wv[j];
+        } else if (valid) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (col + 8 * j < p.head_dim) *reinterpret_cast<uint4*>(orow + col + 8 * j) = wv[j];
+        }
+      }
+      if (use_tma) {
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar + kBStageB);
+        if (threadIdx.x == 0) {
+          if (mbar_wait(bar + kBStageB, 0, abort_flag)) {
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4)
+              tma_store_4d(&tm_out, base + kRingBase + c4 * (kRowsA * 128), c4 * 64, x_off + x0, hx, bcoord);
+            tma_store_commit();
+            tma_store_wait_read();
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0) atomicExch(p.status, static_cast<uint32_t>(SDPA_B200_DEVICE_TIMEOUT));
+}
+
+// delta[row] = sum_d dO[row, d] O[row, d] and lse2 = lse * log2(e) into the padded [batch, heads_q, lq_pad] vectors (padding
+// rows: lse2 = +inf, delta = 0). One warp per row: 32 lanes x 8 elements cover 256 columns.
+struct Pre256Params {
+  const uint16_t* out;
+  const uint16_t* dout;
+  const float* lse;
+  float* lse2;
+  float* delta;
+  const int32_t* cu_q;
+  int64_t o_batch_stride, o_head_stride, o_row_stride;
+  int64_t do_batch_stride, do_head_stride, do_row_stride;
+  int seqlen_q, total_q, heads_q, lq_pad, head_dim;
+};
+
+template <bool kF16>
+__global__ void __launch_bounds__(256) bwd_d256_preprocess_kernel(const Pre256Params p) {
+  const int h = blockIdx.x, b = blockIdx.z;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.y * 8 + (threadIdx.x >> 5);
+  if (row >= p.lq_pad) return;
+  int q_off = 0, len_q = p.seqlen_q;
+  if (p.cu_q != nullptr) {
+    q_off = p.cu_q[b];
+    len_q = p.cu_q[b + 1] - q_off;
+  }
+  float acc = 0.f;
+  if (row < len_q && lane * 8 < p.head_dim) {
+    const uint16_t* o;
+    const uint16_t* dout;
+    if (p.cu_q != nullptr) {
+      o = p.out + static_cast<int64_t>(q_off + row) * p.o_row_stride + h * p.o_head_stride;
+      dout = p.dout + static_cast<int64_t>(q_off + row) * p.do_row_stride + h * p.do_head_stride;
+    } else {
+      o = p.out + b * p.o_batch_stride + h * p.o_head_stride + static_cast<int64_t>(row) * p.o_row_stride;
+      dout = p.dout + b * p.do_batch_stride + h * p.do_head_stride + static_cast<int64_t>(row) * p.do_row_stride;
+    }
+    const uint4 ov = *reinterpret_cast<const uint4*>(o + lane * 8);
+    const uint4 dv = *reinterpret_cast<const uint4*>(dout + lane * 8);
+    const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w}, dw[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 a = unpack_16x2<kF16>(ow[i]), d = unpack_16x2<kF16>(dw[i]);
+      acc += a.x * d.x + a.y * d.y;
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) {
+    const size_t dst = (static_cast<size_t>(b) * p.heads_q + h) * p.lq_pad + row;
+    if (row < len_q) {
+      const float lse = (p.cu_q != nullptr) ? p.lse[static_cast<size_t>(h) * p.total_q + q_off + row]
+                                            : p.lse[(static_cast<size_t>(b) * p.heads_q + h) * p.seqlen_q + row];
+      p.lse2[dst] = lse * 1.4426950408889634f;  // +inf stays +inf
+      p.delta[dst] = acc;
+    } else {
+      p.lse2[dst] = INFINITY;
+      p.delta[dst] = 0.f;
+    }
+  }
+}
+
 // heads per group so that the streamed K + V of a group stay within ~48 MB of L2
 int heads_per_wave_for(double bytes_per_head, int num_bh) {
   int hpw = static_cast<int>((48.0 * 1024 * 1024) / bytes_per_head);
@@ -416,6 +927,129 @@ int heads_per_wave_for(double bytes_per_head, int num_bh) {
 }
 
 }  // namespace
+
+size_t bwd_d256_workspace_bytes(const sdpa_b200_params& p) {
+  const size_t lq_pad = (static_cast<size_t>(p.max_seqlen_q) + kRowsA - 1) / kRowsA * kRowsA;
+  return 2 * static_cast<size_t>(p.batch) * p.heads_q * lq_pad * sizeof(float);
+}
+
+int launch_bwd_d256(const sdpa_b200_params& p, void* workspace, cudaStream_t stream) {
+  const bool f16 = p.dtype == SDPA_B200_F16;
+  const bool varlen = p.cu_seqlens_q != nullptr;
+  const int lq_pad = (p.max_seqlen_q + kRowsA - 1) / kRowsA * kRowsA;
+  const size_t vec_elems = static_cast<size_t>(p.batch) * p.heads_q * lq_pad;
+  float* lse2 = reinterpret_cast<float*>(static_cast<char*>(workspace) + kWorkspaceHeaderBytes);
+  float* delta = lse2 + vec_elems;
+
+  Pre256Params pre;
+  pre.out = static_cast<const uint16_t*>(p.out);
+  pre.dout = static_cast<const uint16_t*>(p.dout);
+  pre.lse = p.lse;
+  pre.lse2 = lse2;
+  pre.delta = delta;
+  pre.cu_q = p.cu_seqlens_q;
+  pre.o_batch_stride = p.o_batch_stride;
+  pre.o_head_stride = p.o_head_stride;
+  pre.o_row_stride = p.o_row_stride;
+  pre.do_batch_stride = p.do_batch_stride;
+  pre.do_head_stride = p.do_head_stride;
+  pre.do_row_stride = p.do_row_stride;
+  pre.seqlen_q = p.max_seqlen_q;
+  pre.total_q = p.total_q;
+  pre.heads_q = p.heads_q;
+  pre.lq_pad = lq_pad;
+  pre.head_dim = p.head_dim;
+  const dim3 pre_grid(p.heads_q, lq_pad / 8, p.batch);
+  if (f16) bwd_d256_preprocess_kernel<true><<<pre_grid, 256, 0, stream>>>(pre);
+  else bwd_d256_preprocess_kernel<false><<<pre_grid, 256, 0, stream>>>(pre);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("head_dim 256 backward pre-pass: launch failed: %s", cudaGetErrorString(err));
+    return SDPA_B200_LAUNCH_FAILED;
+  }
+  count_launch();
+
+  const int64_t rows_q = varlen ? p.total_q : p.max_seqlen_q;
+  const int64_t rows_k = varlen ? p.total_k : p.max_seqlen_k;
+  const int64_t nb = varlen ? 1 : p.batch;
+  // streamed blocks (64 rows), shared-memory resident tiles and outputs (128 rows)
+  CUtensorMap q64, k64, v64, do64, v128, do128, dq128, dk128, dv128;
+  int st;
+  auto map = [&](CUtensorMap* m, const void* ptr, int64_t rows, int heads, int64_t rs, int64_t hs, int64_t bs, int box) {
+    return make_tensor_map_16(f16, m, ptr, p.head_dim, rows, heads, nb, rs, hs, bs, box);
+  };
+  if ((st = map(&q64, p.q, rows_q, p.heads_q, p.q_row_stride, p.q_head_stride, p.q_batch_stride, kRowsB)) != SDPA_B200_OK) return st;
+  if ((st = map(&k64, p.k, rows_k, p.heads_kv, p.k_row_stride, p.k_head_stride, p.k_batch_stride, kRowsB)) != SDPA_B200_OK) return st;
+  if ((st = map(&v64, p.v, rows_k, p.heads_kv, p.v_row_stride, p.v_head_stride, p.v_batch_stride, kRowsB)) != SDPA_B200_OK) return st;
+  if ((st = map(&do64, p.dout, rows_q, p.heads_q, p.do_row_stride, p.do_head_stride, p.do_batch_stride, kRowsB)) != SDPA_B200_OK) return st;
+  if ((st = map(&v128, p.v, rows_k, p.heads_kv, p.v_row_stride, p.v_head_stride, p.v_batch_stride, kRowsA)) != SDPA_B200_OK) return st;
+  if ((st = map(&do128, p.dout, rows_q, p.heads_q, p.do_row_stride, p.do_head_stride, p.do_batch_stride, kRowsA)) != SDPA_B200_OK) return st;
+  if ((st = map(&dq128, p.dq, rows_q, p.heads_q, p.dq_row_stride, p.dq_head_stride, p.dq_batch_stride, kRowsA)) != SDPA_B200_OK) return st;
+  if ((st = map(&dk128, p.dk, rows_k, p.heads_kv, p.dk_row_stride, p.dk_head_stride, p.dk_batch_stride, kRowsA)) != SDPA_B200_OK) return st;
+  if ((st = map(&dv128, p.dv, rows_k, p.heads_kv, p.dv_row_stride, p.dv_head_stride, p.dv_batch_stride, kRowsA)) != SDPA_B200_OK) return st;
+
+  Bwd256Params kp;
+  kp.lse2 = lse2;
+  kp.delta = delta;
+  kp.cu_q = p.cu_seqlens_q;
+  kp.cu_k = p.cu_seqlens_k;
+  kp.status = p.device_status != nullptr ? p.device_status : static_cast<uint32_t*>(workspace);
+  kp.seqlen_q = p.max_seqlen_q;
+  kp.seqlen_k = p.max_seqlen_k;
+  kp.heads_q = p.heads_q;
+  kp.heads_kv = p.heads_kv;
+  kp.kv_group = p.heads_q / p.heads_kv;
+  kp.head_dim = p.head_dim;
+  kp.lq_pad = lq_pad;
+  kp.scale = p.softmax_scale;
+  kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
+  kp.is_causal = p.is_causal;
+
+  auto launch = [&](int mode, const CUtensorMap& x2, const CUtensorMap& y1, const CUtensorMap& y2, const CUtensorMap& out) {
+    void (*kernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const Bwd256Params);
+    if (mode == kDV) kernel = f16 ? bwd_d256_kernel<kDV, true> : bwd_d256_kernel<kDV, false>;
+    else if (mode == kDK) kernel = f16 ? bwd_d256_kernel<kDK, true> : bwd_d256_kernel<kDK, false>;
+    else kernel = f16 ? bwd_d256_kernel<kDQ, true> : bwd_d256_kernel<kDQ, false>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytesBwd256);
+    if (e != cudaSuccess) {
+      set_error("head_dim 256 backward: cudaFuncSetAttribute(%u bytes smem): %s", kSmemBytesBwd256, cudaGetErrorString(e));
+      return static_cast<int>(SDPA_B200_LAUNCH_FAILED);
+    }
+    const bool keys = mode != kDQ;
+    kp.heads_x = keys ? p.heads_kv : p.heads_q;
+    kp.num_bh = p.batch * kp.heads_x;
+    kp.num_row_blocks = ((keys ? p.max_seqlen_k : p.max_seqlen_q) + kRowsA - 1) / kRowsA;
+    // bytes one stationary head streams: Q + dO of its group (keys), or K + V (queries)
+    const double streamed = 2.0 * (keys ? p.max_seqlen_q : p.max_seqlen_k) * p.head_dim * 2 * (keys ? kp.kv_group : 1);
+    kp.heads_per_wave = heads_per_wave_for(streamed, kp.num_bh);
+    const int groups = (kp.num_bh + kp.heads_per_wave - 1) / kp.heads_per_wave;
+    const int grid = groups * kp.heads_per_wave * kp.num_row_blocks;
+    kernel<<<grid, 192, kSmemBytesBwd256, stream>>>(x2, y1, y2, out, kp);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      set_error("head_dim 256 backward (kernel %d): launch failed: %s", mode, cudaGetErrorString(e));
+      return static_cast<int>(SDPA_B200_LAUNCH_FAILED);
+    }
+    count_launch();
+    return static_cast<int>(SDPA_B200_OK);
+  };
+  auto set_io = [&](const void* x1, int64_t bs, int64_t hs, int64_t rs, void* out, int64_t obs, int64_t ohs, int64_t ors) {
+    kp.x1 = static_cast<const uint16_t*>(x1);
+    kp.x1_batch_stride = bs;
+    kp.x1_head_stride = hs;
+    kp.x1_row_stride = rs;
+    kp.out = static_cast<uint16_t*>(out);
+    kp.o_batch_stride = obs;
+    kp.o_head_stride = ohs;
+    kp.o_row_stride = ors;
+  };
+  set_io(p.k, p.k_batch_stride, p.k_head_stride, p.k_row_stride, p.dv, p.dv_batch_stride, p.dv_head_stride, p.dv_row_stride);
+  if ((st = launch(kDV, v128 /*unused*/, q64, do64, dv128)) != SDPA_B200_OK) return st;
+  set_io(p.k, p.k_batch_stride, p.k_head_stride, p.k_row_stride, p.dk, p.dk_batch_stride, p.dk_head_stride, p.dk_row_stride);
+  if ((st = launch(kDK, v128, q64, do64, dk128)) != SDPA_B200_OK) return st;
+  set_io(p.q, p.q_batch_stride, p.q_head_stride, p.q_row_stride, p.dq, p.dq_batch_stride, p.dq_head_stride, p.dq_row_stride);
+  return launch(kDQ, do128, k64, v64, dq128);
+}
 
 int launch_fwd_d256(const sdpa_b200_params& p, void* workspace, cudaStream_t stream) {
   const bool f16 = p.dtype == SDPA_B200_F16;

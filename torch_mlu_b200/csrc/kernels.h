@@ -28,6 +28,9 @@ int launch_fwd_prefill(const sdpa_b200_params& p, void* workspace, cudaStream_t 
 
 // Forward for head dims above 128 (up to 256): one CTA per 128 query rows, Q in tensor memory (d256_sm100.cu).
 int launch_fwd_d256(const sdpa_b200_params& p, void* workspace, cudaStream_t stream);
+// Backward for the same head dims: a pre-pass and one kernel each for dV, dK and dQ (d256_sm100.cu).
+size_t bwd_d256_workspace_bytes(const sdpa_b200_params& p);
+int launch_bwd_d256(const sdpa_b200_params& p, void* workspace, cudaStream_t stream);
 
 // Number of SMs of the current device (cached per device), <= 0 on error.
 int sm_count();

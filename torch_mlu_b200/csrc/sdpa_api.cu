@@ -366,7 +366,7 @@ int sdpa_b200_bwd_workspace_bytes(const sdpa_b200_params* p, size_t* bytes) {
   }
   int st = validate_common(p);
   if (st != SDPA_B200_OK) return st;
-  *bytes = kWorkspaceHeaderBytes + bwd_workspace_bytes(*p);
+  *bytes = kWorkspaceHeaderBytes + (p->head_dim > 128 ? bwd_d256_workspace_bytes(*p) : bwd_workspace_bytes(*p));
   return SDPA_B200_OK;
 }
 
@@ -394,10 +394,7 @@ int sdpa_b200_fwd(const sdpa_b200_params* p, void* workspace, size_t workspace_b
 int sdpa_b200_bwd(const sdpa_b200_params* p, void* workspace, size_t workspace_bytes, void* stream) {
   int st = validate_common(p);
   if (st != SDPA_B200_OK) return st;
-  if (p->head_dim > 128) {
-    set_error("the backward is built for head dims up to 128 (got %d)", p->head_dim);
-    return SDPA_B200_UNSUPPORTED;
-  }
+
   if (p->bias_t != nullptr) {
     auto bad = [](int64_t s) { return s < 0 || (s % 8) != 0; };
     if (p->bias == nullptr || !aligned16(p->bias_t) || bad(p->bias_t_batch_stride) || bad(p->bias_t_head_stride) ||
@@ -433,7 +430,7 @@ int sdpa_b200_bwd(const sdpa_b200_params* p, void* workspace, size_t workspace_b
   if ((st = check_tensor("dv", p->dv, p->dv_batch_stride, p->dv_head_stride, p->dv_row_stride, varlen, p->batch,
                          p->heads_kv)) != SDPA_B200_OK)
     return st;
-  const size_t need = kWorkspaceHeaderBytes + bwd_workspace_bytes(*p);
+  const size_t need = kWorkspaceHeaderBytes + (p->head_dim > 128 ? bwd_d256_workspace_bytes(*p) : bwd_workspace_bytes(*p));
   st = validate_workspace(workspace, workspace_bytes, need);
   if (st != SDPA_B200_OK) return st;
   st = check_device();
@@ -443,6 +440,7 @@ int sdpa_b200_bwd(const sdpa_b200_params* p, void* workspace, size_t workspace_b
     set_error("clearing the workspace header failed: %s", cudaGetErrorString(cudaGetLastError()));
     return SDPA_B200_LAUNCH_FAILED;
   }
+  if (p->head_dim > 128) return launch_bwd_d256(*p, workspace, s);
   return launch_bwd(*p, workspace, workspace_bytes, s);
 }
 
