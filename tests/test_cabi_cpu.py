@@ -80,9 +80,9 @@ def test_workspace_query_and_validation_codes(native_lib):
     expect(lambda p: setattr(p, "heads_kv", 3), _cabi.INVALID_ARG, "must divide number of heads in query")
     expect(lambda p: setattr(p, "head_dim", 100), _cabi.INVALID_ARG, "multiple of 8")
     expect(lambda p: setattr(p, "head_dim", 264), _cabi.INVALID_ARG, "at most 256")
-    def wide_with_dropout(p):
-        p.head_dim, p.dropout_p, p.keep_rows = 192, 0.1, 4096
-    expect(wide_with_dropout, _cabi.UNSUPPORTED, "without dropout")
+    def wide_with_bias(p):
+        p.head_dim, p.bias = 192, 4096
+    expect(wide_with_bias, _cabi.UNSUPPORTED, "without a bias")
     expect(lambda p: setattr(p, "dropout_p", 0.1), _cabi.INVALID_ARG, "needs keep_rows")
     expect(lambda p: setattr(p, "dropout_p", 1.0), _cabi.INVALID_ARG, "inside (0, 1)")
     expect(lambda p: setattr(p, "keep_rows", 4096), _cabi.INVALID_ARG, "must be NULL when dropout_p is 0")

@@ -80,6 +80,8 @@ def set_bwd(p, dout, dq, dk, dv, packed):
     (1, 2, 2, 333, 130, 80, False),    # head_dim 80 runs in the 128-column kernel: columns 80.. are clipped
     (1, 2, 1, 129, 257, 64, True),
     (2, 2, 2, 1, 300, 128, False),     # one query row: the tile kernel's smallest case
+    (1, 4, 2, 200, 333, 160, True),    # head dims above 128: the kernels that stage 256-column tiles
+    (2, 2, 1, 129, 70, 256, False),
 ])
 def test_dense_forward_and_backward_write_nothing_outside_their_outputs(cuda_device, native_lib, B, Hq, Hkv, Lq, Lk, D, causal):
     dev = cuda_device
@@ -115,6 +117,8 @@ def test_dense_forward_and_backward_write_nothing_outside_their_outputs(cuda_dev
     ([130, 70, 1, 255], 4, 2, 128, True),   # every sequence ends inside a tile: row-wise stores next to a neighbour
     ([128, 129, 127], 2, 2, 64, False),
     ([300, 45], 8, 2, 96, True),
+    ([130, 70, 1, 255], 4, 2, 256, True),
+    ([128, 129], 2, 2, 136, False),
 ])
 def test_packed_forward_and_backward_write_nothing_outside_their_outputs(cuda_device, native_lib, lens, Hq, Hkv, D, causal):
     dev = cuda_device

@@ -124,3 +124,39 @@ def test_backward_packed_head_dims_above_128(cuda_device, native_lib, lens, Hq, 
                                                seed, off)
     assert ops.device_status() == 0
     check_grads((dq, dk, dv), orc.varlen_backward(dout, q, k, v, cu, cu, causal=causal))
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Lq,Lk,D,causal,p", [
+    (4, 2, 2, 512, 512, 256, True, 0.22),    # the reference sweeps dropout 0.22 / 0.48 over head_dim 256 too (test_...py:938-946)
+    (1, 2, 2, 512, 1024, 256, False, 0.48),
+    (2, 4, 2, 200, 333, 192, True, 0.1),
+])
+def test_dropout_with_head_dims_above_128(cuda_device, native_lib, B, Hq, Hkv, Lq, Lk, D, causal, p):
+    """Forward and backward with dropout against fp32 math on the CPU with the pattern rebuilt from the Philox pair
+    (the restatement of the mask rule in the oracle)."""
+    from torch_mlu_b200 import dropout
+    dev = cuda_device
+    q, k, v, dout = rand((B, Hq, Lq, D), 1), rand((B, Hkv, Lk, D), 2), rand((B, Hkv, Lk, D), 3), rand((B, Hq, Lq, D), 4)
+    qd, kd, vd, dd = q.to(dev), k.to(dev), v.to(dev), dout.to(dev)
+    seed, offset = 1234, 8
+    keep = dropout.KeepMasks(seed, offset, p, B, Hq, Lq, Lk, dev, causal)
+    sc = D ** -0.5
+    out, lse = ops._dense_forward(qd, kd, vd, causal, sc, allow_gqa=True, kernel=1, keep=keep)
+    dq, dk, dv = ops._dense_backward(dd, qd, kd, vd, out, lse, causal, sc, keep=keep)
+    assert ops.device_status() == 0
+    bits = orc.dropout_keep_mask(seed, offset, p, B, Hq, Lq, Lk)
+    g = Hq // Hkv
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    scores = torch.einsum("bhqd,bhkd->bhqk", qf, kf.repeat_interleave(g, dim=1)) * sc
+    if causal:
+        scores = scores.masked_fill(orc.causal_mask_bottom_right(Lq, Lk), float("-inf"))
+    l_ref = torch.logsumexp(scores, dim=-1)
+    dead = torch.isinf(l_ref)
+    attn = torch.softmax(scores, dim=-1).masked_fill(dead.unsqueeze(-1), 0.0).masked_fill(~bits, 0.0) / (1 - p)
+    ref = torch.einsum("bhqk,bhkd->bhqd", attn, vf.repeat_interleave(g, dim=1))
+    ref.backward(dout.float())
+    orc.assert_close_bf16(out, ref.detach(), "out")
+    orc.assert_close_lse(lse, l_ref.detach().masked_fill(dead, float("inf")))
+    orc.assert_close_grad_bf16(dq, qf.grad, "dq")
+    orc.assert_close_grad_bf16(dk, kf.grad, "dk")
+    orc.assert_close_grad_bf16(dv, vf.grad, "dv")

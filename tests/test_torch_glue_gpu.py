@@ -93,8 +93,8 @@ def test_glue_rejects_what_the_reference_rejects(cuda_device, native_lib):
         torch.ops.b200_sdpa._scaled_dot_product_flash_attention(q.float(), q.float(), q.float())
     with pytest.raises(RuntimeError, match="dropout_p must be inside"):
         torch.ops.b200_sdpa._scaled_dot_product_flash_attention(q, q, q, 1.0)
-    wide = torch.cat([q, q[..., :64]], dim=-1)
-    with pytest.raises(RuntimeError, match="up to 128"):
+    wide = torch.cat([q, q, q[..., :64]], dim=-1)  # head_dim 320: beyond what the reference admits (sdp_utils.h:231-255)
+    with pytest.raises(RuntimeError, match="at most 256"):
         torch.ops.b200_sdpa._scaled_dot_product_flash_attention(wide, wide, wide)
 
 

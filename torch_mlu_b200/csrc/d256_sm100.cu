@@ -61,7 +61,16 @@ struct D256Params {
   int num_m_blocks, num_bh, heads_per_wave;
   float scale_log2;
   int is_causal;
+  // dropout (kernels built with kDrop): one keep bit per (query, key) pair, see dropout_mask.cu
+  const uint32_t* keep_rows;  // dense [batch*heads_q][keep_rows_per][lk_words]; packed [heads_q][total_q + 128][lk_words]
+  int keep_rows_per, lk_words;
+  float keep_scale;           // 1 / (1 - dropout_p)
 };
+
+// both halves of a packed 16-bit pair survive or die by two keep bits (bit 0 -> low half)
+__device__ __forceinline__ uint32_t keep_pair(uint32_t two_bits) {
+  return ((two_bits & 1u) ? 0x0000ffffu : 0u) | ((two_bits & 2u) ? 0xffff0000u : 0u);
+}
 
 template <bool kF16>
 constexpr uint32_t kIdescS64 = umma_idesc_16(kRowsA, kRowsB, false, false, kF16);   // scores: N = 64, B K-major
@@ -108,7 +117,7 @@ __device__ __forceinline__ void row_to_tmem(uint32_t taddr, const uint16_t* row,
   }
 }
 
-template <bool kF16>
+template <bool kF16, bool kDrop>
 __global__ void __launch_bounds__(192, 1)
 fwd_d256_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                 const __grid_constant__ CUtensorMap tm_o, const D256Params p) {
@@ -257,8 +266,14 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     const int mask_from = p.is_causal ? min(len_k, m0 + causal_off + 1) : len_k;
     float m_run = neg_inf, l_run = 0.f;
     bool ok = true;
+    const uint32_t* keep_row = nullptr;  // this row's keep bits, 2 words per key block
+    if constexpr (kDrop)
+      keep_row = p.keep_rows + (p.cu_q != nullptr ? static_cast<size_t>(h) * p.keep_rows_per + q_off + row
+                                                  : static_cast<size_t>(b * p.heads_q + h) * p.keep_rows_per + row) * p.lk_words;
     for (int j = 0; j < n_blocks; ++j) {
       const uint32_t t_s = t_s0 + (j & 1) * 64 + lane_base;
+      uint2 keep = make_uint2(0u, 0u);
+      if constexpr (kDrop) keep = *reinterpret_cast<const uint2*>(keep_row + 2 * j);  // in flight under the wait
       ok = __all_sync(0xffffffffu, mbar_wait(bar + kBSFull + 8 * (j & 1), (j >> 1) & 1, abort_flag));
       if (!ok) break;
       tc_fence_after_sync();
@@ -318,6 +333,8 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
         const float2 pr = make_float2(ex2_approx(x.x), ex2_approx(x.y));
         if (i & 1) lb = add2(lb, pr); else la = add2(la, pr);
         pk[i] = pack_16x2<kF16>(pr.x, pr.y);
+        // the row sum keeps every pair (softmax is normalised before dropout); only P V loses the dropped ones
+        if constexpr (kDrop) pk[i] &= keep_pair((i < 16 ? keep.x : keep.y) >> ((2 * i) & 31));
       }
       l_run += (la.x + la.y) + (lb.x + lb.y);
       // Every phase of the PV barrier is observed, in order, and before this block's P is handed over (PV(j) cannot end
@@ -338,7 +355,8 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
     if (ok && n_blocks > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar + kBODone, (n_blocks - 1) & 1, abort_flag));
     if (ok) {
       tc_fence_after_sync();
-      const float inv_l = (l_run > 0.f) ? 1.f / l_run : 0.f;
+      float inv_l = (l_run > 0.f) ? 1.f / l_run : 0.f;
+      if constexpr (kDrop) inv_l *= p.keep_scale;
       if (valid) {
         const size_t li = (p.cu_q != nullptr) ? static_cast<size_t>(h) * p.total_q + q_off + row
                                               : (static_cast<size_t>(b) * p.heads_q + h) * p.seqlen_q + row;
@@ -459,6 +477,11 @@ struct Bwd256Params {
   int num_row_blocks, num_bh, heads_x, heads_per_wave;
   float scale, scale_log2;
   int is_causal;
+  // dropout (kernels built with kDrop): P is recomputed without it; dV takes P o M / (1 - p), dS = P o (M o dP / (1 - p) - delta)
+  const uint32_t* keep_rows;  // [batch*heads_q][keep_q_rows][keep_lk_pad / 32]: kDQ
+  const uint32_t* keep_cols;  // [batch*heads_q][keep_k_rows][keep_lq_pad / 32]: kDV, kDK
+  int keep_lq_pad, keep_lk_pad, keep_q_rows, keep_k_rows;
+  float keep_scale;
 };
 
 template <bool kF16>
@@ -475,7 +498,7 @@ __device__ __forceinline__ void issue_scores_ss(uint32_t t, uint32_t x2_smem, ui
   }
 }
 
-template <int kMode, bool kF16>
+template <int kMode, bool kF16, bool kDrop>
 __global__ void __launch_bounds__(192, 1)
 bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant__ CUtensorMap tm_y1,
                 const __grid_constant__ CUtensorMap tm_y2, const __grid_constant__ CUtensorMap tm_out,
@@ -728,6 +751,19 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
       const int db = (kMode == kDV) ? sb : (sb ^ 1);     // buffer of dP(i)
       const uint32_t t_s = ((sb) ? t_b : t_a) + lane_base;
       const uint32_t t_d = ((db) ? t_b : t_a) + lane_base;
+      // keep bits of this thread's 64 (row, column) pairs, in flight under the waits below
+      uint2 keep = make_uint2(0u, 0u);
+      if constexpr (kDrop) {
+        const int hq = kKeys ? hx * p.kv_group + hi : hx;  // the query head the pattern belongs to
+        const uint32_t* words =
+            kKeys ? p.keep_cols + (p.cu_q != nullptr ? static_cast<size_t>(hq) * p.keep_k_rows + k_off + xr
+                                                     : static_cast<size_t>(b * p.heads_q + hq) * p.keep_k_rows + xr) *
+                                      (p.keep_lq_pad >> 5)
+                  : p.keep_rows + (p.cu_q != nullptr ? static_cast<size_t>(hq) * p.keep_q_rows + q_off + xr
+                                                     : static_cast<size_t>(b * p.heads_q + hq) * p.keep_q_rows + xr) *
+                                      (p.keep_lk_pad >> 5);
+        keep = *reinterpret_cast<const uint2*>(words + (y0 >> 5));
+      }
       ok = mbar_wait(bar + kBTFull + 8 * sb, seen[sb] & 1u, abort_flag);
       ++seen[sb];
       if (kKeys) ok = ok && mbar_wait(bar + kBFull + 8 * slot_index(2 * i), ((2 * i) / kRing) & 1, abort_flag);  // the vectors
@@ -765,7 +801,10 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
       uint32_t w[kRowsB / 2];
       if (kMode == kDV) {
 #pragma unroll
-        for (int j2 = 0; j2 < kRowsB / 2; ++j2) w[j2] = pack_16x2<kF16>(pr[2 * j2], pr[2 * j2 + 1]);
+        for (int j2 = 0; j2 < kRowsB / 2; ++j2) {
+          w[j2] = pack_16x2<kF16>(pr[2 * j2], pr[2 * j2 + 1]);
+          if constexpr (kDrop) w[j2] &= keep_pair((j2 < 16 ? keep.x : keep.y) >> ((2 * j2) & 31));
+        }
       } else {
         ok = __all_sync(0xffffffffu, mbar_wait(bar + kBTFull + 8 * db, seen[db] & 1u, abort_flag));
         ++seen[db];
@@ -781,8 +820,13 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
         for (int j2 = 0; j2 < kRowsB / 2; ++j2) {
           const float dl0 = kKeys ? vec_delta[2 * j2] : my_delta;
           const float dl1 = kKeys ? vec_delta[2 * j2 + 1] : my_delta;
-          w[j2] = pack_16x2<kF16>(pr[2 * j2] * (__uint_as_float(d[2 * j2]) - dl0),
-                                  pr[2 * j2 + 1] * (__uint_as_float(d[2 * j2 + 1]) - dl1));
+          float dp0 = __uint_as_float(d[2 * j2]), dp1 = __uint_as_float(d[2 * j2 + 1]);
+          if constexpr (kDrop) {
+            const uint32_t two = (j2 < 16 ? keep.x : keep.y) >> ((2 * j2) & 31);
+            dp0 = (two & 1u) ? dp0 * p.keep_scale : 0.f;
+            dp1 = (two & 2u) ? dp1 * p.keep_scale : 0.f;
+          }
+          w[j2] = pack_16x2<kF16>(pr[2 * j2] * (dp0 - dl0), pr[2 * j2 + 1] * (dp1 - dl1));
         }
       }
       tmem_st_x32(t_s, w);  // over the front of S(i): 32 columns = 64 streamed rows
@@ -796,7 +840,7 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
     if (ok && n_items > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar + kBAccFull, 0, abort_flag));
     if (ok) {
       tc_fence_after_sync();
-      const float mul = (kMode == kDV) ? 1.f : p.scale;
+      const float mul = (kMode == kDV) ? (kDrop ? p.keep_scale : 1.f) : p.scale;
       const bool use_tma = (p.cu_q == nullptr) || (x0 + kRowsA <= len_x);
       uint16_t* orow = p.out + ((p.cu_q != nullptr) ? static_cast<int64_t>(x_off + xr) * p.o_row_stride
                                                     : b * p.o_batch_stride + static_cast<int64_t>(xr) * p.o_row_stride) +
@@ -928,6 +972,15 @@ int heads_per_wave_for(double bytes_per_head, int num_bh) {
 
 }  // namespace
 
+namespace {
+using Bwd256Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const Bwd256Params);
+template <int kMode>
+Bwd256Kernel pick_bwd256(bool f16, bool drop) {
+  if (drop) return f16 ? bwd_d256_kernel<kMode, true, true> : bwd_d256_kernel<kMode, false, true>;
+  return f16 ? bwd_d256_kernel<kMode, true, false> : bwd_d256_kernel<kMode, false, false>;
+}
+}  // namespace
+
 size_t bwd_d256_workspace_bytes(const sdpa_b200_params& p) {
   const size_t lq_pad = (static_cast<size_t>(p.max_seqlen_q) + kRowsA - 1) / kRowsA * kRowsA;
   return 2 * static_cast<size_t>(p.batch) * p.heads_q * lq_pad * sizeof(float);
@@ -1004,12 +1057,20 @@ int launch_bwd_d256(const sdpa_b200_params& p, void* workspace, cudaStream_t str
   kp.scale = p.softmax_scale;
   kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   kp.is_causal = p.is_causal;
+  const bool drop = p.dropout_p > 0.f;
+  kp.keep_rows = drop ? p.keep_rows : nullptr;
+  kp.keep_cols = drop ? p.keep_cols : nullptr;
+  kp.keep_lq_pad = (p.max_seqlen_q + 127) / 128 * 128;
+  kp.keep_lk_pad = (p.max_seqlen_k + 127) / 128 * 128;
+  kp.keep_q_rows = varlen ? p.total_q + 128 : kp.keep_lq_pad;
+  kp.keep_k_rows = varlen ? p.total_k + 128 : kp.keep_lk_pad;
+  kp.keep_scale = drop ? 1.f / (1.f - p.dropout_p) : 1.f;
 
   auto launch = [&](int mode, const CUtensorMap& x2, const CUtensorMap& y1, const CUtensorMap& y2, const CUtensorMap& out) {
     void (*kernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap, const Bwd256Params);
-    if (mode == kDV) kernel = f16 ? bwd_d256_kernel<kDV, true> : bwd_d256_kernel<kDV, false>;
-    else if (mode == kDK) kernel = f16 ? bwd_d256_kernel<kDK, true> : bwd_d256_kernel<kDK, false>;
-    else kernel = f16 ? bwd_d256_kernel<kDQ, true> : bwd_d256_kernel<kDQ, false>;
+    if (mode == kDV) kernel = pick_bwd256<kDV>(f16, drop);
+    else if (mode == kDK) kernel = pick_bwd256<kDK>(f16, drop);
+    else kernel = pick_bwd256<kDQ>(f16, drop);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytesBwd256);
     if (e != cudaSuccess) {
       set_error("head_dim 256 backward: cudaFuncSetAttribute(%u bytes smem): %s", kSmemBytesBwd256, cudaGetErrorString(e));
@@ -1092,7 +1153,13 @@ int launch_fwd_d256(const sdpa_b200_params& p, void* workspace, cudaStream_t str
   kp.heads_per_wave = heads_per_wave_for(2.0 * p.max_seqlen_k * p.head_dim * 2 / kp.kv_group, kp.num_bh);
   kp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   kp.is_causal = p.is_causal;
-  auto kernel = f16 ? fwd_d256_kernel<true> : fwd_d256_kernel<false>;
+  const bool drop = p.dropout_p > 0.f;
+  kp.keep_rows = drop ? p.keep_rows : nullptr;
+  kp.keep_rows_per = varlen ? p.total_q + 128 : (p.max_seqlen_q + 127) / 128 * 128;
+  kp.lk_words = (p.max_seqlen_k + 127) / 128 * 4;
+  kp.keep_scale = drop ? 1.f / (1.f - p.dropout_p) : 1.f;
+  auto kernel = drop ? (f16 ? fwd_d256_kernel<true, true> : fwd_d256_kernel<false, true>)
+                     : (f16 ? fwd_d256_kernel<true, false> : fwd_d256_kernel<false, false>);
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytesD256);
   if (err != cudaSuccess) {
     set_error("head_dim 256 forward: cudaFuncSetAttribute(%u bytes smem): %s", kSmemBytesD256, cudaGetErrorString(err));

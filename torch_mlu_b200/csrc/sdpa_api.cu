@@ -144,8 +144,8 @@ int validate_common(const sdpa_b200_params* p) {
     set_error("head_dim must be a multiple of 8 and at most 256 (got %d)", p->head_dim);
     return SDPA_B200_INVALID_ARG;
   }
-  if (p->head_dim > 128 && (p->dropout_p != 0.f || p->bias != nullptr || p->kernel == SDPA_B200_KERNEL_DECODE)) {
-    set_error("head dims above 128 (got %d) run in the tile kernels without dropout and without a bias", p->head_dim);
+  if (p->head_dim > 128 && (p->bias != nullptr || p->kernel == SDPA_B200_KERNEL_DECODE)) {
+    set_error("head dims above 128 (got %d) run in the tile kernels, without a bias", p->head_dim);
     return SDPA_B200_UNSUPPORTED;
   }
   if (!(p->softmax_scale > 0.f) || !(p->softmax_scale < 3.0e38f)) {

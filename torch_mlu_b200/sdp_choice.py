@@ -8,7 +8,7 @@ and math is disabled, every constraint is re-run in debug mode (warnings) and
 ``RuntimeError("No available kernel.  Aborting execution.")`` is raised. What differs on purpose:
 both fused backends run the same kernels here (flash refuses an attn_mask as in the reference; the
 memory-efficient one takes it as an additive bias), and the MLU-occupancy heuristics of sdp_utils.h:479-524 (500-series check, split condition, valid-data
-ratio) are replaced by what this build needs: an sm_100 CUDA device, head_dim at most 128.
+ratio) are replaced by what this build needs: an sm_100 CUDA device, and no attn_mask when head_dim exceeds 128.
 """
 from __future__ import annotations
 
@@ -101,8 +101,9 @@ def _check_fused_kernel_device_support(q, k, v, mask, debug):  # stands where sd
         _warn(debug, "The fused kernel only supports sm_100 (B200). Attempting to run on "
                      f"{torch.cuda.get_device_name(q.device)}.")
         return False
-    if q.size(-1) > 128:
-        _warn(debug, f"This build has fused kernels for head_dim up to 128 only. Got Query.size(-1): {q.size(-1)}.")
+    if q.size(-1) > 128 and mask is not None:
+        _warn(debug, "This build runs head dims above 128 without an attn_mask (the additive bias is built for head_dim up "
+                     f"to 128). Got Query.size(-1): {q.size(-1)}.")
         return False
     return True
 
