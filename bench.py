@@ -326,6 +326,24 @@ def measure_dropout(job: Job, n: int):
             "fwd_bwd_deterministic_ms": ms_pair_det, "fwd_bwd_deterministic_tflops": 3.5 * fwd_flops / ms_pair_det / 1e9}
 
 
+def measure_head_dim_256(job: Job, n: int):
+    """Causal forward and backward at head_dim 256 (B4 H16 L4096): the kernels that keep the stationary operand in
+    tensor memory. Fractions are of the measured burst bf16 peak."""
+    from torch_mlu_b200 import ops
+    rn = device_randn(job.dev, 6)
+    B, H, L, D = 4, 16, 4096, 256
+    q, k, v, do = (rn(B, H, L, D) for _ in range(4))
+    fwd_flops = 4.0 * B * H * L * L * D / 2
+    o, lse = ops.gqa_prefill(q, k, v, is_causal=True)
+    ms_f = job.timed(lambda: ops.gqa_prefill(q, k, v, is_causal=True), n, 3)
+    ms_b = job.timed(lambda: ops._dense_backward(do, q, k, v, o, lse, True, D ** -0.5), n, 3)
+    peak = float(load_peaks()["bf16_tflops"])
+    f_tf, b_tf = fwd_flops / ms_f / 1e9, 2.5 * fwd_flops / ms_b / 1e9
+    return {"workload": "bf16 causal B=4 H=16 L=4096 D=256", "fwd_ms": ms_f, "fwd_tflops": f_tf, "fwd_frac_of_peak": f_tf / peak,
+            "bwd_ms": ms_b, "bwd_tflops": b_tf, "bwd_frac_of_peak": b_tf / peak,
+            "fwd_bwd_tflops": 3.5 * fwd_flops / (ms_f + ms_b) / 1e9, "peak": peak}
+
+
 def measure_varlen(job: Job, n: int):
     """Config 4 (16 packed sequences, Hq 32 / Hkv 8, causal). At N > 1 the 128 (sequence, kv head) units are packed
     onto the ranks by sharding.plan_varlen (longest first by L^2); each rank's units form one packed call with
@@ -590,6 +608,7 @@ def run_ours(args):
         guarded("fwd_bwd", also, lambda: measure_fwd_bwd(job, n))
         if world == 1:
             guarded("fwd_bwd_dropout", also, lambda: measure_dropout(job, n))
+            guarded("head_dim_256", also, lambda: measure_head_dim_256(job, n))
         guarded("varlen_gqa", also, lambda: measure_varlen(job, n))
         guarded("decode", also, lambda: measure_decode(job, n))
         if world > 1:

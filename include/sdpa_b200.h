@@ -68,7 +68,7 @@ extern "C" {
 enum {
   SDPA_B200_OK = 0,
   SDPA_B200_INVALID_ARG = 1,    /* null pointer, bad shape, bad stride/alignment, workspace too small */
-  SDPA_B200_UNSUPPORTED = 2,    /* valid request this build has no kernel for (dtype, head_dim > 128, decode with bias) */
+  SDPA_B200_UNSUPPORTED = 2,    /* valid request this build has no kernel for (dtype, head_dim > 128 with a bias, decode with bias) */
   SDPA_B200_LAUNCH_FAILED = 3,  /* CUDA reported an error while configuring or launching */
   SDPA_B200_DEVICE_TIMEOUT = 4, /* a bounded wait inside a kernel ran out (read back from workspace) */
   SDPA_B200_NO_DEVICE = 5       /* not an sm_100 device / no CUDA driver */
@@ -105,7 +105,7 @@ typedef struct sdpa_b200_params {
   int32_t batch;
   int32_t heads_q;
   int32_t heads_kv;
-  int32_t head_dim;     /* a multiple of 8, at most 128 (SDPA_B200_KERNEL_DECODE: 64 or 128) */
+  int32_t head_dim;     /* a multiple of 8, at most 256 (SDPA_B200_KERNEL_DECODE: 64 or 128; with a bias: at most 128) */
   int32_t max_seqlen_q; /* dense: seqlen_q */
   int32_t max_seqlen_k; /* dense: seqlen_k */
   int32_t total_q;      /* varlen: rows of q/out; dense: ignored */
