@@ -442,6 +442,9 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
 // item i in the issuer's own order.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kDV = 0, kDK = 1, kDQ = 2;
+// warps 0-3 / 4-7: two compute warpgroups, one per 32-row half of every streamed block (thread = stationary row);
+// warp 8 TMA producer, warp 9 MMA issuer
+constexpr int kBwdThreads = 320;
 
 __host__ __device__ constexpr int ring_slots_for(int mode) { return mode == kDV ? 6 : (mode == kDK ? 4 : 5); }
 __host__ __device__ constexpr uint32_t ring_base_for(int mode) { return mode == kDV ? 0u : 2u * kSlotBytes; }  // behind X2
@@ -487,6 +490,37 @@ struct Bwd256Params {
 template <bool kF16>
 constexpr uint32_t kIdescS64SS = umma_idesc_16(kRowsA, kRowsB, false, false, kF16);
 
+// ACC (128 x 256) (+)= W * B with W written by two warpgroups, each over the front of its own 32 score columns: the 16-bit
+// rows 0-31 of the block sit in columns [0,16) of the buffer, rows 32-63 in columns [32,48)
+template <bool kF16>
+__device__ __forceinline__ void issue_accumulate256_split(uint32_t acc, uint32_t w_tmem, uint32_t slot, bool accumulate) {
+#pragma unroll
+  for (int ks = 0; ks < kRowsB / 16; ++ks) {
+    const uint32_t b_lo = umma_desc_lo_mnmajor(slot + ks * 2048, kBoxBytes);
+    umma_ts_lo<kIdescAcc256<kF16>>(acc, w_tmem + (ks >> 1) * 32 + (ks & 1) * 8, b_lo, (accumulate || ks > 0) ? 1u : 0u);
+  }
+}
+
+// half of a row (128 of its 256 elements = 64 TMEM columns), for a loader split over two warpgroups
+__device__ __forceinline__ void row_half_to_tmem(uint32_t taddr, const uint16_t* row, int head_dim, int half) {
+#pragma unroll
+  for (int c2 = 0; c2 < 2; ++c2) {
+    const int c = half * 2 + c2;
+    uint32_t w[32];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uint4 x = make_uint4(0u, 0u, 0u, 0u);
+      const int col = c * 64 + i * 8;
+      if (row != nullptr && col < head_dim) x = *reinterpret_cast<const uint4*>(row + col);
+      w[4 * i] = x.x;
+      w[4 * i + 1] = x.y;
+      w[4 * i + 2] = x.z;
+      w[4 * i + 3] = x.w;
+    }
+    tmem_st_x32(taddr + c * 32, w);
+  }
+}
+
 // T (128 x 64) = X2 (shared memory, 128 rows x 256 as four boxes of 64 columns) * Y^T, Y = one streamed block, both K-major
 template <bool kF16>
 __device__ __forceinline__ void issue_scores_ss(uint32_t t, uint32_t x2_smem, uint32_t slot) {
@@ -499,7 +533,7 @@ __device__ __forceinline__ void issue_scores_ss(uint32_t t, uint32_t x2_smem, ui
 }
 
 template <int kMode, bool kF16, bool kDrop>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant__ CUtensorMap tm_y1,
                 const __grid_constant__ CUtensorMap tm_y2, const __grid_constant__ CUtensorMap tm_out,
                 const Bwd256Params p) {
@@ -565,21 +599,21 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + kSmemBars + kAbortWordB);
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + kSmemBars + kTmemPtrB);
 
-  if (warp == 4 && lane == 0) {
+  if (warp == 8 && lane == 0) {
     tma_prefetch_desc(&tm_y1);
     tma_prefetch_desc(&tm_y2);
     for (int s = 0; s < kRing; ++s) {
       mbar_init(bar + kBFull + 8 * s, 1);
       mbar_init(bar + kBEmpty + 8 * s, 1);
     }
-    mbar_init(bar + kBAReady, 4);
+    mbar_init(bar + kBAReady, 8);
     mbar_init(bar + kBX2Full, 1);
     mbar_init(bar + kBTFull, 1);
     mbar_init(bar + kBTFull + 8, 1);
-    mbar_init(bar + kBDFree, 4);
-    mbar_init(bar + kBWFull, 4);
+    mbar_init(bar + kBDFree, 8);
+    mbar_init(bar + kBWFull, 8);
     mbar_init(bar + kBAccFull, 1);
-    mbar_init(bar + kBStageB, 4);
+    mbar_init(bar + kBStageB, 8);
     *abort_flag = 0;
     fence_mbar_init();
     if (kMode != kDV && n_items > 0) {
@@ -604,7 +638,7 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
   auto slot_index = [&](int t) { return t % kRing; };
   auto slot_addr = [&](int t) { return base + kRingBase + (t % kRing) * kSlotBytes; };
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       for (int t = 0; t < 2 * n_items; ++t) {
@@ -635,7 +669,7 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
       }
       drain_after_abort(abort_flag);
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && n_items > 0) {
       auto wait_full = [&](int t) { return mbar_wait(bar + kBFull + 8 * slot_index(t), (t / kRing) & 1, abort_flag); };
@@ -660,7 +694,7 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
           ok = mbar_wait(bar + kBWFull, i & 1, abort_flag) && wait_full(2 * i + 1);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_accumulate256<kF16>(t_acc, t_buf(i), slot_addr(2 * i + 1), i > 0);
+          issue_accumulate256_split<kF16>(t_acc, t_buf(i), slot_addr(2 * i + 1), i > 0);
           // the Q block goes with it: its slot also carries the per-query vectors the compute warps have just used
           release(2 * i);
           release(2 * i + 1);
@@ -701,7 +735,7 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
           ok = mbar_wait(bar + kBWFull, i & 1, abort_flag);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_accumulate256<kF16>(t_acc, t_buf(i), slot_addr(2 * i), i > 0);  // += dS Y1
+          issue_accumulate256_split<kF16>(t_acc, t_buf(i), slot_addr(2 * i), i > 0);  // += dS Y1
           release(2 * i);
           if (!more) {
             umma_commit(bar + kBAccFull);
@@ -718,17 +752,18 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------------ compute warps (thread = stationary row)
-    const int r = warp * 32 + lane;
+    const int half = warp >> 2;              // which 32 of a block's 64 streamed rows this thread works on
+    const int r = (warp & 3) * 32 + lane;    // stationary row = TMEM lane
     const int xr = x0 + r;
     const bool valid = xr < len_x;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     {
       const uint16_t* xrow = nullptr;
       if (valid)
         xrow = p.x1 + ((p.cu_q != nullptr) ? static_cast<int64_t>(x_off + xr) * p.x1_row_stride
                                            : b * p.x1_batch_stride + static_cast<int64_t>(xr) * p.x1_row_stride) +
                (kKeys ? hkv : hx) * p.x1_head_stride;
-      row_to_tmem(t_x1 + lane_base, xrow, p.head_dim);
+      row_half_to_tmem(t_x1 + lane_base, xrow, p.head_dim, half);  // each warpgroup brings half of the row's columns
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
@@ -749,10 +784,10 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
       const int y0 = (y_lo + (i - hi * blocks_per_head)) * kRowsB;
       const int sb = i & 1;                              // buffer of S(i)
       const int db = (kMode == kDV) ? sb : (sb ^ 1);     // buffer of dP(i)
-      const uint32_t t_s = ((sb) ? t_b : t_a) + lane_base;
-      const uint32_t t_d = ((db) ? t_b : t_a) + lane_base;
+      const uint32_t t_s = ((sb) ? t_b : t_a) + lane_base + half * 32;  // this thread's 32 fp32 columns
+      const uint32_t t_d = ((db) ? t_b : t_a) + lane_base + half * 32;
       // keep bits of this thread's 64 (row, column) pairs, in flight under the waits below
-      uint2 keep = make_uint2(0u, 0u);
+      uint32_t keep = 0u;
       if constexpr (kDrop) {
         const int hq = kKeys ? hx * p.kv_group + hi : hx;  // the query head the pattern belongs to
         const uint32_t* words =
@@ -762,7 +797,7 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
                   : p.keep_rows + (p.cu_q != nullptr ? static_cast<size_t>(hq) * p.keep_q_rows + q_off + xr
                                                      : static_cast<size_t>(b * p.heads_q + hq) * p.keep_q_rows + xr) *
                                       (p.keep_lk_pad >> 5);
-        keep = *reinterpret_cast<const uint2*>(words + (y0 >> 5));
+        keep = words[(y0 >> 5) + half];
       }
       ok = mbar_wait(bar + kBTFull + 8 * sb, seen[sb] & 1u, abort_flag);
       ++seen[sb];
@@ -770,11 +805,12 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      const float* vec_lse = reinterpret_cast<const float*>(smem + kSmemVecs + slot_index(2 * i) * 512);
+      const float* vec_lse = reinterpret_cast<const float*>(smem + kSmemVecs + slot_index(2 * i) * 512) + half * 32;
       const float* vec_delta = vec_lse + 64;
       // visibility of element (row xr, column y0 + j)
       //   keys as rows : key xr, query y0+j : visible iff j >= xr - off - y0 (and the key exists)
       //   queries      : query xr, key y0+j : visible iff y0 + j <= xr + off and y0 + j < len_k
+      constexpr int kCols = kRowsB / 2;  // columns per thread
       int j_lo = 0, j_hi = kRowsB;
       if (kKeys) {
         if (p.is_causal) j_lo = xr - causal_off - y0;
@@ -783,53 +819,57 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
         j_hi = len_k - y0;
         if (p.is_causal) j_hi = min(j_hi, xr + causal_off + 1 - y0);
       }
-      float pr[kRowsB];
+      j_lo -= half * kCols;  // relative to this thread's columns
+      j_hi -= half * kCols;
+      float pr[kCols];
       {
-        uint32_t a[kRowsB];
-        tmem_ld_x64(t_s, a);
+        uint32_t a[kCols];
+        tmem_ld_x32(t_s, a);
         tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < kRowsB; ++j) {
+        for (int j = 0; j < kCols; ++j) {
           const float l2 = kKeys ? vec_lse[j] : my_lse2;
           pr[j] = ex2_approx(fmaf(__uint_as_float(a[j]), c, -l2));
         }
-        if (__any_sync(0xffffffffu, j_lo > 0 || j_hi < kRowsB)) {
+        if (__any_sync(0xffffffffu, j_lo > 0 || j_hi < kCols)) {
 #pragma unroll
-          for (int j = 0; j < kRowsB; ++j) pr[j] = (j >= j_lo && j < j_hi) ? pr[j] : 0.f;
+          for (int j = 0; j < kCols; ++j) pr[j] = (j >= j_lo && j < j_hi) ? pr[j] : 0.f;
         }
       }
-      uint32_t w[kRowsB / 2];
+      uint32_t w[kCols / 2];
       if (kMode == kDV) {
 #pragma unroll
-        for (int j2 = 0; j2 < kRowsB / 2; ++j2) {
+        for (int j2 = 0; j2 < kCols / 2; ++j2) {
           w[j2] = pack_16x2<kF16>(pr[2 * j2], pr[2 * j2 + 1]);
-          if constexpr (kDrop) w[j2] &= keep_pair((j2 < 16 ? keep.x : keep.y) >> ((2 * j2) & 31));
+          if constexpr (kDrop) w[j2] &= keep_pair(keep >> (2 * j2));
         }
       } else {
         ok = __all_sync(0xffffffffu, mbar_wait(bar + kBTFull + 8 * db, seen[db] & 1u, abort_flag));
         ++seen[db];
         if (!ok) break;
         tc_fence_after_sync();
-        uint32_t d[kRowsB];
-        tmem_ld_x64(t_d, d);
+        uint32_t d[kCols];
+        tmem_ld_x32(t_d, d);
         tmem_wait_ld();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar + kBDFree);  // the dP buffer may be overwritten
 #pragma unroll
-        for (int j2 = 0; j2 < kRowsB / 2; ++j2) {
+        for (int j2 = 0; j2 < kCols / 2; ++j2) {
           const float dl0 = kKeys ? vec_delta[2 * j2] : my_delta;
           const float dl1 = kKeys ? vec_delta[2 * j2 + 1] : my_delta;
           float dp0 = __uint_as_float(d[2 * j2]), dp1 = __uint_as_float(d[2 * j2 + 1]);
           if constexpr (kDrop) {
-            const uint32_t two = (j2 < 16 ? keep.x : keep.y) >> ((2 * j2) & 31);
+            const uint32_t two = keep >> (2 * j2);
             dp0 = (two & 1u) ? dp0 * p.keep_scale : 0.f;
             dp1 = (two & 2u) ? dp1 * p.keep_scale : 0.f;
           }
           w[j2] = pack_16x2<kF16>(pr[2 * j2] * (dp0 - dl0), pr[2 * j2 + 1] * (dp1 - dl1));
         }
       }
-      tmem_st_x32(t_s, w);  // over the front of S(i): 32 columns = 64 streamed rows
+      // the 16-bit result over the front of this thread's OWN score columns (16 columns = 32 streamed rows): the other
+      // warpgroup may still be reading its half of the scores
+      tmem_st_x16(t_s, w);
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
@@ -846,7 +886,8 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
                                                     : b * p.o_batch_stride + static_cast<int64_t>(xr) * p.o_row_stride) +
                        hx * p.o_head_stride;
 #pragma unroll
-      for (int cc = 0; cc < kWide / 32; ++cc) {
+      for (int c2 = 0; c2 < kWide / 64; ++c2) {
+        const int cc = half * (kWide / 64) + c2;  // this warpgroup's half of the 256 columns
         uint32_t o[32];
         if (n_items > 0) {
           tmem_ld_x32(t_acc + lane_base + cc * 32, o);
@@ -1085,7 +1126,7 @@ int launch_bwd_d256(const sdpa_b200_params& p, void* workspace, cudaStream_t str
     kp.heads_per_wave = heads_per_wave_for(streamed, kp.num_bh);
     const int groups = (kp.num_bh + kp.heads_per_wave - 1) / kp.heads_per_wave;
     const int grid = groups * kp.heads_per_wave * kp.num_row_blocks;
-    kernel<<<grid, 192, kSmemBytesBwd256, stream>>>(x2, y1, y2, out, kp);
+    kernel<<<grid, kBwdThreads, kSmemBytesBwd256, stream>>>(x2, y1, y2, out, kp);
     e = cudaGetLastError();
     if (e != cudaSuccess) {
       set_error("head_dim 256 backward (kernel %d): launch failed: %s", mode, cudaGetErrorString(e));
