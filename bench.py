@@ -489,7 +489,7 @@ def run_ours(args):
     value = world * flops / ms_per_step / 1e9  # TFLOP/s, whole job
 
     # ---- the same step for about two seconds: what a loop that runs under the power cap gets
-    reps = max(args.steps, int(2000.0 / ms_per_step))
+    reps = max(args.steps, int(args.sustained_seconds * 1000.0 / ms_per_step))
     sampler = ClockSampler(job.local, period_s=0.02).start()
     ms_sus = job.timed(step, reps, 0)
     sus_clocks = sampler.stop()
@@ -647,6 +647,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary configs and the CPU baseline")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0,
+                    help="length of the loop behind the `sustained` figure (a profiler run may want it short)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.gpus > 1 and "WORLD_SIZE" not in os.environ and args.impl == "ours":
