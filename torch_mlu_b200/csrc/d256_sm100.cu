@@ -443,8 +443,8 @@ fwd_d256_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant_
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kDV = 0, kDK = 1, kDQ = 2;
 // warps 0-3 / 4-7: two compute warpgroups, one per 32-row half of every streamed block (thread = stationary row);
-// warp 8 TMA producer, warp 9 MMA issuer
-constexpr int kBwdThreads = 320;
+// warp 8 TMA producer, warps 9 and 10 MMA issuers
+constexpr int kBwdThreads = 352;
 
 __host__ __device__ constexpr int ring_slots_for(int mode) { return mode == kDV ? 6 : (mode == kDK ? 4 : 5); }
 __host__ __device__ constexpr uint32_t ring_base_for(int mode) { return mode == kDV ? 0u : 2u * kSlotBytes; }  // behind X2
@@ -460,7 +460,8 @@ constexpr uint32_t kBX2Full = kBAReady + 8;
 constexpr uint32_t kBTFull = kBX2Full + 8;     // 2: the score GEMM into T[b] has finished
 constexpr uint32_t kBDFree = kBTFull + 16;     // 4 warps: dP has been read out of TMEM
 constexpr uint32_t kBWFull = kBDFree + 8;      // 4 warps: the 16-bit P / dS is in TMEM
-constexpr uint32_t kBAccFull = kBWFull + 8;
+constexpr uint32_t kBWRead = kBWFull + 8;      // the accumulation GEMM of an item has read its P / dS
+constexpr uint32_t kBAccFull = kBWRead + 8;
 constexpr uint32_t kBStageB = kBAccFull + 8;   // 4 warps
 constexpr uint32_t kTmemPtrB = kBStageB + 8;
 constexpr uint32_t kAbortWordB = kTmemPtrB + 4;
@@ -612,6 +613,7 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
     mbar_init(bar + kBTFull + 8, 1);
     mbar_init(bar + kBDFree, 8);
     mbar_init(bar + kBWFull, 8);
+    mbar_init(bar + kBWRead, 1);
     mbar_init(bar + kBAccFull, 1);
     mbar_init(bar + kBStageB, 8);
     *abort_flag = 0;
@@ -669,44 +671,44 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
       }
       drain_after_abort(abort_flag);
     }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == 9 || warp == 10) {
+    // ------------------------------------------------------------------ MMA issuers
+    // One thread needs ~50 cycles to issue an MMA, and the N = 64 score MMAs run for 32 (48 with both operands in shared
+    // memory): a single issuer would hold the pipe back. So warp 9 issues the score GEMMs and warp 10 the accumulations;
+    // what the pipe's own order would guarantee between the two is the `W read` barrier (warp 10 commits it behind an item's
+    // accumulation, warp 9 waits for it before a score GEMM overwrites that item's P / dS).
     if (lane == 0 && n_items > 0) {
       auto wait_full = [&](int t) { return mbar_wait(bar + kBFull + 8 * slot_index(t), (t / kRing) & 1, abort_flag); };
       auto release = [&](int t) { umma_commit(bar + kBEmpty + 8 * slot_index(t)); };
       auto t_buf = [&](int k) { return (k & 1) ? t_b : t_a; };
       bool ok = mbar_wait(bar + kBAReady, 0, abort_flag);
       if (kMode != kDV) ok = ok && mbar_wait(bar + kBX2Full, 0, abort_flag);
-      if (kMode == kDV) {
-        // S(i) in T[i&1]; P over its front; dV += P^T dO. S(i+1) goes out ahead, S(i+2) behind the accumulation of item i.
-        auto issue_s = [&](int i) {
+      if (warp == 10) {
+        // ---------------- accumulations: ACC += W(i) Y, W = P^T (kDV, Y = dO block) or dS (Y = the Y1 block)
+        for (int i = 0; ok && i < n_items; ++i) {
+          const int ty = (kMode == kDV) ? 2 * i + 1 : 2 * i;
+          ok = mbar_wait(bar + kBWFull, i & 1, abort_flag) && wait_full(ty);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_accumulate256_split<kF16>(t_acc, t_buf(i), slot_addr(ty), i > 0);
+          umma_commit(bar + kBWRead);
+          // kDV: the Q block goes too - its slot carries the per-query vectors the compute warps have just used
+          release(2 * i);
+          if (kMode == kDV) release(2 * i + 1);
+          if (i == n_items - 1) umma_commit(bar + kBAccFull);
+        }
+      } else if (kMode == kDV) {
+        // ---------------- scores: S(i) in T[i&1]; S(i+2) follows the accumulation of item i
+        for (int i = 0; ok && i < n_items; ++i) {
+          if (i >= 2) ok = mbar_wait(bar + kBWRead, (i - 2) & 1, abort_flag);
+          ok = ok && wait_full(2 * i);
+          if (!ok) break;
           tc_fence_after_sync();
           issue_scores<kF16>(t_buf(i), t_x1, slot_addr(2 * i));
           umma_commit(bar + kBTFull + 8 * (i & 1));
-        };
-        ok = ok && wait_full(0);
-        if (ok) issue_s(0);
-        if (ok && n_items > 1) {
-          ok = wait_full(2);
-          if (ok) issue_s(1);
-        }
-        for (int i = 0; ok && i < n_items; ++i) {
-          ok = mbar_wait(bar + kBWFull, i & 1, abort_flag) && wait_full(2 * i + 1);
-          if (!ok) break;
-          tc_fence_after_sync();
-          issue_accumulate256_split<kF16>(t_acc, t_buf(i), slot_addr(2 * i + 1), i > 0);
-          // the Q block goes with it: its slot also carries the per-query vectors the compute warps have just used
-          release(2 * i);
-          release(2 * i + 1);
-          if (i == n_items - 1) umma_commit(bar + kBAccFull);
-          if (i + 2 < n_items) {
-            ok = wait_full(2 * i + 4);
-            if (!ok) break;
-            issue_s(i + 2);
-          }
         }
       } else {
-        // S(i) in T[i&1], dP(i) in T[(i&1)^1]
+        // ---------------- scores: S(i) in T[i&1], dP(i) in T[(i&1)^1]
         ok = ok && wait_full(0);
         if (ok) {
           tc_fence_after_sync();
@@ -718,35 +720,22 @@ bwd_d256_kernel(const __grid_constant__ CUtensorMap tm_x2, const __grid_constant
           tc_fence_after_sync();
           issue_scores_ss<kF16>(t_buf(1), base, slot_addr(1));
           umma_commit(bar + kBTFull + 8);
-          release(1);  // the Y2 block is read by this GEMM only
+          release(1);  // a Y2 block is read by this GEMM only
         }
-        for (int i = 0; ok && i < n_items; ++i) {
-          const bool more = i + 1 < n_items;
+        for (int i = 0; ok && i + 1 < n_items; ++i) {
           // dP(i) has left TMEM once the compute warps have read it: its buffer takes S(i+1)
-          ok = mbar_wait(bar + kBDFree, i & 1, abort_flag);
-          if (!ok) break;
-          if (more) {
-            ok = wait_full(2 * i + 2);
-            if (!ok) break;
-            tc_fence_after_sync();
-            issue_scores<kF16>(t_buf(i + 1), t_x1, slot_addr(2 * i + 2));
-            umma_commit(bar + kBTFull + 8 * ((i + 1) & 1));
-          }
-          ok = mbar_wait(bar + kBWFull, i & 1, abort_flag);
+          ok = mbar_wait(bar + kBDFree, i & 1, abort_flag) && wait_full(2 * i + 2);
           if (!ok) break;
           tc_fence_after_sync();
-          issue_accumulate256_split<kF16>(t_acc, t_buf(i), slot_addr(2 * i), i > 0);  // += dS Y1
-          release(2 * i);
-          if (!more) {
-            umma_commit(bar + kBAccFull);
-          } else {
-            ok = wait_full(2 * i + 3);
-            if (!ok) break;
-            tc_fence_after_sync();
-            issue_scores_ss<kF16>(t_buf(i), base, slot_addr(2 * i + 3));  // dP(i+1) over S(i) / dS(i), behind the accumulation
-            umma_commit(bar + kBTFull + 8 * (i & 1));
-            release(2 * i + 3);
-          }
+          issue_scores<kF16>(t_buf(i + 1), t_x1, slot_addr(2 * i + 2));
+          umma_commit(bar + kBTFull + 8 * ((i + 1) & 1));
+          // dS(i) has left TMEM once the accumulation of item i has read it: its buffer takes dP(i+1)
+          ok = mbar_wait(bar + kBWRead, i & 1, abort_flag) && wait_full(2 * i + 3);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_scores_ss<kF16>(t_buf(i), base, slot_addr(2 * i + 3));
+          umma_commit(bar + kBTFull + 8 * (i & 1));
+          release(2 * i + 3);
         }
       }
     }
