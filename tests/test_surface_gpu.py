@@ -209,3 +209,17 @@ def test_status_word_through_the_registered_operators(cuda_device, native_lib):
     from torch_mlu_b200 import torch_glue
     torch_glue.load()
     assert torch.ops.b200_sdpa._device_status(0) == 0
+
+
+@pytest.mark.parametrize("margin", [8, 32, 1000])
+def test_sm_margin_leaves_the_result_alone(cuda_device, native_lib, margin):
+    """`sm_margin` only shrinks the persistent forward grid (what is left over serves a collective on another
+    stream); the units are handed out by a counter, so any grid size - down to one CTA - gives the same bits."""
+    q, k, v = rand((2, 4, 640, 128), 31), rand((2, 4, 640, 128), 32), rand((2, 4, 640, 128), 33)
+    qd, kd, vd = (t.to(cuda_device) for t in (q, k, v))
+    out0, lse0 = ops.gqa_prefill(qd, kd, vd, is_causal=True)
+    out1, lse1 = ops.gqa_prefill(qd, kd, vd, is_causal=True, sm_margin=margin)
+    assert torch.equal(out0, out1) and torch.equal(lse0, lse1)
+    o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=True)
+    orc.assert_close_bf16(out1, o_ref, "out")
+    orc.assert_close_lse(lse1, l_ref)
