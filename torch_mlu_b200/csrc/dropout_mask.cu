@@ -31,14 +31,21 @@ __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
   return c;
 }
 
-// 16 keep bits from 16 bytes: bit j set when byte j >= drop. `drop4` holds the threshold in all four bytes; a
-// per-byte compare gives 0xff / 0x00 per byte, and one multiply gathers bit 0 of each byte into four adjacent bits
-// (2^24 + 2^17 + 2^10 + 2^3 moves bits 0, 8, 16, 24 to 24, 25, 26, 27; the other products stay below bit 20).
+// 16 keep bits from 16 bytes: bit j set when byte j >= drop. `drop4` holds the threshold in all four bytes. The
+// per-byte unsigned compare is done on the whole word: with H = 0x80 in every byte, (w | H) - (t & ~H) cannot borrow
+// across bytes and its top bit per byte says whether the low seven bits of w reach those of t; the bytes' own top bits
+// decide the rest: w >= t  <=>  (wh & ~th) | (~(wh ^ th) & zh), one three-input logic instruction. One multiply then
+// gathers the four top bits into adjacent bits (2^21 + 2^14 + 2^7 + 2^0 moves bits 7, 15, 23, 31 to 28, 29, 30, 31).
 __device__ __forceinline__ uint32_t keep_bits16(uint4 r, uint32_t drop4) {
   const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+  const uint32_t t_low = drop4 & 0x7f7f7f7fu;
   uint32_t bits = 0;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) bits |= ((((__vcmpgeu4(w[i], drop4) & 0x01010101u) * 0x01020408u) >> 24) & 0xfu) << (4 * i);
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t z = (w[i] | 0x80808080u) - t_low;
+    const uint32_t ge = ((w[i] & ~drop4) | (~(w[i] ^ drop4) & z)) & 0x80808080u;
+    bits |= ((ge * 0x00204081u) >> 28) << (4 * i);
+  }
   return bits;
 }
 
