@@ -14,6 +14,7 @@ ProcessGroupCNCL::send/recv, process_group_cncl.cpp:2526-2552).
 from __future__ import annotations
 
 import ctypes
+import functools
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -68,7 +69,7 @@ def zigzag_take(x: torch.Tensor, rank: int, world: int, dim: int = 2) -> torch.T
 
 def ring_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal: bool, scale: Optional[float] = None,
                  group=None, attention_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None,
-                 layout: str = "contiguous", exchange: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+                 layout: str = "contiguous", exchange: bool = True, sm_margin: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
     """q [B,Hq,Ls,D], k/v [B,Hkv,Ls,D]: this rank's slice of the sequence.
     ``layout="contiguous"``: rank r owns rows [r*Ls, (r+1)*Ls). ``layout="zigzag"`` (causal only): rank r owns
     chunks r and 2*world-1-r of 2*world equal chunks (``zigzag_take``), which balances the causal work: every
@@ -77,17 +78,19 @@ def ring_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal
     whole sequence. ``attention_fn(q, k, v, is_causal=, scale=) -> (out, lse)`` and ``merge_fn``
     default to this library's kernels. ``exchange=False`` runs the same kernels hop by hop on the local slice
     without sending anything: a timing aid that shows what the kernels cost without the transfers (its
-    result is not attention over the whole sequence)."""
+    result is not attention over the whole sequence). ``sm_margin`` (with the default ``attention_fn``) keeps that
+    many SMs out of the persistent forward kernel, so that the send/receive kernels of the hop in flight find SMs
+    to run on beside it instead of waiting for it to finish."""
     if layout == "zigzag":
         if not is_causal:
             layout = "contiguous"  # without a mask every slice order is balanced and equivalent
         else:
-            return _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn, exchange)
+            return _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn, exchange, sm_margin)
     elif layout != "contiguous":
         raise ValueError(f"unknown layout {layout!r}")
     if attention_fn is None:
         from . import ops
-        attention_fn = ops.gqa_prefill
+        attention_fn = functools.partial(ops.gqa_prefill, sm_margin=sm_margin)
     if merge_fn is None:
         merge_fn = merge_partial
     rank, world = dist.get_rank(group), dist.get_world_size(group)
@@ -116,7 +119,7 @@ def ring_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal
     return o_acc.to(q.dtype), lse
 
 
-def _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn, exchange=True):
+def _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn, exchange=True, sm_margin=0):
     """Causal ring prefill over zig-zag slices. Local rows are [chunk r | chunk 2W-1-r]; a visiting slice from
     rank s is [chunk s | chunk 2W-1-s]. Which parts meet:
       s == r : plain causal attention over the local slice (its two chunks are in sequence order);
@@ -125,7 +128,7 @@ def _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn, exchange
     Either way a hop is half a block of unmasked work."""
     if attention_fn is None:
         from . import ops
-        attention_fn = ops.gqa_prefill
+        attention_fn = functools.partial(ops.gqa_prefill, sm_margin=sm_margin)
     if merge_fn is None:
         merge_fn = merge_partial
     rank, world = dist.get_rank(group), dist.get_world_size(group)
