@@ -38,6 +38,11 @@ def main():
     o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=True)
     orc.assert_close_bf16(out, take(o_ref), f"zig-zag ring out rank {rank}")
     orc.assert_close_lse(lse, take(l_ref), max_abs=2e-5)
+    # the same with SMs left to the hop's send/receive kernels: the grid size must not show in the result
+    out2, lse2 = ring.ring_prefill(take(q).to(dev), take(k).to(dev), take(v).to(dev), is_causal=True, layout="zigzag",
+                                   sm_margin=16)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2) and torch.equal(lse, lse2), f"sm_margin changed the ring's result on rank {rank}"
     out, lse, _ = sharding.sdpa_batch_head_sharded(q.to(dev), k.to(dev), v.to(dev), is_causal=True)
     torch.cuda.synchronize()
     o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=True)
