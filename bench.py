@@ -423,8 +423,18 @@ def measure_ring(job: Job, n: int):
     # the hop's send/receive kernels need SMs beside the persistent forward kernel: sweep what it leaves them
     by_margin = {m: job.timed(lambda: ring.ring_prefill(q, k, v, is_causal=True, layout="zigzag", sm_margin=m), n, 2)
                  for m in (0, 8, 16, 32)}
+    # the other transport: slices pulled by the copy engines through CUDA IPC mappings (one small all-reduce per hop)
+    try:
+        peer_ms = job.timed(lambda: ring.ring_prefill(q, k, v, is_causal=True, layout="zigzag", exchange="peer"), n, 2)
+        ring.release_peer_buffers()
+    except Exception as e:  # say so, do not hide it
+        peer_ms = None
+        peer_error = f"{type(e).__name__}: {e}"
     best = min(by_margin, key=by_margin.get)
     ms_full = by_margin[best]
+    transport = "NCCL send/recv"
+    if peer_ms is not None and peer_ms < ms_full:
+        ms_full, best, transport = peer_ms, 4, "peer copies (CUDA IPC)"
     no_comm = lambda: ring.ring_prefill(q, k, v, is_causal=True, layout="zigzag", exchange=False)
     ms_kernels = job.timed(no_comm, n, 2)
     nxt, prv = (job.rank + 1) % W, (job.rank - 1) % W
@@ -441,7 +451,8 @@ def measure_ring(job: Job, n: int):
     hop_bytes = 2 * k.numel() * 2
     hidden = (ms_kernels + ms_comm - ms_full) / ms_comm if ms_comm > 0 else None
     return {"workload": f"ring prefill bf16 causal B=1 H=32 L=65536 D=128, zig-zag slices of {Ls} rows per GPU",
-            "ms": ms_full, "sm_margin": best, "ms_by_sm_margin": by_margin,
+            "ms": ms_full, "transport": transport, "sm_margin": best, "ms_by_sm_margin": by_margin,
+            "ms_peer_copies": peer_ms if peer_ms is not None else peer_error,
             "aggregate_tflops": flops / ms_full / 1e9, "per_gpu_tflops": flops / ms_full / 1e9 / W,
             "kernels_only_ms": ms_kernels, "exchange_only_ms": ms_comm, "hops": W - 1,
             "exchange_ms_per_hop": ms_comm / (W - 1), "kernel_ms_per_hop": ms_kernels / W,

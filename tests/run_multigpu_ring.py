@@ -43,6 +43,19 @@ def main():
                                    sm_margin=16)
     torch.cuda.synchronize()
     assert torch.equal(out, out2) and torch.equal(lse, lse2), f"sm_margin changed the ring's result on rank {rank}"
+    # ... and with the slices pulled through CUDA IPC mappings by the copy engines, twice (the buffers are reused)
+    for _ in range(2):
+        out3, lse3 = ring.ring_prefill(take(q).to(dev), take(k).to(dev), take(v).to(dev), is_causal=True, layout="zigzag",
+                                       exchange="peer")
+        torch.cuda.synchronize()
+        assert torch.equal(out, out3) and torch.equal(lse, lse3), f"the peer-copy exchange changed the result on rank {rank}"
+    out4, lse4 = ring.ring_prefill(q[:, :, sl].to(dev), k[:, :, sl].to(dev), v[:, :, sl].to(dev), is_causal=False,
+                                   exchange="peer")
+    torch.cuda.synchronize()
+    o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=False)
+    orc.assert_close_bf16(out4, o_ref[:, :, sl], f"peer-copy ring out rank {rank}")
+    orc.assert_close_lse(lse4, l_ref[:, :, sl], max_abs=2e-5)
+    ring.release_peer_buffers()
     out, lse, _ = sharding.sdpa_batch_head_sharded(q.to(dev), k.to(dev), v.to(dev), is_causal=True)
     torch.cuda.synchronize()
     o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=True)
