@@ -11,7 +11,9 @@ from later ranks are skipped (but still forwarded).
 ``exchange="peer"`` moves the slices another way: every rank keeps its visiting slice in one of two buffers that
 its right-hand neighbour has mapped through CUDA IPC, and a hop is a plain device-to-device copy that the neighbour
 pulls with the copy engines over NVLink (716 GB/s measured, against 135-147 GB/s per direction for the send/receive
-pair, and no SM taken from the attention kernel); one one-word all-reduce per hop orders the ranks. The copy lands in
+pair, and no SM taken from the attention kernel). Neighbours order their hops through two counters each, written and
+waited for by the streams themselves (cuStreamWriteValue32 / cuStreamWaitValue32: "my slice for hop n is in place",
+"I have copied hop n out of your buffer"), or, where those are not available, by a one-word all-reduce per hop. The copy lands in
 this GPU's own memory before any kernel reads it, as before.
 
 The reference has no such path (its attention is single-device; P2P lives in
@@ -89,30 +91,119 @@ class _PeerRing:
         self.k = [torch.empty(k.shape, dtype=k.dtype, device=dev) for _ in range(2)]
         self.v = [torch.empty(v.shape, dtype=v.dtype, device=dev) for _ in range(2)]
         self.stamp = torch.full((4,), float(rank), dtype=torch.float32, device=dev)
-        mine = []
-        for t in (self.k[0], self.v[0], self.k[1], self.v[1], self.stamp):
-            mine.append((t.untyped_storage()._share_cuda_(), t.storage_offset(), tuple(t.shape), t.dtype))
+        # [0] written by the left neighbour: the number of the last hop whose source pair over there is valid;
+        # [1] written by the right neighbour: the number of the last hop it has finished copying out of this rank;
+        # [2], [3]: the set-up's own check that such writes arrive
+        self.flags = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.hops = 0  # hops made so far, over all calls (the same number on every rank)
+        self.pair = 0  # the pair the next call puts its own slice in
+        # Every step below that can fail is followed by an agreement among the ranks, so that they all go on or all
+        # raise: a rank that gave up alone would leave the others waiting in the next collective.
+        try:
+            mine, error = [], None
+            for t in (self.k[0], self.v[0], self.k[1], self.v[1], self.stamp, self.flags):
+                mine.append((t.untyped_storage()._share_cuda_(), t.storage_offset(), tuple(t.shape), t.dtype))
+        except Exception as e:  # noqa: BLE001 - reported below, on every rank
+            mine, error = None, f"{type(e).__name__}: {e}"
         everyone = [None] * world
         dist.all_gather_object(everyone, mine, group=group)
         left = (rank - 1) % world
         self._peer_storages = []
-        peer = []
-        for handle, offset, shape, dtype in everyone[left]:
-            st = torch.UntypedStorage._new_shared_cuda(*handle)
-            self._peer_storages.append(st)
-            peer.append(torch.empty(0, dtype=dtype, device=st.device).set_(st, offset, shape))
-        self.peer_k, self.peer_v = [peer[0], peer[2]], [peer[1], peer[3]]
-        # the mapping must really be the left neighbour's memory (it is not when the processes number the GPUs
-        # differently, e.g. each with its own CUDA_VISIBLE_DEVICES)
-        seen = float(peer[4].to(dev)[0].item())
-        if seen != float(left):
-            raise RuntimeError(f"CUDA IPC mapping of rank {left}'s buffers shows rank {seen:.0f}'s data")
+        if error is None and all(m is not None for m in everyone):
+            try:
+                peer = []
+                for handle, offset, shape, dtype in everyone[left]:
+                    st = torch.UntypedStorage._new_shared_cuda(*handle)
+                    self._peer_storages.append(st)
+                    peer.append(torch.empty(0, dtype=dtype, device=st.device).set_(st, offset, shape))
+                self.peer_k, self.peer_v = [peer[0], peer[2]], [peer[1], peer[3]]
+                self.left_flags = peer[5]
+                handle, offset, shape, dtype = everyone[(rank + 1) % world][5]
+                st = torch.UntypedStorage._new_shared_cuda(*handle)
+                self._peer_storages.append(st)
+                self.right_flags = torch.empty(0, dtype=dtype, device=st.device).set_(st, offset, shape)
+                # the mapping must really be the left neighbour's memory (it is not when the processes number the
+                # GPUs differently, e.g. each with its own CUDA_VISIBLE_DEVICES)
+                seen = float(peer[4].to(dev)[0].item())
+                if seen != float(left):
+                    error = f"CUDA IPC mapping of rank {left}'s buffers shows rank {seen:.0f}'s data"
+            except Exception as e:  # noqa: BLE001
+                error = f"{type(e).__name__}: {e}"
+        elif error is None:
+            error = "another rank could not export its buffers"
+        failed = torch.tensor([0.0 if error is None else 1.0], device=dev)
+        dist.all_reduce(failed, group=group)
+        if failed.item() != 0.0:
+            self.release()
+            raise RuntimeError(f"peer-copy ring exchange unavailable on {int(failed.item())} rank(s)"
+                               + (f"; here: {error}" if error else ""))
         self.stream = torch.cuda.Stream(dev)
         self.word = torch.zeros(1, dtype=torch.float32, device=dev)
         dist.barrier(group=group)
+        # Ordering between neighbours without any kernel: 32-bit writes and waits that the stream itself performs
+        # (cuStreamWriteValue32 / cuStreamWaitValue32). Tried once here, a write into the right neighbour's flags and a
+        # wait for the left neighbour's; if any rank cannot, every rank orders its hops with a one-word all-reduce.
+        self.memops = self._try_memops(dev, group)
+
+    _CU_WAIT_GEQ = 0x0
+
+    def _try_memops(self, dev, group) -> bool:
+        ok = True
+        try:
+            lib = ctypes.CDLL("libcuda.so.1")
+            self._cu_wait = getattr(lib, "cuStreamWaitValue32_v2", None) or lib.cuStreamWaitValue32
+            self._cu_write = getattr(lib, "cuStreamWriteValue32_v2", None) or lib.cuStreamWriteValue32
+            for fn in (self._cu_wait, self._cu_write):
+                fn.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint]
+                fn.restype = ctypes.c_int
+            # Copies are issued on THIS GPU's stream (torch issues a copy between devices on the source's, which here
+            # would be this process's context on the neighbour's GPU: it then waits for a time slice between the
+            # neighbour's own kernels, ~0.5 ms per hop).
+            self._memcpy = ctypes.CDLL("libcudart.so.12").cudaMemcpyAsync
+            self._memcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_void_p]
+            self._memcpy.restype = ctypes.c_int
+            self.stage = torch.zeros(2, dtype=torch.int32, device=dev)  # the words that travel to the neighbours
+            with torch.cuda.device(dev), torch.cuda.stream(self.stream):
+                self.post(self.stream, self.right_flags, 2, 7, 0)     # lands in the right neighbour's flags[2]
+                self.write_flag(self.stream, self.flags, 3, 9)
+                self.wait_flag(self.stream, self.flags, 3, 9)         # already true: this probe cannot wait for ever
+            self.stream.synchronize()
+        except Exception as e:  # noqa: BLE001 - any failure means: use the all-reduce
+            ok, self.memops_note = False, f"{type(e).__name__}: {e}"
+        dist.barrier(group=group)  # every rank's write into its neighbour has been performed
+        if ok:
+            got = (int(self.flags[2].item()), int(self.flags[3].item()))
+            ok = got == (7, 9)
+            self.memops_note = "" if ok else f"flags read back {got}, expected (7, 9)"
+        agreed = torch.tensor([1.0 if ok else 0.0], device=dev)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+        return bool(agreed.item() == 1.0)
+
+    def post(self, stream, peer_flags: torch.Tensor, index: int, value: int, word: int) -> None:
+        """`value` into a neighbour's flag, in stream order: the stream writes it into a word of this GPU's memory
+        (stream memory operations do not take a peer's address) and a four-byte peer copy carries it over. Call with
+        `stream` current."""
+        self.write_flag(stream, self.stage, word, value)
+        self.copy(stream, peer_flags[index:index + 1], self.stage[word:word + 1])
+
+    def copy(self, stream, dst: torch.Tensor, src: torch.Tensor) -> None:
+        """dst <- src (contiguous, same size; either may be a neighbour's mapped memory) by cudaMemcpyAsync on `stream`."""
+        err = self._memcpy(dst.data_ptr(), src.data_ptr(), dst.numel() * dst.element_size(), 4, stream.cuda_stream)
+        if err != 0:
+            raise RuntimeError(f"cudaMemcpyAsync failed with cudaError {err}")
+
+    def write_flag(self, stream, flags: torch.Tensor, index: int, value: int) -> None:
+        err = self._cu_write(ctypes.c_void_p(stream.cuda_stream), flags.data_ptr() + 4 * index, value, 0)
+        if err != 0:
+            raise RuntimeError(f"cuStreamWriteValue32 failed with CUresult {err}")
+
+    def wait_flag(self, stream, flags: torch.Tensor, index: int, value: int) -> None:
+        err = self._cu_wait(ctypes.c_void_p(stream.cuda_stream), flags.data_ptr() + 4 * index, value, self._CU_WAIT_GEQ)
+        if err != 0:
+            raise RuntimeError(f"cuStreamWaitValue32 failed with CUresult {err}")
 
     def release(self):
-        self.peer_k = self.peer_v = None
+        self.peer_k = self.peer_v = self.left_flags = self.right_flags = None
         self._peer_storages = None
 
 
@@ -146,13 +237,21 @@ class _Exchange:
         self.k_cur, self.v_cur = k.contiguous(), v.contiguous()
         self.reqs = []
         if mode == "peer":
-            self.ring = _peer_ring(self.k_cur, self.v_cur, group)
-            # the right neighbour may still be copying out of pair 0 for the previous call's first hop: every rank
-            # comes here behind its own copies of that call, so this all-reduce puts the new slice behind them all
-            dist.all_reduce(self.ring.word, group=group)
-            self.ring.k[0].copy_(self.k_cur)
-            self.ring.v[0].copy_(self.v_cur)
-            self.k_cur, self.v_cur = self.ring.k[0], self.ring.v[0]
+            r = self.ring = _peer_ring(self.k_cur, self.v_cur, group)
+            # The pair that takes this call's own slice is the one the right neighbour copied out of in the previous
+            # call's last hop: the new slice goes in behind that copy.
+            if r.memops:
+                self.first = r.pair
+                r.pair = (r.pair + self.world) % 2
+                if r.hops > 0:
+                    r.wait_flag(torch.cuda.current_stream(), r.flags, 1, r.hops)
+            else:
+                self.first = 0
+                # (every rank comes here behind its own copies of the previous call)
+                dist.all_reduce(r.word, group=group)
+            r.k[self.first].copy_(self.k_cur)
+            r.v[self.first].copy_(self.v_cur)
+            self.k_cur, self.v_cur = r.k[self.first], r.v[self.first]
             self.step_done = torch.cuda.Event()
             self.step_done.record()
         elif mode:
@@ -166,12 +265,26 @@ class _Exchange:
         if step + 1 >= self.world or not self.mode:
             return
         if self.mode == "peer":
-            r, cur, nxt = self.ring, step % 2, (step + 1) % 2
+            r, cur, nxt = self.ring, (self.first + step) % 2, (self.first + step + 1) % 2
             with torch.cuda.stream(r.stream):
                 r.stream.wait_event(self.step_done)  # pair `cur` is written, the attention that read pair `nxt` is done
-                dist.all_reduce(r.word, group=self.group)
-                r.k[nxt].copy_(r.peer_k[cur], non_blocking=True)
-                r.v[nxt].copy_(r.peer_v[cur], non_blocking=True)
+                if r.memops:
+                    hop = r.hops + 1
+                    r.post(r.stream, r.right_flags, 0, hop, 0)         # to the right: my source pair of this hop is valid
+                    r.wait_flag(r.stream, r.flags, 0, hop)             # the left neighbour's is
+                    if hop > 1:
+                        r.wait_flag(r.stream, r.flags, 1, hop - 1)     # the right neighbour has left pair `nxt` alone
+                else:
+                    dist.all_reduce(r.word, group=self.group)
+                if r.memops:
+                    r.copy(r.stream, r.k[nxt], r.peer_k[cur])
+                    r.copy(r.stream, r.v[nxt], r.peer_v[cur])
+                else:
+                    r.k[nxt].copy_(r.peer_k[cur], non_blocking=True)
+                    r.v[nxt].copy_(r.peer_v[cur], non_blocking=True)
+                if r.memops:
+                    r.post(r.stream, r.left_flags, 1, hop, 1)          # to the left: I am done with your pair
+                    r.hops = hop
                 self.pulled = torch.cuda.Event()
                 self.pulled.record()
             self.k_next, self.v_next = r.k[nxt], r.v[nxt]
@@ -211,10 +324,10 @@ def ring_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal
     result is not attention over the whole sequence). ``sm_margin`` (with the default ``attention_fn``) keeps that
     many SMs out of the persistent forward kernel, so that the send/receive kernels of the hop in flight find SMs
     to run on beside it instead of waiting for it to finish. ``exchange="peer"`` pulls the slices with copy-engine
-    copies from the neighbour's IPC-mapped buffers instead (see the module text); the one-word all-reduce per hop still
-    is a kernel, so at least four SMs are left free then. Call ``release_peer_buffers()`` before the process group
+    copies from the neighbour's IPC-mapped buffers instead (see the module text); where the hops have to be ordered by a
+    one-word all-reduce (no stream memory operations), that still is a kernel and at least four SMs are left free. Call ``release_peer_buffers()`` before the process group
     is destroyed."""
-    if exchange == "peer":
+    if exchange == "peer" and not _peer_ring(k.contiguous(), v.contiguous(), group).memops:
         sm_margin = max(int(sm_margin), 4)
     if layout == "zigzag":
         if not is_causal:
