@@ -69,6 +69,6 @@ def test_ring_and_sharding_over_nccl_when_two_gpus_are_present(cuda_device, nati
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                         "--master-addr", "127.0.0.1", "--master-port", "29533", script], capture_output=True, text=True,
-                       env=env, timeout=600)
+                       env=env, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "multigpu ring ok" in r.stdout
