@@ -472,6 +472,17 @@ def run_ours(args):
     from torch_mlu_b200 import _cabi, ops, sharding, workloads
     from torch_mlu_b200.host_pipeline import HostPipeline
     _cabi.load()
+    if args.ring_only:
+        # the long-sequence ring alone, both transports (not the bench line: a separate, short measurement)
+        os.environ["SDPA_BENCH_RING_PEER"] = "1"
+        if world < 2:
+            raise SystemExit("bench.py --ring-only needs --gpus 2 or more")
+        res = measure_ring(job, max(3, min(args.steps, 6)))
+        job.sync()
+        if rank == 0:
+            print(json.dumps({"ring": res, "n_gpus": world}), flush=True)
+        job.dist.destroy_process_group()
+        return
 
     # The global batch is 4 * world; batch slice r is the seeded config-2 draw with seed 1 + r (slice 0 is the
     # BASELINE recipe itself). partition_units splits the global (batch, kv head) units; a rank draws what it owns.
@@ -685,6 +696,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary configs and the CPU baseline")
+    ap.add_argument("--ring-only", action="store_true",
+                    help="N > 1: measure only the ring prefill of one long sequence, with both transports")
     ap.add_argument("--sustained-seconds", type=float, default=2.0,
                     help="length of the loop behind the `sustained` figure (a profiler run may want it short)")
     args = ap.parse_args()

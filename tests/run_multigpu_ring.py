@@ -55,6 +55,16 @@ def main():
     o_ref, l_ref = orc.cpu_sdpa_forward(q, k, v, causal=False)
     orc.assert_close_bf16(out4, o_ref[:, :, sl], f"peer-copy ring out rank {rank}")
     orc.assert_close_lse(lse4, l_ref[:, :, sl], max_abs=2e-5)
+    # The transport's time limit: rank 0 starts a ring call that no other rank joins, so its first hop waits for a
+    # counter nobody writes. The call must come back with an error after the limit, and everything after it must still
+    # work (the waits are released, not left hanging).
+    if rank == 0:
+        try:
+            ring.ring_prefill(take(q).to(dev), take(k).to(dev), take(v).to(dev), is_causal=True, layout="zigzag",
+                              exchange="peer", peer_timeout_s=2.0)
+            raise AssertionError("a ring call without partners returned normally")
+        except RuntimeError as e:
+            assert "did not complete within" in str(e), str(e)
     ring.release_peer_buffers()
     out, lse, _ = sharding.sdpa_batch_head_sharded(q.to(dev), k.to(dev), v.to(dev), is_causal=True)
     torch.cuda.synchronize()

@@ -23,6 +23,7 @@ from __future__ import annotations
 
 import ctypes
 import functools
+import time
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -144,6 +145,9 @@ class _PeerRing:
         # (cuStreamWriteValue32 / cuStreamWaitValue32). Tried once here, a write into the right neighbour's flags and a
         # wait for the left neighbour's; if any rank cannot, every rank orders its hops with a one-word all-reduce.
         self.memops = self._try_memops(dev, group)
+        self.broken = False
+        self._rescue = torch.cuda.Stream(dev)
+        self._all_ones = torch.full((2,), 0x7fffffff, dtype=torch.int32, device=dev)
 
     _CU_WAIT_GEQ = 0x0
 
@@ -192,6 +196,25 @@ class _PeerRing:
         if err != 0:
             raise RuntimeError(f"cudaMemcpyAsync failed with cudaError {err}")
 
+    def finish(self, timeout_s: float) -> None:
+        """The stream waits of this transport have no time limit of their own, so every call ends with one on the host:
+        if the work queued so far is not done after `timeout_s`, this rank's counters are set to their largest value
+        (every wait of this rank then passes, the streams drain, the results are void) and the call raises. A
+        neighbour that was waiting for this rank runs into its own limit the same way."""
+        done = torch.cuda.Event()
+        done.record()
+        deadline = time.monotonic() + timeout_s
+        while not done.query():
+            if time.monotonic() > deadline:
+                self.broken = True
+                with torch.cuda.stream(self._rescue):
+                    self.copy(self._rescue, self.flags[0:2], self._all_ones)
+                self._rescue.synchronize()
+                done.synchronize()
+                raise RuntimeError(f"peer-copy ring exchange: a hop did not complete within {timeout_s:.0f} s; "
+                                   "this rank's waits were released and its result is void")
+            time.sleep(0.0002)
+
     def write_flag(self, stream, flags: torch.Tensor, index: int, value: int) -> None:
         err = self._cu_write(ctypes.c_void_p(stream.cuda_stream), flags.data_ptr() + 4 * index, value, 0)
         if err != 0:
@@ -238,6 +261,9 @@ class _Exchange:
         self.reqs = []
         if mode == "peer":
             r = self.ring = _peer_ring(self.k_cur, self.v_cur, group)
+            if r.broken:
+                raise RuntimeError("peer-copy ring exchange: an earlier call ran into its time limit; "
+                                   "call release_peer_buffers() on every rank before using it again")
             # The pair that takes this call's own slice is the one the right neighbour copied out of in the previous
             # call's last hop: the new slice goes in behind that copy.
             if r.memops:
@@ -260,6 +286,10 @@ class _Exchange:
 
     def current(self):
         return self.k_cur, self.v_cur
+
+    def finish(self, timeout_s: float) -> None:
+        if self.mode == "peer" and self.ring.memops:
+            self.ring.finish(timeout_s)
 
     def start_next(self, step):
         if step + 1 >= self.world or not self.mode:
@@ -312,7 +342,8 @@ class _Exchange:
 
 def ring_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal: bool, scale: Optional[float] = None,
                  group=None, attention_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None,
-                 layout: str = "contiguous", exchange=True, sm_margin: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+                 layout: str = "contiguous", exchange=True, sm_margin: int = 0,
+                 peer_timeout_s: float = 30.0) -> Tuple[torch.Tensor, torch.Tensor]:
     """q [B,Hq,Ls,D], k/v [B,Hkv,Ls,D]: this rank's slice of the sequence.
     ``layout="contiguous"``: rank r owns rows [r*Ls, (r+1)*Ls). ``layout="zigzag"`` (causal only): rank r owns
     chunks r and 2*world-1-r of 2*world equal chunks (``zigzag_take``), which balances the causal work: every
@@ -326,14 +357,15 @@ def ring_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal
     to run on beside it instead of waiting for it to finish. ``exchange="peer"`` pulls the slices with copy-engine
     copies from the neighbour's IPC-mapped buffers instead (see the module text); where the hops have to be ordered by a
     one-word all-reduce (no stream memory operations), that still is a kernel and at least four SMs are left free. Call ``release_peer_buffers()`` before the process group
-    is destroyed."""
+    is destroyed. Such a call returns only when its work on the GPU is done, or raises after ``peer_timeout_s``
+    (the stream waits it uses have no time limit of their own; see ``_PeerRing.finish``)."""
     if exchange == "peer" and not _peer_ring(k.contiguous(), v.contiguous(), group).memops:
         sm_margin = max(int(sm_margin), 4)
     if layout == "zigzag":
         if not is_causal:
             layout = "contiguous"  # without a mask every slice order is balanced and equivalent
         else:
-            return _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn, exchange, sm_margin)
+            return _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn, exchange, sm_margin, peer_timeout_s)
     elif layout != "contiguous":
         raise ValueError(f"unknown layout {layout!r}")
     if attention_fn is None:
@@ -355,10 +387,12 @@ def ring_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal
             merge_fn(o_acc, lse_acc, o_part, lse_part.contiguous())
         ex.finish_next(step)
     lse = torch.where(torch.isneginf(lse_acc), torch.full_like(lse_acc, float("inf")), lse_acc)
-    return o_acc.to(q.dtype), lse
+    out = o_acc.to(q.dtype)
+    ex.finish(peer_timeout_s)
+    return out, lse
 
 
-def _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn, exchange=True, sm_margin=0):
+def _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn, exchange=True, sm_margin=0, peer_timeout_s=30.0):
     """Causal ring prefill over zig-zag slices. Local rows are [chunk r | chunk 2W-1-r]; a visiting slice from
     rank s is [chunk s | chunk 2W-1-s]. Which parts meet:
       s == r : plain causal attention over the local slice (its two chunks are in sequence order);
@@ -397,4 +431,6 @@ def _ring_prefill_zigzag(q, k, v, scale, group, attention_fn, merge_fn, exchange
         ex.finish_next(step)
     o_acc, lse_acc = torch.cat(acc, dim=2), torch.cat(lse, dim=2)
     lse_out = torch.where(torch.isneginf(lse_acc), torch.full_like(lse_acc, float("inf")), lse_acc)
-    return o_acc.to(q.dtype), lse_out
+    out = o_acc.to(q.dtype)
+    ex.finish(peer_timeout_s)
+    return out, lse_out
