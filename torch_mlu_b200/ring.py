@@ -342,7 +342,7 @@ class _Exchange:
 
 def ring_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal: bool, scale: Optional[float] = None,
                  group=None, attention_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None,
-                 layout: str = "contiguous", exchange=True, sm_margin: int = 0,
+                 layout: str = "contiguous", exchange=True, sm_margin: Optional[int] = None,
                  peer_timeout_s: float = 30.0) -> Tuple[torch.Tensor, torch.Tensor]:
     """q [B,Hq,Ls,D], k/v [B,Hkv,Ls,D]: this rank's slice of the sequence.
     ``layout="contiguous"``: rank r owns rows [r*Ls, (r+1)*Ls). ``layout="zigzag"`` (causal only): rank r owns
@@ -354,11 +354,15 @@ def ring_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, is_causal
     without sending anything: a timing aid that shows what the kernels cost without the transfers (its
     result is not attention over the whole sequence). ``sm_margin`` (with the default ``attention_fn``) keeps that
     many SMs out of the persistent forward kernel, so that the send/receive kernels of the hop in flight find SMs
-    to run on beside it instead of waiting for it to finish. ``exchange="peer"`` pulls the slices with copy-engine
+    to run on beside it instead of waiting for it to finish; left at None it is 16 for the send/receive ring on more
+    than two ranks (measured best on four and eight GPUs; on two the hop's kernels are long enough to hide the
+    exchange anyway) and 0 otherwise. ``exchange="peer"`` pulls the slices with copy-engine
     copies from the neighbour's IPC-mapped buffers instead (see the module text); where the hops have to be ordered by a
     one-word all-reduce (no stream memory operations), that still is a kernel and at least four SMs are left free. Call ``release_peer_buffers()`` before the process group
     is destroyed. Such a call returns only when its work on the GPU is done, or raises after ``peer_timeout_s``
     (the stream waits it uses have no time limit of their own; see ``_PeerRing.finish``)."""
+    if sm_margin is None:
+        sm_margin = 16 if (exchange is True and dist.get_world_size(group) > 2) else 0
     if exchange == "peer" and not _peer_ring(k.contiguous(), v.contiguous(), group).memops:
         sm_margin = max(int(sm_margin), 4)
     if layout == "zigzag":
