@@ -77,13 +77,18 @@ def zigzag_take(x: torch.Tensor, rank: int, world: int, dim: int = 2) -> torch.T
 
 
 class _PeerRing:
-    """Two (K, V) buffer pairs per rank plus the left-hand neighbour's two pairs, mapped through CUDA IPC.
+    """Two (K, V) buffer pairs per rank, the left-hand neighbour's two pairs and both neighbours' counters, mapped
+    through CUDA IPC.
 
-    Hop s: this rank's attention reads pair s % 2; meanwhile the pair (s + 1) % 2 receives the left neighbour's pair
-    s % 2 by a copy on `stream`. Before that copy every rank must (a) hold its slice of step s in pair s % 2 and
-    (b) have nobody reading pair (s + 1) % 2 any more - its own attention of step s - 1, and the right neighbour's
-    copy of hop s - 1. (a) and the neighbour's part of (b) are what the all-reduce in front of the copy waits for:
-    each rank enters it only behind its own copy of hop s - 1."""
+    Hop n (counted over all calls): this rank's attention reads its source pair; meanwhile the other pair receives the
+    left neighbour's source pair by copies on `stream`. Before those copies (a) the left neighbour must hold its slice
+    for this hop in its source pair and (b) nobody may be reading the destination pair any more - this rank's own
+    attention of the step before (an event), and the right neighbour's copies of hop n - 1. Each rank therefore keeps
+    two counters that its neighbours write: flags[0] <- n from the left ("my slice for hop n is in place"), flags[1] <- n
+    from the right ("I have copied hop n out of your buffer"); its stream waits for flags[0] >= n and flags[1] >= n - 1
+    before it copies, and a call waits for flags[1] >= (hops so far) before it overwrites a pair with its own slice.
+    Where the streams cannot do that themselves (`memops` false) a one-word all-reduce in front of every hop's copies
+    stands for both conditions: each rank enters it only behind its own copies of the hop before."""
 
     def __init__(self, k: torch.Tensor, v: torch.Tensor, group):
         dev = k.device
