@@ -305,7 +305,11 @@ class _Exchange:
                 r.stream.wait_event(self.step_done)  # pair `cur` is written, the attention that read pair `nxt` is done
                 if r.memops:
                     hop = r.hops + 1
-                    r.post(r.stream, r.right_flags, 0, hop, 0)         # to the right: my source pair of this hop is valid
+                    # to the right: my source pair of this hop is valid. Said here only for a call's first hop; for the
+                    # later ones it was said as soon as the pair was filled (below), a whole step earlier, so that
+                    # the neighbour's wait finds it there: a stream wait that has to wait costs ~0.35 ms.
+                    if step == 0:
+                        r.post(r.stream, r.right_flags, 0, hop, 0)
                     r.wait_flag(r.stream, r.flags, 0, hop)             # the left neighbour's is
                     if hop > 1:
                         r.wait_flag(r.stream, r.flags, 1, hop - 1)     # the right neighbour has left pair `nxt` alone
@@ -319,6 +323,8 @@ class _Exchange:
                     r.v[nxt].copy_(r.peer_v[cur], non_blocking=True)
                 if r.memops:
                     r.post(r.stream, r.left_flags, 1, hop, 1)          # to the left: I am done with your pair
+                    if step + 2 < self.world:
+                        r.post(r.stream, r.right_flags, 0, hop + 1, 0)  # to the right: pair `nxt` is the next hop's source
                     r.hops = hop
                 self.pulled = torch.cuda.Event()
                 self.pulled.record()
