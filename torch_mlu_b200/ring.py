@@ -255,6 +255,28 @@ def release_peer_buffers(group=None) -> None:
         dist.barrier(group=group)
 
 
+def peer_call_plan(world: int, hops_before: int, first_pair: int) -> dict:
+    """The counter protocol of one ring call with the peer transport, as data (what `_Exchange` executes and what
+    `tests/test_ring_cpu.py` replays on a model of the streams). Hops are numbered from 1 over all calls.
+
+    `start`: before the call writes its own slice into pair `first_pair`, the compute stream waits until the right
+    neighbour has copied hop `wait_free` out (None for the first call). `hops[s]` for step s < world - 1, on the
+    copy stream behind the event "pair `src` is written and the attention that read pair `dst` is done":
+    `announce_now` (write hop number to the right neighbour's counter 0 - a call's first hop only), wait counter 0
+    >= `hop`, wait counter 1 >= `hop - 1` (`wait_free`, None for hop 1), copy the left neighbour's pair `src` into
+    pair `dst`, write `hop` to the left neighbour's counter 1, and `announce_next` (hop + 1 to the right neighbour's
+    counter 0: pair `dst` is the next hop's source; None on a call's last hop). `next_first_pair` is where the next call
+    starts."""
+    hops = []
+    for step in range(world - 1):
+        hop = hops_before + step + 1
+        hops.append({"hop": hop, "src": (first_pair + step) % 2, "dst": (first_pair + step + 1) % 2,
+                     "announce_now": step == 0, "wait_free": hop - 1 if hop > 1 else None,
+                     "announce_next": hop + 1 if step + 2 < world else None})
+    return {"start": {"wait_free": hops_before if hops_before > 0 else None, "pair": first_pair}, "hops": hops,
+            "next_first_pair": (first_pair + world) % 2}
+
+
 class _Exchange:
     """The K/V slices of the hop loop, by one of the two transports. `current()` is the pair the step's attention reads;
     `start_next(step)` starts moving the next pair in, `finish_next()` makes the compute stream wait for it."""
@@ -272,10 +294,11 @@ class _Exchange:
             # The pair that takes this call's own slice is the one the right neighbour copied out of in the previous
             # call's last hop: the new slice goes in behind that copy.
             if r.memops:
-                self.first = r.pair
-                r.pair = (r.pair + self.world) % 2
-                if r.hops > 0:
-                    r.wait_flag(torch.cuda.current_stream(), r.flags, 1, r.hops)
+                self.plan = peer_call_plan(self.world, r.hops, r.pair)
+                self.first = self.plan["start"]["pair"]
+                r.pair = self.plan["next_first_pair"]
+                if self.plan["start"]["wait_free"] is not None:
+                    r.wait_flag(torch.cuda.current_stream(), r.flags, 1, self.plan["start"]["wait_free"])
             else:
                 self.first = 0
                 # (every rank comes here behind its own copies of the previous call)
@@ -304,15 +327,17 @@ class _Exchange:
             with torch.cuda.stream(r.stream):
                 r.stream.wait_event(self.step_done)  # pair `cur` is written, the attention that read pair `nxt` is done
                 if r.memops:
-                    hop = r.hops + 1
+                    h = self.plan["hops"][step]
+                    hop = h["hop"]
+                    assert (h["src"], h["dst"]) == (cur, nxt) and hop == r.hops + 1
                     # to the right: my source pair of this hop is valid. Said here only for a call's first hop; for the
                     # later ones it was said as soon as the pair was filled (below), a whole step earlier, so that
                     # the neighbour's wait finds it there: a stream wait that has to wait costs ~0.35 ms.
-                    if step == 0:
+                    if h["announce_now"]:
                         r.post(r.stream, r.right_flags, 0, hop, 0)
                     r.wait_flag(r.stream, r.flags, 0, hop)             # the left neighbour's is
-                    if hop > 1:
-                        r.wait_flag(r.stream, r.flags, 1, hop - 1)     # the right neighbour has left pair `nxt` alone
+                    if h["wait_free"] is not None:
+                        r.wait_flag(r.stream, r.flags, 1, h["wait_free"])  # the right neighbour has left pair `nxt` alone
                 else:
                     dist.all_reduce(r.word, group=self.group)
                 if r.memops:
@@ -323,8 +348,8 @@ class _Exchange:
                     r.v[nxt].copy_(r.peer_v[cur], non_blocking=True)
                 if r.memops:
                     r.post(r.stream, r.left_flags, 1, hop, 1)          # to the left: I am done with your pair
-                    if step + 2 < self.world:
-                        r.post(r.stream, r.right_flags, 0, hop + 1, 0)  # to the right: pair `nxt` is the next hop's source
+                    if h["announce_next"] is not None:
+                        r.post(r.stream, r.right_flags, 0, h["announce_next"], 0)  # pair `nxt` is the next hop's source
                     r.hops = hop
                 self.pulled = torch.cuda.Event()
                 self.pulled.record()
