@@ -423,16 +423,35 @@ def measure_ring(job: Job, n: int):
     # the hop's send/receive kernels need SMs beside the persistent forward kernel: sweep what it leaves them
     by_margin = {m: job.timed(lambda: ring.ring_prefill(q, k, v, is_causal=True, layout="zigzag", sm_margin=m), n, 2)
                  for m in (0, 8, 16, 32)}
-    # The other transport - slices pulled by the copy engines through CUDA IPC mappings, hops ordered by stream memory
-    # operations - is measured on request only (SDPA_BENCH_RING_PEER=1): its waits have no time limit of their own.
-    peer_ms, peer_error = None, "not measured (set SDPA_BENCH_RING_PEER=1)"
-    if os.environ.get("SDPA_BENCH_RING_PEER") == "1":
+    # The other transport: slices pulled by the copy engines through CUDA IPC mappings, hops ordered by stream memory
+    # operations. It pays where a hop's kernels are shorter than its send/receive, i.e. from four GPUs up
+    # (SDPA_BENCH_RING_PEER=1 measures it on two as well). Timed with local events and no collective inside, so that a
+    # rank that runs into the transport's time limit cannot leave the others in a different collective; the one
+    # all-reduce behind it is made by every rank whatever happened.
+    peer_ms, peer_error = None, "not measured on fewer than four GPUs (SDPA_BENCH_RING_PEER=1 forces it)"
+    if W >= 4 or os.environ.get("SDPA_BENCH_RING_PEER") == "1":
+        ok, ms_local = 1.0, 0.0
         try:
-            peer_ms = job.timed(lambda: ring.ring_prefill(q, k, v, is_causal=True, layout="zigzag", exchange="peer"), n, 2)
-            ring.release_peer_buffers()
+            peer_fn = lambda: ring.ring_prefill(q, k, v, is_causal=True, layout="zigzag", exchange="peer")
+            for _ in range(2):
+                peer_fn()
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(n):
+                peer_fn()
+            t1.record()
+            torch.cuda.synchronize()
+            ms_local = t0.elapsed_time(t1) / n
         except Exception as e:  # say so, do not hide it
-            peer_ms = None
-            peer_error = f"{type(e).__name__}: {e}"
+            ok, peer_error = 0.0, f"{type(e).__name__}: {str(e)[:200]}"
+        agreed = torch.tensor([ok, -ms_local], dtype=torch.float32, device=dev)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)  # every rank succeeded? and the slowest rank's time
+        if agreed[0].item() == 1.0:
+            peer_ms = -agreed[1].item()
+            ring.release_peer_buffers()
+        elif ok == 1.0:
+            peer_error = "another rank could not complete the peer-copy ring"
     best = min(by_margin, key=by_margin.get)
     ms_full = by_margin[best]
     transport = "NCCL send/recv"
