@@ -20,8 +20,9 @@ is independent per unit, so the data path needs no collective). Rank 0 prints ON
             gather of step i running on a side stream under the kernel of step i+1.
 `cpu_baseline` / `--impl reference`: torch's CPU fused SDPA in fp32 (the host-runnable reference path)
             on the same per-GPU workload, all host threads.
-`also`    : forward+backward, varlen GQA, split-KV decode (and at N > 1 their sharded forms and the ring /
-            context-parallel prefill of one long sequence).
+`also`    : forward+backward (also with dropout), head_dim 256, varlen GQA, split-KV decode (and at N > 1 their
+            sharded forms and the ring / context-parallel prefill of one long sequence: send/receive with a sweep
+            of the SMs left to it, and from four GPUs up the peer-copy transport; `--ring-only` measures just that).
 """
 from __future__ import annotations
 
