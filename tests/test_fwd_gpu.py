@@ -3,7 +3,6 @@
 Tolerances (bf16 outputs vs the fp32 oracle on the same bf16-rounded inputs): max-abs 2e-2,
 mean-abs 2e-3; fp32 logsumexp max-abs 1e-5.
 """
-import glob
 import os
 
 import pytest
